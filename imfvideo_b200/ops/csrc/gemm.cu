@@ -1,0 +1,257 @@
+// bf16 GEMM on tcgen05 tensor cores with TMEM accumulators, fed by TMA.
+//
+//   C[M, N] = op(A) * op(B)^T (+ bias on the first `bias_rows` rows)
+//
+// A is either K-major ([M, K], K contiguous) or MN-major ([K, M], M
+// contiguous); likewise B ([N, K] or [K, N]).  All four combinations map to
+// UMMA shared-memory descriptors directly, so forward (X W^T), data-gradient
+// (dY W) and weight-gradient (dY^T X) products need no transposed copies.
+// The dual-number forward stacks primal and tangent rows into one launch.
+//
+// CTA = one 128 x BN output tile.  Warps 0-3: epilogue (TMEM -> registers ->
+// global), warp 4: TMA producer, warp 5: MMA issuer.  STAGES-deep mbarrier
+// ring.  Replaces the reference's `_mm16_kernel` / cuBLAS / `_scaled_mm`
+// calls on the JVP path (reference models/triton_mla_block_jvp.py:89-148).
+#include "common.cuh"
+#include "host_util.h"
+
+namespace imf {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  alignas(1024) uint8_t a[STAGES][GEMM_BM * GEMM_BK * 2];
+  alignas(1024) uint8_t b[STAGES][BN * GEMM_BK * 2];
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+            OutT* __restrict__ C, const float* __restrict__ bias, int M, int N, int K,
+            int64_t ldc, int bias_rows, float alpha, int accumulate_out, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  auto& s = *reinterpret_cast<GemmSmem<BN, STAGES>*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * GEMM_BM;
+  const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    mbar_init(&s.acc_full, 1);
+    s.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&s.tmem_base, BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abort_flag = &s.abort_flag;
+
+  if (warp == 4) {
+    // ------------------------------------------------------ TMA producer --
+    if (elect_one()) {
+      prefetch_tmap(&tm_a);
+      prefetch_tmap(&tm_b);
+      constexpr uint32_t bytes = (GEMM_BM + BN) * GEMM_BK * 2;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int st = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        if (kb >= STAGES &&
+            !mbar_wait(&s.empty[st], ph ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY))
+          break;
+        mbar_arrive_expect_tx(&s.full[st], bytes);
+        const int k0 = kb * GEMM_BK;
+        if (!A_MN) {
+          tma_load_2d(s.a[st], &tm_a, &s.full[st], k0, m0);
+        } else {
+          tma_load_2d(s.a[st], &tm_a, &s.full[st], m0, k0);
+          tma_load_2d(s.a[st] + 64 * 128, &tm_a, &s.full[st], m0 + 64, k0);
+        }
+        if (!B_MN) {
+          tma_load_2d(s.b[st], &tm_b, &s.full[st], k0, n0);
+        } else {
+#pragma unroll
+          for (int p = 0; p < BN / 64; ++p)
+            tma_load_2d(s.b[st] + p * 64 * 128, &tm_b, &s.full[st], n0 + p * 64, k0);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------------------------------- MMA issuer --
+    if (elect_one()) {
+      constexpr uint32_t idesc = idesc_bf16(GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int st = kb % STAGES;
+        const uint32_t ph = (kb / STAGES) & 1;
+        ok = mbar_wait(&s.full[st], ph, abort_flag, status, STATUS_TIMEOUT_TMA);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_base = smem_u32(s.a[st]), b_base = smem_u32(s.b[st]);
+#pragma unroll
+        for (int ks = 0; ks < GEMM_BK / 16; ++ks) {
+          const uint64_t da = A_MN ? sdesc_mnmajor(a_base + ks * 2048, 64 * 128)
+                                   : sdesc_kmajor(a_base + ks * 32);
+          const uint64_t db = B_MN ? sdesc_mnmajor(b_base + ks * 2048, 64 * 128)
+                                   : sdesc_kmajor(b_base + ks * 32);
+          mma_ss(tmem, da, db, idesc, (kb | ks) != 0);
+        }
+        tc_commit(&s.empty[st]);
+      }
+      tc_commit(&s.acc_full);
+    }
+  } else {
+    // ---------------------------------------------------------- epilogue --
+    const bool ok = mbar_wait(&s.acc_full, 0, abort_flag, status, STATUS_TIMEOUT_MMA);
+    tc_fence_after();
+    const int row = m0 + warp * 32 + lane;
+    if (ok) {
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tmem, warp * 32, c), r);
+        tc_wait_ld();
+        if (row < M) {
+          OutT* dst = C + (int64_t)row * ldc + n0 + c;
+          const bool add_bias = bias != nullptr && row < bias_rows;
+          if (n0 + c + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 &&
+              !accumulate_out) {
+            if constexpr (sizeof(OutT) == 2) {
+              uint32_t o[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                float x = __uint_as_float(r[2 * i]) * alpha;
+                float y = __uint_as_float(r[2 * i + 1]) * alpha;
+                if (add_bias) {
+                  x += bias[n0 + c + 2 * i];
+                  y += bias[n0 + c + 2 * i + 1];
+                }
+                o[i] = pack_bf16(x, y);
+              }
+              uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                d4[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            } else {
+              float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float4 v;
+                v.x = __uint_as_float(r[4 * i]) * alpha;
+                v.y = __uint_as_float(r[4 * i + 1]) * alpha;
+                v.z = __uint_as_float(r[4 * i + 2]) * alpha;
+                v.w = __uint_as_float(r[4 * i + 3]) * alpha;
+                if (add_bias) {
+                  v.x += bias[n0 + c + 4 * i];
+                  v.y += bias[n0 + c + 4 * i + 1];
+                  v.z += bias[n0 + c + 4 * i + 2];
+                  v.w += bias[n0 + c + 4 * i + 3];
+                }
+                d4[i] = v;
+              }
+            }
+          } else {
+            for (int i = 0; i < 32; ++i) {
+              const int col = n0 + c + i;
+              if (col < N) {
+                float x = __uint_as_float(r[i]) * alpha;
+                if (add_bias) x += bias[col];
+                if (accumulate_out) x += static_cast<float>(dst[i]);
+                dst[i] = static_cast<OutT>(x);
+              }
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, BN);
+  }
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT>
+static int launch_gemm(const void* A, const void* B, void* C, const float* bias, int M, int N,
+                       int K, int64_t lda, int64_t ldb, int64_t ldc, int bias_rows, float alpha,
+                       int accumulate_out, int* status, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int rc;
+  {
+    // K-major: dims (K, M), box (64, 128).  MN-major: dims (M, K), box (64, 64).
+    uint64_t dims[2] = {A_MN ? (uint64_t)M : (uint64_t)K, A_MN ? (uint64_t)K : (uint64_t)M};
+    uint64_t str[2] = {2, (uint64_t)lda * 2};
+    uint32_t box[2] = {64, A_MN ? 64u : (uint32_t)GEMM_BM};
+    rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(A), dims, str, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[2] = {B_MN ? (uint64_t)N : (uint64_t)K, B_MN ? (uint64_t)K : (uint64_t)N};
+    uint64_t str[2] = {2, (uint64_t)ldb * 2};
+    uint32_t box[2] = {64, B_MN ? 64u : (uint32_t)BN};
+    rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(B), dims, str, box);
+    if (rc) return rc;
+  }
+  auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, OutT>;
+  const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return IMF_ERR_LAUNCH;
+    attr_set = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + GEMM_BM - 1) / GEMM_BM);
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, static_cast<OutT*>(C), bias, M, N, K, ldc,
+                                             bias_rows, alpha, accumulate_out, status);
+  return cudaGetLastError() == cudaSuccess ? IMF_OK : IMF_ERR_LAUNCH;
+}
+
+}  // namespace imf
+
+// C = alpha * op(A) op(B)^T (+bias) ; bf16 operands.
+//   a_mn / b_mn: 0 = K-major ([rows, K]), 1 = MN-major ([K, rows]).
+//   out_fp32: 0 = bf16 output, 1 = fp32 output.  lda/ldb/ldc in elements.
+//   accumulate_out: C += result (fp32 read-modify-write, for split products).
+extern "C" int imf_gemm_bf16(const void* A, const void* B, void* C, const float* bias, int M,
+                             int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int a_mn,
+                             int b_mn, int out_fp32, int bias_rows, float alpha,
+                             int accumulate_out, int* status, void* stream) {
+  using namespace imf;
+  if (M <= 0 || N <= 0 || K <= 0) return IMF_ERR_ARG;
+  if ((lda & 7) || (ldb & 7)) return IMF_ERR_ARG;  // TMA strides are multiples of 16 B
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define IMF_GEMM_CASE(AM, BM_, OT)                                                          \
+  return launch_gemm<128, 3, AM, BM_, OT>(A, B, C, bias, M, N, K, lda, ldb, ldc, bias_rows, \
+                                          alpha, accumulate_out, status, st)
+  if (out_fp32) {
+    if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, float);
+    if (!a_mn && b_mn) IMF_GEMM_CASE(false, true, float);
+    if (a_mn && !b_mn) IMF_GEMM_CASE(true, false, float);
+    IMF_GEMM_CASE(true, true, float);
+  } else {
+    if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, __nv_bfloat16);
+    if (!a_mn && b_mn) IMF_GEMM_CASE(false, true, __nv_bfloat16);
+    if (a_mn && !b_mn) IMF_GEMM_CASE(true, false, __nv_bfloat16);
+    IMF_GEMM_CASE(true, true, __nv_bfloat16);
+  }
+#undef IMF_GEMM_CASE
+}
