@@ -78,11 +78,21 @@ class SwiGLUMlp(nn.Module):
     def forward(self, x: Dual) -> Dual:
         x = D.lift(x)
         f = self.w1.out_features
-        # one GEMM for [gate | up]
-        gu = D.linear(x, torch.cat([self.w1.weight, self.w3.weight], dim=0))
-        gate = gu.map(lambda z: z[..., :f])
-        up = gu.map(lambda z: z[..., f:])
-        return D.linear(self.act(gate, up), self.w2.weight)
+        w1, w3, w2 = self.w1.weight, self.w3.weight, self.w2.weight
+        # TMA-fed GEMMs need row strides that are multiples of 16 bytes: pad the
+        # hidden width with zero rows/columns (exact: situ(0, 0) = 0)
+        pad = (-f) % 8 if x.p.is_cuda else 0
+        if pad:
+            z = w1.new_zeros(pad, w1.shape[1])
+            w13 = torch.cat([w1, z, w3, z], dim=0)
+            w2 = torch.nn.functional.pad(w2, (0, pad))
+        else:
+            w13 = torch.cat([w1, w3], dim=0)
+        fp = f + pad
+        gu = D.linear(x, w13)                      # one GEMM for [gate | up]
+        gate = gu.map(lambda z_: z_[..., :fp])
+        up = gu.map(lambda z_: z_[..., fp:])
+        return D.linear(self.act(gate, up), w2)
 
 
 def sinusoid(t: Tensor, dim: int, max_period: float = 10000.0) -> Tuple[Tensor, Tensor]:

@@ -80,9 +80,9 @@ def rmsnorm(x: Dual, weight: Optional[Tensor], eps: float,
         with torch.no_grad():
             _, t = ref.rmsnorm_jvp(x.p.detach(), x.t,
                                    None if weight is None else weight.detach(), eps)
-    if out_dtype is not None:
-        p = p.to(out_dtype)
-        t = None if t is None else t.to(out_dtype)
+    od = out_dtype or x.p.dtype       # the fp32 gain must not promote a bf16 stream
+    p = p.to(od)
+    t = None if t is None else t.to(od)
     return Dual(p, t)
 
 

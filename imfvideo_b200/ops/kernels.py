@@ -30,6 +30,14 @@ _ERR = {-1: "bad shape/stride/alignment", -2: "tensor-map encode failed",
 _status: Dict[int, torch.Tensor] = {}
 
 
+class _LaunchCounter:
+    """Number of kernels of this library launched by this process."""
+    count = 0
+
+
+LAUNCHES = _LaunchCounter
+
+
 def status_word(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx not in _status:
@@ -96,6 +104,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                             M if bias_rows is None else bias_rows, float(alpha), int(accumulate),
                             _ptr(status_word(a.device)), _stream())
     _check(rc, "imf_gemm_bf16")
+    LAUNCHES.count += 1
     return out
 
 
@@ -140,4 +149,111 @@ def attn_fwd(q, k, v, dq=None, dk=None, dv=None, scale: Optional[float] = None,
                            hd, ctypes.cast(arr, c_void_p), o.stride(0), o.stride(1), o.stride(2),
                            float(scale), _ptr(status_word(q.device)), _stream())
     _check(rc, "imf_attn_fwd")
+    LAUNCHES.count += 1
     return o, do, lse
+
+
+# ------------------------------------------------- autograd: attention -----
+def _sdpa_backward(q, k, v, go):
+    """Temporary reverse-mode fallback (library SDPA recompute) used only when
+    the library lacks ``imf_attn_bwd``."""
+    with torch.enable_grad():
+        qq, kk, vv = (t.detach().transpose(1, 2).requires_grad_(True) for t in (q, k, v))
+        oo = torch.nn.functional.scaled_dot_product_attention(qq, kk, vv)
+        gq, gk, gv = torch.autograd.grad(oo, (qq, kk, vv), go.transpose(1, 2))
+    return gq.transpose(1, 2), gk.transpose(1, 2), gv.transpose(1, 2)
+
+
+class _AttnFn(torch.autograd.Function):
+    """o (and the detached tangent do) from the fused kernel; reverse mode
+    through the primal only."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, dq, dk, dv):
+        need_bwd = any(ctx.needs_input_grad[:3])
+        o, do, lse = attn_fwd(q, k, v, dq, dk, dv, need_lse=need_bwd)
+        if need_bwd:
+            ctx.save_for_backward(q, k, v, o, lse)
+        if do is None:
+            do = o.new_empty(0)
+        ctx.mark_non_differentiable(do)
+        return o, do
+
+    @staticmethod
+    def backward(ctx, go, _gdo):
+        q, k, v, o, lse = ctx.saved_tensors
+        if _has("imf_attn_bwd"):
+            gq, gk, gv = attn_bwd(q, k, v, o, lse, go.contiguous())
+        else:
+            gq, gk, gv = _sdpa_backward(q, k, v, go)
+        return gq, gk, gv, None, None, None
+
+
+def attention_dual(q: Dual, k: Dual, v: Dual) -> Dual:
+    if q.p.dtype != torch.bfloat16 or q.p.shape[-1] != 64 or v.p.shape[-1] != 64:
+        raise ValueError("attention kernel needs bf16 tensors with head_dim 64; got "
+                         f"{q.p.dtype}, qk {q.p.shape[-1]}, v {v.p.shape[-1]}")
+    if q.t is not None:
+        o, do = _AttnFn.apply(q.p, k.p, v.p, q.t, k.t, v.t)
+        return Dual(o, do)
+    o, _ = _AttnFn.apply(q.p, k.p, v.p, None, None, None)
+    return Dual(o, None)
+
+
+# ---------------------------------------------------- autograd: linear -----
+def _stacked(xp: torch.Tensor, xt: Optional[torch.Tensor], kdim: int):
+    """2-D [rows, K] view over primal (+ tangent) rows; zero-copy when the
+    tangent sits right behind the primal in memory."""
+    a = xp.reshape(-1, kdim)
+    if xt is None:
+        return a, a.shape[0]
+    b = xt.reshape(-1, kdim)
+    if (a.is_contiguous() and b.is_contiguous()
+            and b.data_ptr() == a.data_ptr() + a.numel() * a.element_size()
+            and a.untyped_storage().data_ptr() == b.untyped_storage().data_ptr()):
+        return torch.as_strided(a, (a.shape[0] * 2, kdim), (kdim, 1)), a.shape[0]
+    return torch.cat([a, b], dim=0), a.shape[0]
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, xp, xt, w, bias):
+        kdim = xp.shape[-1]
+        x2, mp = _stacked(xp, xt, kdim)
+        if x2.stride(0) % 8 or x2.data_ptr() % 16:
+            x2 = x2.contiguous()
+        y = gemm(x2, w, bias=bias, bias_rows=mp)
+        n = w.shape[0]
+        yp = y[:mp].view(*xp.shape[:-1], n)
+        yt = y[mp:].view(*xp.shape[:-1], n) if xt is not None else y.new_empty(0)
+        ctx.save_for_backward(xp, w)
+        ctx.has_bias = bias is not None
+        ctx.mark_non_differentiable(yt)
+        return yp, yt
+
+    @staticmethod
+    def backward(ctx, gyp, _gyt):
+        xp, w = ctx.saved_tensors
+        g2 = gyp.reshape(-1, gyp.shape[-1])
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = (g2 @ w).view_as(xp)
+        if ctx.needs_input_grad[2]:
+            gw = g2.t() @ xp.reshape(-1, xp.shape[-1])
+        if ctx.has_bias and ctx.needs_input_grad[3]:
+            gb = g2.float().sum(0).to(g2.dtype)
+        return gx, None, gw, gb
+
+
+def linear_dual(x: Dual, w: torch.Tensor, bias: Optional[torch.Tensor]) -> Dual:
+    if x.p.shape[-1] % 8:
+        raise ValueError(f"GEMM K={x.p.shape[-1]} must be a multiple of 8 (pad the operand)")
+    w = w if w.is_contiguous() else w.contiguous()
+    yp, yt = _LinearFn.apply(x.p, x.t, w, bias)
+    return Dual(yp, yt if x.t is not None else None)
+
+
+if _has("imf_gemm_bf16"):
+    _cuda.register("gemm", linear_dual=linear_dual)
+if _has("imf_attn_fwd"):
+    _cuda.register("attention", attention_dual=attention_dual)

@@ -283,8 +283,13 @@ class Trainer:
                 self._report_bad_grads()
         self.optimizer.zero_grad(set_to_none=not hasattr(self.grad_sync, "keeps_grad_views"))
         self.step += 1
-        return {"lr": lr, "grad_norm": float(grad_norm), "skipped": not finite,
+        return {"lr": lr, "grad_norm": grad_norm, "skipped": not finite,
                 "qk_hot": n_hot, "qk_smax": s_max}
+
+    def optimizer_step_async(self) -> Dict[str, Any]:
+        """``optimizer_step`` without converting statistics to Python floats
+        (the only host read left is the finite-gradient check)."""
+        return self.optimizer_step()
 
     def _report_bad_grads(self) -> None:
         if not self.verbose:
@@ -317,10 +322,11 @@ class Trainer:
             loss, parts = self.micro_step(lat, lab)
             losses.append(loss)
         stats = self.optimizer_step()
-        vec = torch.stack([torch.stack(losses).mean(), parts["loss_u"], parts["loss_v"]]).tolist()
+        vec = torch.stack([torch.stack(losses).mean(), parts["loss_u"], parts["loss_v"],
+                           stats["grad_norm"].to(losses[0].dtype)]).tolist()
         if not math.isfinite(vec[0]):
             self._dump_nan_batch(parts["_latents"], parts["_labels"])
-        stats.update(loss=vec[0], loss_u=vec[1], loss_v=vec[2])
+        stats.update(loss=vec[0], loss_u=vec[1], loss_v=vec[2], grad_norm=vec[3])
         self.last = stats
         return stats
 

@@ -1,0 +1,112 @@
+"""GPU: each sm_100a kernel against the plain-PyTorch fp32 formulas."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from imfvideo_b200.ops import cuda as cu
+
+    assert cu.available(), "kernel library must load on a GPU box"
+    from imfvideo_b200.ops import kernels
+
+    return kernels
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("M,N,Kd", [(128, 128, 64), (304, 200, 136), (1000, 528, 256), (77, 64, 8)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm(K, M, N, Kd, a_mn, b_mn):
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operand needs a 16-byte-multiple row stride")
+    torch.manual_seed(0)
+    A = torch.randn(M, Kd, device="cuda").bfloat16()
+    B = torch.randn(N, Kd, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda")
+    out = K.gemm(A.t().contiguous() if a_mn else A, B.t().contiguous() if b_mn else B,
+                 a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32, bias=bias, bias_rows=M // 2)
+    ref = A.float() @ B.float().t()
+    ref[: M // 2] += bias
+    assert _rel(out, ref) < 1e-5
+    out16 = K.gemm(A.t().contiguous() if a_mn else A, B.t().contiguous() if b_mn else B,
+                   a_mn=a_mn, b_mn=b_mn)
+    assert _rel(out16, A.float() @ B.float().t()) < 4e-3
+    K.check_status()
+
+
+def test_gemm_rejects_bad_stride(K):
+    A = torch.randn(64, 12, device="cuda").bfloat16()      # K = 12: stride not 16-byte multiple
+    with pytest.raises(ValueError):
+        K.gemm(A, A)
+
+
+@pytest.mark.parametrize("B,L,H", [(1, 256, 1), (1, 300, 2), (2, 1000, 3), (1, 64, 1), (1, 2049, 2)])
+def test_attention_forward(K, B, L, H):
+    from imfvideo_b200.ops import reference as ref
+
+    g = torch.Generator(device="cuda").manual_seed(L)
+    q, k, v = (torch.randn(B, L, H, 64, device="cuda", generator=g).bfloat16() for _ in range(3))
+    o, _, lse = K.attn_fwd(q, k, v)
+    ro = ref.attention(q.float(), k.float(), v.float())
+    assert (o.float() - ro).abs().max() < 2e-2 and _rel(o, ro) < 1e-2
+    assert (lse - ref.attention_lse(q.float(), k.float())).abs().max() < 1e-3
+    K.check_status()
+
+
+@pytest.mark.parametrize("B,L,H", [(1, 256, 1), (1, 212, 2), (2, 1000, 3), (1, 2049, 2)])
+def test_attention_forward_tangent(K, B, L, H):
+    from imfvideo_b200.ops import reference as ref
+
+    g = torch.Generator(device="cuda").manual_seed(L)
+    mk = lambda s: (torch.randn(B, L, H, 64, device="cuda", generator=g) * s).bfloat16()
+    q, k, v, dq, dk, dv = mk(1), mk(1), mk(1), mk(.5), mk(.5), mk(.5)
+    o, do, lse = K.attn_fwd(q, k, v, dq, dk, dv)
+    ro, rdo = ref.attention_jvp(*(t.float() for t in (q, k, v, dq, dk, dv)))
+    assert (o.float() - ro).abs().max() < 2e-2 and _rel(o, ro) < 1e-2
+    assert (do.float() - rdo).abs().max() < 2e-2 and _rel(do, rdo) < 1e-2
+    o2, _, _ = K.attn_fwd(q, k, v)
+    assert _rel(o2, o) < 5e-3            # primal-only and fused kernels agree
+    K.check_status()
+
+
+def test_attention_strided_views_and_run_twice(K):
+    """v as a slice of a wider kv tensor (as in MLA); two runs are bit-equal."""
+    torch.manual_seed(0)
+    B, L, H = 1, 515, 4
+    kv = torch.randn(B, L, H, 112, device="cuda").bfloat16()
+    q = torch.randn(B, L, H, 64, device="cuda").bfloat16()
+    k = torch.randn(B, L, H, 64, device="cuda").bfloat16()
+    v = kv[..., 48:]
+    o1, _, _ = K.attn_fwd(q, k, v)
+    o2, _, _ = K.attn_fwd(q, k, v.contiguous())
+    o3, _, _ = K.attn_fwd(q, k, v)
+    assert torch.equal(o1, o2) and torch.equal(o1, o3)
+    K.check_status()
+
+
+def test_attention_autograd(K):
+    from imfvideo_b200.ops import reference as ref
+    from imfvideo_b200.ops.dual import Dual
+
+    torch.manual_seed(0)
+    B, L, H = 1, 333, 2
+    q, k, v = (torch.randn(B, L, H, 64, device="cuda").bfloat16().requires_grad_(True)
+               for _ in range(3))
+    go = torch.randn(B, L, H, 64, device="cuda").bfloat16()
+    out = K.attention_dual(Dual(q), Dual(k), Dual(v)).p
+    out.backward(go)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref.attention(qf, kf, vf).backward(go.float())
+    for a, b in ((q, qf), (k, kf), (v, vf)):
+        assert _rel(a.grad, b.grad) < 2e-2
+    K.check_status()

@@ -1,0 +1,73 @@
+"""GPU: the model / trainer through the kernel library vs the torch path."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def kernels():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from imfvideo_b200.ops import cuda as cu
+
+    assert cu.available()
+    from imfvideo_b200.ops import kernels as K
+
+    return K
+
+
+def _net(dtype=None, bs=2):
+    from imfvideo_b200.models import IMFDiTVideo, flash_jvp_attention
+
+    torch.manual_seed(0)
+    net = IMFDiTVideo(input_size=(16, 32), num_frames=4, hidden_size=256, depth=3, num_heads=4,
+                      aux_head_depth=1, kv_lora_rank=128, attn_res_block_size=bs,
+                      attn_impl=flash_jvp_attention, compute_dtype=dtype)
+    with torch.no_grad():
+        for p in net.parameters():
+            p.add_(torch.randn_like(p) * 0.03)
+    return net.cuda()
+
+
+def test_model_dual_pass_bf16_kernels_vs_fp32_torch(kernels):
+    from imfvideo_b200.ops import cuda as cu
+    from imfvideo_b200.ops.dual import Dual
+
+    net = _net(torch.bfloat16)
+    B = 2
+    x, dx = torch.randn(B, 16, 4, 16, 32, device="cuda"), torch.randn(B, 16, 4, 16, 32, device="cuda")
+    h = torch.rand(B, device="cuda")
+    w = 1 + torch.rand(B, device="cuda")
+    lo, hi = torch.zeros(B, device="cuda"), torch.ones(B, device="cuda")
+    y = torch.randint(0, 1000, (B,), device="cuda")
+    n0 = kernels.LAUNCHES.count
+    out = net.forward_dual(Dual(x, dx), Dual(h, torch.ones_like(h)), w, lo, hi, y)
+    assert kernels.LAUNCHES.count > n0
+    kernels.check_status()
+    net.compute_dtype = None
+    cu.disable("gemm", "attention", "rmsnorm", "situ", "attn_res")
+    try:
+        ref = net.forward_dual(Dual(x, dx), Dual(h, torch.ones_like(h)), w, lo, hi, y)
+    finally:
+        cu.enable("gemm", "attention", "rmsnorm", "situ", "attn_res")
+    rel = lambda a, b: ((a - b).norm() / b.norm()).item()
+    assert rel(out["u"].p, ref["u"].p) < 3e-2
+    assert rel(out["u"].t, ref["u"].t) < 5e-2
+    assert rel(out["v"].p, ref["v"].p) < 3e-2
+
+
+def test_trainer_steps_on_gpu(kernels):
+    from imfvideo_b200.config import preset
+    from imfvideo_b200.train import Trainer
+
+    cfg = preset("d256")
+    cfg.model.depth, cfg.model.aux_head_depth = 3, 1
+    cfg.data.latent_frames, cfg.data.latent_size = 4, (16, 32)
+    cfg.optim.warmup_steps = 0
+    tr = Trainer(cfg, device=torch.device("cuda", 0), verbose=False)
+    x, y = torch.randn(1, 16, 4, 16, 32).pin_memory(), torch.randint(0, 1000, (1,))
+    st = [tr.train_step(x, y) for _ in range(3)]
+    kernels.check_status()
+    assert all(s["loss"] == s["loss"] and not s["skipped"] for s in st)
+    assert st[-1]["grad_norm"] > 0

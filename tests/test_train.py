@@ -1,0 +1,155 @@
+"""CPU: trainer runtime -- schedule, lr groups, QK-clip, EMA, non-finite skip,
+atomic checkpoint / resume, config overrides, dataset."""
+import math
+import os
+
+import pytest
+import torch
+
+from imfvideo_b200 import config as C
+from imfvideo_b200.config import preset
+from imfvideo_b200.data import LatentDataset
+from imfvideo_b200.train import Trainer, apply_lr_width_groups, build_model, lr_at, qk_clip
+from imfvideo_b200.utils import checkpoint as CK
+from imfvideo_b200.utils.schedule import lr_at as lr_fn
+
+
+def _cfg(tmp_path=None):
+    cfg = preset("tiny")
+    cfg.optim.muon_coeff_mode = "jordan"
+    cfg.run.ema_decay = 0.9
+    if tmp_path is not None:
+        cfg.run.out_dir = str(tmp_path)
+    return cfg
+
+
+def test_lr_schedule_shapes():
+    o = preset("tiny").optim
+    o.lr, o.warmup_steps, o.total_steps, o.decay_fraction, o.min_lr_ratio = 1.0, 10, 100, 0.2, 0.1
+    assert lr_fn(0, o) == 0 and lr_fn(5, o) == 0.5 and lr_fn(10, o) == 1.0 and lr_fn(79, o) == 1.0
+    assert abs(lr_fn(85, o) - (0.1 + 0.9 * (1 - math.sqrt(0.25)))) < 1e-9
+    assert abs(lr_fn(100, o) - 0.1) < 1e-9 and abs(lr_fn(1000, o) - 0.1) < 1e-9
+    o.decay_shape = "cosine"
+    assert abs(lr_fn(90, o) - 0.55) < 1e-9
+    o.lr_schedule = "cosine"
+    assert abs(lr_fn(55, o) - 0.55) < 1e-9
+
+
+def test_config_overrides_and_dict_roundtrip():
+    cfg = preset("tiny")
+    C.apply_overrides(cfg, {"model.hidden_size": "128", "optim": {"lr": 1e-3},
+                            "data.latent_size": "(8, 8)", "loss.autocast_bf16": "true"})
+    assert cfg.model.hidden_size == 128 and cfg.optim.lr == 1e-3
+    assert cfg.data.latent_size == (8, 8) and cfg.loss.autocast_bf16 is True
+    with pytest.raises(KeyError):
+        C.apply_overrides(cfg, {"model.hiden_size": 1})
+    d = C.config_as_dict(cfg)
+    cfg2 = C.load_config_dict(preset("tiny"), d)
+    assert C.config_as_dict(cfg2) == d
+    cfg3 = C.parse_cli(["optim.lr=5e-4", "--model.depth=3"], preset("tiny"))
+    assert cfg3.optim.lr == 5e-4 and cfg3.model.depth == 3
+
+
+def test_lr_width_groups():
+    cfg = _cfg()
+    cfg.model.hidden_size, cfg.model.attn_res_block_size = 128, 1
+    cfg.model.kv_lora_rank = 32
+    tr = Trainer(cfg, verbose=False)
+    mults = sorted({(g["use_muon"], round(g["lr_width_mult"], 4)) for g in tr.optimizer.param_groups})
+    assert mults == [(False, 1.0), (False, 2.0), (True, round(2 ** 0.5, 4)), (True, 2.0)]
+    names = {id(p): n for n, p in tr.net.named_parameters()}
+    for g in tr.optimizer.param_groups:
+        for p in g["params"]:
+            n = names[id(p)]
+            if g["use_muon"]:
+                assert ("_res_proj" in n) == (g["lr_width_mult"] == 2.0)
+            elif g["lr_width_mult"] == 2.0:
+                assert "final_layer.linear" in n
+
+
+def test_train_steps_ema_and_resume(tmp_path):
+    cfg = _cfg(tmp_path)
+    cfg.optim.warmup_steps = 0
+    tr = Trainer(cfg, verbose=False)
+    x, y = torch.randn(2, 16, 4, 16, 16), torch.randint(0, 1000, (2,))
+    w0 = [p.detach().clone() for p in tr.net.parameters()]
+    for _ in range(3):
+        st = tr.train_step(x, y)
+    assert math.isfinite(st["loss"]) and not st["skipped"] and tr.step == 3
+    moved = sum(int(not torch.equal(a, b)) for a, b in zip(w0, tr.net.parameters()))
+    assert moved > 0.9 * len(w0)
+    assert any(not torch.equal(a, b) for a, b in zip(tr.ema.parameters(), tr.net.parameters()))
+    path = tr.save()
+    assert os.path.basename(path) == "step_0000003.pt"
+    ck = torch.load(path, weights_only=True)            # plain containers only
+    assert set(ck) >= {"model", "optimizer", "ema", "step", "config"}
+    tr2 = Trainer(_cfg(tmp_path), verbose=False)
+    tr2.load(path)
+    assert tr2.step == 3
+    for a, b in zip(tr.net.parameters(), tr2.net.parameters()):
+        assert torch.equal(a, b)
+    torch.manual_seed(5)
+    s1 = tr.train_step(x, y)
+    torch.manual_seed(5)
+    s2 = tr2.train_step(x, y)
+    assert abs(s1["loss"] - s2["loss"]) < 1e-6 and abs(s1["grad_norm"] - s2["grad_norm"]) < 1e-5
+
+
+def test_checkpoint_is_atomic_and_corruption_is_reported(tmp_path):
+    cfg = _cfg(tmp_path)
+    tr = Trainer(cfg, verbose=False)
+    path = tr.save()
+    assert not [f for f in os.listdir(tmp_path) if ".tmp." in f]
+    assert CK.latest_checkpoint(str(tmp_path)) == path
+    bad = os.path.join(tmp_path, "step_0000009.pt")
+    with open(path, "rb") as fh:
+        blob = fh.read()
+    with open(bad, "wb") as fh:
+        fh.write(blob[: len(blob) // 2])              # a kill in mid-write
+    with pytest.raises(RuntimeError, match="unreadable"):
+        tr.load(bad)
+    tr.load(path)
+
+
+def test_nonfinite_gradient_skips_step(tmp_path):
+    cfg = _cfg(tmp_path)
+    cfg.optim.warmup_steps = 0
+    tr = Trainer(cfg, verbose=False)
+    x, y = torch.randn(2, 16, 4, 16, 16), torch.randint(0, 1000, (2,))
+    tr.micro_step(x, y)
+    next(tr.net.parameters()).grad.view(-1)[0] = float("nan")     # host-side fault injection
+    w0 = [p.detach().clone() for p in tr.net.parameters()]
+    st = tr.optimizer_step()
+    assert st["skipped"]
+    for a, b in zip(w0, tr.net.parameters()):
+        assert torch.equal(a, b)
+
+
+def test_qk_clip_scales_rope_rows_only():
+    cfg = _cfg()
+    net, _, _ = build_model(cfg)
+    blk = net.shared_blocks[0].attn
+
+    class Impl:
+        logit_max_log2 = torch.tensor([100.0 / math.log(2.0), 10.0])   # head 0 hot: 100 nats
+
+        def __call__(self, q, k, v):
+            raise AssertionError
+
+    blk.attn_impl = Impl()
+    w0 = blk.q_b_proj.weight.detach().clone().view(2, blk.qk_head_dim, -1)
+    hot, smax = qk_clip(net, tau=40.0)
+    w1 = blk.q_b_proj.weight.detach().view(2, blk.qk_head_dim, -1)
+    dn = blk.qk_nope_head_dim
+    assert hot == 1 and abs(smax - 100.0) < 1e-3
+    assert torch.allclose(w1[0, dn:], w0[0, dn:] * 0.4) and torch.equal(w1[0, :dn], w0[0, :dn])
+    assert torch.equal(w1[1], w0[1])
+
+
+def test_synthetic_dataset():
+    cfg = preset("tiny")
+    ds = LatentDataset(cfg.data)
+    a, la = ds[3]
+    b, lb = ds[3]
+    assert a.shape == (16, 4, 16, 16) and torch.equal(a, b) and la == lb == 3
+    assert not torch.equal(a, ds[4][0])
