@@ -292,10 +292,86 @@ class TransformerBlock(nn.Module):
             self.attn_res_proj = mk(hidden_size, 1)
             self.mlp_res_proj = mk(hidden_size, 1)
 
+    # ---- fused CUDA path (one autograd node per block, ops/block.py) ----
+    def fused_geom(self):
+        g = getattr(self, "_geom", None)
+        if g is None:
+            from ..ops.block import BlockGeom
+
+            f = self.mlp.w1.out_features
+            g = self._geom = BlockGeom(self.attn, self.norm1.weight.shape[0], f + (-f) % 8)
+        return g
+
+    def fused_ok(self, x: Tensor, compute_dtype) -> bool:
+        if not (x.is_cuda and compute_dtype == torch.bfloat16 and x.dtype == torch.float32):
+            return False
+        from ..ops import cuda as cu
+
+        if not (cu.available() and cu.has("block")):
+            return False
+        core = getattr(self.attn.attn_impl, "fused_core", None)
+        if core is None and self.attn.attn_impl is not flash_jvp_attention:
+            return False
+        from ..ops.block import supported
+
+        return supported(self.fused_geom())
+
+    def fused_params(self, use_res: bool):
+        """(w1, w2, gains..., bf16 weights) for ops.block.run_block.  Under
+        no_grad the bf16 weight copies are cached until a parameter changes."""
+        a, mlp = self.attn, self.mlp
+        ws = [a.q_a_proj.weight, a.kv_a_proj.weight] + ([a.g_proj.weight] if a.use_output_gate else [])
+        srcs = ws + [a.q_b_proj.weight, a.kv_b_proj.weight, a.out_proj.weight, mlp.w1.weight,
+                     mlp.w3.weight, mlp.w2.weight]
+        key = tuple(w._version for w in srcs)
+        cache = getattr(self, "_wcache", None)
+        if not torch.is_grad_enabled() and cache is not None and cache[0] == key:
+            mats = cache[1]
+        else:
+            bf = torch.bfloat16
+            f = mlp.w1.out_features
+            pad = (-f) % 8
+            w1_, w3_, w2_ = mlp.w1.weight, mlp.w3.weight, mlp.w2.weight
+            if pad:
+                z = w1_.new_zeros(pad, w1_.shape[1])
+                w13 = torch.cat([w1_, z, w3_, z], dim=0)
+                w2_ = torch.nn.functional.pad(w2_, (0, pad))
+            else:
+                w13 = torch.cat([w1_, w3_], dim=0)
+            mats = (torch.cat(ws, dim=0).to(bf), a.q_b_proj.weight.to(bf),
+                    a.kv_b_proj.weight.to(bf), a.out_proj.weight.to(bf), w13.to(bf),
+                    w2_.to(bf).contiguous())
+            if not torch.is_grad_enabled():
+                self._wcache = (key, mats)
+        if use_res:
+            w1 = self.attn_res_norm.weight * self.attn_res_proj.weight.reshape(-1)
+            w2 = self.mlp_res_norm.weight * self.mlp_res_proj.weight.reshape(-1)
+        else:
+            w1 = w2 = None
+        return (w1, w2, self.norm1.weight, self.norm2.weight, a.q_a_layernorm.weight,
+                a.kv_a_layernorm.weight, a.q_norm.weight, a.k_norm.weight, self.attn_scale,
+                self.mlp_scale) + mats
+
+    def fused_forward(self, prefix: Dual, snaps, fresh: bool, use_res: bool, rope_cos, rope_sin,
+                      eps: float) -> Dual:
+        from ..ops.block import DENSE_CORE, run_block
+
+        core = getattr(self.attn.attn_impl, "fused_core", None) or DENSE_CORE
+        act = self.mlp.act
+        has_t = prefix.t is not None
+        p, t = run_block(self.fused_geom(), core, fresh, use_res, eps, act.beta, act.linear_beta,
+                         rope_cos, rope_sin, prefix.p, prefix.t, [s.p for s in snaps],
+                         [s.t for s in snaps] if has_t else [None] * len(snaps),
+                         self.fused_params(use_res))
+        return Dual(p, t)
+
     def forward(self, x, rope_cos, rope_sin, compute_dtype=None):
         """Plain pre-norm block (no attention residual)."""
         plain = not isinstance(x, Dual)
         x = D.lift(x)
+        if self.fused_ok(x.p, compute_dtype):
+            out = self.fused_forward(x, [], False, False, rope_cos, rope_sin, self.norm1.eps)
+            return out.p if plain else out
         a = self.attn(self.norm1(x, compute_dtype), rope_cos, rope_sin)
         x = D.scale_add(x, a, self.attn_scale)
         m = self.mlp(self.norm2(x, compute_dtype))
@@ -535,6 +611,8 @@ class IMFDiTVideo(nn.Module):
     def _res_block(self, blk: TransformerBlock, fresh: bool, prefix: Dual,
                    snaps: List[Dual]) -> Dual:
         eps, cd = self.rmsnorm_eps, self.compute_dtype
+        if blk.fused_ok(prefix.p, cd):
+            return blk.fused_forward(prefix, snaps, fresh, True, self.rope_cos, self.rope_sin, eps)
         h1 = (D.attn_res(prefix, snaps, blk.attn_res_norm.weight, blk.attn_res_proj.weight, eps)
               if snaps else prefix)
         a = blk.attn(blk.norm1(h1, cd), self.rope_cos, self.rope_sin)

@@ -1,0 +1,590 @@
+// Remaining per-token kernels of the MLA block, each with forward-mode
+// tangent and reverse-mode gradient:
+//   * strided RMSNorm over a column band of a wider GEMM output (latent norms)
+//   * q/k preparation: per-head RMSNorm of the position-free band, rotary
+//     embedding of the rope band, shared k_rope broadcast over heads
+//   * sigmoid output gate, SituAndMul activation, gated residual add
+// They replace the reference's `_rmsnorm_jvp_strided_kernel`, `_q_prep_kernel`,
+// `_kv_prep_kernel`, `_out_gate_jvp_kernel`, `_swiglu_row_jvp_kernel` and
+// `_gate_add_kernel` (reference models/triton_mla_block_jvp.py:237-521) and
+// add the backward halves the reference leaves to autograd.
+#include "rowops_common.cuh"
+
+namespace imf {
+
+typedef __nv_bfloat16 bf16;
+
+// ---------------------------------------------------------------------------
+// Strided RMSNorm, up to 2 column segments per launch (grid.y = segment)
+// ---------------------------------------------------------------------------
+struct NormSeg {
+  const bf16* x;
+  const bf16* dx;
+  const float* gain;
+  bf16* out;
+  bf16* dout;
+  const bf16* gy;   // bwd: grad of out
+  bf16* gx;         // bwd: grad of x (strided like x)
+  float* partial;   // bwd: [grid.x, D]
+  int D, ld_x, ld_o;
+};
+struct NormArgs {
+  NormSeg seg[2];
+  int rows;
+  float eps;
+  int has_t;
+};
+
+__global__ void __launch_bounds__(ROW_THREADS) rmsnorm_seg_fwd_kernel(const NormArgs a) {
+  const NormSeg& s = a.seg[blockIdx.y];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float inv_d = 1.f / s.D;
+  for (int row = blockIdx.x * ROW_WARPS + warp; row < a.rows; row += gridDim.x * ROW_WARPS) {
+    const bf16* x = s.x + (size_t)row * s.ld_x;
+    const bf16* dx = a.has_t ? s.dx + (size_t)row * s.ld_x : nullptr;
+    float ss = 0.f, xd = 0.f;
+    for (int c = lane * 4; c < s.D; c += 128) {
+      const float4 v = ld4(x + c);
+      ss += dot4(v, v);
+      if (a.has_t) xd += dot4(v, ld4(dx + c));
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss * inv_d + a.eps);
+    float c2 = 0.f;
+    if (a.has_t) c2 = warp_sum(xd) * inv_d * r * r * r;
+    for (int c = lane * 4; c < s.D; c += 128) {
+      const float4 v = ld4(x + c), g = ld4(s.gain + c);
+      st4(s.out + (size_t)row * s.ld_o + c, v * g * r);
+      if (a.has_t)
+        st4(s.dout + (size_t)row * s.ld_o + c, fma4(v, -c2, ld4(dx + c) * r) * g);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(ROW_THREADS) rmsnorm_seg_bwd_kernel(const NormArgs a) {
+  extern __shared__ float smem_acc[];  // [ROW_WARPS][D]
+  const NormSeg& s = a.seg[blockIdx.y];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float inv_d = 1.f / s.D;
+  float* acc = smem_acc + (size_t)warp * s.D;
+  for (int c = lane; c < s.D; c += 32) acc[c] = 0.f;
+  __syncwarp();
+  for (int row = blockIdx.x * ROW_WARPS + warp; row < a.rows; row += gridDim.x * ROW_WARPS) {
+    const bf16* x = s.x + (size_t)row * s.ld_x;
+    const bf16* gy = s.gy + (size_t)row * s.ld_o;
+    float ss = 0.f, ux = 0.f;
+    for (int c = lane * 4; c < s.D; c += 128) {
+      const float4 v = ld4(x + c);
+      ss += dot4(v, v);
+      ux += dot4(ld4(gy + c) * ld4(s.gain + c), v);
+    }
+    ss = warp_sum(ss);
+    ux = warp_sum(ux);
+    const float r = rsqrtf(ss * inv_d + a.eps);
+    const float c3 = ux * inv_d * r * r * r;
+    for (int c = lane * 4; c < s.D; c += 128) {
+      const float4 v = ld4(x + c), g = ld4(gy + c);
+      st4(s.gx + (size_t)row * s.ld_x + c, fma4(v, -c3, g * ld4(s.gain + c) * r));
+      st4(acc + c, ld4(acc + c) + g * v * r);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < s.D; c += blockDim.x) {
+    float t = 0.f;
+    for (int w = 0; w < ROW_WARPS; ++w) t += smem_acc[(size_t)w * s.D + c];
+    s.partial[(size_t)blockIdx.x * s.D + c] = t;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// q / k preparation
+// ---------------------------------------------------------------------------
+struct PrepArgs {
+  const bf16 *qb, *dqb;        // [rows, H*HD]
+  const bf16 *kvb, *dkvb;      // [rows, H*(dn+dv)]
+  const bf16 *kr, *dkr;        // shared rope key, [rows, dr] with row stride ld_kr
+  const float *cos_, *sin_;    // [L, dr/2]
+  const float *qg, *kg;        // per-head norm gains [dn]
+  bf16 *q, *dq, *k, *dk;       // [rows, H, HD]
+  // backward
+  const bf16 *gq, *gk;         // [rows, H, HD]
+  bf16 *g_qb, *g_kvb, *g_kr;   // same layouts as qb / kvb (nope band only) / kr
+  float* partial;              // [grid, 2, dn]
+  int rows, L, H, dn, dr, dv, ld_kr, ld_gkr;
+  float eps;
+  int has_t;
+};
+
+// one warp per (row, head, q|k); lane owns EPL = HD/32 consecutive channels
+template <int EPL>
+__global__ void __launch_bounds__(ROW_THREADS) qkprep_fwd_kernel(const PrepArgs a) {
+  const int HD = EPL * 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long total = (long)a.rows * a.H * 2;
+  const float inv_dn = 1.f / a.dn;
+  for (long wid = (long)blockIdx.x * ROW_WARPS + warp; wid < total;
+       wid += (long)gridDim.x * ROW_WARPS) {
+    const int which = (int)(wid % 2);
+    const int h = (int)((wid / 2) % a.H);
+    const int row = (int)(wid / (2 * a.H));
+    const int c0 = lane * EPL;
+    const bool nope = c0 < a.dn;
+    const bf16 *src, *dsrc;
+    if (which == 0) {
+      src = a.qb + (size_t)row * a.H * HD + h * HD + c0;
+      dsrc = a.dqb ? a.dqb + (size_t)row * a.H * HD + h * HD + c0 : nullptr;
+    } else if (nope) {
+      src = a.kvb + (size_t)row * a.H * (a.dn + a.dv) + h * (a.dn + a.dv) + c0;
+      dsrc = a.dkvb ? a.dkvb + (size_t)row * a.H * (a.dn + a.dv) + h * (a.dn + a.dv) + c0 : nullptr;
+    } else {
+      src = a.kr + (size_t)row * a.ld_kr + (c0 - a.dn);
+      dsrc = a.dkr ? a.dkr + (size_t)row * a.ld_kr + (c0 - a.dn) : nullptr;
+    }
+    float x[EPL], dx[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      x[e] = __bfloat162float(src[e]);
+      dx[e] = (a.has_t && dsrc) ? __bfloat162float(dsrc[e]) : 0.f;
+    }
+    float ss = 0.f, xd = 0.f;
+    if (nope) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        ss += x[e] * x[e];
+        xd += x[e] * dx[e];
+      }
+    }
+    ss = warp_sum(ss);
+    xd = warp_sum(xd);
+    float y[EPL], dy[EPL];
+    if (nope) {
+      const float r = rsqrtf(ss * inv_dn + a.eps);
+      const float c2 = xd * inv_dn * r * r * r;
+      const float* g = (which == 0 ? a.qg : a.kg) + c0;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        y[e] = x[e] * r * g[e];
+        dy[e] = (dx[e] * r - x[e] * c2) * g[e];
+      }
+    } else {
+      const int pos = row % a.L;
+      const int pr = (c0 - a.dn) / 2;
+#pragma unroll
+      for (int e = 0; e < EPL; e += 2) {
+        const float cs = a.cos_[(size_t)pos * (a.dr / 2) + pr + e / 2];
+        const float sn = a.sin_[(size_t)pos * (a.dr / 2) + pr + e / 2];
+        y[e] = x[e] * cs - x[e + 1] * sn;
+        y[e + 1] = x[e] * sn + x[e + 1] * cs;
+        dy[e] = dx[e] * cs - dx[e + 1] * sn;
+        dy[e + 1] = dx[e] * sn + dx[e + 1] * cs;
+      }
+    }
+    bf16* dst = (which == 0 ? a.q : a.k) + ((size_t)row * a.H + h) * HD + c0;
+    bf16* ddst = (which == 0 ? a.dq : a.dk);
+#pragma unroll
+    for (int e = 0; e < EPL; e += 2)
+      *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(y[e], y[e + 1]);
+    if (a.has_t) {
+      ddst += ((size_t)row * a.H + h) * HD + c0;
+#pragma unroll
+      for (int e = 0; e < EPL; e += 2)
+        *reinterpret_cast<__nv_bfloat162*>(ddst + e) = __floats2bfloat162_rn(dy[e], dy[e + 1]);
+    }
+  }
+}
+
+// backward: warps (row, h, q|k) as forward, plus one extra warp slot per row
+// (index 2H) that sums the shared rope-key gradient over heads.
+template <int EPL>
+__global__ void __launch_bounds__(ROW_THREADS) qkprep_bwd_kernel(const PrepArgs a) {
+  const int HD = EPL * 32;
+  extern __shared__ float smem_acc[];  // [ROW_WARPS][2][dn]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* acc = smem_acc + (size_t)warp * 2 * a.dn;
+  for (int c = lane; c < 2 * a.dn; c += 32) acc[c] = 0.f;
+  __syncwarp();
+  const int per_row = 2 * a.H + 1;
+  const long total = (long)a.rows * per_row;
+  const float inv_dn = 1.f / a.dn;
+  for (long wid = (long)blockIdx.x * ROW_WARPS + warp; wid < total;
+       wid += (long)gridDim.x * ROW_WARPS) {
+    const int slot = (int)(wid % per_row);
+    const int row = (int)(wid / per_row);
+    const int pos = row % a.L;
+    if (slot == 2 * a.H) {
+      // g_k_rope[c'] = sum_h R^T gk[row, h, dn + c']
+      const int npair = a.dr / 2;
+      for (int pr = lane; pr < npair; pr += 32) {
+        const float cs = a.cos_[(size_t)pos * npair + pr], sn = a.sin_[(size_t)pos * npair + pr];
+        float gr = 0.f, gi = 0.f;
+        for (int h = 0; h < a.H; ++h) {
+          const bf16* g = a.gk + ((size_t)row * a.H + h) * HD + a.dn + 2 * pr;
+          const float a0 = __bfloat162float(g[0]), a1 = __bfloat162float(g[1]);
+          gr += a0 * cs + a1 * sn;
+          gi += -a0 * sn + a1 * cs;
+        }
+        *reinterpret_cast<__nv_bfloat162*>(a.g_kr + (size_t)row * a.ld_gkr + 2 * pr) =
+            __floats2bfloat162_rn(gr, gi);
+      }
+      continue;
+    }
+    const int which = slot % 2, h = slot / 2;
+    const int c0 = lane * EPL;
+    const bool nope = c0 < a.dn;
+    // k rope lanes are handled by the extra slot: they only join the reductions
+    const bool skip = (which == 1 && !nope);
+    const bf16* gsrc = (which == 0 ? a.gq : a.gk) + ((size_t)row * a.H + h) * HD + c0;
+    float g[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) g[e] = skip ? 0.f : __bfloat162float(gsrc[e]);
+    const bf16* src = which == 0 ? a.qb + (size_t)row * a.H * HD + h * HD + c0
+                                 : a.kvb + (size_t)row * a.H * (a.dn + a.dv) + h * (a.dn + a.dv) + c0;
+    float x[EPL];
+    float ss = 0.f, ux = 0.f;
+    const float* gain = (which == 0 ? a.qg : a.kg) + c0;
+    if (nope) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        x[e] = __bfloat162float(src[e]);
+        ss += x[e] * x[e];
+        ux += g[e] * gain[e] * x[e];
+      }
+    }
+    ss = warp_sum(ss);
+    ux = warp_sum(ux);
+    float gx[EPL];
+    if (nope) {
+      const float r = rsqrtf(ss * inv_dn + a.eps);
+      const float c3 = ux * inv_dn * r * r * r;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        gx[e] = g[e] * gain[e] * r - x[e] * c3;
+        acc[which * a.dn + c0 + e] += g[e] * x[e] * r;
+      }
+    } else if (!skip) {
+      const int pr = (c0 - a.dn) / 2;
+#pragma unroll
+      for (int e = 0; e < EPL; e += 2) {
+        const float cs = a.cos_[(size_t)pos * (a.dr / 2) + pr + e / 2];
+        const float sn = a.sin_[(size_t)pos * (a.dr / 2) + pr + e / 2];
+        gx[e] = g[e] * cs + g[e + 1] * sn;
+        gx[e + 1] = -g[e] * sn + g[e + 1] * cs;
+      }
+    }
+    if (!skip) {
+      bf16* dst = which == 0
+                      ? a.g_qb + (size_t)row * a.H * HD + h * HD + c0
+                      : a.g_kvb + (size_t)row * a.H * (a.dn + a.dv) + h * (a.dn + a.dv) + c0;
+#pragma unroll
+      for (int e = 0; e < EPL; e += 2)
+        *reinterpret_cast<__nv_bfloat162*>(dst + e) = __floats2bfloat162_rn(gx[e], gx[e + 1]);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * a.dn; c += blockDim.x) {
+    float t = 0.f;
+    for (int w = 0; w < ROW_WARPS; ++w) t += smem_acc[(size_t)w * 2 * a.dn + c];
+    a.partial[(size_t)blockIdx.x * 2 * a.dn + c] = t;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Elementwise: output gate, SituAndMul, gated residual add
+// ---------------------------------------------------------------------------
+struct EwArgs {
+  const bf16 *a0, *da0;    // o / gate-half / y
+  const bf16 *b0, *db0;    // g / up-half
+  const float *res, *dres; // scale_add: residual
+  const float* gate;       // scale_add: per-column gate
+  bf16 *out, *dout;
+  float *fout, *dfout;     // scale_add: fp32 output
+  const bf16* gout;        // bwd: grad of out (bf16)
+  const float* gfout;      // bwd: grad of fp32 out
+  bf16 *ga, *gb;           // bwd: grads of a0 / b0
+  float* partial;          // bwd (scale_add): [grid, D]
+  int rows, D, ld_a, ld_b, ld_o, ld_ga, ld_gb;
+  float beta, lbeta;
+  int has_lbeta, has_t;
+};
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+__global__ void __launch_bounds__(ROW_THREADS) outgate_fwd_kernel(const EwArgs a) {
+  const long n4 = (long)a.rows * (a.D / 4);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+       i += (long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / (a.D / 4)), c = (int)(i % (a.D / 4)) * 4;
+    const float4 o = ld4(a.a0 + (size_t)row * a.ld_a + c), z = ld4(a.b0 + (size_t)row * a.ld_b + c);
+    const float4 s = make_float4(sigmoidf_(z.x), sigmoidf_(z.y), sigmoidf_(z.z), sigmoidf_(z.w));
+    st4(a.out + (size_t)row * a.ld_o + c, o * s);
+    if (a.has_t) {
+      const float4 d_o = ld4(a.da0 + (size_t)row * a.ld_a + c);
+      const float4 dz = ld4(a.db0 + (size_t)row * a.ld_b + c);
+      const float4 one = make_float4(1.f - s.x, 1.f - s.y, 1.f - s.z, 1.f - s.w);
+      st4(a.dout + (size_t)row * a.ld_o + c, d_o * s + o * s * one * dz);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(ROW_THREADS) outgate_bwd_kernel(const EwArgs a) {
+  const long n4 = (long)a.rows * (a.D / 4);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+       i += (long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / (a.D / 4)), c = (int)(i % (a.D / 4)) * 4;
+    const float4 o = ld4(a.a0 + (size_t)row * a.ld_a + c), z = ld4(a.b0 + (size_t)row * a.ld_b + c);
+    const float4 g = ld4(a.gout + (size_t)row * a.ld_o + c);
+    const float4 s = make_float4(sigmoidf_(z.x), sigmoidf_(z.y), sigmoidf_(z.z), sigmoidf_(z.w));
+    const float4 one = make_float4(1.f - s.x, 1.f - s.y, 1.f - s.z, 1.f - s.w);
+    st4(a.ga + (size_t)row * a.ld_ga + c, g * s);
+    st4(a.gb + (size_t)row * a.ld_gb + c, g * o * s * one);
+  }
+}
+
+// situ(g) = beta tanh(g/beta) sigmoid(g); up' = lbeta tanh(up/lbeta)
+__device__ __forceinline__ void situ1(float g, float u, float beta, float lbeta, int has_lb,
+                                      float& a, float& da_dg, float& up, float& dup_du) {
+  const float th = tanhf(g / beta), sg = sigmoidf_(g);
+  a = beta * th * sg;
+  da_dg = (1.f - th * th) * sg + beta * th * sg * (1.f - sg);
+  if (has_lb) {
+    const float tu = tanhf(u / lbeta);
+    up = lbeta * tu;
+    dup_du = 1.f - tu * tu;
+  } else {
+    up = u;
+    dup_du = 1.f;
+  }
+}
+
+// a0 = [gate | up] rows of width 2*D (up at column offset ld_b), out width D
+__global__ void __launch_bounds__(ROW_THREADS) situ_fwd_kernel(const EwArgs a) {
+  const long n2 = (long)a.rows * (a.D / 2);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n2;
+       i += (long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / (a.D / 2)), c = (int)(i % (a.D / 2)) * 2;
+    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(a.a0 + (size_t)row * a.ld_a + c);
+    const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(a.b0 + (size_t)row * a.ld_a + c);
+    const float g[2] = {__low2float(g2), __high2float(g2)}, u[2] = {__low2float(u2), __high2float(u2)};
+    float y[2], dy[2] = {0.f, 0.f};
+    float dg[2] = {0.f, 0.f}, du[2] = {0.f, 0.f};
+    if (a.has_t) {
+      const __nv_bfloat162 dg2 = *reinterpret_cast<const __nv_bfloat162*>(a.da0 + (size_t)row * a.ld_a + c);
+      const __nv_bfloat162 du2 = *reinterpret_cast<const __nv_bfloat162*>(a.db0 + (size_t)row * a.ld_a + c);
+      dg[0] = __low2float(dg2); dg[1] = __high2float(dg2);
+      du[0] = __low2float(du2); du[1] = __high2float(du2);
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float av, dav, up, dup;
+      situ1(g[e], u[e], a.beta, a.lbeta, a.has_lbeta, av, dav, up, dup);
+      y[e] = av * up;
+      dy[e] = dav * dg[e] * up + av * dup * du[e];
+    }
+    *reinterpret_cast<__nv_bfloat162*>(a.out + (size_t)row * a.ld_o + c) = __floats2bfloat162_rn(y[0], y[1]);
+    if (a.has_t)
+      *reinterpret_cast<__nv_bfloat162*>(a.dout + (size_t)row * a.ld_o + c) =
+          __floats2bfloat162_rn(dy[0], dy[1]);
+  }
+}
+
+__global__ void __launch_bounds__(ROW_THREADS) situ_bwd_kernel(const EwArgs a) {
+  const long n2 = (long)a.rows * (a.D / 2);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n2;
+       i += (long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / (a.D / 2)), c = (int)(i % (a.D / 2)) * 2;
+    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(a.a0 + (size_t)row * a.ld_a + c);
+    const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(a.b0 + (size_t)row * a.ld_a + c);
+    const __nv_bfloat162 go2 = *reinterpret_cast<const __nv_bfloat162*>(a.gout + (size_t)row * a.ld_o + c);
+    const float g[2] = {__low2float(g2), __high2float(g2)}, u[2] = {__low2float(u2), __high2float(u2)};
+    const float go[2] = {__low2float(go2), __high2float(go2)};
+    float gg[2], gu[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float av, dav, up, dup;
+      situ1(g[e], u[e], a.beta, a.lbeta, a.has_lbeta, av, dav, up, dup);
+      gg[e] = go[e] * dav * up;
+      gu[e] = go[e] * av * dup;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(a.ga + (size_t)row * a.ld_ga + c) = __floats2bfloat162_rn(gg[0], gg[1]);
+    *reinterpret_cast<__nv_bfloat162*>(a.gb + (size_t)row * a.ld_ga + c) = __floats2bfloat162_rn(gu[0], gu[1]);
+  }
+}
+
+// fout = res + y * gate   (fp32 residual stream; y bf16)
+__global__ void __launch_bounds__(ROW_THREADS) scale_add_fwd_kernel(const EwArgs a) {
+  const long n4 = (long)a.rows * (a.D / 4);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+       i += (long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / (a.D / 4)), c = (int)(i % (a.D / 4)) * 4;
+    const size_t o = (size_t)row * a.D + c;
+    const float4 g = ld4(a.gate + c);
+    float4 v = ld4(a.a0 + o) * g;
+    if (a.res) v = v + ld4(a.res + o);
+    st4(a.fout + o, v);
+    if (a.has_t) {
+      float4 dv = ld4(a.da0 + o) * g;
+      if (a.dres) dv = dv + ld4(a.dres + o);
+      st4(a.dfout + o, dv);
+    }
+  }
+}
+
+// g_y = g * gate (bf16); partial[c] += g * y   (g_res is g itself)
+__global__ void __launch_bounds__(ROW_THREADS) scale_add_bwd_kernel(const EwArgs a) {
+  extern __shared__ float smem_acc[];  // [ROW_WARPS][D]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* acc = smem_acc + (size_t)warp * a.D;
+  for (int c = lane; c < a.D; c += 32) acc[c] = 0.f;
+  __syncwarp();
+  for (int row = blockIdx.x * ROW_WARPS + warp; row < a.rows; row += gridDim.x * ROW_WARPS) {
+    for (int c = lane * 4; c < a.D; c += 128) {
+      const size_t o = (size_t)row * a.D + c;
+      const float4 g = ld4(a.gfout + o);
+      st4(a.ga + o, g * ld4(a.gate + c));
+      st4(acc + c, ld4(acc + c) + g * ld4(a.a0 + o));
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < a.D; c += blockDim.x) {
+    float t = 0.f;
+    for (int w = 0; w < ROW_WARPS; ++w) t += smem_acc[(size_t)w * a.D + c];
+    a.partial[(size_t)blockIdx.x * a.D + c] = t;
+  }
+}
+
+static int ew_grid(long n) {
+  long g = (n + ROW_THREADS - 1) / ROW_THREADS;
+  return (int)(g < 1 ? 1 : (g > 148 * 8 ? 148 * 8 : g));
+}
+
+}  // namespace imf
+
+using namespace imf;
+
+// ptrs (per segment s in 0..nseg-1, 8 pointers each):
+//   x, dx, gain, out, dout, gy, gx, partial ; dims[s] = {D, ld_x, ld_o}
+extern "C" int imf_rmsnorm_seg(void** ptrs, const int* dims, int nseg, int rows, float eps,
+                               int has_t, int bwd, void* stream) {
+  if (nseg < 1 || nseg > 2 || rows <= 0) return -1;
+  NormArgs a;
+  int maxd = 0;
+  for (int s = 0; s < nseg; ++s) {
+    NormSeg& g = a.seg[s];
+    void** p = ptrs + 8 * s;
+    g.x = (const bf16*)p[0];
+    g.dx = (const bf16*)p[1];
+    g.gain = (const float*)p[2];
+    g.out = (bf16*)p[3];
+    g.dout = (bf16*)p[4];
+    g.gy = (const bf16*)p[5];
+    g.gx = (bf16*)p[6];
+    g.partial = (float*)p[7];
+    g.D = dims[3 * s];
+    g.ld_x = dims[3 * s + 1];
+    g.ld_o = dims[3 * s + 2];
+    if (g.D % 4 || g.ld_x % 4 || g.ld_o % 4) return -1;
+    maxd = g.D > maxd ? g.D : maxd;
+  }
+  if (nseg == 1) a.seg[1] = a.seg[0];
+  a.rows = rows;
+  a.eps = eps;
+  a.has_t = has_t;
+  dim3 grid(row_grid(rows), nseg);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!bwd) {
+    rmsnorm_seg_fwd_kernel<<<grid, ROW_THREADS, 0, st>>>(a);
+  } else {
+    const size_t smem = (size_t)ROW_WARPS * maxd * sizeof(float);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(rmsnorm_seg_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return -3;
+    rmsnorm_seg_bwd_kernel<<<grid, ROW_THREADS, smem, st>>>(a);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// ptrs: 0 qb, 1 dqb, 2 kvb, 3 dkvb, 4 kr, 5 dkr, 6 cos, 7 sin, 8 qg, 9 kg, 10 q, 11 dq, 12 k,
+//       13 dk, 14 gq, 15 gk, 16 g_qb, 17 g_kvb, 18 g_kr, 19 partial
+extern "C" int imf_qkprep(void** p, int rows, int L, int H, int dn, int dr, int dv, int ld_kr,
+                          int ld_gkr, float eps, int has_t, int bwd, void* stream) {
+  const int HD = dn + dr;
+  if ((HD != 64 && HD != 128) || rows <= 0) return -1;
+  const int epl = HD / 32;
+  if (dn % epl || dr % 2 || (dn + dv) % 2 || ld_kr % 2) return -1;
+  PrepArgs a;
+  a.qb = (const bf16*)p[0]; a.dqb = (const bf16*)p[1];
+  a.kvb = (const bf16*)p[2]; a.dkvb = (const bf16*)p[3];
+  a.kr = (const bf16*)p[4]; a.dkr = (const bf16*)p[5];
+  a.cos_ = (const float*)p[6]; a.sin_ = (const float*)p[7];
+  a.qg = (const float*)p[8]; a.kg = (const float*)p[9];
+  a.q = (bf16*)p[10]; a.dq = (bf16*)p[11]; a.k = (bf16*)p[12]; a.dk = (bf16*)p[13];
+  a.gq = (const bf16*)p[14]; a.gk = (const bf16*)p[15];
+  a.g_qb = (bf16*)p[16]; a.g_kvb = (bf16*)p[17]; a.g_kr = (bf16*)p[18];
+  a.partial = (float*)p[19];
+  a.rows = rows; a.L = L; a.H = H; a.dn = dn; a.dr = dr; a.dv = dv;
+  a.ld_kr = ld_kr; a.ld_gkr = ld_gkr; a.eps = eps; a.has_t = has_t;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!bwd) {
+    const int grid = row_grid(rows * H * 2);
+    if (epl == 2) qkprep_fwd_kernel<2><<<grid, ROW_THREADS, 0, st>>>(a);
+    else qkprep_fwd_kernel<4><<<grid, ROW_THREADS, 0, st>>>(a);
+  } else {
+    const int grid = row_grid(rows);     // partial buffers are sized by imf_row_grid(rows)
+    const size_t smem = (size_t)ROW_WARPS * 2 * dn * sizeof(float);
+    if (epl == 2) qkprep_bwd_kernel<2><<<grid, ROW_THREADS, smem, st>>>(a);
+    else qkprep_bwd_kernel<4><<<grid, ROW_THREADS, smem, st>>>(a);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// op: 0 out-gate, 1 situ, 2 scale-add.
+// ptrs: 0 a0, 1 da0, 2 b0, 3 db0, 4 res, 5 dres, 6 gate, 7 out, 8 dout, 9 fout, 10 dfout,
+//       11 gout, 12 gfout, 13 ga, 14 gb, 15 partial
+// dims: rows, D, ld_a, ld_b, ld_o, ld_ga, ld_gb
+extern "C" int imf_elementwise(int op, void** p, const int* dims, float beta, float lbeta,
+                               int has_lbeta, int has_t, int bwd, void* stream) {
+  EwArgs a;
+  a.a0 = (const bf16*)p[0]; a.da0 = (const bf16*)p[1];
+  a.b0 = (const bf16*)p[2]; a.db0 = (const bf16*)p[3];
+  a.res = (const float*)p[4]; a.dres = (const float*)p[5];
+  a.gate = (const float*)p[6];
+  a.out = (bf16*)p[7]; a.dout = (bf16*)p[8];
+  a.fout = (float*)p[9]; a.dfout = (float*)p[10];
+  a.gout = (const bf16*)p[11]; a.gfout = (const float*)p[12];
+  a.ga = (bf16*)p[13]; a.gb = (bf16*)p[14];
+  a.partial = (float*)p[15];
+  a.rows = dims[0]; a.D = dims[1]; a.ld_a = dims[2]; a.ld_b = dims[3]; a.ld_o = dims[4];
+  a.ld_ga = dims[5]; a.ld_gb = dims[6];
+  a.beta = beta; a.lbeta = lbeta; a.has_lbeta = has_lbeta; a.has_t = has_t;
+  if (a.rows <= 0 || a.D <= 0 || a.D % 4) return -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (op == 0) {
+    if (a.ld_a % 4 || a.ld_b % 4 || a.ld_o % 4) return -1;
+    const int grid = ew_grid((long)a.rows * a.D / 4);
+    if (!bwd) outgate_fwd_kernel<<<grid, ROW_THREADS, 0, st>>>(a);
+    else {
+      if (a.ld_ga % 4 || a.ld_gb % 4) return -1;
+      outgate_bwd_kernel<<<grid, ROW_THREADS, 0, st>>>(a);
+    }
+  } else if (op == 1) {
+    if (a.ld_a % 2 || a.ld_o % 2) return -1;
+    const int grid = ew_grid((long)a.rows * a.D / 2);
+    if (!bwd) situ_fwd_kernel<<<grid, ROW_THREADS, 0, st>>>(a);
+    else situ_bwd_kernel<<<grid, ROW_THREADS, 0, st>>>(a);
+  } else if (op == 2) {
+    if (!bwd) {
+      scale_add_fwd_kernel<<<ew_grid((long)a.rows * a.D / 4), ROW_THREADS, 0, st>>>(a);
+    } else {
+      const size_t smem = (size_t)ROW_WARPS * a.D * sizeof(float);
+      if (smem > 48 * 1024 &&
+          cudaFuncSetAttribute(scale_add_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem) != cudaSuccess)
+        return -3;
+      scale_add_bwd_kernel<<<row_grid(a.rows), ROW_THREADS, smem, st>>>(a);
+    }
+  } else {
+    return -1;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

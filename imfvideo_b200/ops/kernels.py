@@ -257,3 +257,5 @@ if _has("imf_gemm_bf16"):
     _cuda.register("gemm", linear_dual=linear_dual)
 if _has("imf_attn_fwd"):
     _cuda.register("attention", attention_dual=attention_dual)
+if _has("imf_resnorm") and _has("imf_gemm_bf16") and _has("imf_attn_fwd"):
+    _cuda.register("block")
