@@ -112,7 +112,25 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
 if _has("imf_attn_fwd"):
     _lib.imf_attn_fwd.restype = c_int
     _lib.imf_attn_fwd.argtypes = [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_void_p, c_int64,
-                                                   c_int64, c_int64, c_float, c_void_p, c_void_p]
+                                                   c_int64, c_int64, c_float, c_void_p,
+                                                   ctypes.c_long, c_void_p, c_void_p]
+    _lib.imf_attn_fwd_scratch_bytes.restype = ctypes.c_long
+    _lib.imf_attn_fwd_scratch_bytes.argtypes = [c_int, c_int, c_int, c_int]
+
+_scratch: Dict[Tuple[int, str], torch.Tensor] = {}
+
+
+def _scratch_buf(device: torch.device, nbytes: int, tag: str) -> Optional[torch.Tensor]:
+    """Per-device grow-only scratch (split-item partials of the persistent
+    attention kernels); reused by every call on the same stream order."""
+    if nbytes <= 0:
+        return None
+    key = (device.index or 0, tag)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
 
 
 def _bls(t: torch.Tensor) -> Tuple[int, int, int]:
@@ -143,11 +161,13 @@ def attn_fwd(q, k, v, dq=None, dk=None, dv=None, scale: Optional[float] = None,
     o = torch.empty(B, L, H, hd, dtype=torch.bfloat16, device=q.device)
     do = torch.empty_like(o) if tang else None
     lse = torch.empty(B, H, L, dtype=torch.float32, device=q.device) if need_lse else None
+    nscr = int(_lib.imf_attn_fwd_scratch_bytes(B, L, H, int(tang)))
+    scr = _scratch_buf(q.device, nscr, "attn_fwd")
     rc = _lib.imf_attn_fwd(_ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]),
                            _ptr(ts[3]) if tang else None, _ptr(ts[4]) if tang else None,
                            _ptr(ts[5]) if tang else None, _ptr(o), _ptr(do), _ptr(lse), B, L, H,
                            hd, ctypes.cast(arr, c_void_p), o.stride(0), o.stride(1), o.stride(2),
-                           float(scale), _ptr(status_word(q.device)), _stream())
+                           float(scale), _ptr(scr), nscr, _ptr(status_word(q.device)), _stream())
     _check(rc, "imf_attn_fwd")
     LAUNCHES.count += 1
     return o, do, lse
