@@ -658,3 +658,50 @@ extern "C" int imf_attn_fwd(const void* q, const void* k, const void* v, const v
   return launch_attn_fwd<false>(q, k, v, nullptr, nullptr, nullptr, strides, prm,
                                 (size_t)scratch_bytes, st);
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free entry point (see attn_noalloc.h for who needs it and why).
+// ---------------------------------------------------------------------------
+#include "attn_noalloc.h"
+
+namespace imf {
+constexpr size_t NOALLOC_FLOATS =
+    (size_t)IMF_ATTN_NOALLOC_MAX_CTAS * 2 * ((size_t)ATT_ITEM_M * (ATT_HD + 3));
+// Split-item partials of the primal forward.  In host code this name is only a
+// stand-in for the symbol, not a device address: the address comes from
+// cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_attn_noalloc_scratch[NOALLOC_FLOATS];
+}  // namespace imf
+
+extern "C" int imf_attn_fwd_noalloc(const void* q, const void* k, const void* v, void* o,
+                                    float* lse, int B, int L, int H, int head_dim,
+                                    const int64_t* strides, int64_t o_sb, int64_t o_sl,
+                                    int64_t o_sh, float scale, int* status, void* stream) {
+  using namespace imf;
+  static_assert(NOALLOC_FLOATS == (size_t)IMF_ATTN_NOALLOC_MAX_CTAS * 2 * att_part_floats<false>(),
+                "scratch array and partial record size disagree");
+  constexpr int MAX_DEVICES = 64;
+  static float* scratch_of_device[MAX_DEVICES] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return IMF_ERR_DRIVER;
+  if (scratch_of_device[dev] == nullptr) {
+    // once per device, with that device current; do this outside stream capture
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_attn_noalloc_scratch) != cudaSuccess || ptr == nullptr) {
+      fprintf(stderr, "imf_attn_fwd_noalloc: cudaGetSymbolAddress failed on device %d\n", dev);
+      return IMF_ERR_DRIVER;
+    }
+    scratch_of_device[dev] = static_cast<float*>(ptr);
+  }
+  const long need = imf_attn_fwd_scratch_bytes(B, L, H, 0);
+  if (need > (long)(NOALLOC_FLOATS * sizeof(float))) {
+    fprintf(stderr,
+            "imf_attn_fwd_noalloc: problem needs %ld bytes of partial-result scratch, the "
+            "built-in array holds %zu (at most %d thread blocks)\n",
+            need, NOALLOC_FLOATS * sizeof(float), IMF_ATTN_NOALLOC_MAX_CTAS);
+    return IMF_ERR_TOO_LARGE;
+  }
+  return imf_attn_fwd(q, k, v, nullptr, nullptr, nullptr, o, nullptr, lse, B, L, H, head_dim,
+                      strides, o_sb, o_sl, o_sh, scale, scratch_of_device[dev],
+                      (long)(NOALLOC_FLOATS * sizeof(float)), status, stream);
+}
