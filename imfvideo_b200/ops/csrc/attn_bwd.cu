@@ -1,0 +1,474 @@
+// Dense flash attention backward (reverse mode) on tcgen05 / TMEM.
+//
+// Given Q, K, V, O, dO and the forward's log-sum-exp, computes dQ, dK, dV with
+// O(L) memory by recomputing P tile by tile:
+//
+//   S^T = K Q^T,  P^T = exp2(S^T * scale*log2e - lse2),  dP^T = V dO^T,
+//   dS^T = P^T .* (dP^T - delta),   delta = rowsum(dO .* O)
+//   dV += P^T dO,   dK += scale * dS^T Q,   dQ += scale * dS K
+//
+// Replaces FA4 / SDPA backward in the reference (reference
+// models/attention_op.py:38-60) and `_attn_bwd_*` of its SLA2 backend for the
+// dense case.
+//
+// CTA = one 128-row K/V tile of one (batch, head); it walks over all 128-row
+// Q tiles.  Everything is computed TRANSPOSED (K/V rows on the TMEM lanes), so
+// P^T can stay in TMEM as the A operand of the dV GEMM, and dK/dV accumulate
+// in TMEM for the whole walk.  dS^T goes through shared memory once and feeds
+// both the dK GEMM (K-major view) and the dQ GEMM (MN-major view).  dQ tiles
+// are added to an fp32 accumulator in global memory (red.global.add.v4.f32),
+// converted to bf16 by a small epilogue kernel.
+//
+// Warps 0-3 / 4-7: exp / dS math for columns 0-63 / 64-127 of the S^T tile;
+// warps 8-11: dQ tile TMEM -> global reduction; warp 12: tcgen05.mma issuer;
+// warp 13: TMA producer.  S^T/dP^T of tile i+1 are issued as soon as tile i
+// has been pulled into registers, so the tensor core overlaps the exp math.
+#include "common.cuh"
+#include "host_util.h"
+
+namespace imf {
+
+constexpr int BW_HD = 64;
+constexpr int BW_T = 128;            // tile rows (both q and kv)
+constexpr int BW_THREADS = 512;
+constexpr int BW_QSTAGES = 2;
+
+// TMEM columns
+constexpr int BC_S = 0, BC_DP = 128, BC_P = 256, BC_DK = 320, BC_DV = 384, BC_DQ = 448;
+
+struct BwSmem {
+  alignas(1024) uint8_t k[BW_T * 128];
+  alignas(1024) uint8_t v[BW_T * 128];
+  alignas(1024) uint8_t q[BW_QSTAGES][BW_T * 128];
+  alignas(1024) uint8_t d_o[BW_QSTAGES][BW_T * 128];
+  alignas(1024) uint8_t ds[2][2 * BW_T * 128];       // dS^T: [kv 128][q 128] as two 64-col panels
+  alignas(16) float lse2[BW_QSTAGES][BW_T];
+  alignas(16) float delta[BW_QSTAGES][BW_T];
+  uint64_t kv_full;
+  uint64_t q_full[BW_QSTAGES], q_empty[BW_QSTAGES];
+  uint64_t s_full, s_taken, p_ready, p_free;
+  uint64_t ds_free[2];
+  uint64_t dq_full, dq_free;
+  uint64_t final_bar;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct BwParams {
+  const float* lse2;      // (B, H, Lp) log2-domain LSE, +inf on padding rows
+  const float* delta;     // (B, H, Lp) rowsum(dO .* O), 0 on padding rows
+  float* dq_acc;          // (B, L, H, 64) fp32, zeroed
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  int B, H, L, Lp;
+  int64_t dk_sb, dk_sl, dk_sh, dv_sb, dv_sl, dv_sh;
+  float scale;
+  int* status;
+};
+
+IMF_DEVICE void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+IMF_DEVICE void red_add_v4(float* gptr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gptr), "f"(a), "f"(b),
+               "f"(c), "f"(d)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(BW_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const BwParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  auto& s = *reinterpret_cast<BwSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                       ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int n_q = (p.L + BW_T - 1) / BW_T;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&s.kv_full, 1);
+    for (int i = 0; i < BW_QSTAGES; ++i) {
+      mbar_init(&s.q_full[i], 1);
+      mbar_init(&s.q_empty[i], 1);
+    }
+    mbar_init(&s.s_full, 1);
+    mbar_init(&s.s_taken, 256);
+    mbar_init(&s.p_ready, 256);
+    mbar_init(&s.p_free, 1);
+    mbar_init(&s.ds_free[0], 1);
+    mbar_init(&s.ds_free[1], 1);
+    mbar_init(&s.dq_full, 1);
+    mbar_init(&s.dq_free, 128);
+    mbar_init(&s.final_bar, 1);
+    s.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 12) {
+    tmem_alloc(&s.tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abort_flag = &s.abort_flag;
+
+  if (warp >= 12) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 13) {
+      // ---------------------------------------------------- TMA producer --
+      if (elect_one()) {
+        prefetch_tmap(&tm_q);
+        prefetch_tmap(&tm_k);
+        prefetch_tmap(&tm_v);
+        prefetch_tmap(&tm_do);
+        mbar_arrive_expect_tx(&s.kv_full, 2 * BW_T * 128);
+        tma_load_4d(s.k, &tm_k, &s.kv_full, 0, h, kvb * BW_T, b);
+        tma_load_4d(s.v, &tm_v, &s.kv_full, 0, h, kvb * BW_T, b);
+        const float* lse_row = p.lse2 + ((size_t)b * p.H + h) * p.Lp;
+        const float* dl_row = p.delta + ((size_t)b * p.H + h) * p.Lp;
+        for (int i = 0; i < n_q; ++i) {
+          const int st = i % BW_QSTAGES;
+          if (i >= BW_QSTAGES &&
+              !mbar_wait(&s.q_empty[st], (uint32_t)(((i / BW_QSTAGES) - 1) & 1), abort_flag,
+                         p.status, STATUS_TIMEOUT_EMPTY))
+            break;
+          mbar_arrive_expect_tx(&s.q_full[st], 2 * BW_T * 128 + 2 * BW_T * 4);
+          tma_load_4d(s.q[st], &tm_q, &s.q_full[st], 0, h, i * BW_T, b);
+          tma_load_4d(s.d_o[st], &tm_do, &s.q_full[st], 0, h, i * BW_T, b);
+          bulk_load_1d(s.lse2[st], lse_row + (size_t)i * BW_T, BW_T * 4, &s.q_full[st]);
+          bulk_load_1d(s.delta[st], dl_row + (size_t)i * BW_T, BW_T * 4, &s.q_full[st]);
+        }
+      }
+    } else if (warp == 12) {
+      // ------------------------------------------------------ MMA issuer --
+      if (elect_one()) {
+        constexpr uint32_t id_st = idesc_bf16(BW_T, BW_T, 0, 0);     // S^T, dP^T
+        constexpr uint32_t id_kn = idesc_bf16(BW_T, BW_HD, 0, 1);    // dV (TS), dK (SS, A K-major)
+        constexpr uint32_t id_mn = idesc_bf16(BW_T, BW_HD, 1, 1);    // dQ (A MN-major)
+        const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v);
+        auto issue_s = [&](int st) {
+          const uint32_t qa = smem_u32(s.q[st]), doa = smem_u32(s.d_o[st]);
+#pragma unroll
+          for (int ks = 0; ks < BW_HD / 16; ++ks)
+            mma_ss(tmem + BC_S, sdesc_kmajor(ka + ks * 32), sdesc_kmajor(qa + ks * 32), id_st, ks != 0);
+#pragma unroll
+          for (int ks = 0; ks < BW_HD / 16; ++ks)
+            mma_ss(tmem + BC_DP, sdesc_kmajor(va + ks * 32), sdesc_kmajor(doa + ks * 32), id_st, ks != 0);
+          tc_commit(&s.s_full);
+        };
+        bool ok = mbar_wait(&s.kv_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA) &&
+                  mbar_wait(&s.q_full[0], 0, abort_flag, p.status, STATUS_TIMEOUT_TMA);
+        if (ok) {
+          tc_fence_after();
+          issue_s(0);
+        }
+        for (int i = 0; i < n_q && ok; ++i) {
+          const int st = i % BW_QSTAGES;
+          const uint32_t par = (uint32_t)(i & 1);
+          ok = mbar_wait(&s.s_taken, par, abort_flag, p.status, STATUS_TIMEOUT_SOFTMAX);
+          if (!ok) break;
+          if (i + 1 < n_q) {
+            const int st1 = (i + 1) % BW_QSTAGES;
+            ok = mbar_wait(&s.q_full[st1], (uint32_t)(((i + 1) / BW_QSTAGES) & 1), abort_flag,
+                           p.status, STATUS_TIMEOUT_TMA);
+            if (!ok) break;
+            tc_fence_after();
+            issue_s(st1);
+          }
+          ok = mbar_wait(&s.p_ready, par, abort_flag, p.status, STATUS_TIMEOUT_SOFTMAX);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t qa = smem_u32(s.q[st]), doa = smem_u32(s.d_o[st]);
+          const uint32_t dsa = smem_u32(s.ds[i & 1]);
+          // dV += P^T dO   (A = P^T in TMEM: 128 q as K -> 8 k-steps of 8 columns)
+#pragma unroll
+          for (int ks = 0; ks < BW_T / 16; ++ks)
+            mma_ts(tmem + BC_DV, tmem + BC_P + ks * 8, sdesc_mnmajor(doa + ks * 2048, BW_T * 128),
+                   id_kn, (i | ks) != 0);
+          tc_commit(&s.p_free);
+          // dK += dS^T Q   (A = dS^T from smem, K-major view: K = q)
+#pragma unroll
+          for (int ks = 0; ks < BW_T / 16; ++ks)
+            mma_ss(tmem + BC_DK, sdesc_kmajor(dsa + (ks / 4) * (BW_T * 128) + (ks % 4) * 32),
+                   sdesc_mnmajor(qa + ks * 2048, BW_T * 128), id_kn, (i | ks) != 0);
+          // dQ_i = dS K    (A = dS^T from smem, MN-major view: M = q, K = kv)
+          if (i > 0) {
+            ok = mbar_wait(&s.dq_free, (uint32_t)((i - 1) & 1), abort_flag, p.status,
+                           STATUS_TIMEOUT_SOFTMAX);
+            if (!ok) break;
+            tc_fence_after();
+          }
+#pragma unroll
+          for (int ks = 0; ks < BW_T / 16; ++ks)
+            mma_ss(tmem + BC_DQ, sdesc_mnmajor(dsa + ks * 2048, BW_T * 128),
+                   sdesc_mnmajor(ka + ks * 2048, BW_T * 128), id_mn, ks != 0);
+          tc_commit(&s.dq_full);
+          tc_commit(&s.q_empty[st]);
+          tc_commit(&s.ds_free[i & 1]);
+        }
+        if (ok) tc_commit(&s.final_bar);
+      }
+    }
+  } else if (warp >= 8) {
+    // ------------------------------------------ dQ tile -> global reduction --
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+    const int wl = warp & 3;
+    const uint32_t tb = tmem_addr(tmem, wl * 32, BC_DQ);
+    bool ok = true;
+    for (int i = 0; i < n_q && ok; ++i) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&s.dq_full, (uint32_t)(i & 1), abort_flag, p.status,
+                                             STATUS_TIMEOUT_MMA));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t r[64];
+      tmem_ld32(tb, r);
+      tmem_ld32(tb + 32, r + 32);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&s.dq_free);
+      const int q_row = i * BW_T + wl * 32 + lane;
+      if (q_row < p.L) {
+        float* dst = p.dq_acc + (((size_t)b * p.L + q_row) * p.H + h) * BW_HD;
+#pragma unroll
+        for (int c = 0; c < 64; c += 4)
+          red_add_v4(dst + c, __uint_as_float(r[c]), __uint_as_float(r[c + 1]),
+                     __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
+      }
+    }
+  } else {
+    // ---------------------------------------------------- exp / dS math ----
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+    const int wg = warp >> 2;           // column half: q columns [64 wg, 64 wg + 64)
+    const int wl = warp & 3;
+    const int row = wl * 32 + lane;     // kv row of this thread (TMEM lane)
+    const uint32_t tb = tmem_addr(tmem, wl * 32, 0);
+    const float scale_log2 = p.scale * 1.4426950408889634f;
+    bool ok = true;
+    for (int i = 0; i < n_q && ok; ++i) {
+      const int st = i % BW_QSTAGES;
+      const uint32_t par = (uint32_t)(i & 1);
+      ok = __all_sync(0xffffffffu,
+                      mbar_wait(&s.s_full, par, abort_flag, p.status, STATUS_TIMEOUT_MMA));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[64], dp[64];
+      tmem_ld32(tb + BC_S + wg * 64, sv);
+      tmem_ld32(tb + BC_S + wg * 64 + 32, sv + 32);
+      tmem_ld32(tb + BC_DP + wg * 64, dp);
+      tmem_ld32(tb + BC_DP + wg * 64 + 32, dp + 32);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&s.s_taken);
+      // the stats of this q tile arrived with its q_full stage (s_full implies it)
+      const float4* lse4 = reinterpret_cast<const float4*>(s.lse2[st] + wg * 64);
+      const float4* dl4 = reinterpret_cast<const float4*>(s.delta[st] + wg * 64);
+      // P^T goes to TMEM (A operand of the dV GEMM): dV of tile i-1 must have read it;
+      // dS^T goes to smem buffer i&1: the GEMMs of tile i-2 must have read it
+      if (i > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&s.p_free, (uint32_t)((i - 1) & 1), abort_flag,
+                                               p.status, STATUS_TIMEOUT_MMA));
+        if (!ok) break;
+      }
+      if (i >= 2) {
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(&s.ds_free[i & 1], (uint32_t)(((i / 2) - 1) & 1), abort_flag,
+                                  p.status, STATUS_TIMEOUT_MMA));
+        if (!ok) break;
+      }
+      uint8_t* dsb = s.ds[i & 1] + wg * (BW_T * 128) + row * 128;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t pk[16], dk_[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          const int cg = hh * 32 + c;
+          const float4 l4 = lse4[cg / 4], d4 = dl4[cg / 4];
+          const float p0 = ex2(fmaf(__uint_as_float(sv[cg]), scale_log2, -l4.x));
+          const float p1 = ex2(fmaf(__uint_as_float(sv[cg + 1]), scale_log2, -l4.y));
+          const float p2 = ex2(fmaf(__uint_as_float(sv[cg + 2]), scale_log2, -l4.z));
+          const float p3 = ex2(fmaf(__uint_as_float(sv[cg + 3]), scale_log2, -l4.w));
+          pk[c / 2] = pack_bf16(p0, p1);
+          pk[c / 2 + 1] = pack_bf16(p2, p3);
+          dk_[c / 2] = pack_bf16(p0 * (__uint_as_float(dp[cg]) - d4.x),
+                                 p1 * (__uint_as_float(dp[cg + 1]) - d4.y));
+          dk_[c / 2 + 1] = pack_bf16(p2 * (__uint_as_float(dp[cg + 2]) - d4.z),
+                                     p3 * (__uint_as_float(dp[cg + 3]) - d4.w));
+        }
+        tmem_st16(tb + BC_P + wg * 32 + hh * 16, pk);
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int chunk = hh * 4 + cc;
+          uint4 val = make_uint4(dk_[4 * cc], dk_[4 * cc + 1], dk_[4 * cc + 2], dk_[4 * cc + 3]);
+          *reinterpret_cast<uint4*>(dsb + ((chunk ^ (row & 7)) << 4)) = val;
+        }
+      }
+      tc_wait_st();
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&s.p_ready);
+    }
+    // ---- epilogue: WG0 stores dK (scaled), WG1 stores dV ----
+    if (ok) ok = mbar_wait(&s.final_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const int kv_row = kvb * BW_T + row;
+      const float mul = wg == 0 ? p.scale : 1.f;
+      __nv_bfloat16* base =
+          wg == 0 ? p.dk + (int64_t)b * p.dk_sb + (int64_t)kv_row * p.dk_sl + (int64_t)h * p.dk_sh
+                  : p.dv + (int64_t)b * p.dv_sb + (int64_t)kv_row * p.dv_sl + (int64_t)h * p.dv_sh;
+#pragma unroll
+      for (int c = 0; c < BW_HD; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tb + (wg == 0 ? BC_DK : BC_DV) + c, r);
+        tc_wait_ld();
+        if (kv_row < p.L) {
+          uint32_t ob[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            ob[e] = pack_bf16(__uint_as_float(r[2 * e]) * mul, __uint_as_float(r[2 * e + 1]) * mul);
+          uint4* dst = reinterpret_cast<uint4*>(base + c);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            dst[e] = make_uint4(ob[4 * e], ob[4 * e + 1], ob[4 * e + 2], ob[4 * e + 3]);
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 12) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// delta = rowsum(dO .* O), lse2 = lse * log2(e), both padded to Lp rows per
+// (b, h); one warp per (b, l, h) row of 64 channels.
+__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o,
+                                     const __nv_bfloat16* __restrict__ d_o,
+                                     const float* __restrict__ lse, float* __restrict__ lse2,
+                                     float* __restrict__ delta, int B, int L, int H, int Lp,
+                                     int64_t o_sb, int64_t o_sl, int64_t o_sh, int64_t g_sb,
+                                     int64_t g_sl, int64_t g_sh) {
+  const int lane = threadIdx.x & 31;
+  const long wid = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long total = (long)B * H * Lp;
+  if (wid >= total) return;
+  const int l = (int)(wid % Lp), h = (int)((wid / Lp) % H), b = (int)(wid / ((long)Lp * H));
+  if (l >= L) {
+    if (lane == 0) {
+      lse2[wid] = INFINITY;
+      delta[wid] = 0.f;
+    }
+    return;
+  }
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(
+      o + b * o_sb + (int64_t)l * o_sl + h * o_sh + lane * 2);
+  const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(
+      d_o + b * g_sb + (int64_t)l * g_sl + h * g_sh + lane * 2);
+  float v = __low2float(a) * __low2float(g) + __high2float(a) * __high2float(g);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  if (lane == 0) {
+    delta[wid] = v;
+    lse2[wid] = lse[((long)b * H + h) * L + l] * 1.4426950408889634f;
+  }
+}
+
+__global__ void attn_bwd_post_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
+                                     long n4, float scale) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  const float4 v = reinterpret_cast<const float4*>(acc)[i];
+  uint2 o;
+  o.x = pack_bf16(v.x * scale, v.y * scale);
+  o.y = pack_bf16(v.z * scale, v.w * scale);
+  reinterpret_cast<uint2*>(dq)[i] = o;
+}
+
+static int make_map64(CUtensorMap* m, const void* ptr, int B, int L, int H, int64_t sb, int64_t sl,
+                      int64_t sh) {
+  uint64_t dims[4] = {(uint64_t)BW_HD, (uint64_t)H, (uint64_t)L, (uint64_t)B};
+  uint64_t str[4] = {2, (uint64_t)sh * 2, (uint64_t)sl * 2, (uint64_t)sb * 2};
+  uint32_t box[4] = {(uint32_t)BW_HD, 1, (uint32_t)BW_T, 1};
+  return make_tmap(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, str, box);
+}
+
+}  // namespace imf
+
+// Scratch (bytes) the backward needs: fp32 dQ accumulator + padded lse2/delta.
+extern "C" long imf_attn_bwd_scratch_bytes(int B, int L, int H) {
+  const long Lp = ((L + 127) / 128) * 128;
+  return (long)B * L * H * 64 * 4 + 2 * (long)B * H * Lp * 4 + 256;
+}
+
+// All tensors (B, L, H, 64) bf16; strides[0..11]: (batch,row,head) for q,k,v,do;
+// o contiguous-like with its own strides; dq contiguous (B, L, H, 64);
+// dk/dv with given strides (dv may point into a wider buffer).
+extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const void* o,
+                            const void* d_o, const float* lse, void* dq, void* dk, void* dv, int B,
+                            int L, int H, int head_dim, const int64_t* strides,
+                            const int64_t* o_strides, const int64_t* dk_strides,
+                            const int64_t* dv_strides, float scale, void* scratch,
+                            long scratch_bytes, int* status, void* stream) {
+  using namespace imf;
+  if (head_dim != BW_HD || B <= 0 || L <= 0 || H <= 0) return IMF_ERR_ARG;
+  if (scratch == nullptr || scratch_bytes < imf_attn_bwd_scratch_bytes(B, L, H)) return IMF_ERR_ARG;
+  if ((reinterpret_cast<uintptr_t>(scratch) & 255) || (reinterpret_cast<uintptr_t>(dq) & 15) ||
+      (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15))
+    return IMF_ERR_ARG;
+  for (int i = 0; i < 3; ++i)
+    if ((dk_strides[i] & 7) || (dv_strides[i] & 7) || (o_strides[i] & 1)) return IMF_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int Lp = ((L + 127) / 128) * 128;
+  float* dq_acc = static_cast<float*>(scratch);
+  const size_t acc_bytes = (size_t)B * L * H * 64 * 4;
+  float* lse2 = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + ((acc_bytes + 255) & ~size_t(255)));
+  float* delta = lse2 + (size_t)B * H * Lp;
+  if (cudaMemsetAsync(dq_acc, 0, acc_bytes, st) != cudaSuccess) return IMF_ERR_LAUNCH;
+  {
+    const long warps = (long)B * H * Lp;
+    const int threads = 256;
+    const long blocks = (warps * 32 + threads - 1) / threads;
+    attn_bwd_prep_kernel<<<(unsigned)blocks, threads, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse, lse2,
+        delta, B, L, H, Lp, o_strides[0], o_strides[1], o_strides[2], strides[9], strides[10],
+        strides[11]);
+    if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
+  }
+  CUtensorMap mq, mk, mv, mdo;
+  int rc;
+  if ((rc = make_map64(&mq, q, B, L, H, strides[0], strides[1], strides[2]))) return rc;
+  if ((rc = make_map64(&mk, k, B, L, H, strides[3], strides[4], strides[5]))) return rc;
+  if ((rc = make_map64(&mv, v, B, L, H, strides[6], strides[7], strides[8]))) return rc;
+  if ((rc = make_map64(&mdo, d_o, B, L, H, strides[9], strides[10], strides[11]))) return rc;
+  BwParams prm;
+  prm.lse2 = lse2;
+  prm.delta = delta;
+  prm.dq_acc = dq_acc;
+  prm.dk = static_cast<__nv_bfloat16*>(dk);
+  prm.dv = static_cast<__nv_bfloat16*>(dv);
+  prm.B = B; prm.H = H; prm.L = L; prm.Lp = Lp;
+  prm.dk_sb = dk_strides[0]; prm.dk_sl = dk_strides[1]; prm.dk_sh = dk_strides[2];
+  prm.dv_sb = dv_strides[0]; prm.dv_sl = dv_strides[1]; prm.dv_sh = dv_strides[2];
+  prm.scale = scale;
+  prm.status = status;
+  const size_t smem = sizeof(BwSmem) + 1024;
+  if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem) != cudaSuccess)
+    return IMF_ERR_LAUNCH;
+  dim3 grid((L + BW_T - 1) / BW_T, H, B);
+  attn_bwd_kernel<<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, prm);
+  if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
+  const long n4 = (long)B * L * H * 64 / 4;
+  attn_bwd_post_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(
+      dq_acc, static_cast<__nv_bfloat16*>(dq), n4, scale);
+  return cudaGetLastError() == cudaSuccess ? IMF_OK : IMF_ERR_LAUNCH;
+}

@@ -173,6 +173,45 @@ def attn_fwd(q, k, v, dq=None, dk=None, dv=None, scale: Optional[float] = None,
     return o, do, lse
 
 
+if _has("imf_attn_bwd"):
+    _lib.imf_attn_bwd.restype = c_int
+    _lib.imf_attn_bwd.argtypes = [c_void_p] * 9 + [c_int] * 4 + [c_void_p] * 4 + \
+        [c_float, c_void_p, ctypes.c_long, c_void_p, c_void_p]
+    _lib.imf_attn_bwd_scratch_bytes.restype = ctypes.c_long
+    _lib.imf_attn_bwd_scratch_bytes.argtypes = [c_int, c_int, c_int]
+
+
+def attn_bwd(q, k, v, o, lse, go, scale: Optional[float] = None,
+             gv_out: Optional[torch.Tensor] = None):
+    """(dq, dk, dv) of dense attention; ``gv_out`` lets dv land in a strided
+    view (e.g. the value band of the kv up-projection gradient)."""
+    B, L, H, hd = q.shape
+    scale = 1.0 / math.sqrt(hd) if scale is None else scale
+    ts = [_tma_ok(t) for t in (q, k, v, go)]
+    strides = []
+    for t in ts:
+        strides += list(_bls(t))
+    arr = (c_int64 * 12)(*strides)
+    o = o if o.stride(3) == 1 else o.contiguous()
+    dq = torch.empty(B, L, H, hd, dtype=torch.bfloat16, device=q.device)
+    dk = torch.empty(B, L, H, hd, dtype=torch.bfloat16, device=q.device)
+    dv = gv_out if gv_out is not None else torch.empty(B, L, H, hd, dtype=torch.bfloat16,
+                                                        device=q.device)
+    if dv.stride(3) != 1 or dv.data_ptr() % 16 or any(s_ % 8 for s_ in dv.stride()[:3]):
+        raise ValueError("dv output needs 16-byte aligned rows")
+    i3 = lambda t: (c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    nscr = int(_lib.imf_attn_bwd_scratch_bytes(B, L, H))
+    scr = _scratch_buf(q.device, nscr, "attn_bwd")
+    rc = _lib.imf_attn_bwd(_ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]), _ptr(o), _ptr(ts[3]),
+                           _ptr(lse), _ptr(dq), _ptr(dk), _ptr(dv), B, L, H, hd,
+                           ctypes.cast(arr, c_void_p), ctypes.cast(i3(o), c_void_p),
+                           ctypes.cast(i3(dk), c_void_p), ctypes.cast(i3(dv), c_void_p),
+                           float(scale), _ptr(scr), nscr, _ptr(status_word(q.device)), _stream())
+    _check(rc, "imf_attn_bwd")
+    LAUNCHES.count += 3
+    return dq, dk, dv
+
+
 # ------------------------------------------------- autograd: attention -----
 def _sdpa_backward(q, k, v, go):
     """Temporary reverse-mode fallback (library SDPA recompute) used only when

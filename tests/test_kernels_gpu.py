@@ -110,3 +110,23 @@ def test_attention_autograd(K):
     for a, b in ((q, qf), (k, kf), (v, vf)):
         assert _rel(a.grad, b.grad) < 2e-2
     K.check_status()
+
+
+@pytest.mark.parametrize("B,L,H", [(1, 128, 1), (1, 300, 2), (2, 1000, 3), (1, 2049, 2)])
+def test_attention_backward(K, B, L, H):
+    from imfvideo_b200.ops import reference as ref
+
+    g = torch.Generator(device="cuda").manual_seed(L)
+    q, k, v, go = (torch.randn(B, L, H, 64, device="cuda", generator=g).bfloat16() for _ in range(4))
+    o, _, lse = K.attn_fwd(q, k, v)
+    kvbuf = torch.zeros(B, L, H, 112, dtype=torch.bfloat16, device="cuda")
+    dq, dk, dv = K.attn_bwd(q, k, v, o, lse, go, gv_out=kvbuf[..., 48:])
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    ref.attention(qf, kf, vf).backward(go.float())
+    for name, a, b in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+        assert _rel(a, b) < 1.5e-2, (name, _rel(a, b))
+    assert (kvbuf[..., :48] == 0).all()        # only the value band was written
+    dq2, dk2, dv2 = K.attn_bwd(q, k, v, o, lse, go)
+    assert torch.equal(dk, dk2) and torch.equal(dv2, dv.contiguous())   # deterministic parts
+    assert _rel(dq2, dq) < 1e-3              # dQ uses fp32 atomics: order may differ
+    K.check_status()
