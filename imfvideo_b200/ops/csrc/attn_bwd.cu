@@ -42,6 +42,7 @@ struct BwSmem {
   alignas(1024) uint8_t q[BW_QSTAGES][BW_T * 128];
   alignas(1024) uint8_t d_o[BW_QSTAGES][BW_T * 128];
   alignas(1024) uint8_t ds[2][2 * BW_T * 128];       // dS^T: [kv 128][q 128] as two 64-col panels
+  alignas(1024) float dq_stage[BW_T * BW_HD];        // dQ tile staged for the TMA reduce-add
   alignas(16) float lse2[BW_QSTAGES][BW_T];
   alignas(16) float delta[BW_QSTAGES][BW_T];
   uint64_t kv_full;
@@ -81,7 +82,7 @@ IMF_DEVICE void red_add_v4(float* gptr, float a, float b, float c, float d) {
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const BwParams p) {
+                const __grid_constant__ CUtensorMap tm_dq, const BwParams p) {
   extern __shared__ uint8_t smem_raw[];
   auto& s = *reinterpret_cast<BwSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                        ~uintptr_t(1023));
@@ -231,15 +232,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_wait_ld();
       tc_fence_before();
       mbar_arrive(&s.dq_free);
-      const int q_row = i * BW_T + wl * 32 + lane;
-      if (q_row < p.L) {
-        float* dst = p.dq_acc + (((size_t)b * p.L + q_row) * p.H + h) * BW_HD;
+      // stage the tile in shared memory (plain [128][64] fp32) and let TMA add it to
+      // the fp32 accumulator in global memory: coalesced, asynchronous, rows >= L clipped
+      if (i > 0) {
+        if (threadIdx.x == 8 * 32) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      // two 128-byte-swizzled panels [128 rows][32 floats] (columns 0-31 / 32-63)
+      const int srow = wl * 32 + lane;
+      uint8_t* stage = reinterpret_cast<uint8_t*>(s.dq_stage);
 #pragma unroll
-        for (int c = 0; c < 64; c += 4)
-          red_add_v4(dst + c, __uint_as_float(r[c]), __uint_as_float(r[c + 1]),
-                     __uint_as_float(r[c + 2]), __uint_as_float(r[c + 3]));
+      for (int c = 0; c < 16; ++c) {
+        uint8_t* dst = stage + (c / 8) * (BW_T * 128) + srow * 128 + (((c & 7) ^ (srow & 7)) << 4);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 8 * 32) {
+#pragma unroll
+        for (int pnl = 0; pnl < 2; ++pnl)
+          asm volatile(
+              "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group"
+              " [%0, {%2, %3, %4, %5}], [%1];"
+              ::"l"(reinterpret_cast<uint64_t>(&tm_dq)),
+              "r"(smem_u32(stage + pnl * (BW_T * 128))), "r"(pnl * 32), "r"(h), "r"(i * BW_T), "r"(b)
+              : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     }
+    if (threadIdx.x == 8 * 32) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
     // ---------------------------------------------------- exp / dS math ----
     asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
@@ -443,12 +464,19 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
         strides[11]);
     if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   }
-  CUtensorMap mq, mk, mv, mdo;
+  CUtensorMap mq, mk, mv, mdo, mdq;
   int rc;
   if ((rc = make_map64(&mq, q, B, L, H, strides[0], strides[1], strides[2]))) return rc;
   if ((rc = make_map64(&mk, k, B, L, H, strides[3], strides[4], strides[5]))) return rc;
   if ((rc = make_map64(&mv, v, B, L, H, strides[6], strides[7], strides[8]))) return rc;
   if ((rc = make_map64(&mdo, d_o, B, L, H, strides[9], strides[10], strides[11]))) return rc;
+  {
+    uint64_t dims[4] = {(uint64_t)BW_HD, (uint64_t)H, (uint64_t)L, (uint64_t)B};
+    uint64_t str[4] = {4, (uint64_t)BW_HD * 4, (uint64_t)H * BW_HD * 4, (uint64_t)L * H * BW_HD * 4};
+    uint32_t box[4] = {32, 1, (uint32_t)BW_T, 1};
+    if ((rc = make_tmap(&mdq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dq_acc, dims, str, box)))
+      return rc;
+  }
   BwParams prm;
   prm.lse2 = lse2;
   prm.delta = delta;
@@ -465,7 +493,7 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
                            (int)smem) != cudaSuccess)
     return IMF_ERR_LAUNCH;
   dim3 grid((L + BW_T - 1) / BW_T, H, B);
-  attn_bwd_kernel<<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, prm);
+  attn_bwd_kernel<<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, mdq, prm);
   if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   const long n4 = (long)B * L * H * 64 / 4;
   attn_bwd_post_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(
