@@ -13,13 +13,13 @@ from typing import Optional
 import torch
 
 
-def try_create(world: int, rank: int, device: torch.device, seg_numel: int):
+def try_create(world: int, rank: int, device: torch.device, total: int, seg_pad: int):
     try:
         from .comm_impl import PeerComm
     except Exception:
         return None
     try:
-        return PeerComm(world, rank, device, seg_numel)
+        return PeerComm(world, rank, device, total, seg_pad)
     except Exception as exc:      # fall back loudly, once
         if rank == 0:
             print(f"imf_b200: peer-memory collectives unavailable ({type(exc).__name__}: {exc}); "

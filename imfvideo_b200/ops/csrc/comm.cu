@@ -1,0 +1,192 @@
+// NVLink-side collectives over peer memory for the flat gradient / update
+// arenas (one process per GPU; every rank runs the same launch sequence).
+//
+//   reduce_grads   : cross-rank arrival barrier, then
+//                      Muon segment `rank`  <- mean over ranks (fixed order)
+//                      AdamW shard  `rank`  <- mean over ranks
+//                    read with plain peer loads (or one multimem.ld_reduce per
+//                    16 bytes when an NVLS multicast mapping is given), scaled
+//                    by 1/W and written to this rank's arena in the same pass.
+//   gather         : barrier, then pull the other ranks' reduced AdamW shards /
+//                    orthogonalised update segments into the local arena.
+//
+// Barriers are epoch flags in symmetric memory: rank r writes flag[r] = epoch
+// into every peer's flag array (st.release.sys) and every CTA polls its LOCAL
+// copy (ld.acquire.sys) with a wall-clock bound; on expiry the kernel records
+// STATUS_TIMEOUT_PEER and returns, the host raises.  No TMA multicast, no
+// library kernel touches peer memory.  Replaces the reference's flat NCCL
+// all-reduce (reference train.py:353-371).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace imf {
+
+constexpr int MAX_RANKS = 16;
+constexpr unsigned long long PEER_WAIT_NS = 2000000000ull;
+
+struct CommPeers {
+  float* arena[MAX_RANKS];      // peer base pointers of the fp32 arena
+  int* flags[MAX_RANKS];        // peer base pointers of the flag arrays [MAX_RANKS]
+};
+
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Signal (block 0) and wait (every block).  Returns false on timeout.
+__device__ __forceinline__ bool peer_barrier(const CommPeers& peers, int rank, int world, int epoch,
+                                             int* status) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      for (int q = 0; q < world; ++q) st_release_sys(peers.flags[q] + rank, epoch);
+    }
+    int ok = 1;
+    const unsigned long long t0 = gtime();
+    for (int q = 0; q < world && ok; ++q) {
+      while (ld_acquire_sys(peers.flags[rank] + q) < epoch) {
+        if (gtime() - t0 > PEER_WAIT_NS) {
+          ok = 0;
+          if (status) atomicCAS(status, 0, 6);
+          break;
+        }
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+
+// ranges: [lo0, hi0) = this rank's Muon segment, [lo1, hi1) = its AdamW shard
+__global__ void __launch_bounds__(512)
+comm_reduce_kernel(const CommPeers peers, const float* mc_arena, int rank, int world, long lo0,
+                   long hi0, long lo1, long hi1, int epoch, int* status) {
+  if (!peer_barrier(peers, rank, world, epoch, status)) return;
+  const float inv = 1.f / world;
+  float* mine = peers.arena[rank];
+  const long n0 = (hi0 - lo0) / 4, n1 = (hi1 - lo1) / 4;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n0 + n1;
+       i += (long)gridDim.x * blockDim.x) {
+    const long off = i < n0 ? lo0 + i * 4 : lo1 + (i - n0) * 4;
+    float4 acc;
+    if (mc_arena) {
+      acc = multimem_ld_reduce_f32x4(mc_arena + off);
+    } else {
+      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int q = 0; q < world; ++q) {      // fixed order: same bits whoever owns the segment
+        const float4 v = *reinterpret_cast<const float4*>(peers.arena[q] + off);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    *reinterpret_cast<float4*>(mine + off) = acc;
+  }
+}
+
+// Pull [base + q*len, base + (q+1)*len) from rank q for every q != rank.
+template <typename T>
+__global__ void __launch_bounds__(512)
+comm_gather_kernel(const CommPeers peers, int rank, int world, long base, long len, int epoch,
+                   int* status) {
+  if (!peer_barrier(peers, rank, world, epoch, status)) return;
+  constexpr int V = 16 / sizeof(T);
+  T* mine = reinterpret_cast<T*>(peers.arena[rank]);
+  const long nv = len / V;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nv * (world - 1);
+       i += (long)gridDim.x * blockDim.x) {
+    int q = (int)(i / nv);
+    if (q >= rank) ++q;
+    const long off = base + (long)q * len + (i % nv) * V;
+    const T* src = reinterpret_cast<const T*>(peers.arena[q]);
+    *reinterpret_cast<uint4*>(mine + off) = *reinterpret_cast<const uint4*>(src + off);
+  }
+}
+
+__global__ void comm_barrier_kernel(const CommPeers peers, int rank, int world, int epoch,
+                                    int* status) {
+  peer_barrier(peers, rank, world, epoch, status);
+}
+
+static int fill(CommPeers& p, void* const* arena_ptrs, void* const* flag_ptrs, int world) {
+  if (world < 1 || world > MAX_RANKS) return -1;
+  for (int q = 0; q < MAX_RANKS; ++q) {
+    p.arena[q] = q < world ? static_cast<float*>(arena_ptrs[q]) : nullptr;
+    p.flags[q] = q < world ? static_cast<int*>(flag_ptrs[q]) : nullptr;
+  }
+  return 0;
+}
+
+}  // namespace imf
+
+using namespace imf;
+
+// Mean-reduce this rank's Muon segment and AdamW shard of the fp32 arena.
+// arena_ptrs / flag_ptrs: host arrays of `world` device pointers (peer mapped).
+// mc_arena: NVLS multicast address of the arena or null.
+extern "C" int imf_comm_reduce(void* const* arena_ptrs, void* const* flag_ptrs, const void* mc_arena,
+                               int rank, int world, long seg_pad, long muon_total, long adam_numel,
+                               int epoch, int* status, void* stream) {
+  CommPeers p;
+  if (fill(p, arena_ptrs, flag_ptrs, world)) return -1;
+  if ((seg_pad & 3) || (adam_numel % (4L * world))) return -1;
+  const long shard = adam_numel / world;
+  const long lo0 = rank * seg_pad, hi0 = lo0 + seg_pad;
+  const long lo1 = muon_total + rank * shard, hi1 = lo1 + shard;
+  long blocks = ((seg_pad + shard) / 4 + 511) / 512;
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks < 1) blocks = 1;
+  comm_reduce_kernel<<<(unsigned)blocks, 512, 0, (cudaStream_t)stream>>>(
+      p, static_cast<const float*>(mc_arena), rank, world, lo0, hi0, lo1, hi1, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// All-gather equal slices [base + q*len, ...) of a symmetric buffer; elem_size 4 or 2.
+extern "C" int imf_comm_gather(void* const* arena_ptrs, void* const* flag_ptrs, int rank, int world,
+                               long base, long len, int elem_size, int epoch, int* status,
+                               void* stream) {
+  CommPeers p;
+  if (fill(p, arena_ptrs, flag_ptrs, world)) return -1;
+  if ((len * elem_size) % 16 || (base * elem_size) % 16) return -1;
+  long blocks = (len * elem_size / 16 * (world - 1) + 511) / 512;
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks < 1) blocks = 1;
+  if (elem_size == 4)
+    comm_gather_kernel<float><<<(unsigned)blocks, 512, 0, (cudaStream_t)stream>>>(
+        p, rank, world, base, len, epoch, status);
+  else if (elem_size == 2)
+    comm_gather_kernel<__nv_bfloat16><<<(unsigned)blocks, 512, 0, (cudaStream_t)stream>>>(
+        p, rank, world, base, len, epoch, status);
+  else
+    return -1;
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int imf_comm_barrier(void* const* arena_ptrs, void* const* flag_ptrs, int rank, int world,
+                                int epoch, int* status, void* stream) {
+  CommPeers p;
+  if (fill(p, arena_ptrs, flag_ptrs, world)) return -1;
+  comm_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p, rank, world, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

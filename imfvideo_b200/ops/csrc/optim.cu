@@ -1,0 +1,133 @@
+// Fused optimizer kernels over flat parameter arenas (fp32 master weights).
+//
+//   muon_momentum : buf = mu buf + c g ; dir = c g + mu buf (Nesterov) or buf
+//   muon_apply    : p = p (1 - lr_i wd) - lr_i s_i Phi ;  ema = lerp(ema, p)
+//   adamw         : bias-corrected AdamW with decoupled decay ; ema lerp
+//
+// clip[0] is the gradient-clip factor and clip[1] a skip flag (non-finite
+// gradient norm), both read from device memory, so no host round trip
+// separates backward from the update.  One launch covers every parameter
+// of a class; per-parameter constants come from a small segment table.
+// Replaces the reference's per-parameter Python loops (reference
+// moonlight.py:395-469, train.py:290-298, train.py:582).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace imf {
+
+struct Seg {          // one parameter inside an arena
+  long start;         // element offset
+  long numel;
+  float a;            // muon_apply: 1 - lr wd        adamw: lr
+  float b;            // muon_apply: lr * scale       adamw: 1 - lr wd
+};
+
+__global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ buf,
+                                     float* __restrict__ dir, long n, float mu, int nesterov,
+                                     const float* __restrict__ clip) {
+  if (clip && clip[1] != 0.f) return;      // non-finite gradient: the whole step is skipped
+  const float c = clip ? clip[0] : 1.f;
+  for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n;
+       i += (long)gridDim.x * blockDim.x * 4) {
+    float4 gv = *reinterpret_cast<const float4*>(g + i);
+    float4 bv = *reinterpret_cast<const float4*>(buf + i);
+    gv.x *= c; gv.y *= c; gv.z *= c; gv.w *= c;
+    bv.x = mu * bv.x + gv.x; bv.y = mu * bv.y + gv.y;
+    bv.z = mu * bv.z + gv.z; bv.w = mu * bv.w + gv.w;
+    *reinterpret_cast<float4*>(buf + i) = bv;
+    float4 dv = bv;
+    if (nesterov) {
+      dv.x = gv.x + mu * bv.x; dv.y = gv.y + mu * bv.y;
+      dv.z = gv.z + mu * bv.z; dv.w = gv.w + mu * bv.w;
+    }
+    *reinterpret_cast<float4*>(dir + i) = dv;
+  }
+}
+
+template <typename UT>
+__global__ void muon_apply_kernel(float* __restrict__ p, const UT* __restrict__ upd,
+                                  float* __restrict__ ema, const Seg* __restrict__ segs,
+                                  long upd_offset, float ema_w, const float* __restrict__ clip) {
+  if (clip && clip[1] != 0.f) return;
+  const Seg s = segs[blockIdx.y];
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < s.numel;
+       i += (long)gridDim.x * blockDim.x) {
+    const long j = s.start + i;
+    const float u = static_cast<float>(upd[j - upd_offset]);
+    const float v = p[j] * s.a - s.b * u;
+    p[j] = v;
+    if (ema) ema[j] += ema_w * (v - ema[j]);
+  }
+}
+
+__global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
+                             float* __restrict__ m, float* __restrict__ v,
+                             float* __restrict__ ema, const Seg* __restrict__ segs, long state_offset,
+                             float b1, float b2, float eps, float bias1, float bias2,
+                             const float* __restrict__ clip, float ema_w) {
+  if (clip && clip[1] != 0.f) return;
+  const Seg s = segs[blockIdx.y];
+  const float c = clip ? clip[0] : 1.f;
+  const float inv_b1 = 1.f / bias1, inv_b2 = 1.f / bias2;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < s.numel;
+       i += (long)gridDim.x * blockDim.x) {
+    const long j = s.start + i, k = j - state_offset;
+    const float gv = g[j] * c;
+    const float mv = b1 * m[k] + (1.f - b1) * gv;
+    const float vv = b2 * v[k] + (1.f - b2) * gv * gv;
+    m[k] = mv;
+    v[k] = vv;
+    const float den = sqrtf(vv * inv_b2) + eps;
+    const float nv = p[j] * s.b - s.a * (mv * inv_b1) / den;
+    p[j] = nv;
+    if (ema) ema[j] += ema_w * (nv - ema[j]);
+  }
+}
+
+}  // namespace imf
+
+using namespace imf;
+
+extern "C" int imf_muon_momentum(const float* g, float* buf, float* dir, long n, float mu,
+                                 int nesterov, const float* clip, void* stream) {
+  if (n <= 0 || (n & 3)) return -1;
+  long blocks = (n / 4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  muon_momentum_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(g, buf, dir, n, mu,
+                                                                          nesterov, clip);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// segs: device array of nseg records {long start, long numel, float a, float b}
+extern "C" int imf_muon_apply(float* p, const void* upd, int upd_bf16, float* ema,
+                              const void* segs, int nseg, long max_numel, long upd_offset,
+                              float ema_w, const float* clip, void* stream) {
+  if (nseg <= 0) return 0;
+  long bx = (max_numel + 1023) / 1024;
+  if (bx > 256) bx = 256;
+  if (bx < 1) bx = 1;
+  dim3 grid((unsigned)bx, nseg);
+  if (upd_bf16)
+    muon_apply_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        p, (const __nv_bfloat16*)upd, ema, (const Seg*)segs, upd_offset, ema_w, clip);
+  else
+    muon_apply_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        p, (const float*)upd, ema, (const Seg*)segs, upd_offset, ema_w, clip);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+extern "C" int imf_adamw(float* p, const float* g, float* m, float* v, float* ema,
+                         const void* segs, int nseg, long max_numel, long state_offset, float b1,
+                         float b2, float eps, float bias1, float bias2, const float* clip,
+                         float ema_w, void* stream) {
+  if (nseg <= 0) return 0;
+  long bx = (max_numel + 1023) / 1024;
+  if (bx > 256) bx = 256;
+  if (bx < 1) bx = 1;
+  dim3 grid((unsigned)bx, nseg);
+  adamw_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, ema, (const Seg*)segs,
+                                                      state_offset, b1, b2, eps, bias1, bias2,
+                                                      clip, ema_w);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -1,0 +1,396 @@
+"""Flat-arena optimizer engine for Moonlight (1 or N ranks).
+
+All parameters, gradients, EMA weights and optimizer moments live in a few
+contiguous fp32 arenas; ``p.data`` / ``p.grad`` / ``state[p][...]`` are views,
+so ``state_dict()`` and checkpoints keep the reference layout while a whole
+optimizer phase is a handful of launches instead of ~10 per parameter
+(reference ``moonlight.py:395-469``, ``train.py:290-298``, ``:353-371``,
+``:582``).
+
+Arena layout (element offsets):
+
+    [ Muon matrices owned by rank 0 | rank 1 | ... | rank W-1 | AdamW params ]
+
+Each Muon segment is padded to ``seg_pad`` elements; inside a segment the
+matrices are sorted by shape so every shape is one contiguous (k, n, m) batch
+for Newton-Schulz.  The AdamW slice is padded to a multiple of 256 * W.
+
+Per step:
+  * gradient mean: Muon segment r is reduced onto rank r only, the AdamW
+    slice on every rank (own peer-memory kernels when available, else NCCL /
+    gloo on the same contiguous slices);
+  * global norm -> device-side clip factor and skip flag (no host sync);
+  * owner: momentum + batched Newton-Schulz on its segment; update all-gather;
+    every rank applies ``p <- p (1 - lr wd) - lr s Phi`` (+ EMA) to all Muon
+    parameters and AdamW (+ EMA) to the rest -> replicas stay bit-identical.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from collections import defaultdict
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..optim.moonlight import Moonlight, get_ns_coefficients, zeropower_via_newtonschulz5
+from .grad_sync import GradSync
+from .owner import assign_owners
+
+SEG_DTYPE = np.dtype([("start", "<i8"), ("numel", "<i8"), ("a", "<f4"), ("b", "<f4")])
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class FlatEngine(GradSync):
+    keeps_grad_views = True
+    handles_ema = True
+
+    def __init__(self, optimizer: Moonlight, net: torch.nn.Module, ema: Optional[torch.nn.Module],
+                 rank: int, world: int, ema_decay: float = 0.0, mode: str = "fused_p2p"):
+        self.opt, self.net, self.ema = optimizer, net, ema
+        self.rank, self.world, self.mode = rank, world, mode
+        self.ema_w = (1.0 - ema_decay) if ema is not None else 0.0
+        name_of = {id(p): n for n, p in net.named_parameters()}
+        ema_of = dict(ema.named_parameters()) if ema is not None else {}
+        self.muon: List[Tuple[dict, torch.nn.Parameter]] = []
+        self.adam: List[Tuple[dict, torch.nn.Parameter]] = []
+        for g in optimizer.param_groups:
+            for p in g["params"]:
+                (self.muon if g["use_muon"] else self.adam).append((g, p))
+        dev = next(net.parameters()).device
+        self.device = dev
+        self.cuda = dev.type == "cuda"
+        shapes = [Moonlight._matrix_shape(p) for _, p in self.muon]
+        self.shapes = shapes
+        self.owner = assign_owners(shapes, world, optimizer.defaults["ns_steps"])
+        # ---- layout ---------------------------------------------------------
+        self.seg_items: List[List[int]] = [[] for _ in range(world)]
+        for i, r in enumerate(self.owner):
+            self.seg_items[r].append(i)
+        for items in self.seg_items:                      # same-shape runs are contiguous
+            items.sort(key=lambda i: (shapes[i], i))
+        seg_numel = [sum(self.muon[i][1].numel() for i in it) for it in self.seg_items]
+        self.seg_pad = _round_up(max(1, max(seg_numel)), 256)
+        self.muon_off: Dict[int, int] = {}
+        for r, items in enumerate(self.seg_items):
+            off = r * self.seg_pad
+            for i in items:
+                self.muon_off[i] = off
+                off += self.muon[i][1].numel()
+        self.muon_total = world * self.seg_pad
+        self.adam_off: List[int] = []
+        off = self.muon_total
+        for _, p in self.adam:
+            self.adam_off.append(off)
+            off += _round_up(p.numel(), 4)
+        self.adam_numel = _round_up(off - self.muon_total, 256 * world)
+        self.total = self.muon_total + self.adam_numel
+        # ---- arenas ---------------------------------------------------------
+        z = lambda n, dt=torch.float32: torch.zeros(n, dtype=dt, device=dev)
+        self.P = z(self.total)
+        self.comm = None
+        if world > 1 and mode == "fused_p2p" and self.cuda:
+            from ..ops import comm as comm_mod
+
+            self.comm = comm_mod.try_create(world, rank, dev, self.total, self.seg_pad)
+        self.G = self.comm.grad_arena if self.comm is not None else z(self.total)
+        self.E = z(self.total) if ema is not None else None
+        self.M = z(self.muon_total)                       # momentum (own segment is live)
+        self.A1, self.A2 = z(self.adam_numel), z(self.adam_numel)
+        self.Dir = z(self.seg_pad)
+        self.upd_dtype = (optimizer.defaults["ns_dtype"] or
+                          (torch.bfloat16 if self.cuda else torch.float32))
+        self.U = (self.comm.update_arena(self.upd_dtype) if self.comm is not None
+                  else z(self.muon_total, self.upd_dtype))
+        self.clip = z(2)                                  # [coef, skip flag]
+        self.norm = z(1)
+        self._repoint(name_of, ema_of)
+        self._muon_seg_host = np.zeros(len(self.muon), dtype=SEG_DTYPE)
+        self._adam_seg_host = np.zeros(len(self.adam), dtype=SEG_DTYPE)
+        for i, (_, p) in enumerate(self.muon):
+            self._muon_seg_host[i]["start"] = self.muon_off[i]
+            self._muon_seg_host[i]["numel"] = p.numel()
+        for i, (_, p) in enumerate(self.adam):
+            self._adam_seg_host[i]["start"] = self.adam_off[i]
+            self._adam_seg_host[i]["numel"] = p.numel()
+        self._muon_seg_dev = torch.zeros(max(1, len(self.muon)) * SEG_DTYPE.itemsize,
+                                         dtype=torch.uint8, device=dev)
+        self._adam_seg_dev = torch.zeros(max(1, len(self.adam)) * SEG_DTYPE.itemsize,
+                                         dtype=torch.uint8, device=dev)
+        self._max_muon = max([p.numel() for _, p in self.muon] + [1])
+        self._max_adam = max([p.numel() for _, p in self.adam] + [1])
+        self._lib = None
+        if self.cuda:
+            from ..ops import cuda as cu
+
+            if cu.available():
+                from ..ops import kernels as K
+
+                if K._has("imf_adamw"):
+                    self._lib = K._lib
+                    self._K = K
+                    self._bind()
+        optimizer.distributed = self
+        self.skipped_last = False
+
+    # ------------------------------------------------------------- set-up ---
+    def _repoint(self, name_of, ema_of) -> None:
+        opt = self.opt
+        with torch.no_grad():
+            def place(p, off):
+                n = p.numel()
+                self.P[off:off + n].copy_(p.detach().reshape(-1))
+                p.data = self.P[off:off + n].view(p.shape)
+                p.grad = self.G[off:off + n].view(p.shape)
+                if self.E is not None:
+                    q = ema_of.get(name_of[id(p)])
+                    if q is not None:
+                        self.E[off:off + n].copy_(q.detach().reshape(-1))
+                        q.data = self.E[off:off + n].view(q.shape)
+            for i, (_, p) in enumerate(self.muon):
+                place(p, self.muon_off[i])
+                st = opt.state[p]
+                o, n = self.muon_off[i], p.numel()
+                if "momentum_buffer" in st:
+                    self.M[o:o + n].copy_(st["momentum_buffer"].reshape(-1))
+                st["momentum_buffer"] = self.M[o:o + n].view(self.shapes[i])
+            for i, (_, p) in enumerate(self.adam):
+                place(p, self.adam_off[i])
+                st = opt.state[p]
+                o, n = self.adam_off[i] - self.muon_total, p.numel()
+                for key, arena in (("exp_avg", self.A1), ("exp_avg_sq", self.A2)):
+                    if key in st:
+                        arena[o:o + n].copy_(st[key].reshape(-1))
+                    st[key] = arena[o:o + n].view(p.shape)
+                st.setdefault("step", 0)
+
+    def _bind(self) -> None:
+        L = self._lib
+        vp, ci, cl, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float
+        L.imf_muon_momentum.restype = ci
+        L.imf_muon_momentum.argtypes = [vp, vp, vp, cl, cf, ci, vp, vp]
+        L.imf_muon_apply.restype = ci
+        L.imf_muon_apply.argtypes = [vp, vp, ci, vp, vp, ci, cl, cl, cf, vp, vp]
+        L.imf_adamw.restype = ci
+        L.imf_adamw.argtypes = [vp, vp, vp, vp, vp, vp, ci, cl, cl, cf, cf, cf, cf, cf, vp, cf, vp]
+
+    # ---------------------------------------------------------------- grads --
+    def zero_grad(self) -> None:
+        self.G.zero_()
+        for _, p in self.muon + self.adam:      # autograd may have replaced a view
+            pass
+
+    def _check_grad_views(self) -> None:
+        """Autograd accumulates in place into existing ``.grad`` views; a grad
+        that was set to None elsewhere is re-attached here."""
+        for i, (_, p) in enumerate(self.muon):
+            if p.grad is None or p.grad.data_ptr() != self.G.data_ptr() + self.muon_off[i] * 4:
+                o, n = self.muon_off[i], p.numel()
+                if p.grad is not None:
+                    self.G[o:o + n].copy_(p.grad.reshape(-1))
+                p.grad = self.G[o:o + n].view(p.shape)
+        for i, (_, p) in enumerate(self.adam):
+            if p.grad is None or p.grad.data_ptr() != self.G.data_ptr() + self.adam_off[i] * 4:
+                o, n = self.adam_off[i], p.numel()
+                if p.grad is not None:
+                    self.G[o:o + n].copy_(p.grad.reshape(-1))
+                p.grad = self.G[o:o + n].view(p.shape)
+
+    @torch.no_grad()
+    def sync(self) -> None:
+        self._check_grad_views()
+        w = self.world
+        if w == 1:
+            return
+        if self.comm is not None:
+            self.comm.reduce_grads()            # own kernels: Muon segment -> owner, AdamW -> all
+            return
+        gm = self.G[:self.muon_total]
+        ga = self.G[self.muon_total:]
+        if dist.get_backend() == "nccl":
+            own = gm[self.rank * self.seg_pad:(self.rank + 1) * self.seg_pad]
+            dist.reduce_scatter_tensor(own, gm, op=dist.ReduceOp.SUM)
+            own.div_(w)
+        else:
+            dist.all_reduce(gm, op=dist.ReduceOp.SUM)
+            gm.div_(w)
+        dist.all_reduce(ga, op=dist.ReduceOp.SUM)
+        ga.div_(w)
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, max_norm: float) -> torch.Tensor:
+        own = self.G[self.rank * self.seg_pad:(self.rank + 1) * self.seg_pad]
+        sq = own.double().pow(2).sum()
+        if self.world > 1:
+            sq = sq.reshape(1)
+            dist.all_reduce(sq, op=dist.ReduceOp.SUM)
+            sq = sq[0]
+        sq = sq + self.G[self.muon_total:].double().pow(2).sum()
+        norm = sq.sqrt().float()
+        finite = torch.isfinite(norm)
+        coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
+        self.clip[0] = torch.where(finite, coef, torch.zeros_like(coef))
+        self.clip[1] = (~finite).float()
+        self.norm[0] = norm
+        return norm
+
+    # ----------------------------------------------------------------- step --
+    def _upload_segments(self) -> None:
+        wd_of = lambda g: g["weight_decay"]
+        for i, (g, p) in enumerate(self.muon):
+            lr = g["lr"]
+            self._muon_seg_host[i]["a"] = 1.0 - lr * wd_of(g)
+            self._muon_seg_host[i]["b"] = lr * Moonlight.muon_lr_scale(self.shapes[i],
+                                                                       g["lr_scale_constant"])
+        for i, (g, p) in enumerate(self.adam):
+            self._adam_seg_host[i]["a"] = g["lr"]
+            self._adam_seg_host[i]["b"] = 1.0 - g["lr"] * wd_of(g)
+        for host, devbuf in ((self._muon_seg_host, self._muon_seg_dev),
+                             (self._adam_seg_host, self._adam_seg_dev)):
+            if len(host):
+                devbuf[:host.nbytes].copy_(torch.from_numpy(host.view(np.uint8).reshape(-1)),
+                                           non_blocking=True)
+
+    @torch.no_grad()
+    def step(self, opt: Moonlight) -> None:
+        use_k = self._lib is not None
+        if use_k:
+            self._upload_segments()
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream) if use_k else None
+        skip = self.clip[1]
+        r = self.rank
+        if self.muon:
+            g0 = next(g for g, _ in self.muon)
+            mu, nest = g0["momentum"], g0["nesterov"]
+            own_g = self.G[r * self.seg_pad:(r + 1) * self.seg_pad]
+            own_m = self.M[r * self.seg_pad:(r + 1) * self.seg_pad]
+            if use_k:
+                self._K._check(self._lib.imf_muon_momentum(
+                    own_g.data_ptr(), own_m.data_ptr(), self.Dir.data_ptr(), self.seg_pad,
+                    float(mu), int(nest), self.clip.data_ptr(), stream), "imf_muon_momentum")
+                self._K.LAUNCHES.count += 1
+            else:
+                gc = own_g * self.clip[0]
+                new_m = own_m * mu + gc
+                own_m.copy_(torch.where(skip.bool(), own_m, new_m))
+                self.Dir.copy_(gc + mu * own_m if nest else own_m)
+            # batched Newton-Schulz per contiguous same-shape run of the owned segment
+            items = self.seg_items[r]
+            j = 0
+            own_u = self.U[r * self.seg_pad:(r + 1) * self.seg_pad]
+            while j < len(items):
+                shp = self.shapes[items[j]]
+                k = j
+                while k < len(items) and self.shapes[items[k]] == shp:
+                    k += 1
+                lo = self.muon_off[items[j]] - r * self.seg_pad
+                cnt = k - j
+                n, m = shp
+                batch = self.Dir[lo:lo + cnt * n * m].view(cnt, n, m)
+                coeffs = get_ns_coefficients(n, m, steps=g0["ns_steps"], mode=g0["coeff_mode"],
+                                             **opt._solve_kw)
+                upd = zeropower_via_newtonschulz5(batch, steps=g0["ns_steps"],
+                                                  dtype=g0["ns_dtype"], coeffs=coeffs)
+                own_u[lo:lo + cnt * n * m].view(cnt, n, m).copy_(upd)
+                j = k
+            if self.world > 1:
+                if self.comm is not None:
+                    self.comm.all_gather_updates()
+                elif dist.get_backend() == "nccl":
+                    dist.all_gather_into_tensor(self.U, own_u)
+                else:
+                    parts = [torch.empty_like(own_u) for _ in range(self.world)]
+                    dist.all_gather(parts, own_u.clone())
+                    for q, part in enumerate(parts):
+                        self.U[q * self.seg_pad:(q + 1) * self.seg_pad].copy_(part)
+            if use_k:
+                self._K._check(self._lib.imf_muon_apply(
+                    self.P.data_ptr(), self.U.data_ptr(), int(self.upd_dtype == torch.bfloat16),
+                    self.E.data_ptr() if self.E is not None else None,
+                    self._muon_seg_dev.data_ptr(), len(self.muon), self._max_muon, 0,
+                    float(self.ema_w), self.clip.data_ptr(), stream), "imf_muon_apply")
+                self._K.LAUNCHES.count += 1
+            else:
+                keep = skip.bool()
+                for i, (g, p) in enumerate(self.muon):
+                    o, n = self.muon_off[i], p.numel()
+                    lr = g["lr"]
+                    sc = Moonlight.muon_lr_scale(self.shapes[i], g["lr_scale_constant"])
+                    new = self.P[o:o + n] * (1 - lr * g["weight_decay"]) \
+                        - lr * sc * self.U[o:o + n].float()
+                    self.P[o:o + n].copy_(torch.where(keep, self.P[o:o + n], new))
+        if self.adam:
+            g0 = next(g for g, _ in self.adam)
+            b1, b2 = g0["adamw_betas"]
+            eps = g0["adamw_eps"]
+            for _, p in self.adam:
+                opt.state[p]["step"] += 1
+            t = opt.state[self.adam[0][1]]["step"]
+            bias1, bias2 = 1 - b1 ** t, 1 - b2 ** t
+            if use_k:
+                self._K._check(self._lib.imf_adamw(
+                    self.P.data_ptr(), self.G.data_ptr(), self.A1.data_ptr(), self.A2.data_ptr(),
+                    self.E.data_ptr() if self.E is not None else None,
+                    self._adam_seg_dev.data_ptr(), len(self.adam), self._max_adam,
+                    self.muon_total, float(b1), float(b2), float(eps), float(bias1), float(bias2),
+                    self.clip.data_ptr(), float(self.ema_w), stream), "imf_adamw")
+                self._K.LAUNCHES.count += 1
+            else:
+                keep = skip.bool()
+                sl = slice(self.muon_total, self.total)
+                g = self.G[sl] * self.clip[0]
+                m_new = self.A1 * b1 + (1 - b1) * g
+                v_new = self.A2 * b2 + (1 - b2) * g * g
+                den = (v_new / bias2).sqrt() + eps
+                lr_vec = torch.zeros_like(g)
+                dec_vec = torch.ones_like(g)
+                for i, (gr, p) in enumerate(self.adam):
+                    o, n = self.adam_off[i] - self.muon_total, p.numel()
+                    lr_vec[o:o + n] = gr["lr"]
+                    dec_vec[o:o + n] = 1 - gr["lr"] * gr["weight_decay"]
+                new_p = self.P[sl] * dec_vec - lr_vec * (m_new / bias1) / den
+                self.A1.copy_(torch.where(keep, self.A1, m_new))
+                self.A2.copy_(torch.where(keep, self.A2, v_new))
+                self.P[sl].copy_(torch.where(keep, self.P[sl], new_p))
+        if not use_k and self.E is not None:
+            lerp = self.E + self.ema_w * (self.P - self.E)
+            self.E.copy_(torch.where(skip.bool(), self.E, lerp))
+
+    def undo_step_count(self) -> None:
+        """Called by the trainer when it learns (from the device skip flag) that
+        the last step was skipped, so AdamW's bias-correction count stays exact."""
+        for _, p in self.adam:
+            self.opt.state[p]["step"] -= 1
+
+    # ---------------------------------------------------------- checkpoints --
+    @torch.no_grad()
+    def gather_state(self) -> None:
+        if self.world == 1 or not self.muon:
+            return
+        own = self.M[self.rank * self.seg_pad:(self.rank + 1) * self.seg_pad].clone()
+        parts = [torch.empty_like(own) for _ in range(self.world)]
+        dist.all_gather(parts, own)
+        for q, part in enumerate(parts):
+            self.M[q * self.seg_pad:(q + 1) * self.seg_pad].copy_(part)
+
+    @torch.no_grad()
+    def after_load(self) -> None:
+        """``load_state_dict`` replaced parameter / state tensors: pull the loaded
+        values back into the arenas and re-attach the views."""
+        name_of = {id(p): n for n, p in self.net.named_parameters()}
+        ema_of = dict(self.ema.named_parameters()) if self.ema is not None else {}
+        self._repoint(name_of, ema_of)
+
+    def owner_table(self) -> List[int]:
+        return list(self.owner)
+
+
+def attach_engine(trainer, mode: str) -> FlatEngine:
+    return FlatEngine(trainer.optimizer, trainer.net, trainer.ema, trainer.rank, trainer.world,
+                      trainer.cfg.run.ema_decay, mode)

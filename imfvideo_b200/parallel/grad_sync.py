@@ -4,7 +4,7 @@
 the whole backward, ``train.py:353-371``) and serves as the baseline arm.
 The NVLink-native path (bucketed reduce-scatter overlapped with backward,
 owner-partitioned Moonlight, fused update + all-gather) lives in
-``parallel/arena.py`` and ``parallel/dist_moonlight.py``.
+``parallel/flat_engine.py`` and ``ops/comm_impl.py``.
 """
 
 from __future__ import annotations

@@ -228,13 +228,13 @@ class Trainer:
                   f"v={a.v_head_dim}", flush=True)
 
     def _build_grad_sync(self) -> GradSync:
+        mode = self.cfg.parallel.grad_sync
+        if self.cfg.optim.optimizer == "moonlight" and mode != "nccl_flat":
+            from .parallel.flat_engine import attach_engine
+
+            return attach_engine(self, mode)      # flat arenas; owner-partitioned when world > 1
         if self.world == 1:
             return NoSync()
-        mode = self.cfg.parallel.grad_sync
-        if mode != "nccl_flat" and self.cfg.optim.optimizer == "moonlight":
-            from .parallel.dist_moonlight import attach_distributed
-
-            return attach_distributed(self, mode)
         return FlatAllReduce(list(self.net.parameters()), self.world)
 
     # ----------------------------------------------------------- stepping --
@@ -262,9 +262,12 @@ class Trainer:
             return self.grad_sync.clip_grad_norm_(max_norm)
         return torch.nn.utils.clip_grad_norm_(self.net.parameters(), max_norm)
 
-    def optimizer_step(self) -> Dict[str, float]:
-        """Sync, lr, clip, (skip if non-finite) step, QK-clip, EMA."""
+    def optimizer_step(self) -> Dict[str, Any]:
+        """Sync, lr, clip, (skip if non-finite) step, QK-clip, EMA.  With the
+        flat engine the non-finite check happens on the device (skip flag), so
+        nothing here waits for the GPU; statistics are returned as tensors."""
         o = self.cfg.optim
+        eng = self.grad_sync if getattr(self.grad_sync, "handles_ema", False) else None
         with self.timer.phase("grad_sync"):
             self.grad_sync.sync()
         lr = _lr_at(self.step, o)
@@ -272,18 +275,27 @@ class Trainer:
             g["lr"] = lr * g.get("lr_width_mult", 1.0)
         with self.timer.phase("optimizer"):
             grad_norm = self._grad_norm_and_clip(o.grad_clip)
-            finite = bool(torch.isfinite(grad_norm))
-            if finite:
+            if eng is not None:
                 self.optimizer.step()
+                skipped = eng.clip[1]
                 n_hot, s_max = qk_clip(self.net, o.qk_clip_tau, self.world)
-                if self.ema is not None:
-                    ema_update(self.ema, self.net, self.cfg.run.ema_decay)
             else:
-                n_hot, s_max = 0, float("nan")
-                self._report_bad_grads()
-        self.optimizer.zero_grad(set_to_none=not hasattr(self.grad_sync, "keeps_grad_views"))
+                finite = bool(torch.isfinite(grad_norm))
+                skipped = torch.tensor(float(not finite))
+                if finite:
+                    self.optimizer.step()
+                    n_hot, s_max = qk_clip(self.net, o.qk_clip_tau, self.world)
+                    if self.ema is not None:
+                        ema_update(self.ema, self.net, self.cfg.run.ema_decay)
+                else:
+                    n_hot, s_max = 0, float("nan")
+                    self._report_bad_grads()
+        if eng is not None:
+            eng.zero_grad()
+        else:
+            self.optimizer.zero_grad(set_to_none=True)
         self.step += 1
-        return {"lr": lr, "grad_norm": grad_norm, "skipped": not finite,
+        return {"lr": lr, "grad_norm": grad_norm, "skipped": skipped,
                 "qk_hot": n_hot, "qk_smax": s_max}
 
     def optimizer_step_async(self) -> Dict[str, Any]:
@@ -322,11 +334,18 @@ class Trainer:
             loss, parts = self.micro_step(lat, lab)
             losses.append(loss)
         stats = self.optimizer_step()
+        dt = losses[0].dtype
         vec = torch.stack([torch.stack(losses).mean(), parts["loss_u"], parts["loss_v"],
-                           stats["grad_norm"].to(losses[0].dtype)]).tolist()
+                           stats["grad_norm"].to(dt).reshape(()),
+                           stats["skipped"].to(dt).to(losses[0].device).reshape(())]).tolist()
         if not math.isfinite(vec[0]):
             self._dump_nan_batch(parts["_latents"], parts["_labels"])
-        stats.update(loss=vec[0], loss_u=vec[1], loss_v=vec[2], grad_norm=vec[3])
+        skipped = bool(vec[4])
+        if skipped:
+            if hasattr(self.grad_sync, "undo_step_count"):
+                self.grad_sync.undo_step_count()
+                self._report_bad_grads()
+        stats.update(loss=vec[0], loss_u=vec[1], loss_v=vec[2], grad_norm=vec[3], skipped=skipped)
         self.last = stats
         return stats
 

@@ -27,12 +27,18 @@ def ref_modules():
     d = reference_dir()
     if d is None:
         pytest.skip("reference sources not available")
+    names = ("models", "models.imf_dit_video", "imf_video", "moonlight", "config", "train")
+    saved = {n: sys.modules.pop(n) for n in names if n in sys.modules}
     sys.path.insert(0, d)
     try:
         import importlib
 
         mods = {name: importlib.import_module(name)
                 for name in ("models.imf_dit_video", "imf_video", "moonlight")}
+        assert all(os.path.abspath(m.__file__).startswith(os.path.abspath(d)) for m in mods.values())
     finally:
         sys.path.remove(d)
+        for n in names:               # leave no reference module behind under a shared name
+            sys.modules.pop(n, None)
+        sys.modules.update(saved)
     return mods
