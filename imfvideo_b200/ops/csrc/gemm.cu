@@ -36,12 +36,15 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             OutT* __restrict__ C, const float* __restrict__ bias, int M, int N, int K,
-            int64_t ldc, int bias_rows, float alpha, int accumulate_out, int* status) {
+            int64_t ldc, int bias_rows, float alpha, int accumulate_out, int* status,
+            const OutT* __restrict__ Cin, float beta, int64_t batch_stride_c) {
   extern __shared__ uint8_t smem_raw[];
   auto& s = *reinterpret_cast<GemmSmem<BN, STAGES>*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * GEMM_BM;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * GEMM_BM, bz = blockIdx.z;
+  C += (int64_t)bz * batch_stride_c;
+  if (Cin) Cin += (int64_t)bz * batch_stride_c;
   const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
 
   if (threadIdx.x == 0) {
@@ -78,17 +81,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         mbar_arrive_expect_tx(&s.full[st], bytes);
         const int k0 = kb * GEMM_BK;
         if (!A_MN) {
-          tma_load_2d(s.a[st], &tm_a, &s.full[st], k0, m0);
+          tma_load_3d(s.a[st], &tm_a, &s.full[st], k0, m0, bz);
         } else {
-          tma_load_2d(s.a[st], &tm_a, &s.full[st], m0, k0);
-          tma_load_2d(s.a[st] + 64 * 128, &tm_a, &s.full[st], m0 + 64, k0);
+          tma_load_3d(s.a[st], &tm_a, &s.full[st], m0, k0, bz);
+          tma_load_3d(s.a[st] + 64 * 128, &tm_a, &s.full[st], m0 + 64, k0, bz);
         }
         if (!B_MN) {
-          tma_load_2d(s.b[st], &tm_b, &s.full[st], k0, n0);
+          tma_load_3d(s.b[st], &tm_b, &s.full[st], k0, n0, bz);
         } else {
 #pragma unroll
           for (int p = 0; p < BN / 64; ++p)
-            tma_load_2d(s.b[st] + p * 64 * 128, &tm_b, &s.full[st], n0 + p * 64, k0);
+            tma_load_3d(s.b[st] + p * 64 * 128, &tm_b, &s.full[st], n0 + p * 64, k0, bz);
         }
       }
     }
@@ -134,10 +137,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
               !accumulate_out) {
             if constexpr (sizeof(OutT) == 2) {
               uint32_t o[16];
+              uint32_t cv[16];
+              if (Cin) {
+                const uint4* c4 = reinterpret_cast<const uint4*>(Cin + (int64_t)row * ldc + n0 + c);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const uint4 t = c4[i];
+                  cv[4 * i] = t.x; cv[4 * i + 1] = t.y; cv[4 * i + 2] = t.z; cv[4 * i + 3] = t.w;
+                }
+              }
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
                 float x = __uint_as_float(r[2 * i]) * alpha;
                 float y = __uint_as_float(r[2 * i + 1]) * alpha;
+                if (Cin) {
+                  x += beta * bf16_lo(cv[i]);
+                  y += beta * bf16_hi(cv[i]);
+                }
                 if (add_bias) {
                   x += bias[n0 + c + 2 * i];
                   y += bias[n0 + c + 2 * i + 1];
@@ -157,6 +173,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 v.y = __uint_as_float(r[4 * i + 1]) * alpha;
                 v.z = __uint_as_float(r[4 * i + 2]) * alpha;
                 v.w = __uint_as_float(r[4 * i + 3]) * alpha;
+                if (Cin) {
+                  const float4 cvf = reinterpret_cast<const float4*>(
+                      reinterpret_cast<const float*>(Cin) + (int64_t)row * ldc + n0 + c)[i];
+                  v.x += beta * cvf.x; v.y += beta * cvf.y; v.z += beta * cvf.z; v.w += beta * cvf.w;
+                }
                 if (add_bias) {
                   v.x += bias[n0 + c + 4 * i];
                   v.y += bias[n0 + c + 4 * i + 1];
@@ -173,6 +194,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 float x = __uint_as_float(r[i]) * alpha;
                 if (add_bias) x += bias[col];
                 if (accumulate_out) x += static_cast<float>(dst[i]);
+                if (Cin) x += beta * static_cast<float>(Cin[(int64_t)row * ldc + col]);
                 dst[i] = static_cast<OutT>(x);
               }
             }
@@ -192,22 +214,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT>
 static int launch_gemm(const void* A, const void* B, void* C, const float* bias, int M, int N,
                        int K, int64_t lda, int64_t ldb, int64_t ldc, int bias_rows, float alpha,
-                       int accumulate_out, int* status, cudaStream_t stream) {
+                       int accumulate_out, int* status, cudaStream_t stream, int batch = 1,
+                       int64_t sa = 0, int64_t sb = 0, int64_t sc = 0, const void* Cin = nullptr,
+                       float beta = 0.f) {
   CUtensorMap ta, tb;
   int rc;
   {
     // K-major: dims (K, M), box (64, 128).  MN-major: dims (M, K), box (64, 64).
-    uint64_t dims[2] = {A_MN ? (uint64_t)M : (uint64_t)K, A_MN ? (uint64_t)K : (uint64_t)M};
-    uint64_t str[2] = {2, (uint64_t)lda * 2};
-    uint32_t box[2] = {64, A_MN ? 64u : (uint32_t)GEMM_BM};
-    rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(A), dims, str, box);
+    uint64_t dims[3] = {A_MN ? (uint64_t)M : (uint64_t)K, A_MN ? (uint64_t)K : (uint64_t)M,
+                        (uint64_t)batch};
+    uint64_t str[3] = {2, (uint64_t)lda * 2, (uint64_t)(batch > 1 ? sa : (int64_t)lda) * 2};
+    uint32_t box[3] = {64, A_MN ? 64u : (uint32_t)GEMM_BM, 1};
+    rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(A), dims, str, box);
     if (rc) return rc;
   }
   {
-    uint64_t dims[2] = {B_MN ? (uint64_t)N : (uint64_t)K, B_MN ? (uint64_t)K : (uint64_t)N};
-    uint64_t str[2] = {2, (uint64_t)ldb * 2};
-    uint32_t box[2] = {64, B_MN ? 64u : (uint32_t)BN};
-    rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(B), dims, str, box);
+    uint64_t dims[3] = {B_MN ? (uint64_t)N : (uint64_t)K, B_MN ? (uint64_t)K : (uint64_t)N,
+                        (uint64_t)batch};
+    uint64_t str[3] = {2, (uint64_t)ldb * 2, (uint64_t)(batch > 1 ? sb : (int64_t)ldb) * 2};
+    uint32_t box[3] = {64, B_MN ? 64u : (uint32_t)BN, 1};
+    rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(B), dims, str, box);
     if (rc) return rc;
   }
   auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, OutT>;
@@ -219,9 +245,10 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
       return IMF_ERR_LAUNCH;
     attr_set = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + GEMM_BM - 1) / GEMM_BM);
+  dim3 grid((N + BN - 1) / BN, (M + GEMM_BM - 1) / GEMM_BM, batch);
   kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, static_cast<OutT*>(C), bias, M, N, K, ldc,
-                                             bias_rows, alpha, accumulate_out, status);
+                                             bias_rows, alpha, accumulate_out, status,
+                                             static_cast<const OutT*>(Cin), beta, sc);
   return cudaGetLastError() == cudaSuccess ? IMF_OK : IMF_ERR_LAUNCH;
 }
 
@@ -242,6 +269,35 @@ extern "C" int imf_gemm_bf16(const void* A, const void* B, void* C, const float*
 #define IMF_GEMM_CASE(AM, BM_, OT)                                                          \
   return launch_gemm<128, 3, AM, BM_, OT>(A, B, C, bias, M, N, K, lda, ldb, ldc, bias_rows, \
                                           alpha, accumulate_out, status, st)
+  if (out_fp32) {
+    if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, float);
+    if (!a_mn && b_mn) IMF_GEMM_CASE(false, true, float);
+    if (a_mn && !b_mn) IMF_GEMM_CASE(true, false, float);
+    IMF_GEMM_CASE(true, true, float);
+  } else {
+    if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, __nv_bfloat16);
+    if (!a_mn && b_mn) IMF_GEMM_CASE(false, true, __nv_bfloat16);
+    if (a_mn && !b_mn) IMF_GEMM_CASE(true, false, __nv_bfloat16);
+    IMF_GEMM_CASE(true, true, __nv_bfloat16);
+  }
+#undef IMF_GEMM_CASE
+}
+
+// Batched form with an additive source: C[z] = alpha * op(A[z]) op(B[z])^T + beta * Cin[z].
+// sa/sb/sc: batch strides in elements (multiples of 8 for A, B).  Used by the
+// Newton-Schulz iteration (X X^T, b A + c A A, a X + B X as three launches).
+extern "C" int imf_gemm_bf16_batched(const void* A, const void* B, void* C, const void* Cin, int M,
+                                     int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                                     int batch, int64_t sa, int64_t sb, int64_t sc, int a_mn,
+                                     int b_mn, int out_fp32, float alpha, float beta, int* status,
+                                     void* stream) {
+  using namespace imf;
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return IMF_ERR_ARG;
+  if ((lda & 7) || (ldb & 7) || (batch > 1 && ((sa & 7) || (sb & 7)))) return IMF_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define IMF_GEMM_CASE(AM, BM_, OT)                                                              \
+  return launch_gemm<128, 3, AM, BM_, OT>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, alpha, 0, \
+                                          status, st, batch, sa, sb, sc, Cin, beta)
   if (out_fp32) {
     if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, float);
     if (!a_mn && b_mn) IMF_GEMM_CASE(false, true, float);

@@ -318,3 +318,71 @@ if _has("imf_attn_fwd"):
     _cuda.register("attention", attention_dual=attention_dual)
 if _has("imf_resnorm") and _has("imf_gemm_bf16") and _has("imf_attn_fwd"):
     _cuda.register("block")
+
+
+# ------------------------------------------------ batched GEMM / Newton-Schulz
+if _has("imf_gemm_bf16_batched"):
+    _lib.imf_gemm_bf16_batched.restype = c_int
+    _lib.imf_gemm_bf16_batched.argtypes = [c_void_p] * 4 + [c_int] * 3 + [c_int64] * 3 + [c_int] + \
+        [c_int64] * 3 + [c_int] * 3 + [c_float, c_float, c_void_p, c_void_p]
+
+
+def gemm_batched(a, b, *, a_mn=False, b_mn=False, cin=None, alpha=1.0, beta=0.0, out=None,
+                 out_dtype=torch.bfloat16):
+    """out[z] = alpha * op(a[z]) op(b[z])^T + beta * cin[z] for 3-D bf16 tensors."""
+    assert a.dim() == 3 and b.dim() == 3 and a.stride(2) == 1 and b.stride(2) == 1
+    Z = a.shape[0]
+    M, K = (a.shape[2], a.shape[1]) if a_mn else (a.shape[1], a.shape[2])
+    N, Kb = (b.shape[2], b.shape[1]) if b_mn else (b.shape[1], b.shape[2])
+    assert K == Kb and b.shape[0] == Z
+    if out is None:
+        out = torch.empty(Z, M, N, dtype=out_dtype, device=a.device)
+    assert out.stride(2) == 1 and (cin is None or (cin.shape == out.shape and
+                                                   cin.stride() == out.stride()
+                                                   and cin.dtype == out.dtype))
+    rc = _lib.imf_gemm_bf16_batched(_ptr(a), _ptr(b), _ptr(out), _ptr(cin), M, N, K, a.stride(1),
+                                    b.stride(1), out.stride(1), Z, a.stride(0), b.stride(0),
+                                    out.stride(0), int(a_mn), int(b_mn),
+                                    int(out.dtype == torch.float32), float(alpha), float(beta),
+                                    _ptr(status_word(a.device)), _stream())
+    _check(rc, "imf_gemm_bf16_batched")
+    LAUNCHES.count += 1
+    return out
+
+
+def newton_schulz(G: torch.Tensor, coeffs, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
+    """Quintic Newton-Schulz on a batch (k, n, m) with the tcgen05 GEMM:
+    per iteration A = X X^T (or X^T X when n > m), B = b A + c A A,
+    X <- a X + B X (or X B), three launches for the whole batch.  The Gram
+    side is chosen by operand major flags, so no transposed copy is made."""
+    a_, b_, c_ = coeffs
+    k, n, m = G.shape
+    if min(n, m) < 8 or (n > m and m % 8):
+        return None                 # tiny / odd Gram side: the caller uses the torch path
+    mp = (m + 7) // 8 * 8
+    Gf = G.float()
+    nrm = Gf.flatten(1).norm(dim=1).view(k, 1, 1) + eps
+    X = torch.zeros(k, n, mp, dtype=torch.bfloat16, device=G.device)
+    X[:, :, :m] = (Gf / nrm).to(torch.bfloat16)
+    Y = torch.empty_like(X)
+    small_rows = n <= m
+    g = n if small_rows else mp
+    if (not small_rows) and mp != m:
+        Y.zero_()
+    A = torch.empty(k, g, g, dtype=torch.bfloat16, device=G.device)
+    B = torch.empty_like(A)
+    for _ in range(steps):
+        if small_rows:
+            gemm_batched(X, X, out=A)                                        # X X^T
+            gemm_batched(A, A, cin=A, alpha=c_, beta=b_, out=B)              # b A + c A A
+            gemm_batched(B, X, b_mn=True, cin=X, alpha=1.0, beta=a_, out=Y)  # a X + B X
+        else:
+            gemm_batched(X, X, a_mn=True, b_mn=True, out=A)                  # X^T X
+            gemm_batched(A, A, cin=A, alpha=c_, beta=b_, out=B)
+            gemm_batched(X, B, cin=X, alpha=1.0, beta=a_, out=Y)             # a X + X B
+        X, Y = Y, X
+    return X[:, :, :m]
+
+
+if _has("imf_gemm_bf16_batched"):
+    _cuda.register("newton_schulz", newton_schulz=newton_schulz)

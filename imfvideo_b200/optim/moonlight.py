@@ -140,7 +140,9 @@ def zeropower_via_newtonschulz5(G: Tensor, steps=5, eps=1e-7, dtype=None, coeffs
         from ..ops import cuda as cu
 
         if cu.available() and cu.has("newton_schulz") and dtype == torch.bfloat16:
-            return cu.newton_schulz(G, (a, b, c), steps, eps)
+            out = cu.newton_schulz(G, (a, b, c), steps, eps)
+            if out is not None:
+                return out
     X = G.to(dtype)
     nrm = X.flatten(-2).norm(dim=-1)
     X = X / (nrm.reshape(nrm.shape + (1, 1)) + eps)

@@ -130,3 +130,33 @@ def test_attention_backward(K, B, L, H):
     assert torch.equal(dk, dk2) and torch.equal(dv2, dv.contiguous())   # deterministic parts
     assert _rel(dq2, dq) < 1e-3              # dQ uses fp32 atomics: order may differ
     K.check_status()
+
+
+@pytest.mark.parametrize("k,n,m", [(3, 128, 256), (2, 256, 128), (2, 256, 682), (2, 682, 256),
+                                   (4, 1, 256), (1, 448, 128)])
+def test_newton_schulz_kernel(K, k, n, m):
+    from imfvideo_b200.ops import reference as ref
+
+    torch.manual_seed(n + m)
+    G = torch.randn(k, n, m, device="cuda")
+    coeffs = (3.4445, -4.7750, 2.0315)
+    X = K.newton_schulz(G, coeffs, steps=5)
+    if n == 1:
+        assert X is None            # vectors take the torch path
+        return
+    assert X.shape == (k, n, m)
+    for i in range(k):
+        R = ref.newton_schulz(G[i], coeffs, steps=5, dtype=torch.float32)
+        assert _rel(X[i], R) < 4e-2, (i, _rel(X[i], R))
+    K.check_status()
+
+
+def test_batched_gemm_with_additive_source(K):
+    torch.manual_seed(0)
+    a = torch.randn(3, 200, 136, device="cuda").bfloat16()
+    b = torch.randn(3, 96, 136, device="cuda").bfloat16()
+    cin = torch.randn(3, 200, 96, device="cuda").bfloat16()
+    out = K.gemm_batched(a, b, cin=cin, alpha=0.5, beta=2.0)
+    ref = 0.5 * torch.einsum("zmk,znk->zmn", a.float(), b.float()) + 2.0 * cin.float()
+    assert _rel(out, ref) < 5e-3
+    K.check_status()
