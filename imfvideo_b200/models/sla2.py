@@ -57,7 +57,7 @@ def block_mean(x: Tensor, block: int) -> Tensor:
     B, H, L, D = x.shape
     nb = -(-L // block)
     pad = nb * block - L
-    xf = F.pad(x.float(), (0, 0, 0, pad)).view(B, H, nb, block, D).sum(3)
+    xf = F.pad(x.float(), (0, 0, 0, pad)).reshape(B, H, nb, block, D).sum(3)
     cnt = torch.full((nb,), float(block), device=x.device)
     cnt[-1] = block - pad
     return xf / cnt.view(1, 1, nb, 1)
@@ -148,10 +148,10 @@ def fake_quant_blocks(x: Tensor, block: int) -> Tensor:
     B, H, L, D = x.shape
     nb = -(-L // block)
     pad = nb * block - L
-    xp = F.pad(x.float(), (0, 0, 0, pad)).view(B, H, nb, block * D)
+    xp = F.pad(x.float(), (0, 0, 0, pad)).reshape(B, H, nb, block * D)
     s = (xp.detach().abs().amax(-1, keepdim=True) / 127.0 + 1e-12)
     y = _round_ste(xp / s).clamp(-127, 127) * s
-    return y.view(B, H, nb * block, D)[:, :, :L].to(x.dtype)
+    return y.reshape(B, H, nb * block, D)[:, :, :L].to(x.dtype)
 
 
 def quantize_blocks(x: Tensor, block: int) -> Tuple[Tensor, Tensor]:
@@ -159,10 +159,10 @@ def quantize_blocks(x: Tensor, block: int) -> Tuple[Tensor, Tensor]:
     B, H, L, D = x.shape
     nb = -(-L // block)
     pad = nb * block - L
-    xp = F.pad(x.float(), (0, 0, 0, pad)).view(B, H, nb, block * D)
+    xp = F.pad(x.float(), (0, 0, 0, pad)).reshape(B, H, nb, block * D)
     s = xp.abs().amax(-1) / 127.0 + 1e-12
     xq = (torch.sign(xp) * torch.floor((xp / s[..., None]).abs() + 0.5)).clamp(-127, 127)
-    return xq.view(B, H, nb * block, D)[:, :, :L].to(torch.int8), s
+    return xq.reshape(B, H, nb * block, D)[:, :, :L].to(torch.int8), s
 
 
 # -------------------------------------------------- block sparse + linear ---
@@ -187,8 +187,8 @@ def sparse_linear_attention(q: Tensor, k: Tensor, v: Tensor, sel: Tensor, bq: in
     if int8:
         qs, ks, vs = fake_quant_blocks(q, bq), fake_quant_blocks(k, bk), fake_quant_blocks(v, bk)
     pad_q, pad_k = Mb * bq - L, Nb * bk - L
-    padq = lambda t: F.pad(t.float(), (0, 0, 0, pad_q)).view(B, H, Mb, bq, D)
-    padk = lambda t: F.pad(t.float(), (0, 0, 0, pad_k)).view(B, H, Nb, bk, D)
+    padq = lambda t: F.pad(t.float(), (0, 0, 0, pad_q)).reshape(B, H, Mb, bq, D)
+    padk = lambda t: F.pad(t.float(), (0, 0, 0, pad_k)).reshape(B, H, Nb, bk, D)
     qb, kb, vb = padq(qs), padk(ks), padk(vs)
     idx = sel.long()
     gather = lambda t: torch.gather(

@@ -1,0 +1,109 @@
+"""Wrappers for the block-sparse attention kernels (``csrc/attn_sparse.cu``):
+per-block INT8 quantiser, query-tile LUT construction, forward (+ tangent),
+and ``SparseCore``, the attention core that plugs SLA2 / cube attention into
+the fused transformer-block node (``ops/block.py``)."""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import kernels as K
+
+_lib = K._lib
+vp, ci, cf, c64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_int64
+
+if K._has("imf_attn_sparse_fwd"):
+    _lib.imf_quantize_blocks.restype = ci
+    _lib.imf_quantize_blocks.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, c64, c64, c64, vp]
+    _lib.imf_attn_sparse_fwd.restype = ci
+    _lib.imf_attn_sparse_fwd.argtypes = [vp] * 15 + [ci] * 5 + [vp, c64, c64, c64, cf, ci, ci, vp, vp]
+
+
+def quantize_blocks(x: torch.Tensor, block: int, want_q: bool = True, want_fq: bool = False):
+    """x: (B, L, H, 64) bf16 -> (int8 (B,L,H,64) | None, scales (B,H,nblk) fp32,
+    de-quantised bf16 copy | None)."""
+    B, L, H, D = x.shape
+    assert D == 64 and x.dtype == torch.bfloat16 and x.stride(3) == 1
+    nb = -(-L // block)
+    xq = torch.empty(B, L, H, D, dtype=torch.int8, device=x.device) if want_q else None
+    xs = torch.empty(B, H, nb, dtype=torch.float32, device=x.device)
+    xf = torch.empty(B, L, H, D, dtype=torch.bfloat16, device=x.device) if want_fq else None
+    K._check(_lib.imf_quantize_blocks(K._ptr(x), K._ptr(xq), K._ptr(xs), K._ptr(xf), B, L, H, block,
+                                      x.stride(0), x.stride(1), x.stride(2), K._stream()),
+             "imf_quantize_blocks")
+    K.LAUNCHES.count += 1
+    return xq, xs, xf
+
+
+def build_tile_lut(sel: torch.Tensor, qblk: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-128-row query tile list of 64-key blocks from the per-routing-block
+    selection ``sel`` (B, H, Mb, T).  qblk 128: one routing block per tile.
+    qblk 64: a tile holds two routing blocks; the list is their union and the
+    flags say which half attends each entry (bit0 rows 0-63, bit1 rows 64-127).
+    Returns (lut int32 (B,H,n_mt,tmax) padded with -1, flags uint8)."""
+    B, H, Mb, T = sel.shape
+    sel = sel.to(torch.int32)
+    if qblk == 128:
+        return sel.contiguous(), torch.full(sel.shape, 3, dtype=torch.uint8, device=sel.device)
+    n_mt = (Mb + 1) // 2
+    if Mb % 2:
+        sel = torch.cat([sel, torch.full((B, H, 1, T), -1, dtype=torch.int32, device=sel.device)], 2)
+    pair = sel.view(B, H, n_mt, 2 * T)
+    fl = torch.cat([torch.ones(T, dtype=torch.int32, device=sel.device),
+                    torch.full((T,), 2, dtype=torch.int32, device=sel.device)]).expand(B, H, n_mt, 2 * T)
+    big = torch.iinfo(torch.int32).max
+    ids = torch.where(pair < 0, torch.full_like(pair, big), pair)
+    ids, order = ids.sort(dim=-1)
+    fl = torch.gather(fl, -1, order)
+    dup = torch.zeros_like(ids, dtype=torch.bool)
+    dup[..., 1:] = (ids[..., 1:] == ids[..., :-1]) & (ids[..., 1:] != big)
+    # a block selected by both halves appears twice in a row: merge the flags into the first
+    fl_next = torch.zeros_like(fl)
+    fl_next[..., :-1] = torch.where(dup[..., 1:], fl[..., 1:], torch.zeros_like(fl[..., 1:]))
+    fl = fl | fl_next
+    ids = torch.where(dup, torch.full_like(ids, big), ids)
+    ids, order = ids.sort(dim=-1)
+    fl = torch.gather(fl, -1, order)
+    lut = torch.where(ids == big, torch.full_like(ids, -1), ids)
+    return lut.contiguous(), fl.to(torch.uint8).contiguous()
+
+
+def sparse_fwd(q, k, v, dq, dk, dv, lut, flags, qblk: int, int8: bool, quant_p: bool,
+               need_lse: bool = True, scale: Optional[float] = None):
+    """Block-sparse softmax branch: (o_s, do_s | None, lse | None).
+    q, k, v (+ tangents): (B, L, H, 64) bf16, token order = routing order."""
+    B, L, H, D = q.shape
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    tang = dq is not None
+    q8 = k8 = qs = ks = None
+    vv = K._tma_ok(v)
+    if int8:
+        q8, qs, _ = quantize_blocks(K._tma_ok(q), qblk)
+        k8, ks, _ = quantize_blocks(K._tma_ok(k), 64)
+        _, _, vv = quantize_blocks(vv, 64, want_q=False, want_fq=True)
+    ts = [K._tma_ok(q), K._tma_ok(k), vv]
+    if tang:
+        ts += [K._tma_ok(dq), K._tma_ok(dk), K._tma_ok(dv)]
+    strides = []
+    for t in ts:
+        strides += [t.stride(0), t.stride(1), t.stride(2)]
+    arr = (c64 * 18)(*(strides + [0] * (18 - len(strides))))
+    o = torch.empty(B, L, H, D, dtype=torch.bfloat16, device=q.device)
+    do = torch.empty_like(o) if tang else None
+    lse = torch.empty(B, H, L, dtype=torch.float32, device=q.device) if need_lse else None
+    need_qk = tang or not int8
+    rc = _lib.imf_attn_sparse_fwd(
+        K._ptr(q8), K._ptr(k8), K._ptr(qs), K._ptr(ks),
+        K._ptr(ts[0]) if need_qk else None, K._ptr(ts[1]) if need_qk else None, K._ptr(ts[2]),
+        K._ptr(ts[3]) if tang else None, K._ptr(ts[4]) if tang else None,
+        K._ptr(ts[5]) if tang else None, K._ptr(lut), K._ptr(flags), K._ptr(o), K._ptr(do),
+        K._ptr(lse), B, L, H, lut.shape[-1], qblk, ctypes.cast(arr, vp), o.stride(0), o.stride(1),
+        o.stride(2), float(scale), int(quant_p), int(int8), K._ptr(K.status_word(q.device)),
+        K._stream())
+    K._check(rc, "imf_attn_sparse_fwd")
+    K.LAUNCHES.count += 1
+    return o, do, lse

@@ -1,0 +1,80 @@
+"""GPU: block-sparse INT8 attention kernel (primal + tangent) and quantiser
+against the SLA2 torch formulas."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def SP():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from imfvideo_b200.ops import cuda as cu
+
+    assert cu.available()
+    from imfvideo_b200.ops import sparse
+
+    return sparse
+
+
+def _rel(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def test_quantiser_matches_reference(SP):
+    from imfvideo_b200.models import sla2 as S
+
+    torch.manual_seed(0)
+    x = torch.randn(2, 333, 3, 64, device="cuda").bfloat16()
+    xq, xs, xf = SP.quantize_blocks(x, 64, want_fq=True)
+    rq, rs = S.quantize_blocks(x.permute(0, 2, 1, 3).float(), 64)
+    diff = (xq.permute(0, 2, 1, 3).int() - rq.int()).abs()
+    assert diff.max() <= 1 and (diff > 0).float().mean() < 1e-3
+    assert torch.allclose(xs, rs, rtol=1e-6)
+    rf = S.fake_quant_blocks(x.permute(0, 2, 1, 3).float(), 64).permute(0, 2, 1, 3)
+    assert _rel(xf, rf) < 4e-3
+
+
+def test_tile_lut_union(SP):
+    sel = torch.tensor([[[[0, 3], [3, 5], [1, 2]]]], device="cuda")        # Mb = 3, T = 2
+    lut, fl = SP.build_tile_lut(sel, 64)
+    assert lut.shape == (1, 1, 2, 4)
+    assert lut[0, 0, 0].tolist() == [0, 3, 5, -1] and fl[0, 0, 0].tolist()[:3] == [1, 3, 2]
+    assert lut[0, 0, 1].tolist() == [1, 2, -1, -1] and fl[0, 0, 1].tolist()[:2] == [1, 1]
+
+
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("qblk,L", [(128, 640), (64, 583), (64, 1024)])
+def test_sparse_forward_and_tangent(SP, int8, qblk, L):
+    from imfvideo_b200.models import sla2 as S
+
+    torch.manual_seed(L + qblk)
+    B, H, D = 1, 2, 64
+    mk = lambda s=1.0: (torch.randn(B, L, H, D, device="cuda") * s).bfloat16()
+    q, k, v, dq, dk, dv = mk(), mk(), mk(), mk(.5), mk(.5), mk(.5)
+    Mb, Nb = -(-L // qblk), -(-L // 64)
+    T = max(2, Nb // 4)
+    sel = torch.stack([torch.stack([torch.randperm(Nb, device="cuda")[:T] for _ in range(Mb)])
+                       for _ in range(H)]).unsqueeze(0)
+    lut, flags = SP.build_tile_lut(sel, qblk)
+    o, do, lse = SP.sparse_fwd(q, k, v, dq, dk, dv, lut, flags, qblk, int8, quant_p=int8)
+    o2, _, _ = SP.sparse_fwd(q, k, v, None, None, None, lut, flags, qblk, int8, quant_p=int8)
+    ph = lambda t: t.permute(0, 2, 1, 3).float()
+    a_rows = torch.ones(H, L, device="cuda")          # alpha = 1: sparse branch only
+
+    def f(a, b, c):
+        out, o_s, _o_l, ls = S.sparse_linear_attention(a, b, c, sel, qblk, 64, a_rows, int8=int8,
+                                                       return_parts=True)
+        return o_s, ls
+    (ro, rl), (rdo, _) = torch.func.jvp(f, (ph(q), ph(k), ph(v)), (ph(dq), ph(dk), ph(dv)))
+    tol = 3e-2 if int8 else 1e-2
+    assert _rel(o.permute(0, 2, 1, 3), ro) < tol
+    assert _rel(do.permute(0, 2, 1, 3), rdo) < (8e-2 if int8 else 1.5e-2)
+    assert (lse - rl).abs().max() < (5e-2 if int8 else 2e-3)
+    assert _rel(o2, o) < 5e-3
+    from imfvideo_b200.ops import kernels
+    kernels.check_status()
