@@ -208,30 +208,38 @@ def sparse_linear_attention(q: Tensor, k: Tensor, v: Tensor, sel: Tensor, bq: in
         p = _round_ste(p / pm * 127.0) / 127.0 * pm
     o_s = torch.einsum("bhmqk,bhmkd->bhmqd", p, vg.flatten(3, 4)).reshape(B, H, Mb * bq, D)[:, :, :L]
 
-    # ---- linear complement branch through per-block states ----
-    phi_q = F.softmax(q.float(), dim=-1)
-    phi_k = F.softmax(k.float(), dim=-1)
-    nc = Nb if n_comp_blocks is None else n_comp_blocks
-    kmask = (torch.arange(Nb * bk, device=q.device) < min(L, nc * bk)).view(1, 1, Nb, bk, 1)
-    pkb = padk(phi_k) * kmask                                 # zero outside the complement domain
-    vb_raw = padk(v)
-    Hs = torch.einsum("bhnkd,bhnke->bhnde", pkb, vb_raw)      # (B,H,Nb,D,D)
-    zs = pkb.sum(3)                                           # (B,H,Nb,D)
-    Htot, ztot = Hs.sum(2, keepdim=True), zs.sum(2, keepdim=True)
-    Hsel = torch.gather(Hs.unsqueeze(2).expand(B, H, Mb, Nb, D, D), 3,
-                        idx.view(B, H, Mb, T, 1, 1).expand(B, H, Mb, T, D, D)).sum(3)
-    zsel = torch.gather(zs.unsqueeze(2).expand(B, H, Mb, Nb, D), 3,
-                        idx.view(B, H, Mb, T, 1).expand(B, H, Mb, T, D)).sum(3)
-    Hc, zc = Htot - Hsel, ztot - zsel                         # (B,H,Mb,D,D), (B,H,Mb,D)
-    pq = padq(phi_q)
-    num = torch.einsum("bhmqd,bhmde->bhmqe", pq, Hc)
-    den = torch.einsum("bhmqd,bhmd->bhmq", pq, zc).unsqueeze(-1) + EPS_LINEAR
-    o_l = (num / den).reshape(B, H, Mb * bq, D)[:, :, :L]
+    o_l = linear_branch(q, k, v, sel, bq, bk, n_comp_blocks)
     a = alpha_rows.view(1, H, L, 1).float()
     out = a * o_s + (1.0 - a) * o_l
     if return_parts:
         return out, o_s, o_l, lse.reshape(B, H, Mb * bq)[:, :, :L]
     return out
+
+
+def linear_branch(q: Tensor, k: Tensor, v: Tensor, sel: Tensor, bq: int, bk: int,
+                  n_comp_blocks: Optional[int] = None) -> Tensor:
+    """Complement linear attention through per-key-block states
+    H_j = phi(K_j)^T V_j, z_j = sum phi(K_j): for query block i the complement
+    state is (sum_j H_j) - sum_{j in sel(i)} H_j, formed with one small
+    (Mb x Nb) mask matmul.  (B, H, L, D) fp32 in and out."""
+    B, H, L, D = q.shape
+    Mb, Nb = -(-L // bq), -(-L // bk)
+    pad_q, pad_k = Mb * bq - L, Nb * bk - L
+    phi_q = F.softmax(q.float(), dim=-1)
+    phi_k = F.softmax(k.float(), dim=-1)
+    nc = Nb if n_comp_blocks is None else n_comp_blocks
+    kmask = (torch.arange(Nb * bk, device=q.device) < min(L, nc * bk)).view(1, 1, Nb, bk, 1)
+    pkb = F.pad(phi_k, (0, 0, 0, pad_k)).reshape(B, H, Nb, bk, D) * kmask
+    vb = F.pad(v.float(), (0, 0, 0, pad_k)).reshape(B, H, Nb, bk, D)
+    Hs = torch.einsum("bhnkd,bhnke->bhnde", pkb, vb)          # (B,H,Nb,D,D)
+    zs = pkb.sum(3)                                           # (B,H,Nb,D)
+    msel = torch.zeros(B, H, Mb, Nb, device=q.device).scatter_(-1, sel.long(), 1.0)
+    Hc = Hs.sum(2, keepdim=True) - torch.einsum("bhmn,bhnde->bhmde", msel, Hs)
+    zc = zs.sum(2, keepdim=True) - torch.einsum("bhmn,bhnd->bhmd", msel, zs)
+    pq = F.pad(phi_q, (0, 0, 0, pad_q)).reshape(B, H, Mb, bq, D)
+    num = torch.einsum("bhmqd,bhmde->bhmqe", pq, Hc)
+    den = torch.einsum("bhmqd,bhmd->bhmq", pq, zc).unsqueeze(-1) + EPS_LINEAR
+    return (num / den).reshape(B, H, Mb * bq, D)[:, :, :L]
 
 
 def expand_mask(mc: Tensor, bq: int, bk: int, L: int) -> Tensor:
@@ -426,3 +434,104 @@ def cube_dense_ref(q, k, v, alpha, lut, Np: int, E: int, prefix_len: int):
     o_l = (w @ v.float()) / (w.sum(-1, keepdim=True) + EPS_LINEAR)
     a = alpha[:, rows].view(1, H, L, 1)
     return a * o_s + (1.0 - a) * o_l
+
+
+# ------------------------------------------------- CUDA core (fused block) ---
+class SparseCore:
+    """Attention core for ``ops.block``: block-sparse INT8 tcgen05 kernel for
+    the softmax branch (primal + tangent), per-block-state linear branch and
+    the alpha mix.  Reverse mode recomputes the op with the torch formulas
+    (straight-through for the INT8 grid)."""
+
+    def __init__(self, mod, qblk: int, bk: int, n_comp: Optional[int], int8: bool):
+        self.mod, self.qblk, self.bk, self.n_comp, self.int8 = mod, qblk, bk, n_comp, int8
+
+    def _sel_and_alpha(self, qh, kh):
+        m = self.mod
+        L = qh.shape[2]
+        if isinstance(m, SLA2CubeQATAttentionImpl):
+            sel, _ = m.route(qh, kh)
+            a_rows = torch.sigmoid(m.alpha_logit)[:, m.a_index]
+        else:
+            with torch.no_grad():
+                _, sel, _, _ = m.sla2.router(qh, kh, m.sla2.topk, need_mask=False)
+            a_rows = torch.sigmoid(m.sla2.alpha_logit).repeat_interleave(m.bq, dim=-1)[:, :L]
+        return sel, a_rows
+
+    def fwd(self, q, k, v, dq, dk, dv, need_bwd: bool):
+        from ..ops import sparse as SP
+
+        qh, kh, vh = (x.permute(0, 2, 1, 3) for x in (q, k, v))
+        sel, a_rows = self._sel_and_alpha(qh.detach(), kh.detach())
+        lut, flags = SP.build_tile_lut(sel, self.qblk)
+        o_s, do_s, lse = SP.sparse_fwd(q, k, v, dq, dk, dv, lut, flags, self.qblk, self.int8,
+                                       quant_p=self.int8, need_lse=True)
+        f = lambda a, b, c: linear_branch(a, b, c, sel, self.qblk, self.bk, self.n_comp)
+        with torch.no_grad():
+            if dq is not None:
+                o_l, do_l = torch.func.jvp(f, (qh.float(), kh.float(), vh.float()),
+                                           (dq.permute(0, 2, 1, 3).float(),
+                                            dk.permute(0, 2, 1, 3).float(),
+                                            dv.permute(0, 2, 1, 3).float()))
+            else:
+                o_l, do_l = f(qh.float(), kh.float(), vh.float()), None
+            a = a_rows.detach().t().reshape(1, -1, a_rows.shape[0], 1)       # (1, L, H, 1)
+            o = (a * o_s.float() + (1 - a) * o_l.permute(0, 2, 1, 3)).to(q.dtype).contiguous()
+            do = None
+            if dq is not None:
+                do = (a * do_s.float() + (1 - a) * do_l.permute(0, 2, 1, 3)).to(q.dtype).contiguous()
+            if need_bwd and isinstance(self.mod, SLA2CubeQATAttentionImpl):
+                self.mod.logit_max_log2 = (lse.amax(dim=(0, 2)) * 1.4426950408889634).float()
+        return o, do, (sel,)
+
+    def bwd(self, q, k, v, o, saved, go, gv_out=None):
+        (sel,) = saved
+        m = self.mod
+        alpha_param = m.alpha_logit if isinstance(m, SLA2CubeQATAttentionImpl) else m.sla2.alpha_logit
+        with torch.enable_grad():
+            ql, kl, vl = (x.detach().permute(0, 2, 1, 3).float().requires_grad_(True)
+                          for x in (q, k, v))
+            L = ql.shape[2]
+            if isinstance(m, SLA2CubeQATAttentionImpl):
+                a_rows = torch.sigmoid(alpha_param)[:, m.a_index]
+            else:
+                a_rows = torch.sigmoid(alpha_param).repeat_interleave(m.bq, dim=-1)[:, :L]
+            out = sparse_linear_attention(ql, kl, vl, sel, self.qblk, self.bk, a_rows,
+                                          n_comp_blocks=self.n_comp, int8=self.int8)
+            gq, gk, gv, ga = torch.autograd.grad(out, (ql, kl, vl, alpha_param),
+                                                 go.permute(0, 2, 1, 3).float())
+        alpha_param.grad = ga if alpha_param.grad is None else alpha_param.grad + ga
+        back = lambda t: t.permute(0, 2, 1, 3).to(q.dtype).contiguous()
+        gv_ = back(gv)
+        if gv_out is not None:
+            gv_out.copy_(gv_)
+            gv_ = gv_out
+        return back(gq), back(gk), gv_
+
+
+def _cuda_sparse_ready(t: Tensor) -> bool:
+    if not t.is_cuda:
+        return False
+    from ..ops import cuda as cu
+
+    if not cu.available():
+        return False
+    from ..ops import kernels as K
+
+    return K._has("imf_attn_sparse_fwd")
+
+
+def _cube_fused_core(self):
+    if self.E != 64 or not _cuda_sparse_ready(self.alpha_logit) or not self.pre_permuted:
+        return None
+    return SparseCore(self, 64, 64, self.Np, self.use_int8)
+
+
+def _sla2_fused_core(self):
+    if self.bk != 64 or self.bq not in (64, 128) or not _cuda_sparse_ready(self.sla2.alpha_logit):
+        return None
+    return SparseCore(self, self.bq, 64, None, False)
+
+
+SLA2CubeQATAttentionImpl.fused_core = property(_cube_fused_core)
+SLA2AttentionImpl.fused_core = property(_sla2_fused_core)

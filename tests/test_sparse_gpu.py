@@ -78,3 +78,59 @@ def test_sparse_forward_and_tangent(SP, int8, qblk, L):
     assert _rel(o2, o) < 5e-3
     from imfvideo_b200.ops import kernels
     kernels.check_status()
+
+
+@pytest.mark.parametrize("kind", ["sla2_jvp", "sla2_cube_qat"])
+def test_sla2_model_fused_core_vs_torch_formulas(SP, kind):
+    """Model with SLA2 attention: fused block node + sparse kernel vs the op-by-op
+    torch path (same routing, same INT8 grid)."""
+    from imfvideo_b200.config import preset
+    from imfvideo_b200.ops import cuda as cu
+    from imfvideo_b200.ops import kernels
+    from imfvideo_b200.ops.dual import Dual
+    from imfvideo_b200.train import build_model
+
+    cfg = preset("d256")
+    cfg.model.depth, cfg.model.aux_head_depth = 2, 1
+    cfg.model.attn_impl = kind
+    cfg.model.sla2_topk, cfg.model.sla2_bq, cfg.model.sla2_bk = 0.25, 128, 64
+    cfg.model.sla2_tile = (4, 4, 4)
+    cfg.data.latent_frames, cfg.data.latent_size = 8, (16, 32)      # grid (8, 8, 16) -> 16 tiles
+    torch.manual_seed(0)
+    net, _, _ = build_model(cfg)
+    net = net.cuda()
+    net.compute_dtype = torch.bfloat16
+    with torch.no_grad():
+        for p in net.parameters():
+            p.add_(torch.randn_like(p) * 0.03)
+    B = 1
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(B, 16, 8, 16, 32, device="cuda", generator=g)
+    dx = torch.randn(B, 16, 8, 16, 32, device="cuda", generator=g)
+    h = torch.rand(B, device="cuda", generator=g)
+    w = 1 + torch.rand(B, device="cuda", generator=g)
+    lo, hi = torch.zeros(B, device="cuda"), torch.ones(B, device="cuda")
+    y = torch.randint(0, 1000, (B,), device="cuda")
+
+    def run():
+        net.zero_grad()
+        out = net.forward_dual(Dual(x, dx), Dual(h, torch.ones_like(h)), w, lo, hi, y)
+        (out["u"].p.square().sum() + out["v"].p.square().sum()).backward()
+        return out, {n: p.grad.clone() for n, p in net.named_parameters() if p.grad is not None}
+
+    n0 = kernels.LAUNCHES.count
+    out_f, g_f = run()
+    kernels.check_status()
+    assert kernels.LAUNCHES.count - n0 > 20
+    cu.disable("block")
+    try:
+        out_g, g_g = run()
+    finally:
+        cu.enable("block")
+    assert _rel(out_f["u"].p, out_g["u"].p) < 5e-2 and _rel(out_f["v"].p, out_g["v"].p) < 5e-2
+    assert _rel(out_f["u"].t, out_g["u"].t) < 8e-2
+    al = [n for n in g_f if "alpha_logit" in n]
+    assert al and all(torch.isfinite(g_f[n]).all() for n in g_f)
+    bad = [(n, _rel(g_f[n], g_g[n])) for n in g_g if n in g_f and g_g[n].norm() > 0
+           and _rel(g_f[n], g_g[n]) > 0.15]
+    assert len(bad) <= 2, bad
