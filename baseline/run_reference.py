@@ -24,10 +24,13 @@ import time
 
 MODEL_KW = {
     "d256": dict(hidden_size=256, depth=12, aux_head_depth=4, num_heads=4, kv_lora_rank=128),
+    "d256_sla2": dict(hidden_size=256, depth=12, aux_head_depth=4, num_heads=4, kv_lora_rank=128,
+                      attn_impl="sla2_cube_qat", sla2_tile=(4, 4, 4), sla2_topk=0.10),
     "d1024": dict(hidden_size=1024, depth=24, aux_head_depth=4, num_heads=16, kv_lora_rank=512,
                   max_params=600_000_000),
 }
 DATA_KW = {"d256": dict(latent_frames=20, latent_size=(56, 104)),
+           "d256_sla2": dict(latent_frames=20, latent_size=(56, 104)),
            "d1024": dict(latent_frames=21, latent_size=(60, 104))}
 
 
@@ -52,7 +55,8 @@ def run(args, ref_dir, TOKENS, ClockSampler, L2Flush):
         setattr(cfg.model, k, v)
     for k, v in DATA_KW[args.config].items():
         setattr(cfg.data, k, v)
-    cfg.model.attn_impl = "sdpa_flash"
+    if "attn_impl" not in MODEL_KW[args.config]:
+        cfg.model.attn_impl = "sdpa_flash"
     cfg.loss.jvp_impl = "fast"
     cfg.loss.autocast_bf16 = True
     cfg.optim.warmup_steps = 0
@@ -155,7 +159,7 @@ def run(args, ref_dir, TOKENS, ClockSampler, L2Flush):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"model": f"reference IMFDiTVideo {args.config} attn=sdpa_flash jvp=fast "
+            "config": {"model": f"reference IMFDiTVideo {args.config} attn={cfg.model.attn_impl} jvp=fast "
                                 f"grad_checkpoint={cfg.model.grad_checkpoint}",
                        "global_batch": B * world, "seq_len": TOKENS[args.config],
                        "parallelism": f"dp{world} (flat fp32 NCCL all-reduce)"},

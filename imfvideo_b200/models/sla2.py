@@ -482,31 +482,49 @@ class SparseCore:
                 do = (a * do_s.float() + (1 - a) * do_l.permute(0, 2, 1, 3)).to(q.dtype).contiguous()
             if need_bwd and isinstance(self.mod, SLA2CubeQATAttentionImpl):
                 self.mod.logit_max_log2 = (lse.amax(dim=(0, 2)) * 1.4426950408889634).float()
-        return o, do, (sel,)
+        return o, do, (sel, lut, flags, o_s, lse)
 
     def bwd(self, q, k, v, o, saved, go, gv_out=None):
-        (sel,) = saved
+        """o = a o_s + (1 - a) o_l: the sparse branch goes through the block-sparse
+        backward kernel (S recomputed in bf16 from the fake-quantised operands with the
+        forward's LSE: straight-through), the linear branch and alpha through autograd
+        of the per-block-state formulas."""
+        from ..ops import kernels as K
+        from ..ops import sparse as SP
+
+        sel, lut, flags, o_s, lse = saved
         m = self.mod
-        alpha_param = m.alpha_logit if isinstance(m, SLA2CubeQATAttentionImpl) else m.sla2.alpha_logit
+        cube = isinstance(m, SLA2CubeQATAttentionImpl)
+        alpha_param = m.alpha_logit if cube else m.sla2.alpha_logit
+        B, L, H, D = q.shape
         with torch.enable_grad():
+            a_rows = (torch.sigmoid(alpha_param)[:, m.a_index] if cube else
+                      torch.sigmoid(alpha_param).repeat_interleave(m.bq, dim=-1)[:, :L])
             ql, kl, vl = (x.detach().permute(0, 2, 1, 3).float().requires_grad_(True)
                           for x in (q, k, v))
-            L = ql.shape[2]
-            if isinstance(m, SLA2CubeQATAttentionImpl):
-                a_rows = torch.sigmoid(alpha_param)[:, m.a_index]
-            else:
-                a_rows = torch.sigmoid(alpha_param).repeat_interleave(m.bq, dim=-1)[:, :L]
-            out = sparse_linear_attention(ql, kl, vl, sel, self.qblk, self.bk, a_rows,
-                                          n_comp_blocks=self.n_comp, int8=self.int8)
-            gq, gk, gv, ga = torch.autograd.grad(out, (ql, kl, vl, alpha_param),
-                                                 go.permute(0, 2, 1, 3).float())
+            o_l = linear_branch(ql, kl, vl, sel, self.qblk, self.bk, self.n_comp)
+            a = a_rows.t().reshape(1, L, H, 1)
+            gof = go.float()
+            mix = (a * o_s.float().detach() + (1 - a) * o_l.permute(0, 2, 1, 3))
+            gq_l, gk_l, gv_l, ga = torch.autograd.grad(mix, (ql, kl, vl, alpha_param), gof)
         alpha_param.grad = ga if alpha_param.grad is None else alpha_param.grad + ga
-        back = lambda t: t.permute(0, 2, 1, 3).to(q.dtype).contiguous()
-        gv_ = back(gv)
-        if gv_out is not None:
-            gv_out.copy_(gv_)
-            gv_ = gv_out
-        return back(gq), back(gk), gv_
+        with torch.no_grad():
+            g_os = (a.detach() * gof).to(q.dtype).contiguous()
+            qq, kk, vv = q, k, v
+            if self.int8:
+                _, _, qq = SP.quantize_blocks(K._tma_ok(q), self.qblk, want_q=False, want_fq=True)
+                _, _, kk = SP.quantize_blocks(K._tma_ok(k), 64, want_q=False, want_fq=True)
+                _, _, vv = SP.quantize_blocks(K._tma_ok(v), 64, want_q=False, want_fq=True)
+            qlist, qflags = SP.build_kv_lists(lut, flags, L)
+            gq_s, gk_s, gv_s = K.attn_bwd(qq, kk, vv, o_s, lse, g_os, qlist=qlist, qflags=qflags)
+            back = lambda t: t.permute(0, 2, 1, 3)
+            gq = (gq_s.float() + back(gq_l)).to(q.dtype)
+            gk = (gk_s.float() + back(gk_l)).to(q.dtype)
+            gv = (gv_s.float() + back(gv_l)).to(q.dtype)
+            if gv_out is not None:
+                gv_out.copy_(gv)
+                gv = gv_out
+        return gq, gk, gv
 
 
 def _cuda_sparse_ready(t: Tensor) -> bool:

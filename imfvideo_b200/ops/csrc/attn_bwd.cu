@@ -65,6 +65,12 @@ struct BwParams {
   int64_t dk_sb, dk_sl, dk_sh, dv_sb, dv_sl, dv_sh;
   float scale;
   int* status;
+  // block-sparse mode (null = dense): per K/V tile the list of query tiles that attend it
+  // (-1 terminated, at most qmax entries) and, per entry, 4 flag bits
+  // (kv half * 2 + q half) saying which 64 x 64 quadrants are live
+  const int* qlist;
+  const uint8_t* qflags;
+  int qmax;
 };
 
 IMF_DEVICE void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -88,7 +94,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                        ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int n_q = (p.L + BW_T - 1) / BW_T;
+  const size_t lrow = (((size_t)b * p.H + h) * gridDim.x + kvb) * (size_t)p.qmax;
+  const int* qlist = p.qlist ? p.qlist + lrow : nullptr;
+  const uint8_t* qflags = p.qflags ? p.qflags + lrow : nullptr;
+  int n_q = (p.L + BW_T - 1) / BW_T;
+  if (qlist) {
+    n_q = 0;
+    while (n_q < p.qmax && qlist[n_q] >= 0) ++n_q;
+  }
 
   if (threadIdx.x == 0) {
     mbar_init(&s.kv_full, 1);
@@ -138,11 +151,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               !mbar_wait(&s.q_empty[st], (uint32_t)(((i / BW_QSTAGES) - 1) & 1), abort_flag,
                          p.status, STATUS_TIMEOUT_EMPTY))
             break;
+          const int qt = qlist ? qlist[i] : i;
           mbar_arrive_expect_tx(&s.q_full[st], 2 * BW_T * 128 + 2 * BW_T * 4);
-          tma_load_4d(s.q[st], &tm_q, &s.q_full[st], 0, h, i * BW_T, b);
-          tma_load_4d(s.d_o[st], &tm_do, &s.q_full[st], 0, h, i * BW_T, b);
-          bulk_load_1d(s.lse2[st], lse_row + (size_t)i * BW_T, BW_T * 4, &s.q_full[st]);
-          bulk_load_1d(s.delta[st], dl_row + (size_t)i * BW_T, BW_T * 4, &s.q_full[st]);
+          tma_load_4d(s.q[st], &tm_q, &s.q_full[st], 0, h, qt * BW_T, b);
+          tma_load_4d(s.d_o[st], &tm_do, &s.q_full[st], 0, h, qt * BW_T, b);
+          bulk_load_1d(s.lse2[st], lse_row + (size_t)qt * BW_T, BW_T * 4, &s.q_full[st]);
+          bulk_load_1d(s.delta[st], dl_row + (size_t)qt * BW_T, BW_T * 4, &s.q_full[st]);
         }
       }
     } else if (warp == 12) {
@@ -162,7 +176,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mma_ss(tmem + BC_DP, sdesc_kmajor(va + ks * 32), sdesc_kmajor(doa + ks * 32), id_st, ks != 0);
           tc_commit(&s.s_full);
         };
-        bool ok = mbar_wait(&s.kv_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA) &&
+        bool ok = n_q > 0 &&      // a K/V tile that no query tile attends has zero gradients
+                  mbar_wait(&s.kv_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA) &&
                   mbar_wait(&s.q_full[0], 0, abort_flag, p.status, STATUS_TIMEOUT_TMA);
         if (ok) {
           tc_fence_after();
@@ -255,7 +270,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group"
               " [%0, {%2, %3, %4, %5}], [%1];"
               ::"l"(reinterpret_cast<uint64_t>(&tm_dq)),
-              "r"(smem_u32(stage + pnl * (BW_T * 128))), "r"(pnl * 32), "r"(h), "r"(i * BW_T), "r"(b)
+              "r"(smem_u32(stage + pnl * (BW_T * 128))), "r"(pnl * 32), "r"(h),
+              "r"((qlist ? qlist[i] : i) * BW_T), "r"(b)
               : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
@@ -302,6 +318,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!ok) break;
       }
       uint8_t* dsb = s.ds[i & 1] + wg * (BW_T * 128) + row * 128;
+      // block-sparse: this thread's 64 columns are one (kv half, q half) quadrant
+      const bool live = !qflags || ((qflags[i] >> ((row >> 6) * 2 + wg)) & 1);
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         uint32_t pk[16], dk_[16];
@@ -309,10 +327,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int c = 0; c < 32; c += 4) {
           const int cg = hh * 32 + c;
           const float4 l4 = lse4[cg / 4], d4 = dl4[cg / 4];
-          const float p0 = ex2(fmaf(__uint_as_float(sv[cg]), scale_log2, -l4.x));
-          const float p1 = ex2(fmaf(__uint_as_float(sv[cg + 1]), scale_log2, -l4.y));
-          const float p2 = ex2(fmaf(__uint_as_float(sv[cg + 2]), scale_log2, -l4.z));
-          const float p3 = ex2(fmaf(__uint_as_float(sv[cg + 3]), scale_log2, -l4.w));
+          float p0 = ex2(fmaf(__uint_as_float(sv[cg]), scale_log2, -l4.x));
+          float p1 = ex2(fmaf(__uint_as_float(sv[cg + 1]), scale_log2, -l4.y));
+          float p2 = ex2(fmaf(__uint_as_float(sv[cg + 2]), scale_log2, -l4.z));
+          float p3 = ex2(fmaf(__uint_as_float(sv[cg + 3]), scale_log2, -l4.w));
+          if (!live) p0 = p1 = p2 = p3 = 0.f;
           pk[c / 2] = pack_bf16(p0, p1);
           pk[c / 2 + 1] = pack_bf16(p2, p3);
           dk_[c / 2] = pack_bf16(p0 * (__uint_as_float(dp[cg]) - d4.x),
@@ -334,12 +353,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_arrive(&s.p_ready);
     }
     // ---- epilogue: WG0 stores dK (scaled), WG1 stores dV ----
-    if (ok) ok = mbar_wait(&s.final_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+    if (ok && n_q > 0) ok = mbar_wait(&s.final_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_MMA);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       tc_fence_after();
       const int kv_row = kvb * BW_T + row;
-      const float mul = wg == 0 ? p.scale : 1.f;
+      const float mul = n_q == 0 ? 0.f : (wg == 0 ? p.scale : 1.f);
       __nv_bfloat16* base =
           wg == 0 ? p.dk + (int64_t)b * p.dk_sb + (int64_t)kv_row * p.dk_sl + (int64_t)h * p.dk_sh
                   : p.dv + (int64_t)b * p.dv_sb + (int64_t)kv_row * p.dv_sl + (int64_t)h * p.dv_sh;
@@ -352,7 +371,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           uint32_t ob[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e)
-            ob[e] = pack_bf16(__uint_as_float(r[2 * e]) * mul, __uint_as_float(r[2 * e + 1]) * mul);
+            ob[e] = n_q == 0 ? 0u
+                             : pack_bf16(__uint_as_float(r[2 * e]) * mul,
+                                         __uint_as_float(r[2 * e + 1]) * mul);
           uint4* dst = reinterpret_cast<uint4*>(base + c);
 #pragma unroll
           for (int e = 0; e < 4; ++e)
@@ -438,7 +459,8 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
                             int L, int H, int head_dim, const int64_t* strides,
                             const int64_t* o_strides, const int64_t* dk_strides,
                             const int64_t* dv_strides, float scale, void* scratch,
-                            long scratch_bytes, int* status, void* stream) {
+                            long scratch_bytes, const int* qlist, const uint8_t* qflags, int qmax,
+                            int* status, void* stream) {
   using namespace imf;
   if (head_dim != BW_HD || B <= 0 || L <= 0 || H <= 0) return IMF_ERR_ARG;
   if (scratch == nullptr || scratch_bytes < imf_attn_bwd_scratch_bytes(B, L, H)) return IMF_ERR_ARG;
@@ -488,6 +510,9 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
   prm.dv_sb = dv_strides[0]; prm.dv_sl = dv_strides[1]; prm.dv_sh = dv_strides[2];
   prm.scale = scale;
   prm.status = status;
+  prm.qlist = qlist;
+  prm.qflags = qflags;
+  prm.qmax = qlist ? qmax : 0;
   const size_t smem = sizeof(BwSmem) + 1024;
   if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem) != cudaSuccess)

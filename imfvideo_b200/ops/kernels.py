@@ -176,15 +176,19 @@ def attn_fwd(q, k, v, dq=None, dk=None, dv=None, scale: Optional[float] = None,
 if _has("imf_attn_bwd"):
     _lib.imf_attn_bwd.restype = c_int
     _lib.imf_attn_bwd.argtypes = [c_void_p] * 9 + [c_int] * 4 + [c_void_p] * 4 + \
-        [c_float, c_void_p, ctypes.c_long, c_void_p, c_void_p]
+        [c_float, c_void_p, ctypes.c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
     _lib.imf_attn_bwd_scratch_bytes.restype = ctypes.c_long
     _lib.imf_attn_bwd_scratch_bytes.argtypes = [c_int, c_int, c_int]
 
 
 def attn_bwd(q, k, v, o, lse, go, scale: Optional[float] = None,
-             gv_out: Optional[torch.Tensor] = None):
+             gv_out: Optional[torch.Tensor] = None, qlist: Optional[torch.Tensor] = None,
+             qflags: Optional[torch.Tensor] = None):
     """(dq, dk, dv) of dense attention; ``gv_out`` lets dv land in a strided
-    view (e.g. the value band of the kv up-projection gradient)."""
+    view (e.g. the value band of the kv up-projection gradient).  With
+    ``qlist`` / ``qflags`` (see ``ops.sparse.build_kv_lists``) the same kernel
+    runs the block-sparse backward: each 128-row K/V tile walks only the query
+    tiles that attend it."""
     B, L, H, hd = q.shape
     scale = 1.0 / math.sqrt(hd) if scale is None else scale
     ts = [_tma_ok(t) for t in (q, k, v, go)]
@@ -206,7 +210,9 @@ def attn_bwd(q, k, v, o, lse, go, scale: Optional[float] = None,
                            _ptr(lse), _ptr(dq), _ptr(dk), _ptr(dv), B, L, H, hd,
                            ctypes.cast(arr, c_void_p), ctypes.cast(i3(o), c_void_p),
                            ctypes.cast(i3(dk), c_void_p), ctypes.cast(i3(dv), c_void_p),
-                           float(scale), _ptr(scr), nscr, _ptr(status_word(q.device)), _stream())
+                           float(scale), _ptr(scr), nscr, _ptr(qlist), _ptr(qflags),
+                           0 if qlist is None else qlist.shape[-1],
+                           _ptr(status_word(q.device)), _stream())
     _check(rc, "imf_attn_bwd")
     LAUNCHES.count += 3
     return dq, dk, dv

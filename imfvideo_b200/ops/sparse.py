@@ -107,3 +107,25 @@ def sparse_fwd(q, k, v, dq, dk, dv, lut, flags, qblk: int, int8: bool, quant_p: 
     K._check(rc, "imf_attn_sparse_fwd")
     K.LAUNCHES.count += 1
     return o, do, lse
+
+
+def build_kv_lists(lut: torch.Tensor, flags: torch.Tensor, L: int):
+    """Invert the query-tile LUT for the backward: for every 128-row K/V tile
+    (two 64-key blocks) the list of 128-row query tiles that attend it, with 4
+    flag bits per entry (bit = kv half * 2 + q half).  Returns
+    (qlist int32 (B,H,n_kvt,qmax) padded with -1, qflags uint8)."""
+    B, H, n_mt, tmax = lut.shape
+    n_kvt = -(-L // 128)
+    valid = lut >= 0
+    kb = torch.where(valid, lut, torch.zeros_like(lut)).long()
+    val = (flags.to(torch.int32) << (2 * (kb % 2)).to(torch.int32)) * valid.to(torch.int32)
+    F = torch.zeros(B, H, n_kvt, n_mt, dtype=torch.int32, device=lut.device)
+    mt = torch.arange(n_mt, device=lut.device).view(1, 1, n_mt, 1).expand(B, H, n_mt, tmax)
+    flat = (kb // 2) * n_mt + mt                        # index into (n_kvt * n_mt)
+    F.view(B, H, -1).scatter_add_(2, flat.reshape(B, H, -1), val.reshape(B, H, -1))
+    live = F > 0
+    qmax = int(live.sum(-1).max().item())
+    order = torch.argsort((~live).to(torch.int8), dim=-1, stable=True)[..., :qmax]
+    qf = torch.gather(F, -1, order)
+    ql = torch.where(qf > 0, order.to(torch.int32), torch.full_like(order, -1, dtype=torch.int32))
+    return ql.contiguous(), qf.to(torch.uint8).contiguous()

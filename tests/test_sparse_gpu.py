@@ -134,3 +134,30 @@ def test_sla2_model_fused_core_vs_torch_formulas(SP, kind):
     bad = [(n, _rel(g_f[n], g_g[n])) for n in g_g if n in g_f and g_g[n].norm() > 0
            and _rel(g_f[n], g_g[n]) > 0.15]
     assert len(bad) <= 2, bad
+
+
+@pytest.mark.parametrize("qblk,L", [(128, 640), (64, 583)])
+def test_sparse_backward_kernel(SP, qblk, L):
+    from imfvideo_b200.models import sla2 as S
+    from imfvideo_b200.ops import kernels
+
+    torch.manual_seed(L)
+    B, H, D = 1, 2, 64
+    mk = lambda: torch.randn(B, L, H, D, device="cuda").bfloat16()
+    q, k, v, go = mk(), mk(), mk(), mk()
+    Mb, Nb = -(-L // qblk), -(-L // 64)
+    T = max(2, Nb // 4)
+    sel = torch.stack([torch.stack([torch.randperm(Nb, device="cuda")[:T] for _ in range(Mb)])
+                       for _ in range(H)]).unsqueeze(0)
+    lut, flags = SP.build_tile_lut(sel, qblk)
+    o, _, lse = SP.sparse_fwd(q, k, v, None, None, None, lut, flags, qblk, False, quant_p=False)
+    qlist, qflags = SP.build_kv_lists(lut, flags, L)
+    dq, dk, dv = kernels.attn_bwd(q, k, v, o, lse, go, qlist=qlist, qflags=qflags)
+    ph = lambda t: t.permute(0, 2, 1, 3).float()
+    ql, kl, vl = (ph(t).requires_grad_(True) for t in (q, k, v))
+    a_rows = torch.ones(H, L, device="cuda")
+    _, o_s, _, _ = S.sparse_linear_attention(ql, kl, vl, sel, qblk, 64, a_rows, return_parts=True)
+    o_s.backward(ph(go))
+    for name, a, b in (("dq", dq, ql.grad), ("dk", dk, kl.grad), ("dv", dv, vl.grad)):
+        assert _rel(a.permute(0, 2, 1, 3), b) < 2e-2, (name, _rel(a.permute(0, 2, 1, 3), b))
+    kernels.check_status()
