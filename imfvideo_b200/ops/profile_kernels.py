@@ -1,0 +1,120 @@
+"""Launch one kernel of the library a few times on a chosen shape, for use
+under ``ncu`` (or for a quick CUDA-event timing without it).
+
+    python -m imfvideo_b200.ops.profile_kernels attn_fwd  --L 9472
+    python -m imfvideo_b200.ops.profile_kernels attn_jvp  --L 9472
+    python -m imfvideo_b200.ops.profile_kernels attn_bwd  --L 4736
+    python -m imfvideo_b200.ops.profile_kernels gemm      --M 58280 --N 528 --K 256
+    python -m imfvideo_b200.ops.profile_kernels sparse    --L 9472
+    python -m imfvideo_b200.ops.profile_kernels resnorm   --rows 29140
+
+Prints the CUDA-event time per launch (after warm-up, inputs larger than L2
+or L2 flushed between launches) and the achieved fraction of the measured
+peaks in MEASURED_PEAKS.json when that file is present.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+
+def _time(fn, iters: int, flush) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["attn_fwd", "attn_jvp", "attn_bwd", "gemm", "sparse",
+                                       "sparse_jvp", "resnorm"])
+    ap.add_argument("--L", type=int, default=9472)
+    ap.add_argument("--B", type=int, default=1)
+    ap.add_argument("--H", type=int, default=4)
+    ap.add_argument("--M", type=int, default=58280)
+    ap.add_argument("--N", type=int, default=528)
+    ap.add_argument("--K", type=int, default=256)
+    ap.add_argument("--rows", type=int, default=29140)
+    ap.add_argument("--iters", type=int, default=3)
+    args = ap.parse_args()
+    from . import cuda as cu
+
+    assert cu.available()
+    from . import kernels as K
+
+    dev = torch.device("cuda")
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = lambda: flush_buf.fill_(0)
+    B, L, H = args.B, args.L, args.H
+    mk = lambda: torch.randn(B, L, H, 64, device=dev).bfloat16()
+    flops = bytes_ = None
+    if args.kernel in ("attn_fwd", "attn_jvp", "attn_bwd"):
+        q, k, v, dq, dk, dv = (mk() for _ in range(6))
+        base = 4.0 * B * H * L * L * 64
+        if args.kernel == "attn_fwd":
+            fn, flops = (lambda: K.attn_fwd(q, k, v)), base
+        elif args.kernel == "attn_jvp":
+            fn, flops = (lambda: K.attn_fwd(q, k, v, dq, dk, dv)), 3 * base
+        else:
+            o, _, lse = K.attn_fwd(q, k, v)
+            fn, flops = (lambda: K.attn_bwd(q, k, v, o, lse, dq)), 2.5 * base
+    elif args.kernel == "gemm":
+        a = torch.randn(args.M, args.K, device=dev).bfloat16()
+        b = torch.randn(args.N, args.K, device=dev).bfloat16()
+        fn, flops = (lambda: K.gemm(a, b)), 2.0 * args.M * args.N * args.K
+        bytes_ = 2.0 * (args.M * args.K + args.N * args.K + args.M * args.N)
+    elif args.kernel in ("sparse", "sparse_jvp"):
+        from . import sparse as SP
+
+        q, k, v, dq, dk, dv = (mk() for _ in range(6))
+        Mb, Nb = -(-L // 64), -(-L // 64)
+        T = max(1, Nb // 10)
+        sel = torch.stack([torch.stack([torch.randperm(Nb, device=dev)[:T] for _ in range(Mb)])
+                           for _ in range(H)]).unsqueeze(0).expand(B, -1, -1, -1).contiguous()
+        lut, flags = SP.build_tile_lut(sel, 64)
+        tang = args.kernel == "sparse_jvp"
+        fn = lambda: SP.sparse_fwd(q, k, v, dq if tang else None, dk if tang else None,
+                                   dv if tang else None, lut, flags, 64, True, True)
+    else:
+        from . import rowops as R
+
+        rows, D = args.rows, 256
+        res = torch.randn(rows, D, device=dev)
+        y = torch.randn(rows, D, device=dev).bfloat16()
+        snaps = [torch.randn(rows, D, device=dev) for _ in range(3)]
+        gate, w, gain = (torch.randn(D, device=dev) for _ in range(3))
+        n, pf = torch.empty(rows, D, dtype=torch.bfloat16, device=dev), torch.empty(rows, D, device=dev)
+        fn = lambda: R.resnorm_fwd(res, None, y, None, gate, snaps, [None] * 3, w, gain, 1e-5, n,
+                                   None, pf, None)
+        bytes_ = rows * D * (4 * 5 + 2 + 2)
+    ms = _time(fn, args.iters, flush)
+    K.check_status()
+    line = {"kernel": args.kernel, "ms": ms}
+    peaks = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                         "MEASURED_PEAKS.json")
+    pk = json.load(open(peaks)) if os.path.exists(peaks) else {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0}
+    if flops:
+        line["tflops"] = flops / ms / 1e9
+        line["frac_of_measured_bf16"] = line["tflops"] / pk["bf16_tflops"]
+    if bytes_:
+        line["gbs"] = bytes_ / ms / 1e6
+        line["frac_of_measured_hbm"] = line["gbs"] / pk["hbm_gbs"]
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()
