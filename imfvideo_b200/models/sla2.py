@@ -466,6 +466,15 @@ class SparseCore:
         lut, flags = SP.build_tile_lut(sel, self.qblk)
         o_s, do_s, lse = SP.sparse_fwd(q, k, v, dq, dk, dv, lut, flags, self.qblk, self.int8,
                                        quant_p=self.int8, need_lse=True)
+        from ..ops import linattn as LA
+
+        if LA.AVAILABLE:
+            with torch.no_grad():
+                o, do, C = LA.forward(q, k, v, dq, dk, dv, o_s, do_s, sel, a_rows, self.qblk,
+                                      self.bk, self.n_comp)
+                if need_bwd and isinstance(self.mod, SLA2CubeQATAttentionImpl):
+                    self.mod.logit_max_log2 = (lse.amax(dim=(0, 2)) * 1.4426950408889634).float()
+            return o, do, (sel, lut, flags, o_s, lse, C if need_bwd else None)
         f = lambda a, b, c: linear_branch(a, b, c, sel, self.qblk, self.bk, self.n_comp)
         with torch.no_grad():
             if dq is not None:
@@ -482,7 +491,7 @@ class SparseCore:
                 do = (a * do_s.float() + (1 - a) * do_l.permute(0, 2, 1, 3)).to(q.dtype).contiguous()
             if need_bwd and isinstance(self.mod, SLA2CubeQATAttentionImpl):
                 self.mod.logit_max_log2 = (lse.amax(dim=(0, 2)) * 1.4426950408889634).float()
-        return o, do, (sel, lut, flags, o_s, lse)
+        return o, do, (sel, lut, flags, o_s, lse, None)
 
     def bwd(self, q, k, v, o, saved, go, gv_out=None):
         """o = a o_s + (1 - a) o_l: the sparse branch goes through the block-sparse
@@ -492,11 +501,13 @@ class SparseCore:
         from ..ops import kernels as K
         from ..ops import sparse as SP
 
-        sel, lut, flags, o_s, lse = saved
+        sel, lut, flags, o_s, lse, C = saved
         m = self.mod
         cube = isinstance(m, SLA2CubeQATAttentionImpl)
         alpha_param = m.alpha_logit if cube else m.sla2.alpha_logit
         B, L, H, D = q.shape
+        if C is not None:
+            return self._bwd_kernels(q, k, v, saved, go, gv_out, alpha_param, cube)
         with torch.enable_grad():
             a_rows = (torch.sigmoid(alpha_param)[:, m.a_index] if cube else
                       torch.sigmoid(alpha_param).repeat_interleave(m.bq, dim=-1)[:, :L])
@@ -525,6 +536,43 @@ class SparseCore:
                 gv_out.copy_(gv)
                 gv = gv_out
         return gq, gk, gv
+
+
+def _sparse_core_bwd_kernels(self, q, k, v, saved, go, gv_out, alpha_param, cube):
+    """Reverse mode with the linear branch on this library's kernels: row side first
+    (it produces the sparse branch's upstream gradient a*go), then the block-sparse
+    backward kernel, then the key side, which adds both branches."""
+    from ..ops import kernels as K
+    from ..ops import linattn as LA
+    from ..ops import sparse as SP
+
+    sel, lut, flags, o_s, lse, C = saved
+    m = self.mod
+    B, L, H, D = q.shape
+    with torch.no_grad():
+        a_rows = (torch.sigmoid(alpha_param)[:, m.a_index] if cube else
+                  torch.sigmoid(alpha_param).repeat_interleave(m.bq, dim=-1)[:, :L])
+        gq_l, gnum, gden, ga_row, g_os = LA.backward_rows(q, o_s, go, C, a_rows, self.qblk)
+        Mb = -(-L // self.qblk)
+        ga = F.pad(ga_row.sum(0), (0, Mb * self.qblk - L)).view(H, Mb, self.qblk).sum(-1)
+        if ga.shape[1] < alpha_param.shape[1]:
+            ga = F.pad(ga, (0, alpha_param.shape[1] - ga.shape[1]))
+        ga = ga.to(alpha_param.dtype)
+        alpha_param.grad = ga if alpha_param.grad is None else alpha_param.grad + ga
+        qq, kk, vv = q, k, v
+        if self.int8:
+            _, _, qq = SP.quantize_blocks(K._tma_ok(q), self.qblk, want_q=False, want_fq=True)
+            _, _, kk = SP.quantize_blocks(K._tma_ok(k), 64, want_q=False, want_fq=True)
+            _, _, vv = SP.quantize_blocks(K._tma_ok(v), 64, want_q=False, want_fq=True)
+        qlist, qflags = SP.build_kv_lists(lut, flags, L)
+        gq_s, gk_s, gv_s = K.attn_bwd(qq, kk, vv, o_s, lse, g_os, qlist=qlist, qflags=qflags)
+        gq = (gq_s.float() + gq_l).to(q.dtype)
+        gk, gv = LA.backward_kv(q, k, v, gnum, gden, sel, gk_s, gv_s, self.qblk, self.bk,
+                                self.n_comp, gv_out=gv_out)
+    return gq, gk, gv
+
+
+SparseCore._bwd_kernels = _sparse_core_bwd_kernels
 
 
 def _cuda_sparse_ready(t: Tensor) -> bool:

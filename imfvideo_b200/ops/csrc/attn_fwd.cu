@@ -10,23 +10,27 @@
 // flash-JVP kernel (reference models/flash_jvp_kernel.py:51-570,
 // models/triton_block_jvp.py:228-346) and the FA/SDPA primal forward.
 //
-// Work item = 256 query rows (two 128-row tiles that share every K/V tile) of
-// one (batch, head).  Warps 0-3 / 4-7: softmax + O-correction + epilogue of
-// tile 0 / 1 (one query row per thread, rows live in TMEM lanes); warp 8:
-// single-thread tcgen05.mma issuer; warp 9: TMA producer; warps 10-11 only
-// donate registers (setmaxnreg).  The two tiles ping-pong: while one tile's
-// softmax runs on the CUDA cores the tensor core works on the other tile.
-// P (and T) are written back to TMEM as bf16 over the S (dS) columns and are
-// the A operand of the second GEMM.  In the primal kernel V carries 16 extra
-// columns of ones, so the row sum l comes out of the tensor core as column 64
-// of O.  O is rescaled lazily (only when the running max grows by > 2^8).
+// Work item = NT 128-row query tiles that share every K/V tile, of one (batch,
+// head): NT = 3 tiles against 64-row K/V tiles in the primal kernel, 2 tiles
+// in the tangent kernel.  Warps 4t .. 4t+3: softmax + O-correction + epilogue
+// of tile t (one query row per thread, rows live in TMEM lanes); then one warp
+// with the single-thread tcgen05.mma issuer, one TMA producer warp and two
+// warps that only donate registers (setmaxnreg).  The tiles take turns: while
+// one tile's softmax runs on the CUDA cores the tensor core works on another.
+// The softmax warps are bound by instruction issue and dependency latency
+// (two of them per scheduler reach 0.43 instructions per cycle), which is why
+// the primal kernel keeps three tiles in flight.  P (and T) are written back
+// to TMEM as bf16 over the S (dS) columns and are the A operand of the second
+// GEMM.  In the primal kernel V carries 16 extra columns of ones, so the row
+// sum l comes out of the tensor core as column 64 of O.  O is rescaled lazily
+// (only when the running max grows by > 2^8).
 //
 // Scheduling: the grid is persistent (one CTA per SM).  The flattened
 // (item, K/V tile) iteration space is cut into equal contiguous shares, so an
 // item may be split between two neighbouring CTAs; such partial results
 // (un-normalised accumulators + running max) go to a scratch buffer and a
-// small second kernel merges them.  This removes the 3.08 -> 4 wave
-// quantisation that 456 equal items on 148 SMs would cost.
+// small second kernel merges them.  This removes the wave quantisation that
+// equal items on 148 SMs would cost (304 items = 2.05 waves at 29,140 rows).
 //
 // Tensors are (B, L, H, 64) bf16 with arbitrary 16-byte-aligned strides;
 // ragged L is handled by TMA zero fill + masking of the last K/V tile.
@@ -37,47 +41,71 @@ namespace imf {
 
 constexpr int ATT_HD = 64;
 constexpr int ATT_TILE_M = 128;
-constexpr int ATT_ITEM_M = 2 * ATT_TILE_M;
-constexpr int ATT_THREADS = 384;
-constexpr int ATT_STAGES = 3;
+#ifndef IMF_ATT_PRIMAL_NT
+#define IMF_ATT_PRIMAL_NT 3
+#endif
 
+// Work item = NT query tiles of 128 rows that share every K/V tile.
+//   tangent kernel : NT 2, K/V tiles of 64 rows, TMEM per tile S|dS|O|dO
+//   primal kernel  : NT 2, K/V tiles of 128 rows, row sum on the tensor core (ones column)
+//                    NT 3, K/V tiles of 64 rows, ones column
+//                    NT 4, K/V tiles of 64 rows, row sum in registers
+// More tiles in flight put more softmax warps on each scheduler (the softmax
+// warps are bound by instruction issue and dependency latency, not by a pipe).
 template <bool TANGENT>
 struct AttCfg {
-  static constexpr int BN = TANGENT ? 64 : 128;
+  static constexpr int NT = TANGENT ? 2 : IMF_ATT_PRIMAL_NT;
+  static constexpr int ITEM_M = NT * ATT_TILE_M;
+  static constexpr int BN = (TANGENT || NT > 2) ? 64 : 128;
   static constexpr int NQ = TANGENT ? 2 : 1;       // q + dq
   static constexpr int NKV = TANGENT ? 4 : 2;      // k, v (+ dk, dv)
-  static constexpr bool ONES = !TANGENT;           // row sum on the tensor core
+  static constexpr int STAGES = (!TANGENT && NT > 2) ? 4 : 3;
+  static constexpr bool ONES = !TANGENT && NT < 4; // row sum on the tensor core
   static constexpr int N_PV = ONES ? ATT_HD + 16 : ATT_HD;
+  static constexpr int SOFT_WARPS = 4 * NT;
+  static constexpr int WARP_MMA = SOFT_WARPS, WARP_TMA = SOFT_WARPS + 1;
+  // softmax warps + one warpgroup holding the MMA warp, the TMA warp and two warps that
+  // only donate registers (setmaxnreg is a warpgroup-wide instruction)
+  static constexpr int THREADS = (SOFT_WARPS + 4) * 32;
+  static constexpr int REG_SOFT = NT == 2 ? 216 : (NT == 3 ? 136 : 104);
+  static constexpr int REG_OTHER = NT == 2 ? 72 : (NT == 3 ? 104 : 64);
+  // setmaxnreg.inc draws from what the CTA was launched with (threads x registers per
+  // thread as compiled: 168 / 128 / 96 for 384 / 512 / 640 threads); a request beyond
+  // that pool blocks for ever
+  static constexpr int REG_LAUNCH = NT == 2 ? 168 : (NT == 3 ? 128 : 96);
+  static_assert(SOFT_WARPS * 32 * REG_SOFT + (THREADS - SOFT_WARPS * 32) * REG_OTHER <=
+                    THREADS * REG_LAUNCH, "register pool exceeded");
   // TMEM columns per query tile
   static constexpr int COL_S = 0;
   static constexpr int COL_DS = BN;
   static constexpr int COL_O = TANGENT ? 2 * BN : BN;
   static constexpr int COL_DO = COL_O + ATT_HD;    // tangent only
-  static constexpr int TILE_COLS = 256;
+  static constexpr int TILE_COLS = NT == 2 ? 256 : (NT == 3 ? 160 : 128);
   static constexpr int TMEM_COLS = 512;
+  static_assert(COL_O + (TANGENT ? 2 * ATT_HD : N_PV) <= TILE_COLS && NT * TILE_COLS <= 512, "");
   static constexpr int ACC = TANGENT ? 2 * ATT_HD : ATT_HD;   // fp32 accumulators per row
 };
 
-// scratch record of one half of a split item: [ATT_ITEM_M][ACC] accumulators,
+// scratch record of one half of a split item: [ITEM_M][ACC] accumulators,
 // then m, l, mu per row
 template <bool TANGENT>
 constexpr size_t att_part_floats() {
-  return (size_t)ATT_ITEM_M * (AttCfg<TANGENT>::ACC + 3);
+  return (size_t)AttCfg<TANGENT>::ITEM_M * (AttCfg<TANGENT>::ACC + 3);
 }
 
 template <bool TANGENT>
 struct AttSmem {
   using C = AttCfg<TANGENT>;
-  alignas(1024) uint8_t q[C::NQ][2][ATT_TILE_M * 128];               // [q|dq][tile]
-  alignas(1024) uint8_t kv[ATT_STAGES][C::NKV][C::BN * 128];         // k, v, dk, dv
+  alignas(1024) uint8_t q[C::NQ][C::NT][ATT_TILE_M * 128];           // [q|dq][tile]
+  alignas(1024) uint8_t kv[C::STAGES][C::NKV][C::BN * 128];          // k, v, dk, dv
   alignas(1024) uint8_t ones[C::ONES ? C::BN * 128 : 1024];          // bf16 1.0 panel
   uint64_t q_full, q_empty;
-  uint64_t kv_full[ATT_STAGES];
-  uint64_t kv_empty[ATT_STAGES];
-  uint64_t s_full[2];
-  uint64_t p_full[2];
-  uint64_t o_done[2];
-  uint64_t o_free[2];
+  uint64_t kv_full[C::STAGES];
+  uint64_t kv_empty[C::STAGES];
+  uint64_t s_full[C::NT];
+  uint64_t p_full[C::NT];
+  uint64_t o_done[C::NT];
+  uint64_t o_free[C::NT];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -125,7 +153,7 @@ __device__ __forceinline__ bool get_segment(const AttParams& p, int c, int G, in
 }
 
 template <bool TANGENT>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(AttCfg<TANGENT>::THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_dq,
                 const __grid_constant__ CUtensorMap tm_dk,
@@ -141,11 +169,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(&s.q_full, 1);
     mbar_init(&s.q_empty, 1);
-    for (int i = 0; i < ATT_STAGES; ++i) {
+    for (int i = 0; i < C::STAGES; ++i) {
       mbar_init(&s.kv_full[i], 1);
       mbar_init(&s.kv_empty[i], 1);
     }
-    for (int t = 0; t < 2; ++t) {
+    for (int t = 0; t < C::NT; ++t) {
       mbar_init(&s.s_full[t], 1);
       mbar_init(&s.p_full[t], ATT_TILE_M);
       mbar_init(&s.o_done[t], 1);
@@ -156,10 +184,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   if (C::ONES) {
     uint32_t* o32 = reinterpret_cast<uint32_t*>(s.ones);
-    for (int i = threadIdx.x; i < BN * 128 / 4; i += ATT_THREADS) o32[i] = 0x3f803f80u;  // bf16 1.0 x2
+    for (int i = threadIdx.x; i < BN * 128 / 4; i += C::THREADS) o32[i] = 0x3f803f80u;  // bf16 1.0 x2
     fence_proxy_async_smem();
   }
-  if (warp == 8) {
+  if (warp == C::WARP_MMA) {
     tmem_alloc(&s.tmem_base, C::TMEM_COLS);
     tmem_relinquish();
   }
@@ -169,9 +197,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem = s.tmem_base;
   volatile int* abort_flag = &s.abort_flag;
 
-  if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp == 9) {
+  if (warp >= C::SOFT_WARPS) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REG_OTHER));
+    if (warp == C::WARP_TMA) {
       // ---------------------------------------------------- TMA producer --
       if (elect_one()) {
         prefetch_tmap(&tm_q);
@@ -183,19 +211,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int si = 0; ok && get_segment(p, cta, G, si, sg); ++si) {
           const int qb = sg.item % p.n_qblk, h = (sg.item / p.n_qblk) % p.H,
                     b = sg.item / (p.n_qblk * p.H);
-          const int q0 = qb * ATT_ITEM_M;
+          const int q0 = qb * C::ITEM_M;
           if (si > 0) ok = mbar_wait(&s.q_empty, (si - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_EMPTY);
           if (!ok) break;
-          mbar_arrive_expect_tx(&s.q_full, C::NQ * 2 * ATT_TILE_M * 128);
-          for (int t = 0; t < 2; ++t) {
+          mbar_arrive_expect_tx(&s.q_full, C::NQ * C::NT * ATT_TILE_M * 128);
+          for (int t = 0; t < C::NT; ++t) {
             tma_load_4d(s.q[0][t], &tm_q, &s.q_full, 0, h, q0 + t * ATT_TILE_M, b);
             if (TANGENT)
               tma_load_4d(s.q[C::NQ - 1][t], &tm_dq, &s.q_full, 0, h, q0 + t * ATT_TILE_M, b);
           }
           for (int j = sg.j0; j < sg.j1; ++j, ++kv_it) {
-            const int st = (int)(kv_it % ATT_STAGES);
-            if (kv_it >= ATT_STAGES) {
-              ok = mbar_wait(&s.kv_empty[st], (uint32_t)((kv_it / ATT_STAGES) & 1) ^ 1, abort_flag,
+            const int st = (int)(kv_it % C::STAGES);
+            if (kv_it >= C::STAGES) {
+              ok = mbar_wait(&s.kv_empty[st], (uint32_t)((kv_it / C::STAGES) & 1) ^ 1, abort_flag,
                              p.status, STATUS_TIMEOUT_EMPTY);
               if (!ok) break;
             }
@@ -209,7 +237,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
-    } else if (warp == 8) {
+    } else if (warp == C::WARP_MMA) {
       // ------------------------------------------------------ MMA issuer --
       if (elect_one()) {
         constexpr uint32_t idesc_qk = idesc_bf16(ATT_TILE_M, BN, 0, 0);
@@ -267,16 +295,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int si = 0; ok && get_segment(p, cta, G, si, sg); ++si) {
           const int n_j = sg.j1 - sg.j0;
           ok = mbar_wait(&s.q_full, si & 1, abort_flag, p.status, STATUS_TIMEOUT_TMA) &&
-               mbar_wait(&s.kv_full[kv_it % ATT_STAGES], (uint32_t)((kv_it / ATT_STAGES) & 1),
+               mbar_wait(&s.kv_full[kv_it % C::STAGES], (uint32_t)((kv_it / C::STAGES) & 1),
                          abort_flag, p.status, STATUS_TIMEOUT_TMA);
           if (!ok) break;
           tc_fence_after();
-          issue_qk(0, (int)(kv_it % ATT_STAGES), &s.s_full[0]);
-          issue_qk(1, (int)(kv_it % ATT_STAGES), &s.s_full[1]);
+#pragma unroll
+          for (int t = 0; t < C::NT; ++t) issue_qk(t, (int)(kv_it % C::STAGES), &s.s_full[t]);
           if (n_j == 1) tc_commit(&s.q_empty);
           for (int jj = 0; jj < n_j && ok; ++jj, ++kv_it, ++it) {
-            const int st = (int)(kv_it % ATT_STAGES);
-            for (int t = 0; t < 2 && ok; ++t) {
+            const int st = (int)(kv_it % C::STAGES);
+#pragma unroll
+            for (int t = 0; t < C::NT; ++t) {
+              if (!ok) break;
               ok = mbar_wait(&s.p_full[t], (uint32_t)(it & 1), abort_flag, p.status,
                              STATUS_TIMEOUT_SOFTMAX);
               if (ok && jj == 0 && si > 0)   // epilogue of the previous segment has drained O
@@ -285,18 +315,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               if (!ok) break;
               tc_fence_after();
               issue_pv(t, st, jj == 0);
-              if (t == 1) tc_commit(&s.kv_empty[st]);
+              if (t == C::NT - 1) tc_commit(&s.kv_empty[st]);
               if (jj + 1 < n_j) {
                 const long nk = kv_it + 1;
-                const int st1 = (int)(nk % ATT_STAGES);
+                const int st1 = (int)(nk % C::STAGES);
                 if (t == 0) {
-                  ok = mbar_wait(&s.kv_full[st1], (uint32_t)((nk / ATT_STAGES) & 1), abort_flag,
+                  ok = mbar_wait(&s.kv_full[st1], (uint32_t)((nk / C::STAGES) & 1), abort_flag,
                                  p.status, STATUS_TIMEOUT_TMA);
                   if (!ok) break;
                   tc_fence_after();
                 }
                 issue_qk(t, st1, &s.s_full[t]);
-                if (t == 1 && jj + 2 == n_j) tc_commit(&s.q_empty);   // last Q read of the item
+                if (t == C::NT - 1 && jj + 2 == n_j) tc_commit(&s.q_empty);   // last Q read of the item
               }
             }
           }
@@ -305,7 +335,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else {
     // ------------------------------------- softmax / correction / epilogue --
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::REG_SOFT));
     const int t = warp >> 2;
     const int wl = warp & 3;
     const int row_in_item = t * ATT_TILE_M + wl * 32 + lane;
@@ -317,7 +347,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int si = 0; ok && get_segment(p, cta, G, si, sg); ++si) {
       const int qb = sg.item % p.n_qblk, h = (sg.item / p.n_qblk) % p.H,
                 b = sg.item / (p.n_qblk * p.H);
-      const int q_row = qb * ATT_ITEM_M + row_in_item;
+      const int q_row = qb * C::ITEM_M + row_in_item;
       float m_used = -INFINITY, l_sum = 0.f, l_sum2 = 0.f, mu_sum = 0.f, mu_sum2 = 0.f;
       for (int j = sg.j0; j < sg.j1 && ok; ++j, ++it) {
         ok = __all_sync(0xffffffffu, mbar_wait(&s.s_full[t], (uint32_t)(it & 1), abort_flag,
@@ -395,9 +425,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const float p0 = ex2(fmaf(__uint_as_float(sv[c + i]), scale_log2, neg_m));
             const float p1 = ex2(fmaf(__uint_as_float(sv[c + i + 1]), scale_log2, neg_m));
             pk[i / 2] = pack_bf16(p0, p1);
-            if (TANGENT) {
+            if (!C::ONES) {
               l_sum += p0;
               l_sum2 += p1;
+            }
+            if (TANGENT) {
               const float t0 = p0 * __uint_as_float(dsv[c + i]) * p.scale;
               const float t1 = p1 * __uint_as_float(dsv[c + i + 1]) * p.scale;
               mu_sum += t0;
@@ -485,10 +517,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             dst[i] = make_float4(__uint_as_float(ov[4 * i]), __uint_as_float(ov[4 * i + 1]),
                                  __uint_as_float(ov[4 * i + 2]), __uint_as_float(ov[4 * i + 3]));
         }
-        float* stats = part + (size_t)ATT_ITEM_M * C::ACC;
+        float* stats = part + (size_t)C::ITEM_M * C::ACC;
         stats[row_in_item] = m_used;
-        stats[ATT_ITEM_M + row_in_item] = l_tot;
-        stats[2 * ATT_ITEM_M + row_in_item] = mu_tot;
+        stats[C::ITEM_M + row_in_item] = l_tot;
+        stats[2 * C::ITEM_M + row_in_item] = mu_tot;
       }
       tc_fence_before();
       mbar_arrive(&s.o_free[t]);
@@ -496,7 +528,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_before();
   }
   __syncthreads();
-  if (warp == 8) {
+  if (warp == C::WARP_MMA) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem, C::TMEM_COLS);
@@ -505,7 +537,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
 // Merge the two halves of every split item (one CTA per share boundary).
 template <bool TANGENT>
-__global__ void __launch_bounds__(ATT_ITEM_M) attn_fwd_combine_kernel(const AttParams p, int G) {
+__global__ void __launch_bounds__(AttCfg<TANGENT>::ITEM_M) attn_fwd_combine_kernel(const AttParams p, int G) {
   using C = AttCfg<TANGENT>;
   const int c = blockIdx.x;              // boundary between CTA c and c + 1
   const long bound = (long)(c + 1) * p.total_iters / G;
@@ -514,18 +546,18 @@ __global__ void __launch_bounds__(ATT_ITEM_M) attn_fwd_combine_kernel(const AttP
   if (item >= p.n_items) return;
   const int qb = item % p.n_qblk, h = (item / p.n_qblk) % p.H, b = item / (p.n_qblk * p.H);
   const int r = threadIdx.x;
-  const int q_row = qb * ATT_ITEM_M + r;
+  const int q_row = qb * C::ITEM_M + r;
   if (q_row >= p.L) return;
   const float* pa = p.scratch + ((size_t)c * 2 + 0) * att_part_floats<TANGENT>();
   const float* pb = p.scratch + ((size_t)c * 2 + 1) * att_part_floats<TANGENT>();
-  const float* sa = pa + (size_t)ATT_ITEM_M * C::ACC;
-  const float* sb = pb + (size_t)ATT_ITEM_M * C::ACC;
+  const float* sa = pa + (size_t)C::ITEM_M * C::ACC;
+  const float* sb = pb + (size_t)C::ITEM_M * C::ACC;
   const float ma = sa[r], mb = sb[r];
   const float m = fmaxf(ma, mb);
   const float scale_log2 = p.scale * 1.4426950408889634f;
   const float wa = ex2((ma - m) * scale_log2), wb = ex2((mb - m) * scale_log2);
-  const float l = sa[ATT_ITEM_M + r] * wa + sb[ATT_ITEM_M + r] * wb;
-  const float mu = sa[2 * ATT_ITEM_M + r] * wa + sb[2 * ATT_ITEM_M + r] * wb;
+  const float l = sa[C::ITEM_M + r] * wa + sb[C::ITEM_M + r] * wb;
+  const float mu = sa[2 * C::ITEM_M + r] * wa + sb[2 * C::ITEM_M + r] * wb;
   const float inv_l = 1.f / l;
   const float* aa = pa + (size_t)r * C::ACC;
   const float* ab = pb + (size_t)r * C::ACC;
@@ -571,7 +603,7 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const vo
   CUtensorMap mq, mk, mv, mdq, mdk, mdv;
   int rc;
   const int B = prm.B, L = prm.L, H = prm.H;
-  prm.n_qblk = (L + ATT_ITEM_M - 1) / ATT_ITEM_M;
+  prm.n_qblk = (L + C::ITEM_M - 1) / C::ITEM_M;
   prm.n_items = prm.n_qblk * H * B;
   prm.n_kv = (L + C::BN - 1) / C::BN;
   prm.total_iters = (long)prm.n_items * prm.n_kv;
@@ -602,10 +634,10 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const vo
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return IMF_ERR_LAUNCH;
-  kern<<<G, ATT_THREADS, smem, stream>>>(mq, mk, mv, mdq, mdk, mdv, prm);
+  kern<<<G, C::THREADS, smem, stream>>>(mq, mk, mv, mdq, mdk, mdv, prm);
   if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   if (G > 1 && prm.n_items > G) {
-    attn_fwd_combine_kernel<TANGENT><<<G - 1, ATT_ITEM_M, 0, stream>>>(prm, G);
+    attn_fwd_combine_kernel<TANGENT><<<G - 1, C::ITEM_M, 0, stream>>>(prm, G);
     if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   }
   return IMF_OK;
@@ -616,7 +648,8 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const vo
 // Bytes of scratch the forward needs for (B, L, H): 0 when no item is split.
 extern "C" long imf_attn_fwd_scratch_bytes(int B, int L, int H, int tangent) {
   using namespace imf;
-  const int n_items = ((L + ATT_ITEM_M - 1) / ATT_ITEM_M) * H * B;
+  const int item_m = tangent ? AttCfg<true>::ITEM_M : AttCfg<false>::ITEM_M;
+  const int n_items = ((L + item_m - 1) / item_m) * H * B;
   const int G = att_grid(n_items);
   if (G <= 1 || n_items <= G) return 0;
   const size_t per = tangent ? att_part_floats<true>() : att_part_floats<false>();
@@ -666,7 +699,7 @@ extern "C" int imf_attn_fwd(const void* q, const void* k, const void* v, const v
 
 namespace imf {
 constexpr size_t NOALLOC_FLOATS =
-    (size_t)IMF_ATTN_NOALLOC_MAX_CTAS * 2 * ((size_t)ATT_ITEM_M * (ATT_HD + 3));
+    (size_t)IMF_ATTN_NOALLOC_MAX_CTAS * 2 * ((size_t)AttCfg<false>::ITEM_M * (ATT_HD + 3));
 // Split-item partials of the primal forward.  In host code this name is only a
 // stand-in for the symbol, not a device address: the address comes from
 // cudaGetSymbolAddress below.

@@ -16,7 +16,7 @@
 //  * primal forward only (no tangent), head_dim 64, bf16, same layouts as
 //    imf_attn_fwd;
 //  * the built-in scratch holds the partials of at most
-//    IMF_ATTN_NOALLOC_MAX_CTAS (160) thread blocks = 21,954,560 bytes; every
+//    IMF_ATTN_NOALLOC_MAX_CTAS (160) thread blocks = 32,931,840 bytes; every
 //    GPU that loads the library keeps that much reserved until the process
 //    exits.  A device with more SMs than that, for a problem that needs one
 //    partial slot per SM, is rejected with IMF_ERR_TOO_LARGE (-4);

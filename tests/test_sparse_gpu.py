@@ -161,3 +161,47 @@ def test_sparse_backward_kernel(SP, qblk, L):
     for name, a, b in (("dq", dq, ql.grad), ("dk", dk, kl.grad), ("dv", dv, vl.grad)):
         assert _rel(a.permute(0, 2, 1, 3), b) < 2e-2, (name, _rel(a.permute(0, 2, 1, 3), b))
     kernels.check_status()
+
+
+def test_linear_branch_kernels_match_formulas():
+    """Complement linear branch (states, mask product on the tcgen05 GEMM, apply, reverse
+    mode) against the fp32 formulas of models/sla2.py and their torch.func.jvp / autograd."""
+    from imfvideo_b200.models.sla2 import linear_branch
+    from imfvideo_b200.ops import linattn as LA
+
+    assert LA.AVAILABLE
+    torch.manual_seed(3)
+    dev = "cuda"
+    B, L, H, D, blk, T, n_comp = 2, 1000, 2, 64, 64, 3, 14
+    Mb = Nb = -(-L // blk)
+    mk = lambda: torch.randn(B, L, H, D, device=dev).bfloat16()
+    q, k, v, dq, dk, dv, o_s, do_s, go = (mk() for _ in range(9))
+    sel = torch.stack([torch.stack([torch.stack([torch.randperm(Nb, device=dev)[:T]
+                                                 for _ in range(Mb)]) for _ in range(H)])
+                       for _ in range(B)]).int()
+    logit = torch.randn(H, L, device=dev, requires_grad=True)
+    hp = lambda t: t.permute(0, 2, 1, 3).float()
+    f = lambda a, b, c: linear_branch(a, b, c, sel, blk, blk, n_comp)
+    o_l, do_l = torch.func.jvp(f, (hp(q), hp(k), hp(v)), (hp(dq), hp(dk), hp(dv)))
+    a4 = torch.sigmoid(logit).detach().t().reshape(1, L, H, 1)
+    o_ref = a4 * o_s.float() + (1 - a4) * o_l.permute(0, 2, 1, 3)
+    do_ref = a4 * do_s.float() + (1 - a4) * do_l.permute(0, 2, 1, 3)
+    a_rows = torch.sigmoid(logit).detach()
+    o, do, C = LA.forward(q, k, v, dq, dk, dv, o_s, do_s, sel, a_rows, blk, blk, n_comp)
+    rel = lambda x, y: ((x.float() - y.float()).norm() / y.float().norm()).item()
+    assert rel(o, o_ref) < 6e-3 and rel(do, do_ref) < 6e-3
+    o1, _, _ = LA.forward(q, k, v, None, None, None, o_s, None, sel, a_rows, blk, blk, n_comp)
+    assert torch.equal(o1, o)
+    # reverse mode
+    ql, kl, vl = (hp(t).requires_grad_(True) for t in (q, k, v))
+    al = torch.sigmoid(logit).t().reshape(1, L, H, 1)
+    mix = al * o_s.float() + (1 - al) * linear_branch(ql, kl, vl, sel, blk, blk, n_comp).permute(0, 2, 1, 3)
+    gq_r, gk_r, gv_r, gl_r = torch.autograd.grad(mix, (ql, kl, vl, logit), go.float())
+    gq_l, gnum, gden, ga_row, g_os = LA.backward_rows(q, o_s, go, C, a_rows, blk)
+    assert rel(gq_l, gq_r.permute(0, 2, 1, 3)) < 2e-3
+    assert rel(ga_row.sum(0), gl_r) < 2e-3
+    assert rel(g_os, a4 * go.float()) < 6e-3
+    zero = torch.zeros_like(q)
+    gk, gv = LA.backward_kv(q, k, v, gnum, gden, sel, zero, zero, blk, blk, n_comp)
+    assert rel(gk, gk_r.permute(0, 2, 1, 3)) < 6e-3
+    assert rel(gv, gv_r.permute(0, 2, 1, 3)) < 6e-3

@@ -49,7 +49,7 @@ def test_noalloc_entry_matches_regular_entry_twice():
     status = K.status_word(torch.device("cuda", 0))
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     for seed, (B, L, H) in enumerate([(1, 2100, 40), (2, 4000, 24)]):
-        assert B * H * math.ceil(L / 256) > sms       # items are split: the scratch is in use
+        assert B * H * math.ceil(L / 384) > sms       # items are split: the scratch is in use
         g = torch.Generator(device="cuda").manual_seed(seed)
         q, k, v = (torch.randn(B, L, H, 64, device="cuda", generator=g).bfloat16() for _ in range(3))
         o_ref, _, lse_ref = K.attn_fwd(q, k, v)
@@ -80,6 +80,6 @@ def test_noalloc_entry_rejects_oversize_request():
     assert rc == -1
     if sms <= 160:
         pytest.skip("this GPU never needs more partial slots than the built-in array holds")
-    big = torch.zeros(1, 256 * (sms + 1), 1, 64, dtype=torch.bfloat16, device="cuda")
+    big = torch.zeros(1, 384 * (sms + 1), 1, 64, dtype=torch.bfloat16, device="cuda")
     rc, _, _ = _call_noalloc(lib, big, big, big, status)
     assert rc == -4
