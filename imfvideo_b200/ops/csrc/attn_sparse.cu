@@ -15,9 +15,20 @@
 // models/sla2_vendor/kernel_sparse_qat.py:28-117, models/sla2_cube_qat.py:59-169,
 // models/sla2_mla_jvp.py:108-197); `imf_quantize_blocks` replaces `_quant_blocks`.
 //
-// CTA = one query tile.  Warps 0-3: softmax / correction / epilogue (one row
-// per thread), warp 4: tcgen05.mma issuer, warp 5: TMA producer.  TMEM use is
-// 256 columns, so two CTAs share an SM and overlap each other's phases.
+// A CTA runs NT independent query tiles side by side (4 in the primal kernel,
+// 1 with the tangent, where two CTAs share an SM): warps 4t .. 4t+3 are the
+// softmax / correction / epilogue warps of tile slot t (one row per thread),
+// one thread of the MMA warp issues every slot's tcgen05.mma stream and one
+// thread of the TMA warp loads every slot's K/V blocks, both by probing the
+// slots' barriers without blocking, so the slots never wait for one another.
+// Slots walk over the query tiles with a fixed stride (persistent grid).  The
+// softmax warps are bound by instruction issue and latency, so what matters is
+// how many of them each scheduler can pick from (four per scheduler) and how
+// few instructions an element costs: the de-quantisation scale and the softmax
+// scale are one FMA, the x127 of the QAT grid is folded into the exponent, the
+// rounding is a magic-number add, P is stored as the integer grid value (the
+// 1/127 cancels in O / l), and a 64-row half that does not attend a block
+// writes zeros without touching the scores.
 #include "common.cuh"
 #include "host_util.h"
 
@@ -26,33 +37,66 @@ namespace imf {
 constexpr int SP_HD = 64;
 constexpr int SP_M = 128;
 constexpr int SP_BK = 64;          // key block
-constexpr int SP_THREADS = 192;
-constexpr int SP_STAGES = 2;
 
-// TMEM columns
-constexpr int SC_S = 0, SC_DS = 64, SC_O = 128, SC_DO = 192;
+template <bool TANGENT, bool INT8>
+struct SpCfg {
+  static constexpr int NT = TANGENT ? 1 : 4;
+  static constexpr int STAGES = (!TANGENT && INT8) ? 3 : 2;   // K/V ring per slot (shared memory bound)
+  static constexpr bool NEED_QK = TANGENT || !INT8;     // bf16 q / k tiles are needed
+  static constexpr int SOFT_WARPS = 4 * NT;
+  static constexpr int WARP_MMA = SOFT_WARPS, WARP_TMA = SOFT_WARPS + 1;
+  // NT 4: one more warpgroup (MMA, TMA, two register donors); NT 1: MMA and TMA warps only
+  static constexpr int THREADS = NT == 1 ? 192 : (SOFT_WARPS + 4) * 32;
+  static constexpr int CTAS_PER_SM = NT == 1 ? 2 : 1;
+  static constexpr bool SETMAXNREG = NT > 1;
+  // 640 threads are launched with 96 registers each; setmaxnreg.inc draws from that pool only
+  static constexpr int REG_SOFT = 104, REG_OTHER = 64;
+  static_assert(!SETMAXNREG || SOFT_WARPS * 32 * REG_SOFT + 128 * REG_OTHER <= THREADS * 96, "");
+  // TMEM columns of one slot: S (P in place) | dS (T in place) | O | dO
+  static constexpr int SC_S = 0;
+  static constexpr int SC_DS = 64;
+  static constexpr int SC_O = TANGENT ? 128 : 64;
+  static constexpr int SC_DO = 192;
+  static constexpr int TILE_COLS = TANGENT ? 256 : 128;
+  static constexpr int TMEM_COLS = NT * TILE_COLS < 256 ? 256 : NT * TILE_COLS;
+  static constexpr int NQ = NEED_QK ? (TANGENT ? 2 : 1) : 0;          // q, dq (bf16)
+  static constexpr int NKV = 1 + (NEED_QK ? 1 : 0) + (TANGENT ? 2 : 0);   // v, k, dk, dv
+};
 
+template <bool TANGENT, bool INT8>
+struct SpSlot {
+  using C = SpCfg<TANGENT, INT8>;
+  alignas(1024) uint8_t q8[INT8 ? SP_M * 64 : 1024];           // int8, 64-byte rows, SWIZZLE_64B
+  alignas(1024) uint8_t q[C::NQ ? C::NQ : 1][C::NQ ? SP_M * 128 : 1024];
+  alignas(1024) uint8_t k8[C::STAGES][INT8 ? SP_BK * 64 : 1024];
+  alignas(1024) uint8_t kv[C::STAGES][C::NKV][SP_BK * 128];    // v, k, dk, dv (bf16)
+  uint64_t q_full, q_empty;
+  uint64_t kv_full[C::STAGES], kv_empty[C::STAGES];
+  uint64_t s_full, p_full, o_done, o_free;
+};
+
+template <bool TANGENT, bool INT8>
 struct SpSmem {
-  alignas(1024) uint8_t q8[SP_M * 64];                         // int8, 64-byte rows, SWIZZLE_64B
-  alignas(1024) uint8_t q[2][SP_M * 128];                      // q, dq (bf16)
-  alignas(1024) uint8_t k8[SP_STAGES][SP_BK * 64];
-  alignas(1024) uint8_t kv[SP_STAGES][4][SP_BK * 128];         // k, dk, v, dv (bf16)
-  uint64_t q_full;
-  uint64_t kv_full[SP_STAGES], kv_empty[SP_STAGES];
-  uint64_t s_full, p_full, o_done;
+  SpSlot<TANGENT, INT8> slot[SpCfg<TANGENT, INT8>::NT];
   uint32_t tmem_base;
   int abort_flag;
 };
+static_assert(sizeof(SpSmem<false, true>) + 1024 <= 232448 && sizeof(SpSmem<false, false>) + 1024 <= 232448 &&
+                  2 * (sizeof(SpSmem<true, true>) + 2048) <= 233472 &&
+                  2 * (sizeof(SpSmem<true, false>) + 2048) <= 233472,
+              "shared memory per CTA / per SM exceeded");
 
 struct SpParams {
   const int* lut;            // (B, H, n_mt, tmax) key-block ids, -1 = end of list
   const uint8_t* flags;      // (B, H, n_mt, tmax) bit0: rows 0-63 attend, bit1: rows 64-127
-  const float* q_scale;      // (B, H, n_qblk)  per 64-row... per `qblk` rows
+  const int* cnt;            // (B, H, n_mt) entries per list
+  const float* q_scale;      // (B, H, n_qblk)  per `qblk` rows
   const float* k_scale;      // (B, H, n_kblk)
   __nv_bfloat16* o;
   __nv_bfloat16* dout;
   float* lse;                // (B, H, L) natural log
   int B, H, L, n_mt, tmax, n_qblk, n_kblk, qblk;   // qblk: rows per query scale block (64 or 128)
+  int n_tiles;
   int64_t o_sb, o_sl, o_sh;
   float scale;
   int quant_p;               // quantise P to the 127-level grid
@@ -70,8 +114,25 @@ IMF_DEVICE uint64_t sdesc_kmajor_sw64(uint32_t smem_addr) {
   return d;
 }
 
+struct SpTile {
+  int mt, h, b, n_j;
+  const int* lut;
+  const uint8_t* flg;
+};
+IMF_DEVICE SpTile sp_tile(const SpParams& p, int ti) {
+  SpTile t;
+  t.mt = ti % p.n_mt;
+  t.h = (ti / p.n_mt) % p.H;
+  t.b = ti / (p.n_mt * p.H);
+  const size_t lrow = (size_t)ti * p.tmax;       // (b, h, mt) is the tile order
+  t.lut = p.lut + lrow;
+  t.flg = p.flags + lrow;
+  t.n_j = p.cnt[ti];
+  return t;
+}
+
 template <bool TANGENT, bool INT8>
-__global__ void __launch_bounds__(SP_THREADS, 2)
+__global__ void __launch_bounds__(SpCfg<TANGENT, INT8>::THREADS, SpCfg<TANGENT, INT8>::CTAS_PER_SM)
 attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
                        const __grid_constant__ CUtensorMap tm_k8,
                        const __grid_constant__ CUtensorMap tm_q,
@@ -80,33 +141,35 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
                        const __grid_constant__ CUtensorMap tm_dq,
                        const __grid_constant__ CUtensorMap tm_dk,
                        const __grid_constant__ CUtensorMap tm_dv, const SpParams p) {
+  using C = SpCfg<TANGENT, INT8>;
+  constexpr int NT = C::NT;
+  constexpr bool NEED_QK = C::NEED_QK;
+  constexpr int VI = 0, KI = 1, DKI = 2, DVI = 3;          // kv[stage][...]
   extern __shared__ uint8_t smem_raw[];
-  auto& s = *reinterpret_cast<SpSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                       ~uintptr_t(1023));
-  constexpr bool NEED_QK = TANGENT || !INT8;     // bf16 q / k tiles are needed
+  auto& s = *reinterpret_cast<SpSmem<TANGENT, INT8>*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int mt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int q0 = mt * SP_M;
-  const size_t lrow = (((size_t)b * p.H + h) * p.n_mt + mt) * p.tmax;
-  const int* lut = p.lut + lrow;
-  const uint8_t* flg = p.flags + lrow;
-  int n_j = 0;
-  while (n_j < p.tmax && lut[n_j] >= 0) ++n_j;
+  const int tile_stride = gridDim.x * NT;
 
   if (threadIdx.x == 0) {
-    mbar_init(&s.q_full, 1);
-    for (int i = 0; i < SP_STAGES; ++i) {
-      mbar_init(&s.kv_full[i], 1);
-      mbar_init(&s.kv_empty[i], 1);
+    for (int t = 0; t < NT; ++t) {
+      auto& sl = s.slot[t];
+      mbar_init(&sl.q_full, 1);
+      mbar_init(&sl.q_empty, 1);
+      for (int i = 0; i < C::STAGES; ++i) {
+        mbar_init(&sl.kv_full[i], 1);
+        mbar_init(&sl.kv_empty[i], 1);
+      }
+      mbar_init(&sl.s_full, 1);
+      mbar_init(&sl.p_full, 4);        // one arrival per softmax warp
+      mbar_init(&sl.o_done, 1);
+      mbar_init(&sl.o_free, 4);
     }
-    mbar_init(&s.s_full, 1);
-    mbar_init(&s.p_full, SP_M);
-    mbar_init(&s.o_done, 1);
     s.abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4) {
-    tmem_alloc(&s.tmem_base, 256);
+  if (warp == C::WARP_MMA) {
+    tmem_alloc(&s.tmem_base, C::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -114,206 +177,396 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
   tc_fence_after();
   const uint32_t tmem = s.tmem_base;
   volatile int* abort_flag = &s.abort_flag;
-  constexpr int VI = 2;                    // kv[stage] = {k, dk, v, dv}
 
-  if (warp == 5) {
-    if (elect_one()) {
-      mbar_arrive_expect_tx(&s.q_full, (INT8 ? SP_M * 64 : 0) + (NEED_QK ? SP_M * 128 : 0) +
-                                           (TANGENT ? SP_M * 128 : 0));
-      if (INT8) tma_load_4d(s.q8, &tm_q8, &s.q_full, 0, h, q0, b);
-      if (NEED_QK) tma_load_4d(s.q[0], &tm_q, &s.q_full, 0, h, q0, b);
-      if (TANGENT) tma_load_4d(s.q[1], &tm_dq, &s.q_full, 0, h, q0, b);
-      for (int j = 0; j < n_j; ++j) {
-        const int st = j % SP_STAGES;
-        if (j >= SP_STAGES &&
-            !mbar_wait(&s.kv_empty[st], (uint32_t)(((j / SP_STAGES) - 1) & 1), abort_flag, p.status,
-                       STATUS_TIMEOUT_EMPTY))
-          break;
-        const int k0 = lut[j] * SP_BK;
-        mbar_arrive_expect_tx(&s.kv_full[st], (INT8 ? SP_BK * 64 : 0) +
-                                                  (1 + (NEED_QK ? 1 : 0) + (TANGENT ? 2 : 0)) * SP_BK * 128);
-        if (INT8) tma_load_4d(s.k8[st], &tm_k8, &s.kv_full[st], 0, h, k0, b);
-        tma_load_4d(s.kv[st][VI], &tm_v, &s.kv_full[st], 0, h, k0, b);
-        if (NEED_QK) tma_load_4d(s.kv[st][0], &tm_k, &s.kv_full[st], 0, h, k0, b);
-        if (TANGENT) {
-          tma_load_4d(s.kv[st][1], &tm_dk, &s.kv_full[st], 0, h, k0, b);
-          tma_load_4d(s.kv[st][3], &tm_dv, &s.kv_full[st], 0, h, k0, b);
+  if (warp >= C::SOFT_WARPS) {
+    if (C::SETMAXNREG) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REG_OTHER));
+    // The TMA producer and the MMA issuer are one thread each for ALL slots: a loop that
+    // probes every slot's barriers without blocking (mbarrier.test_wait) and serves whichever
+    // slot is ready, so that no slot's wait holds up another slot's work.
+    if (warp == C::WARP_TMA && elect_one()) {
+      // ------------------------------------------------------- TMA producer --
+      int ti[NT] = {}, n_j[NT] = {}, jj[NT] = {}, kbn[NT] = {}, hq[NT] = {}, bq[NT] = {};
+      uint32_t kv_it[NT], qn[NT];
+      bool q_sent[NT];
+      const int* lutp[NT];
+      int n_active = 0;
+      auto open_tile = [&](int t) {      // skip tiles with empty lists, read the first entry
+        while (ti[t] < p.n_tiles) {
+          const SpTile tl = sp_tile(p, ti[t]);
+          if (tl.n_j > 0) {
+            n_j[t] = tl.n_j; jj[t] = 0; lutp[t] = tl.lut; kbn[t] = tl.lut[0];
+            hq[t] = tl.h; bq[t] = tl.b; q_sent[t] = false;
+            return;
+          }
+          ti[t] += tile_stride;
+        }
+        n_j[t] = 0;
+      };
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        ti[t] = blockIdx.x * NT + t; kv_it[t] = 0; qn[t] = 0;
+        open_tile(t);
+        n_active += n_j[t] > 0;
+      }
+      uint32_t spins = 0;
+      uint64_t t_start = globaltimer_ns();
+      while (n_active > 0) {
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          if (n_j[t] == 0) continue;
+          auto& sl = s.slot[t];
+          if (!q_sent[t]) {
+            if (qn[t] > 0 && !mbar_test(&sl.q_empty, (qn[t] - 1) & 1)) continue;
+            const int q0 = (ti[t] % p.n_mt) * SP_M;
+            mbar_arrive_expect_tx(&sl.q_full, (INT8 ? SP_M * 64 : 0) + C::NQ * SP_M * 128);
+            if (INT8) tma_load_4d(sl.q8, &tm_q8, &sl.q_full, 0, hq[t], q0, bq[t]);
+            if (NEED_QK) tma_load_4d(sl.q[0], &tm_q, &sl.q_full, 0, hq[t], q0, bq[t]);
+            if (TANGENT) tma_load_4d(sl.q[C::NQ - 1], &tm_dq, &sl.q_full, 0, hq[t], q0, bq[t]);
+            q_sent[t] = true;
+          }
+          const int st = kv_it[t] % C::STAGES;
+          if (kv_it[t] >= C::STAGES &&
+              !mbar_test(&sl.kv_empty[st], ((kv_it[t] / C::STAGES) - 1) & 1))
+            continue;
+          const int k0 = kbn[t] * SP_BK;
+          mbar_arrive_expect_tx(&sl.kv_full[st], (INT8 ? SP_BK * 64 : 0) + C::NKV * SP_BK * 128);
+          if (INT8) tma_load_4d(sl.k8[st], &tm_k8, &sl.kv_full[st], 0, hq[t], k0, bq[t]);
+          tma_load_4d(sl.kv[st][VI], &tm_v, &sl.kv_full[st], 0, hq[t], k0, bq[t]);
+          if (NEED_QK) tma_load_4d(sl.kv[st][KI], &tm_k, &sl.kv_full[st], 0, hq[t], k0, bq[t]);
+          if (TANGENT) {
+            tma_load_4d(sl.kv[st][DKI], &tm_dk, &sl.kv_full[st], 0, hq[t], k0, bq[t]);
+            tma_load_4d(sl.kv[st][DVI], &tm_dv, &sl.kv_full[st], 0, hq[t], k0, bq[t]);
+          }
+          ++kv_it[t];
+          spins = 0;
+          if (++jj[t] < n_j[t]) {
+            kbn[t] = lutp[t][jj[t]];           // in flight until this slot's next turn
+          } else {
+            ++qn[t];
+            ti[t] += tile_stride;
+            open_tile(t);
+            n_active -= n_j[t] == 0;
+          }
+        }
+        if ((++spins & 1023u) == 0) {
+          if (*abort_flag) break;
+          if (spins == 1024u) t_start = globaltimer_ns();
+          else if (globaltimer_ns() - t_start > IMF_WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            if (p.status) atomicCAS(p.status, 0, STATUS_TIMEOUT_EMPTY);
+            break;
+          }
         }
       }
-    }
-  } else if (warp == 4) {
-    if (elect_one()) {
+    } else if (warp == C::WARP_MMA && elect_one()) {
+      // --------------------------------------------------------- MMA issuer --
       // s32 accumulate, signed 8-bit operands, both K-major
       constexpr uint32_t id_i8 = make_idesc(SP_M, SP_BK, FMT_S8, FMT_S8, 2, 0, 0);
       constexpr uint32_t id_qk = idesc_bf16(SP_M, SP_BK, 0, 0);
       constexpr uint32_t id_pv = idesc_bf16(SP_M, SP_HD, 0, 1);
-      bool ok = mbar_wait(&s.q_full, 0, abort_flag, p.status, STATUS_TIMEOUT_TMA);
-      for (int j = 0; j < n_j && ok; ++j) {
-        const int st = j % SP_STAGES;
-        ok = mbar_wait(&s.kv_full[st], (uint32_t)((j / SP_STAGES) & 1), abort_flag, p.status,
-                       STATUS_TIMEOUT_TMA);
-        if (!ok) break;
-        tc_fence_after();
-        // S (s32) = Q8 K8^T : K = 64 int8 = two k-steps of 32 bytes
-        if (INT8) {
-          const uint32_t q8a = smem_u32(s.q8), k8a = smem_u32(s.k8[st]);
-#pragma unroll
-          for (int ks = 0; ks < 2; ++ks)
-            mma_ss_i8(tmem + SC_S, sdesc_kmajor_sw64(q8a + ks * 32),
-                      sdesc_kmajor_sw64(k8a + ks * 32), id_i8, ks != 0);
-        } else {
-          const uint32_t qa = smem_u32(s.q[0]), ka = smem_u32(s.kv[st][0]);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_ss(tmem + SC_S, sdesc_kmajor(qa + ks * 32), sdesc_kmajor(ka + ks * 32), id_qk,
-                   ks != 0);
+      int ti[NT] = {}, n_j[NT] = {}, jj[NT] = {};
+      uint32_t kv_it[NT], step[NT], qn[NT];
+      bool want_pv[NT];
+      int n_active = 0;
+      auto open_tile = [&](int t) {
+        while (ti[t] < p.n_tiles) {
+          const int n = p.cnt[ti[t]];
+          if (n > 0) {
+            n_j[t] = n; jj[t] = 0; want_pv[t] = false;
+            return;
+          }
+          ti[t] += tile_stride;
         }
-        if (TANGENT) {
-          const uint32_t qa = smem_u32(s.q[0]), dqa = smem_u32(s.q[1]);
-          const uint32_t ka = smem_u32(s.kv[st][0]), dka = smem_u32(s.kv[st][1]);
+        n_j[t] = 0;
+      };
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_ss(tmem + SC_DS, sdesc_kmajor(dqa + ks * 32), sdesc_kmajor(ka + ks * 32), id_qk,
-                   ks != 0);
+      for (int t = 0; t < NT; ++t) {
+        ti[t] = blockIdx.x * NT + t; kv_it[t] = 0; step[t] = 0; qn[t] = 0;
+        open_tile(t);
+        n_active += n_j[t] > 0;
+      }
+      uint32_t spins = 0;
+      uint64_t t_start = globaltimer_ns();
+      while (n_active > 0) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_ss(tmem + SC_DS, sdesc_kmajor(qa + ks * 32), sdesc_kmajor(dka + ks * 32), id_qk, 1);
+        for (int t = 0; t < NT; ++t) {
+          if (n_j[t] == 0) continue;
+          auto& sl = s.slot[t];
+          const uint32_t tb = tmem + t * C::TILE_COLS;
+          const int st = kv_it[t] % C::STAGES;
+          if (!want_pv[t]) {
+            if (jj[t] == 0 && !mbar_test(&sl.q_full, qn[t] & 1)) continue;
+            if (!mbar_test(&sl.kv_full[st], (kv_it[t] / C::STAGES) & 1)) continue;
+            tc_fence_after();
+            // S (s32) = Q8 K8^T : K = 64 int8 = two k-steps of 32 bytes
+            if (INT8) {
+              const uint32_t q8a = smem_u32(sl.q8), k8a = smem_u32(sl.k8[st]);
+#pragma unroll
+              for (int ks = 0; ks < 2; ++ks)
+                mma_ss_i8(tb + C::SC_S, sdesc_kmajor_sw64(q8a + ks * 32),
+                          sdesc_kmajor_sw64(k8a + ks * 32), id_i8, ks != 0);
+            } else {
+              const uint32_t qa = smem_u32(sl.q[0]), ka = smem_u32(sl.kv[st][KI]);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks)
+                mma_ss(tb + C::SC_S, sdesc_kmajor(qa + ks * 32), sdesc_kmajor(ka + ks * 32), id_qk,
+                       ks != 0);
+            }
+            if (TANGENT) {
+              const uint32_t qa = smem_u32(sl.q[0]), dqa = smem_u32(sl.q[C::NQ - 1]);
+              const uint32_t ka = smem_u32(sl.kv[st][KI]), dka = smem_u32(sl.kv[st][DKI]);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks)
+                mma_ss(tb + C::SC_DS, sdesc_kmajor(dqa + ks * 32), sdesc_kmajor(ka + ks * 32),
+                       id_qk, ks != 0);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks)
+                mma_ss(tb + C::SC_DS, sdesc_kmajor(qa + ks * 32), sdesc_kmajor(dka + ks * 32),
+                       id_qk, 1);
+            }
+            tc_commit(&sl.s_full);
+            if (jj[t] == n_j[t] - 1) tc_commit(&sl.q_empty);      // last read of this tile's Q
+            want_pv[t] = true;
+            spins = 0;
+          } else {
+            if (!mbar_test(&sl.p_full, step[t] & 1)) continue;
+            // first PV of a tile overwrites O: the previous tile's epilogue must have read it
+            if (jj[t] == 0 && qn[t] > 0 && !mbar_test(&sl.o_free, (qn[t] - 1) & 1)) continue;
+            tc_fence_after();
+            const uint32_t va = smem_u32(sl.kv[st][VI]);
+            const int j0 = jj[t];
+#pragma unroll
+            for (int ks = 0; ks < SP_BK / 16; ++ks)
+              mma_ts(tb + C::SC_O, tb + C::SC_S + ks * 8,
+                     sdesc_mnmajor(va + ks * 2048, SP_BK * 128), id_pv, (j0 | ks) != 0);
+            if (TANGENT) {
+              const uint32_t dva = smem_u32(sl.kv[st][DVI]);
+#pragma unroll
+              for (int ks = 0; ks < SP_BK / 16; ++ks)
+                mma_ts(tb + C::SC_DO, tb + C::SC_DS + ks * 8,
+                       sdesc_mnmajor(va + ks * 2048, SP_BK * 128), id_pv, (j0 | ks) != 0);
+#pragma unroll
+              for (int ks = 0; ks < SP_BK / 16; ++ks)
+                mma_ts(tb + C::SC_DO, tb + C::SC_S + ks * 8,
+                       sdesc_mnmajor(dva + ks * 2048, SP_BK * 128), id_pv, 1);
+            }
+            tc_commit(&sl.o_done);
+            tc_commit(&sl.kv_empty[st]);
+            want_pv[t] = false;
+            spins = 0;
+            ++kv_it[t];
+            ++step[t];
+            if (++jj[t] == n_j[t]) {
+              ++qn[t];
+              ti[t] += tile_stride;
+              open_tile(t);
+              n_active -= n_j[t] == 0;
+            }
+          }
         }
-        tc_commit(&s.s_full);
-        ok = mbar_wait(&s.p_full, (uint32_t)(j & 1), abort_flag, p.status, STATUS_TIMEOUT_SOFTMAX);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t va = smem_u32(s.kv[st][VI]);
-#pragma unroll
-        for (int ks = 0; ks < SP_BK / 16; ++ks)
-          mma_ts(tmem + SC_O, tmem + SC_S + ks * 8, sdesc_mnmajor(va + ks * 2048, SP_BK * 128),
-                 id_pv, (j | ks) != 0);
-        if (TANGENT) {
-          const uint32_t dva = smem_u32(s.kv[st][3]);
-#pragma unroll
-          for (int ks = 0; ks < SP_BK / 16; ++ks)
-            mma_ts(tmem + SC_DO, tmem + SC_DS + ks * 8, sdesc_mnmajor(va + ks * 2048, SP_BK * 128),
-                   id_pv, (j | ks) != 0);
-#pragma unroll
-          for (int ks = 0; ks < SP_BK / 16; ++ks)
-            mma_ts(tmem + SC_DO, tmem + SC_S + ks * 8, sdesc_mnmajor(dva + ks * 2048, SP_BK * 128),
-                   id_pv, 1);
+        if ((++spins & 1023u) == 0) {
+          if (*abort_flag) break;
+          if (spins == 1024u) t_start = globaltimer_ns();
+          else if (globaltimer_ns() - t_start > IMF_WAIT_LIMIT_NS) {
+            *abort_flag = 1;
+            if (p.status) atomicCAS(p.status, 0, STATUS_TIMEOUT_MMA);
+            break;
+          }
         }
-        tc_commit(&s.o_done);
-        tc_commit(&s.kv_empty[st]);
       }
     }
   } else {
-    const int row = warp * 32 + lane;
-    const int half = row >> 6;
-    const int q_row = q0 + row;
-    const uint32_t tb = tmem_addr(tmem, warp * 32, 0);
+    // --------------------------------------- softmax / correction / epilogue --
+    if (C::SETMAXNREG) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::REG_SOFT));
+    const int t = warp >> 2, wl = warp & 3;
+    auto& sl = s.slot[t];
+    const int row = wl * 32 + lane;
+    const int half = wl >> 1;                      // warp-uniform
+    const uint32_t tb = tmem_addr(tmem, wl * 32, t * C::TILE_COLS);
     const float scale_log2 = p.scale * 1.4426950408889634f;
-    const int qb_idx = q_row / p.qblk;
-    const float sq = p.q_scale[((size_t)b * p.H + h) * p.n_qblk + (qb_idx < p.n_qblk ? qb_idx : p.n_qblk - 1)];
-    const float* ksc = p.k_scale + ((size_t)b * p.H + h) * p.n_kblk;
-    float m_used = -INFINITY, l_sum = 0.f, l_sum2 = 0.f, mu_sum = 0.f, mu_sum2 = 0.f;
+    // with the QAT grid, 127 * 2^x = 2^(x + log2 127) and P is stored as the integer grid value
+    const float grid_log2 = p.quant_p ? 6.9886846867721655f : 0.f;
+    uint32_t step = 0;
     bool ok = true;
-    for (int j = 0; j < n_j && ok; ++j) {
-      ok = __all_sync(0xffffffffu, mbar_wait(&s.s_full, (uint32_t)(j & 1), abort_flag, p.status,
-                                             STATUS_TIMEOUT_MMA));
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t sv[SP_BK];
-      tmem_ld32(tb + SC_S, sv);
-      tmem_ld32(tb + SC_S + 32, sv + 32);
-      uint32_t dsv[TANGENT ? SP_BK : 1];
-      if (TANGENT) {
-        tmem_ld32(tb + SC_DS, dsv);
-        tmem_ld32(tb + SC_DS + 32, dsv + 32);
-      }
-      tc_wait_ld();
-      const int kb = lut[j];
-      const bool attend = (flg[j] >> half) & 1;
-      const int kv_rem = p.L - kb * SP_BK;
-      const float deq = INT8 ? sq * ksc[kb] : 1.f;   // s32 -> real score (before the softmax scale)
-      float mx = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < SP_BK; ++i) {
-        float x = INT8 ? static_cast<float>(static_cast<int>(sv[i])) * deq : __uint_as_float(sv[i]);
-        if (!attend || i >= kv_rem) x = -INFINITY;
-        sv[i] = __float_as_uint(x);
-        mx = fmaxf(mx, x);
-      }
-      if (j == 0) {
-        m_used = mx;
-      } else {
-        // with the QAT grid on P the running max is tracked exactly (P <= 1), otherwise
-        // lazily; both tests are false for NaN (-inf - -inf)
-        const bool need = p.quant_p ? (mx > m_used) : ((mx - m_used) * scale_log2 > 8.0f);
-        if (__any_sync(0xffffffffu, need)) {
-          float alpha = 1.f;
-          if (need) {
-            alpha = ex2((m_used - mx) * scale_log2);             // 0 when m_used == -inf
-            m_used = mx;
+    for (int ti = blockIdx.x * NT + t; ti < p.n_tiles && ok; ti += tile_stride) {
+      const SpTile tl = sp_tile(p, ti);
+      const int q_row = tl.mt * SP_M + row;
+      const bool live = q_row < p.L;
+      const int64_t off = (int64_t)tl.b * p.o_sb + (int64_t)q_row * p.o_sl + (int64_t)tl.h * p.o_sh;
+      if (tl.n_j == 0) {                           // no key block at all: zero output
+        if (live) {
+          for (int c = 0; c < SP_HD; c += 8) {
+            *reinterpret_cast<uint4*>(p.o + off + c) = make_uint4(0, 0, 0, 0);
+            if (TANGENT) *reinterpret_cast<uint4*>(p.dout + off + c) = make_uint4(0, 0, 0, 0);
           }
-          l_sum *= alpha; l_sum2 *= alpha; mu_sum *= alpha; mu_sum2 *= alpha;
-          ok = __all_sync(0xffffffffu, mbar_wait(&s.o_done, (uint32_t)((j - 1) & 1), abort_flag,
-                                                 p.status, STATUS_TIMEOUT_MMA));
-          if (!ok) break;
-          tc_fence_after();
+          if (p.lse) p.lse[((int64_t)tl.b * p.H + tl.h) * p.L + q_row] = -INFINITY;
+        }
+        continue;
+      }
+      const int qb_idx = q_row / p.qblk;
+      const float sq = INT8 ? p.q_scale[((size_t)tl.b * p.H + tl.h) * p.n_qblk +
+                                        (qb_idx < p.n_qblk ? qb_idx : p.n_qblk - 1)]
+                            : 1.f;
+      const float* ksc = p.k_scale + ((size_t)tl.b * p.H + tl.h) * p.n_kblk;
+      float m2 = -INFINITY, l_sum = 0.f, l_sum2 = 0.f, mu_sum = 0.f, mu_sum2 = 0.f;   // m2: log2 units
+      // list entries are read two steps ahead and the key scale one step ahead, so that no
+      // step waits for a dependent pair of global loads
+      int kb1 = tl.lut[0], kb2 = tl.n_j > 1 ? tl.lut[1] : 0;
+      uint32_t fl1 = tl.flg[0];
+      float ks1 = INT8 ? ksc[kb1] : 1.f;
+      for (int j = 0; j < tl.n_j && ok; ++j, ++step) {
+        const int kb = kb1;
+        const uint32_t fl = fl1;
+        const float ks = ks1;
+        kb1 = kb2;
+        if (j + 1 < tl.n_j) {
+          fl1 = tl.flg[j + 1];
+          if (INT8) ks1 = ksc[kb1];
+        }
+        if (j + 2 < tl.n_j) kb2 = tl.lut[j + 2];
+        ok = __all_sync(0xffffffffu, mbar_wait(&sl.s_full, step & 1, abort_flag, p.status,
+                                               STATUS_TIMEOUT_MMA));
+        if (!ok) break;
+        tc_fence_after();
+        if (!((fl >> half) & 1)) {
+          // this half of the tile does not attend the block: P = T = 0
+          uint32_t z[16];
 #pragma unroll
-          for (int c = 0; c < (TANGENT ? 128 : 64); c += 32) {
-            uint32_t ov[32];
-            tmem_ld32(tb + SC_O + c, ov);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tmem_st32(tb + SC_O + c, ov);
+          for (int i = 0; i < 16; ++i) z[i] = 0u;
+          tmem_st16(tb + C::SC_S, z);
+          tmem_st16(tb + C::SC_S + 16, z);
+          if (TANGENT) {
+            tmem_st16(tb + C::SC_DS, z);
+            tmem_st16(tb + C::SC_DS + 16, z);
           }
           tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sl.p_full);
+          continue;
         }
-      }
-      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used * scale_log2;
+        // raw score -> log2 units: one factor for de-quantisation and softmax scale
+        const float cf = INT8 ? sq * ks * scale_log2 : scale_log2;
+        const int kv_rem = p.L - kb * SP_BK;
+        // pass 1: row maximum of the raw scores (integer compare for INT8 scores).  The
+        // scores are read from TMEM again in pass 2, 32 columns at a time, so that a row
+        // never needs 64 score registers next to the packed results.
+        float mx2;
+        {
+          uint32_t a[32], c[32];
+          tmem_ld32(tb + C::SC_S, a);
+          tmem_ld32(tb + C::SC_S + 32, c);
+          tc_wait_ld();
+          if (kv_rem < SP_BK) {
+            const uint32_t lowest = INT8 ? 0x80000000u : 0xff800000u;   // INT_MIN / -inf
 #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t pk[16];
-        uint32_t tk[TANGENT ? 16 : 1];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int c = hh * 32 + i;
-          float p0 = ex2(fmaf(__uint_as_float(sv[c]), scale_log2, neg_m));
-          float p1 = ex2(fmaf(__uint_as_float(sv[c + 1]), scale_log2, neg_m));
-          if (p.quant_p) {
-            p0 = rintf(p0 * 127.f) * (1.f / 127.f);
-            p1 = rintf(p1 * 127.f) * (1.f / 127.f);
+            for (int i = 0; i < 32; ++i) {
+              if (i >= kv_rem) a[i] = lowest;
+              if (i + 32 >= kv_rem) c[i] = lowest;
+            }
           }
-          l_sum += p0;
-          l_sum2 += p1;
-          pk[i / 2] = pack_bf16(p0, p1);
-          if (TANGENT) {
-            const float t0 = p0 * __uint_as_float(dsv[c]) * p.scale;
-            const float t1 = p1 * __uint_as_float(dsv[c + 1]) * p.scale;
-            mu_sum += t0;
-            mu_sum2 += t1;
-            tk[i / 2] = pack_bf16(t0, t1);
+          if (INT8) {
+            int m0 = (int)a[0], m1 = (int)c[0];
+#pragma unroll
+            for (int i = 1; i + 1 < 32; i += 2) {
+              m0 = __vimax3_s32(m0, (int)a[i], (int)a[i + 1]);
+              m1 = __vimax3_s32(m1, (int)c[i], (int)c[i + 1]);
+            }
+            mx2 = static_cast<float>(__vimax3_s32(m0, m1, max((int)a[31], (int)c[31]))) * cf;
+          } else {
+            float m0 = __uint_as_float(a[0]), m1 = __uint_as_float(c[0]);
+#pragma unroll
+            for (int i = 1; i + 1 < 32; i += 2) {
+              asm("max.f32 %0, %0, %1, %2;" : "+f"(m0) : "f"(__uint_as_float(a[i])), "f"(__uint_as_float(a[i + 1])));
+              asm("max.f32 %0, %0, %1, %2;" : "+f"(m1) : "f"(__uint_as_float(c[i])), "f"(__uint_as_float(c[i + 1])));
+            }
+            mx2 = fmaxf(fmaxf(m0, m1), fmaxf(__uint_as_float(a[31]), __uint_as_float(c[31]))) * cf;
           }
         }
-        tmem_st16(tb + SC_S + hh * 16, pk);
-        if (TANGENT) tmem_st16(tb + SC_DS + hh * 16, tk);
+        if (m2 == -INFINITY) {
+          m2 = mx2;                                // first attended block: O and l are still zero
+        } else {
+          // with the QAT grid the running max is tracked exactly (P <= 1), otherwise lazily
+          const bool need = p.quant_p ? (mx2 > m2) : (mx2 - m2 > 8.0f);
+          if (__any_sync(0xffffffffu, need)) {
+            float alpha = 1.f;
+            if (need) {
+              alpha = ex2(m2 - mx2);
+              m2 = mx2;
+            }
+            l_sum *= alpha; l_sum2 *= alpha; mu_sum *= alpha; mu_sum2 *= alpha;
+            ok = __all_sync(0xffffffffu, mbar_wait(&sl.o_done, (step - 1) & 1, abort_flag, p.status,
+                                                   STATUS_TIMEOUT_MMA));
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < (TANGENT ? 128 : 64); c += 32) {
+              uint32_t ov[32];
+              tmem_ld32(tb + C::SC_O + c, ov);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+              tmem_st32(tb + C::SC_O + c, ov);
+            }
+            tc_wait_st();
+          }
+        }
+        const float neg_m = grid_log2 - m2;
+        const float magic = 12582912.f;            // 1.5 * 2^23: (x + magic) - magic rounds to nearest
+        // pass 2: P (and T) for 32 columns at a time; the packed bf16 results go over the
+        // first columns of S (dS), which have been read by then
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t sv[32];
+          uint32_t dsv[TANGENT ? 32 : 1];
+          tmem_ld32(tb + C::SC_S + hh * 32, sv);
+          if (TANGENT) tmem_ld32(tb + C::SC_DS + hh * 32, dsv);
+          tc_wait_ld();
+          uint32_t pk[16];
+          uint32_t tk[TANGENT ? 16 : 1];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float x0 = INT8 ? static_cast<float>(static_cast<int>(sv[i])) : __uint_as_float(sv[i]);
+            const float x1 =
+                INT8 ? static_cast<float>(static_cast<int>(sv[i + 1])) : __uint_as_float(sv[i + 1]);
+            float p0 = ex2(fmaf(x0, cf, neg_m));
+            float p1 = ex2(fmaf(x1, cf, neg_m));
+            if (hh * 32 + i >= kv_rem) p0 = 0.f;         // ragged last key block
+            if (hh * 32 + i + 1 >= kv_rem) p1 = 0.f;
+            if (p.quant_p) {
+              p0 = (p0 + magic) - magic;
+              p1 = (p1 + magic) - magic;
+            }
+            l_sum += p0;
+            l_sum2 += p1;
+            pk[i / 2] = pack_bf16(p0, p1);
+            if (TANGENT) {
+              const float t0 = p0 * __uint_as_float(dsv[i]) * p.scale;
+              const float t1 = p1 * __uint_as_float(dsv[i + 1]) * p.scale;
+              mu_sum += t0;
+              mu_sum2 += t1;
+              tk[i / 2] = pack_bf16(t0, t1);
+            }
+          }
+          tmem_st16(tb + C::SC_S + hh * 16, pk);
+          if (TANGENT) tmem_st16(tb + C::SC_DS + hh * 16, tk);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sl.p_full);
       }
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(&s.p_full);
-    }
-    if (ok && n_j > 0)
-      ok = mbar_wait(&s.o_done, (uint32_t)((n_j - 1) & 1), abort_flag, p.status, STATUS_TIMEOUT_MMA);
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok && n_j > 0) {
+      if (ok)
+        ok = mbar_wait(&sl.o_done, (step - 1) & 1, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after();
       const float l_tot = l_sum + l_sum2, mu_tot = mu_sum + mu_sum2;
       const float inv_l = l_tot > 0.f ? 1.f / l_tot : 0.f;
-      const bool live = q_row < p.L;
-      const int64_t off = (int64_t)b * p.o_sb + (int64_t)q_row * p.o_sl + (int64_t)h * p.o_sh;
 #pragma unroll
       for (int c = 0; c < SP_HD; c += 32) {
         uint32_t ov[32];
-        tmem_ld32(tb + SC_O + c, ov);
+        tmem_ld32(tb + C::SC_O + c, ov);
         tc_wait_ld();
         uint32_t ob[16];
 #pragma unroll
@@ -329,7 +582,7 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
         }
         if (TANGENT) {
           uint32_t dv_[32];
-          tmem_ld32(tb + SC_DO + c, dv_);
+          tmem_ld32(tb + C::SC_DO + c, dv_);
           tc_wait_ld();
           const float mul = mu_tot * inv_l;
 #pragma unroll
@@ -347,16 +600,20 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
           }
         }
       }
-      if (live && p.lse)
-        p.lse[((int64_t)b * p.H + h) * p.L + q_row] = m_used * p.scale + __logf(l_tot);
+      if (live && p.lse)        // natural log; the grid factor 127 of l is taken out again
+        p.lse[((int64_t)tl.b * p.H + tl.h) * p.L + q_row] =
+            m2 * 0.6931471805599453f + __logf(l_tot) - grid_log2 * 0.6931471805599453f;
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sl.o_free);
     }
     tc_fence_before();
   }
   __syncthreads();
-  if (warp == 4) {
+  if (warp == C::WARP_MMA) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem, 256);
+    tmem_dealloc(tmem, C::TMEM_COLS);
   }
 }
 
@@ -435,11 +692,13 @@ extern "C" int imf_quantize_blocks(const void* x, void* xq, float* xs, void* xfq
 extern "C" int imf_attn_sparse_fwd(const void* q8, const void* k8, const float* q_scale,
                                    const float* k_scale, const void* q, const void* k,
                                    const void* v, const void* dq, const void* dk, const void* dv,
-                                   const int* lut, const uint8_t* flags, void* o, void* dout,
+                                   const int* lut, const uint8_t* flags, const int* cnt, void* o,
+                                   void* dout,
                                    float* lse, int B, int L, int H, int tmax, int qblk,
                                    const int64_t* strides, int64_t o_sb, int64_t o_sl, int64_t o_sh,
                                    float scale, int quant_p, int int8_qk, int* status, void* stream) {
-  if (B <= 0 || L <= 0 || H <= 0 || tmax <= 0 || (qblk != 64 && qblk != 128)) return IMF_ERR_ARG;
+  if (B <= 0 || L <= 0 || H <= 0 || tmax <= 0 || (qblk != 64 && qblk != 128) || cnt == nullptr)
+    return IMF_ERR_ARG;
   const bool tang = dq != nullptr;
   CUtensorMap mq8, mk8, mq, mk, mv, mdq, mdk, mdv;
   int rc;
@@ -460,22 +719,32 @@ extern "C" int imf_attn_sparse_fwd(const void* q8, const void* k8, const float* 
     if ((rc = map_rows(&mdv, dv, B, L, H, strides[15], strides[16], strides[17], SP_BK, false))) return rc;
   }
   SpParams p;
-  p.lut = lut; p.flags = flags; p.q_scale = q_scale; p.k_scale = k_scale;
+  p.lut = lut; p.flags = flags; p.cnt = cnt; p.q_scale = q_scale; p.k_scale = k_scale;
   p.o = (__nv_bfloat16*)o; p.dout = (__nv_bfloat16*)dout; p.lse = lse;
   p.B = B; p.H = H; p.L = L; p.n_mt = (L + SP_M - 1) / SP_M; p.tmax = tmax;
   p.qblk = qblk; p.n_qblk = (L + qblk - 1) / qblk; p.n_kblk = (L + SP_BK - 1) / SP_BK;
   p.o_sb = o_sb; p.o_sl = o_sl; p.o_sh = o_sh; p.scale = scale; p.quant_p = quant_p;
   p.status = status;
-  dim3 grid(p.n_mt, H, B);
+  p.n_tiles = p.n_mt * H * B;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = sizeof(SpSmem) + 1024;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
 #define IMF_SP_LAUNCH(T_, I_)                                                                   \
   do {                                                                                          \
+    using C_ = SpCfg<T_, I_>;                                                                   \
+    const size_t smem = sizeof(SpSmem<T_, I_>) + 1024;                                          \
+    int grid = (p.n_tiles + C_::NT - 1) / C_::NT;                                               \
+    if (grid > sms * C_::CTAS_PER_SM) grid = sms * C_::CTAS_PER_SM;                             \
     if (cudaFuncSetAttribute(attn_sparse_fwd_kernel<T_, I_>,                                    \
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
       return IMF_ERR_LAUNCH;                                                                    \
-    attn_sparse_fwd_kernel<T_, I_><<<grid, SP_THREADS, smem, st>>>(mq8, mk8, mq, mk, mv, mdq, mdk, \
-                                                                   mdv, p);                     \
+    attn_sparse_fwd_kernel<T_, I_><<<grid, C_::THREADS, smem, st>>>(mq8, mk8, mq, mk, mv, mdq,  \
+                                                                    mdk, mdv, p);               \
   } while (0)
   if (tang && int8_qk) IMF_SP_LAUNCH(true, true);
   else if (tang) IMF_SP_LAUNCH(true, false);

@@ -20,7 +20,7 @@ if K._has("imf_attn_sparse_fwd"):
     _lib.imf_quantize_blocks.restype = ci
     _lib.imf_quantize_blocks.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, c64, c64, c64, vp]
     _lib.imf_attn_sparse_fwd.restype = ci
-    _lib.imf_attn_sparse_fwd.argtypes = [vp] * 15 + [ci] * 5 + [vp, c64, c64, c64, cf, ci, ci, vp, vp]
+    _lib.imf_attn_sparse_fwd.argtypes = [vp] * 16 + [ci] * 5 + [vp, c64, c64, c64, cf, ci, ci, vp, vp]
 
 
 def quantize_blocks(x: torch.Tensor, block: int, want_q: bool = True, want_fq: bool = False):
@@ -96,11 +96,14 @@ def sparse_fwd(q, k, v, dq, dk, dv, lut, flags, qblk: int, int8: bool, quant_p: 
     do = torch.empty_like(o) if tang else None
     lse = torch.empty(B, H, L, dtype=torch.float32, device=q.device) if need_lse else None
     need_qk = tang or not int8
+    # entries per list = position of the first -1
+    cnt = (lut >= 0).to(torch.int32).cumprod(-1).sum(-1, dtype=torch.int32).contiguous()
     rc = _lib.imf_attn_sparse_fwd(
         K._ptr(q8), K._ptr(k8), K._ptr(qs), K._ptr(ks),
         K._ptr(ts[0]) if need_qk else None, K._ptr(ts[1]) if need_qk else None, K._ptr(ts[2]),
         K._ptr(ts[3]) if tang else None, K._ptr(ts[4]) if tang else None,
-        K._ptr(ts[5]) if tang else None, K._ptr(lut), K._ptr(flags), K._ptr(o), K._ptr(do),
+        K._ptr(ts[5]) if tang else None, K._ptr(lut), K._ptr(flags), K._ptr(cnt), K._ptr(o),
+        K._ptr(do),
         K._ptr(lse), B, L, H, lut.shape[-1], qblk, ctypes.cast(arr, vp), o.stride(0), o.stride(1),
         o.stride(2), float(scale), int(quant_p), int(int8), K._ptr(K.status_word(q.device)),
         K._stream())
