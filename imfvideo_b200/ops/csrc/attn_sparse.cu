@@ -73,17 +73,18 @@ struct SpSlot {
   uint64_t q_full, q_empty;
   uint64_t kv_full[C::STAGES], kv_empty[C::STAGES];
   uint64_t s_full, p_full, o_done, o_free;
+  uint32_t tmem_base;        // used in slot 0 only (kept here: the slot's padding has room)
+  int abort_flag;
 };
 
 template <bool TANGENT, bool INT8>
 struct SpSmem {
   SpSlot<TANGENT, INT8> slot[SpCfg<TANGENT, INT8>::NT];
-  uint32_t tmem_base;
-  int abort_flag;
 };
-static_assert(sizeof(SpSmem<false, true>) + 1024 <= 232448 && sizeof(SpSmem<false, false>) + 1024 <= 232448 &&
-                  2 * (sizeof(SpSmem<true, true>) + 2048) <= 233472 &&
-                  2 * (sizeof(SpSmem<true, false>) + 2048) <= 233472,
+// 228 KB of shared memory per SM, 1 KB of it reserved per resident CTA, 227 KB per CTA at most
+static_assert(sizeof(SpSmem<false, true>) <= 232448 && sizeof(SpSmem<false, false>) <= 232448 &&
+                  2 * (sizeof(SpSmem<true, true>) + 1024) <= 233472 &&
+                  2 * (sizeof(SpSmem<true, false>) + 1024) <= 233472,
               "shared memory per CTA / per SM exceeded");
 
 struct SpParams {
@@ -145,9 +146,14 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
   constexpr int NT = C::NT;
   constexpr bool NEED_QK = C::NEED_QK;
   constexpr int VI = 0, KI = 1, DKI = 2, DVI = 3;          // kv[stage][...]
-  extern __shared__ uint8_t smem_raw[];
-  auto& s = *reinterpret_cast<SpSmem<TANGENT, INT8>*>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // no slack for a manual round-up (the tangent kernel needs every byte for two CTAs per
+  // SM): the swizzled TMA tiles need the base on a 1024-byte boundary, checked here
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if (smem_u32(smem_raw) & 1023u) {
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, STATUS_BAD_ARG);
+    return;
+  }
+  auto& s = *reinterpret_cast<SpSmem<TANGENT, INT8>*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_stride = gridDim.x * NT;
 
@@ -165,18 +171,18 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
       mbar_init(&sl.o_done, 1);
       mbar_init(&sl.o_free, 4);
     }
-    s.abort_flag = 0;
+    s.slot[0].abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == C::WARP_MMA) {
-    tmem_alloc(&s.tmem_base, C::TMEM_COLS);
+    tmem_alloc(&s.slot[0].tmem_base, C::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = s.tmem_base;
-  volatile int* abort_flag = &s.abort_flag;
+  const uint32_t tmem = s.slot[0].tmem_base;
+  volatile int* abort_flag = &s.slot[0].abort_flag;
 
   if (warp >= C::SOFT_WARPS) {
     if (C::SETMAXNREG) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REG_OTHER));
@@ -737,7 +743,7 @@ extern "C" int imf_attn_sparse_fwd(const void* q8, const void* k8, const float* 
 #define IMF_SP_LAUNCH(T_, I_)                                                                   \
   do {                                                                                          \
     using C_ = SpCfg<T_, I_>;                                                                   \
-    const size_t smem = sizeof(SpSmem<T_, I_>) + 1024;                                          \
+    const size_t smem = sizeof(SpSmem<T_, I_>);                                                 \
     int grid = (p.n_tiles + C_::NT - 1) / C_::NT;                                               \
     if (grid > sms * C_::CTAS_PER_SM) grid = sms * C_::CTAS_PER_SM;                             \
     if (cudaFuncSetAttribute(attn_sparse_fwd_kernel<T_, I_>,                                    \
