@@ -8,10 +8,17 @@
 // (dY W) and weight-gradient (dY^T X) products need no transposed copies.
 // The dual-number forward stacks primal and tangent rows into one launch.
 //
-// CTA = one 128 x BN output tile.  Warps 0-3: epilogue (TMEM -> registers ->
-// global), warp 4: TMA producer, warp 5: MMA issuer.  STAGES-deep mbarrier
-// ring.  Replaces the reference's `_mm16_kernel` / cuBLAS / `_scaled_mm`
-// calls on the JVP path (reference models/triton_mla_block_jvp.py:89-148).
+// Persistent grid: one CTA per SM walks over the 128 x BN output tiles (n
+// fastest, so neighbouring CTAs share the A tile in L2).  Warps 0-3: epilogue,
+// warp 4: TMA producer, warp 5: MMA issuer.  STAGES-deep mbarrier ring for the
+// operands and TWO accumulator buffers in TMEM, so the MMAs of the next tile
+// run while the previous tile is drained.  The epilogue converts the
+// accumulator in registers, stages the tile in shared memory in the swizzled
+// TMA layout (conflict-free 16-byte stores) and writes it with one TMA store
+// per 128-byte-wide panel; when C cannot be described by a tensor map (odd
+// pitch or base) it falls back to direct stores.  Replaces the reference's
+// `_mm16_kernel` / cuBLAS / `_scaled_mm` calls on the JVP path (reference
+// models/triton_mla_block_jvp.py:89-148).
 #include "common.cuh"
 #include "host_util.h"
 
@@ -21,43 +28,51 @@ constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, typename OutT>
 struct GemmSmem {
   alignas(1024) uint8_t a[STAGES][GEMM_BM * GEMM_BK * 2];
   alignas(1024) uint8_t b[STAGES][BN * GEMM_BK * 2];
+  alignas(1024) uint8_t c[GEMM_BM * BN * sizeof(OutT)];   // panels of [128 rows][128 bytes]
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
-  uint64_t acc_full;
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
+struct GemmTiles {
+  int n_m, n_n, total;     // tiles along M, N; total = n_m * n_n * batch
+};
+
 template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT>
-__global__ void __launch_bounds__(GEMM_THREADS)
+__global__ void __launch_bounds__(GEMM_THREADS, 2)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-            OutT* __restrict__ C, const float* __restrict__ bias, int M, int N, int K,
-            int64_t ldc, int bias_rows, float alpha, int accumulate_out, int* status,
-            const OutT* __restrict__ Cin, float beta, int64_t batch_stride_c) {
+            const __grid_constant__ CUtensorMap tm_c, OutT* __restrict__ Cbase,
+            const float* __restrict__ bias, int M, int N, int K, int64_t ldc, int bias_rows,
+            float alpha, int accumulate_out, int* status, const OutT* __restrict__ Cin_base,
+            float beta, int64_t batch_stride_c, GemmTiles tiles, int tma_store) {
   extern __shared__ uint8_t smem_raw[];
-  auto& s = *reinterpret_cast<GemmSmem<BN, STAGES>*>(
+  auto& s = *reinterpret_cast<GemmSmem<BN, STAGES, OutT>*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * GEMM_BM, bz = blockIdx.z;
-  C += (int64_t)bz * batch_stride_c;
-  if (Cin) Cin += (int64_t)bz * batch_stride_c;
   const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  constexpr int PANEL_COLS = 128 / (int)sizeof(OutT);      // 64 bf16 or 32 fp32 columns
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) {
       mbar_init(&s.full[i], 1);
       mbar_init(&s.empty[i], 1);
     }
-    mbar_init(&s.acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.acc_full[i], 1);
+      mbar_init(&s.acc_empty[i], 4);     // one arrival per epilogue warp
+    }
     s.abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 5) {
-    tmem_alloc(&s.tmem_base, BN);
+    tmem_alloc(&s.tmem_base, 2 * BN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -65,6 +80,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   tc_fence_after();
   const uint32_t tmem = s.tmem_base;
   volatile int* abort_flag = &s.abort_flag;
+  auto tile_coords = [&](int tile, int& n0, int& m0, int& bz) {
+    n0 = (tile % tiles.n_n) * BN;
+    m0 = ((tile / tiles.n_n) % tiles.n_m) * GEMM_BM;
+    bz = tile / (tiles.n_n * tiles.n_m);
+  };
 
   if (warp == 4) {
     // ------------------------------------------------------ TMA producer --
@@ -72,26 +92,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       prefetch_tmap(&tm_a);
       prefetch_tmap(&tm_b);
       constexpr uint32_t bytes = (GEMM_BM + BN) * GEMM_BK * 2;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int st = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (kb >= STAGES &&
-            !mbar_wait(&s.empty[st], ph ^ 1, abort_flag, status, STATUS_TIMEOUT_EMPTY))
-          break;
-        mbar_arrive_expect_tx(&s.full[st], bytes);
-        const int k0 = kb * GEMM_BK;
-        if (!A_MN) {
-          tma_load_3d(s.a[st], &tm_a, &s.full[st], k0, m0, bz);
-        } else {
-          tma_load_3d(s.a[st], &tm_a, &s.full[st], m0, k0, bz);
-          tma_load_3d(s.a[st] + 64 * 128, &tm_a, &s.full[st], m0 + 64, k0, bz);
-        }
-        if (!B_MN) {
-          tma_load_3d(s.b[st], &tm_b, &s.full[st], k0, n0, bz);
-        } else {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles.total && ok; tile += gridDim.x) {
+        int n0, m0, bz;
+        tile_coords(tile, n0, m0, bz);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int st = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&s.empty[st], ((it / STAGES) & 1) ^ 1, abort_flag, status,
+                                         STATUS_TIMEOUT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&s.full[st], bytes);
+          const int k0 = kb * GEMM_BK;
+          if (!A_MN) {
+            tma_load_3d(s.a[st], &tm_a, &s.full[st], k0, m0, bz);
+          } else {
+            tma_load_3d(s.a[st], &tm_a, &s.full[st], m0, k0, bz);
+            tma_load_3d(s.a[st] + 64 * 128, &tm_a, &s.full[st], m0 + 64, k0, bz);
+          }
+          if (!B_MN) {
+            tma_load_3d(s.b[st], &tm_b, &s.full[st], k0, n0, bz);
+          } else {
 #pragma unroll
-          for (int p = 0; p < BN / 64; ++p)
-            tma_load_3d(s.b[st] + p * 64 * 128, &tm_b, &s.full[st], n0 + p * 64, k0, bz);
+            for (int p = 0; p < BN / 64; ++p)
+              tma_load_3d(s.b[st] + p * 64 * 128, &tm_b, &s.full[st], n0 + p * 64, k0, bz);
+          }
         }
       }
     }
@@ -99,115 +126,169 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     // -------------------------------------------------------- MMA issuer --
     if (elect_one()) {
       constexpr uint32_t idesc = idesc_bf16(GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t it = 0, tn = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int st = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        ok = mbar_wait(&s.full[st], ph, abort_flag, status, STATUS_TIMEOUT_TMA);
+      for (int tile = blockIdx.x; tile < tiles.total && ok; tile += gridDim.x, ++tn) {
+        const uint32_t buf = tn & 1;
+        if (tn >= 2)     // the epilogue has drained this accumulator buffer
+          ok = mbar_wait(&s.acc_empty[buf], ((tn >> 1) - 1) & 1, abort_flag, status,
+                         STATUS_TIMEOUT_SOFTMAX);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_base = smem_u32(s.a[st]), b_base = smem_u32(s.b[st]);
+        const uint32_t acc = tmem + buf * BN;
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+          const int st = it % STAGES;
+          ok = mbar_wait(&s.full[st], (it / STAGES) & 1, abort_flag, status, STATUS_TIMEOUT_TMA);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(s.a[st]), b_base = smem_u32(s.b[st]);
 #pragma unroll
-        for (int ks = 0; ks < GEMM_BK / 16; ++ks) {
-          const uint64_t da = A_MN ? sdesc_mnmajor(a_base + ks * 2048, 64 * 128)
-                                   : sdesc_kmajor(a_base + ks * 32);
-          const uint64_t db = B_MN ? sdesc_mnmajor(b_base + ks * 2048, 64 * 128)
-                                   : sdesc_kmajor(b_base + ks * 32);
-          mma_ss(tmem, da, db, idesc, (kb | ks) != 0);
+          for (int ks = 0; ks < GEMM_BK / 16; ++ks) {
+            const uint64_t da = A_MN ? sdesc_mnmajor(a_base + ks * 2048, 64 * 128)
+                                     : sdesc_kmajor(a_base + ks * 32);
+            const uint64_t db = B_MN ? sdesc_mnmajor(b_base + ks * 2048, 64 * 128)
+                                     : sdesc_kmajor(b_base + ks * 32);
+            mma_ss(acc, da, db, idesc, (kb | ks) != 0);
+          }
+          tc_commit(&s.empty[st]);
         }
-        tc_commit(&s.empty[st]);
+        tc_commit(&s.acc_full[buf]);
       }
-      tc_commit(&s.acc_full);
     }
   } else {
     // ---------------------------------------------------------- epilogue --
-    const bool ok = mbar_wait(&s.acc_full, 0, abort_flag, status, STATUS_TIMEOUT_MMA);
-    tc_fence_after();
-    const int row = m0 + warp * 32 + lane;
-    if (ok) {
+    uint32_t tn = 0;
+    bool dead = false;     // a wait gave up: keep walking (the named barriers below are
+                           // counted per tile by all four warps) but touch nothing
+    for (int tile = blockIdx.x; tile < tiles.total; tile += gridDim.x, ++tn) {
+      int n0, m0, bz;
+      tile_coords(tile, n0, m0, bz);
+      const uint32_t buf = tn & 1;
+      OutT* C = Cbase + (int64_t)bz * batch_stride_c;
+      const OutT* Cin = Cin_base ? Cin_base + (int64_t)bz * batch_stride_c : nullptr;
+      if (!dead)
+        dead = !__all_sync(0xffffffffu, mbar_wait(&s.acc_full[buf], (tn >> 1) & 1, abort_flag,
+                                                  status, STATUS_TIMEOUT_MMA));
+      tc_fence_after();
+      const int r_in = warp * 32 + lane;
+      const int row = m0 + r_in;
+      const bool full_tile = tma_store && !accumulate_out;
+      if (full_tile && tn > 0) {
+        // the previous tile's TMA store has finished reading the staging buffer
+        if (threadIdx.x == 0) tma_store_wait_read();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      if (!dead) {
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
-        tmem_ld32(tmem_addr(tmem, warp * 32, c), r);
+        tmem_ld32(tmem_addr(tmem + buf * BN, warp * 32, c), r);
         tc_wait_ld();
-        if (row < M) {
-          OutT* dst = C + (int64_t)row * ldc + n0 + c;
-          const bool add_bias = bias != nullptr && row < bias_rows;
-          if (n0 + c + 32 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0 &&
-              !accumulate_out) {
-            if constexpr (sizeof(OutT) == 2) {
-              uint32_t o[16];
-              uint32_t cv[16];
-              if (Cin) {
-                const uint4* c4 = reinterpret_cast<const uint4*>(Cin + (int64_t)row * ldc + n0 + c);
+        const bool add_bias = bias != nullptr && row < bias_rows;
+        if (full_tile) {
+          // convert and stage: 16-byte chunk k of row r goes to chunk k ^ (r % 8) of the
+          // row's 128-byte line in its panel (SWIZZLE_128B)
+          if constexpr (sizeof(OutT) == 2) {
+            uint32_t o[16];
+            uint32_t cv[16];
+            const bool have_cin =
+                Cin && row < M && n0 + c + 32 <= N &&
+                (reinterpret_cast<uintptr_t>(Cin + (int64_t)row * ldc + n0 + c) & 15u) == 0;
+            if (have_cin) {
+              const uint4* c4 = reinterpret_cast<const uint4*>(Cin + (int64_t)row * ldc + n0 + c);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const uint4 t = c4[i];
-                  cv[4 * i] = t.x; cv[4 * i + 1] = t.y; cv[4 * i + 2] = t.z; cv[4 * i + 3] = t.w;
-                }
-              }
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                float x = __uint_as_float(r[2 * i]) * alpha;
-                float y = __uint_as_float(r[2 * i + 1]) * alpha;
-                if (Cin) {
-                  x += beta * bf16_lo(cv[i]);
-                  y += beta * bf16_hi(cv[i]);
-                }
-                if (add_bias) {
-                  x += bias[n0 + c + 2 * i];
-                  y += bias[n0 + c + 2 * i + 1];
-                }
-                o[i] = pack_bf16(x, y);
-              }
-              uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                d4[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
-            } else {
-              float4* d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float4 v;
-                v.x = __uint_as_float(r[4 * i]) * alpha;
-                v.y = __uint_as_float(r[4 * i + 1]) * alpha;
-                v.z = __uint_as_float(r[4 * i + 2]) * alpha;
-                v.w = __uint_as_float(r[4 * i + 3]) * alpha;
-                if (Cin) {
-                  const float4 cvf = reinterpret_cast<const float4*>(
-                      reinterpret_cast<const float*>(Cin) + (int64_t)row * ldc + n0 + c)[i];
-                  v.x += beta * cvf.x; v.y += beta * cvf.y; v.z += beta * cvf.z; v.w += beta * cvf.w;
-                }
-                if (add_bias) {
-                  v.x += bias[n0 + c + 4 * i];
-                  v.y += bias[n0 + c + 4 * i + 1];
-                  v.z += bias[n0 + c + 4 * i + 2];
-                  v.w += bias[n0 + c + 4 * i + 3];
-                }
-                d4[i] = v;
+              for (int i = 0; i < 4; ++i) {
+                const uint4 t = c4[i];
+                cv[4 * i] = t.x; cv[4 * i + 1] = t.y; cv[4 * i + 2] = t.z; cv[4 * i + 3] = t.w;
               }
             }
-          } else {
-            for (int i = 0; i < 32; ++i) {
-              const int col = n0 + c + i;
-              if (col < N) {
-                float x = __uint_as_float(r[i]) * alpha;
-                if (add_bias) x += bias[col];
-                if (accumulate_out) x += static_cast<float>(dst[i]);
-                if (Cin) x += beta * static_cast<float>(Cin[(int64_t)row * ldc + col]);
-                dst[i] = static_cast<OutT>(x);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float x = __uint_as_float(r[2 * i]) * alpha;
+              float y = __uint_as_float(r[2 * i + 1]) * alpha;
+              if (have_cin) {
+                x += beta * bf16_lo(cv[i]);
+                y += beta * bf16_hi(cv[i]);
+              } else if (Cin && row < M) {
+                if (n0 + c + 2 * i < N) x += beta * __bfloat162float(Cin[(int64_t)row * ldc + n0 + c + 2 * i]);
+                if (n0 + c + 2 * i + 1 < N) y += beta * __bfloat162float(Cin[(int64_t)row * ldc + n0 + c + 2 * i + 1]);
               }
+              if (add_bias) {
+                if (n0 + c + 2 * i < N) x += bias[n0 + c + 2 * i];
+                if (n0 + c + 2 * i + 1 < N) y += bias[n0 + c + 2 * i + 1];
+              }
+              o[i] = pack_bf16(x, y);
+            }
+            uint8_t* panel = s.c + (c / PANEL_COLS) * (GEMM_BM * 128) + r_in * 128;
+            const int k0 = (c % PANEL_COLS) / 8;          // first 16-byte chunk of this group
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(panel + (((k0 + i) ^ (r_in & 7)) << 4)) =
+                  make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          } else {
+            uint8_t* panel = s.c + (c / PANEL_COLS) * (GEMM_BM * 128) + r_in * 128;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float4 v;
+              v.x = __uint_as_float(r[4 * i]) * alpha;
+              v.y = __uint_as_float(r[4 * i + 1]) * alpha;
+              v.z = __uint_as_float(r[4 * i + 2]) * alpha;
+              v.w = __uint_as_float(r[4 * i + 3]) * alpha;
+              const int col = n0 + c + 4 * i;
+              if (Cin && row < M) {
+                const float* ci = reinterpret_cast<const float*>(Cin) + (int64_t)row * ldc + col;
+                if (col < N) v.x += beta * ci[0];
+                if (col + 1 < N) v.y += beta * ci[1];
+                if (col + 2 < N) v.z += beta * ci[2];
+                if (col + 3 < N) v.w += beta * ci[3];
+              }
+              if (add_bias) {
+                if (col < N) v.x += bias[col];
+                if (col + 1 < N) v.y += bias[col + 1];
+                if (col + 2 < N) v.z += bias[col + 2];
+                if (col + 3 < N) v.w += bias[col + 3];
+              }
+              *reinterpret_cast<float4*>(panel + ((i ^ (r_in & 7)) << 4)) = v;
+            }
+          }
+        } else if (row < M) {
+          OutT* dst = C + (int64_t)row * ldc + n0 + c;
+          for (int i = 0; i < 32; ++i) {
+            const int col = n0 + c + i;
+            if (col < N) {
+              float x = __uint_as_float(r[i]) * alpha;
+              if (add_bias) x += bias[col];
+              if (accumulate_out) x += static_cast<float>(dst[i]);
+              if (Cin) x += beta * static_cast<float>(Cin[(int64_t)row * ldc + col]);
+              dst[i] = static_cast<OutT>(x);
             }
           }
         }
       }
+      // the accumulator buffer is free again
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.acc_empty[buf]);
+      }
+      if (full_tile) {
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 0 && !dead) {
+#pragma unroll
+          for (int pn = 0; pn < BN / PANEL_COLS; ++pn)
+            if (n0 + pn * PANEL_COLS < N)
+              tma_store_3d(&tm_c, s.c + pn * (GEMM_BM * 128), n0 + pn * PANEL_COLS, m0, bz);
+          tma_store_commit();
+        }
+      }
     }
+    if (threadIdx.x == 0) tma_store_wait_all();
     tc_fence_before();
   }
   __syncthreads();
   if (warp == 5) {
     tc_fence_after();
-    tmem_dealloc(tmem, BN);
+    tmem_dealloc(tmem, 2 * BN);
   }
 }
 
@@ -217,7 +298,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
                        int accumulate_out, int* status, cudaStream_t stream, int batch = 1,
                        int64_t sa = 0, int64_t sb = 0, int64_t sc = 0, const void* Cin = nullptr,
                        float beta = 0.f) {
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tc;
   int rc;
   {
     // K-major: dims (K, M), box (64, 128).  MN-major: dims (M, K), box (64, 64).
@@ -236,8 +317,22 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
     rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(B), dims, str, box);
     if (rc) return rc;
   }
+  // C through TMA when its pitch, batch stride and base are 16-byte multiples
+  constexpr int ES = (int)sizeof(OutT);
+  int tma_store = ((ldc * ES) % 16 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) &&
+                  (batch == 1 || (sc * ES) % 16 == 0) && !accumulate_out;
+  tc = ta;
+  if (tma_store) {
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
+    uint64_t str[3] = {(uint64_t)ES, (uint64_t)ldc * ES,
+                       (uint64_t)(batch > 1 ? sc : ldc * (int64_t)M) * ES};
+    uint32_t box[3] = {(uint32_t)(128 / ES), (uint32_t)GEMM_BM, 1};
+    if (make_tmap(&tc, ES == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                        3, C, dims, str, box))
+      tma_store = 0;
+  }
   auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, OutT>;
-  const size_t smem = sizeof(GemmSmem<BN, STAGES>) + 1024;
+  const size_t smem = sizeof(GemmSmem<BN, STAGES, OutT>) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
@@ -245,10 +340,24 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
       return IMF_ERR_LAUNCH;
     attr_set = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + GEMM_BM - 1) / GEMM_BM, batch);
-  kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, static_cast<OutT*>(C), bias, M, N, K, ldc,
+  GemmTiles tiles;
+  tiles.n_n = (N + BN - 1) / BN;
+  tiles.n_m = (M + GEMM_BM - 1) / GEMM_BM;
+  tiles.total = tiles.n_n * tiles.n_m * batch;
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  // two persistent CTAs per SM when their shared memory allows it (256 TMEM columns each)
+  const int per_sm = (2 * (smem + 1024) <= 233472) ? 2 : 1;
+  const int grid = tiles.total < sms * per_sm ? tiles.total : sms * per_sm;
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, tc, static_cast<OutT*>(C), bias, M, N, K, ldc,
                                              bias_rows, alpha, accumulate_out, status,
-                                             static_cast<const OutT*>(Cin), beta, sc);
+                                             static_cast<const OutT*>(Cin), beta, sc, tiles,
+                                             tma_store);
   return cudaGetLastError() == cudaSuccess ? IMF_OK : IMF_ERR_LAUNCH;
 }
 
@@ -267,7 +376,7 @@ extern "C" int imf_gemm_bf16(const void* A, const void* B, void* C, const float*
   if ((lda & 7) || (ldb & 7)) return IMF_ERR_ARG;  // TMA strides are multiples of 16 B
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define IMF_GEMM_CASE(AM, BM_, OT)                                                          \
-  return launch_gemm<128, 3, AM, BM_, OT>(A, B, C, bias, M, N, K, lda, ldb, ldc, bias_rows, \
+  return launch_gemm<128, 2, AM, BM_, OT>(A, B, C, bias, M, N, K, lda, ldb, ldc, bias_rows, \
                                           alpha, accumulate_out, status, st)
   if (out_fp32) {
     if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, float);
@@ -296,7 +405,7 @@ extern "C" int imf_gemm_bf16_batched(const void* A, const void* B, void* C, cons
   if ((lda & 7) || (ldb & 7) || (batch > 1 && ((sa & 7) || (sb & 7)))) return IMF_ERR_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define IMF_GEMM_CASE(AM, BM_, OT)                                                              \
-  return launch_gemm<128, 3, AM, BM_, OT>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, alpha, 0, \
+  return launch_gemm<128, 2, AM, BM_, OT>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, alpha, 0, \
                                           status, st, batch, sa, sb, sc, Cin, beta)
   if (out_fp32) {
     if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, float);
