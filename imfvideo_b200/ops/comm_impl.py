@@ -19,11 +19,14 @@ vp, ci, cl = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
 
 if K._has("imf_comm_reduce"):
     _lib.imf_comm_reduce.restype = ci
-    _lib.imf_comm_reduce.argtypes = [vp, vp, vp, ci, ci, cl, cl, cl, ci, vp, vp]
+    _lib.imf_comm_reduce.argtypes = [vp, vp, vp, ci, ci, cl, cl, cl, ci, vp, vp, vp, vp, vp]
     _lib.imf_comm_gather.restype = ci
     _lib.imf_comm_gather.argtypes = [vp, vp, ci, ci, cl, cl, ci, ci, vp, vp]
     _lib.imf_comm_barrier.restype = ci
     _lib.imf_comm_barrier.argtypes = [vp, vp, ci, ci, ci, vp, vp]
+    _lib.imf_comm_muon_apply.restype = ci
+    _lib.imf_comm_muon_apply.argtypes = [vp, vp, ci, ci, cl, vp, vp, vp, ci, cl, ctypes.c_float, vp,
+                                         ci, ci, vp, vp]
 
 
 def _ptr_array(ptrs: List[int]):
@@ -53,6 +56,13 @@ class PeerComm:
         self._hF = symm.rendezvous(self._flags, group)
         self._g_ptrs = _ptr_array(list(self._hG.buffer_ptrs))
         self._f_ptrs = _ptr_array(list(self._hF.buffer_ptrs))
+        # squared gradient norms: slot r of every rank's array receives rank r's share
+        self.norms = symm.empty(self.MAX_RANKS, dtype=torch.float64, device=device)
+        self.norms.zero_()
+        self._hN = symm.rendezvous(self.norms, group)
+        self._n_ptrs = _ptr_array(list(self._hN.buffer_ptrs))
+        self._norm_part = torch.zeros(512, dtype=torch.float64, device=device)
+        self._norm_done = torch.zeros(1, dtype=torch.int32, device=device)
         self._U: Optional[torch.Tensor] = None
         self._u_ptrs = None
         self.epoch = 0
@@ -79,11 +89,14 @@ class PeerComm:
         return K._ptr(K.status_word(self.device))
 
     def reduce_grads(self) -> None:
-        """Muon segment -> owner, AdamW slice -> every rank (mean)."""
+        """Muon segment -> owner, AdamW slice -> every rank (mean); the reduce pass also
+        publishes every rank's squared norm of its reduced slices (``grad_sq_norm``)."""
         mc = vp(int(self._hG.multicast_ptr)) if self.use_multimem else None
         K._check(_lib.imf_comm_reduce(self._g_ptrs, self._f_ptrs, mc, self.rank, self.world,
                                       self.seg_pad, self.muon_total, self.adam_numel,
-                                      self._next(), self._status(), K._stream()), "imf_comm_reduce")
+                                      self._next(), self._status(), self._n_ptrs,
+                                      K._ptr(self._norm_part), K._ptr(self._norm_done),
+                                      K._stream()), "imf_comm_reduce")
         shard = self.adam_numel // self.world
         K._check(_lib.imf_comm_gather(self._g_ptrs, self._f_ptrs, self.rank, self.world,
                                       self.muon_total, shard, 4, self._next(), self._status(),
@@ -94,6 +107,22 @@ class PeerComm:
         K._check(_lib.imf_comm_gather(self._u_ptrs, self._f_ptrs, self.rank, self.world, 0,
                                       self.seg_pad, self._U.element_size(), self._next(),
                                       self._status(), K._stream()), "imf_comm_gather")
+        K.LAUNCHES.count += 1
+
+    def grad_sq_norm(self) -> torch.Tensor:
+        """Squared global gradient norm (fp64 scalar on the device); valid after
+        ``reduce_grads`` (its gather launch starts with a barrier that orders the slots)."""
+        return self.norms[:self.world].sum()
+
+    def apply_muon_updates(self, P: torch.Tensor, E: Optional[torch.Tensor], segs_dev: torch.Tensor,
+                           nseg: int, max_numel: int, ema_w: float, clip: torch.Tensor) -> None:
+        """p <- p (1 - lr wd) - lr s Phi (+ EMA) for every Muon parameter, Phi read from the
+        owner's update arena over peer memory (no separate all-gather)."""
+        K._check(_lib.imf_comm_muon_apply(self._u_ptrs, self._f_ptrs, self.rank, self.world,
+                                          self.seg_pad, K._ptr(P), K._ptr(E), K._ptr(segs_dev), nseg,
+                                          max_numel, float(ema_w), K._ptr(clip),
+                                          int(self._U.dtype == torch.bfloat16), self._next(),
+                                          self._status(), K._stream()), "imf_comm_muon_apply")
         K.LAUNCHES.count += 1
 
     def barrier(self) -> None:

@@ -7,8 +7,14 @@
 //                    read with plain peer loads (or one multimem.ld_reduce per
 //                    16 bytes when an NVLS multicast mapping is given), scaled
 //                    by 1/W and written to this rank's arena in the same pass.
+//                    The same pass accumulates the squared norm of what it wrote
+//                    (fp64, fixed order) and publishes it to every rank, so the
+//                    global gradient norm needs no second pass and no collective.
 //   gather         : barrier, then pull the other ranks' reduced AdamW shards /
 //                    orthogonalised update segments into the local arena.
+//   muon_apply     : barrier, then p <- p (1 - lr wd) - lr s Phi (+ EMA) for EVERY Muon
+//                    parameter with Phi read straight from its owner's memory: the
+//                    update all-gather is fused into its consumer.
 //
 // Barriers are epoch flags in symmetric memory: rank r writes flag[r] = epoch
 // into every peer's flag array (st.release.sys) and every CTA polls its LOCAL
@@ -44,12 +50,12 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   return v;
 }
 
-// Signal (block 0) and wait (every block).  Returns false on timeout.
+// Signal (first block) and wait (every block).  Returns false on timeout.
 __device__ __forceinline__ bool peer_barrier(const CommPeers& peers, int rank, int world, int epoch,
                                              int* status) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
-    if (blockIdx.x == 0) {
+    if (blockIdx.x == 0 && blockIdx.y == 0) {
       __threadfence_system();
       for (int q = 0; q < world; ++q) st_release_sys(peers.flags[q] + rank, epoch);
     }
@@ -79,14 +85,21 @@ __device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc) {
   return v;
 }
 
+struct NormOut {
+  double* part;                 // [gridDim.x] per-block partial sums (local scratch)
+  unsigned int* done;           // block counter (local, returns to zero)
+  double* slots[MAX_RANKS];     // peer base pointers of the per-rank norm arrays [MAX_RANKS]
+};
+
 // ranges: [lo0, hi0) = this rank's Muon segment, [lo1, hi1) = its AdamW shard
 __global__ void __launch_bounds__(512)
 comm_reduce_kernel(const CommPeers peers, const float* mc_arena, int rank, int world, long lo0,
-                   long hi0, long lo1, long hi1, int epoch, int* status) {
+                   long hi0, long lo1, long hi1, int epoch, int* status, const NormOut nrm) {
   if (!peer_barrier(peers, rank, world, epoch, status)) return;
   const float inv = 1.f / world;
   float* mine = peers.arena[rank];
   const long n0 = (hi0 - lo0) / 4, n1 = (hi1 - lo1) / 4;
+  double ss = 0.0;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n0 + n1;
        i += (long)gridDim.x * blockDim.x) {
     const long off = i < n0 ? lo0 + i * 4 : lo1 + (i - n0) * 4;
@@ -102,6 +115,32 @@ comm_reduce_kernel(const CommPeers peers, const float* mc_arena, int rank, int w
     }
     acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
     *reinterpret_cast<float4*>(mine + off) = acc;
+    ss += (double)acc.x * acc.x + (double)acc.y * acc.y + (double)acc.z * acc.z +
+          (double)acc.w * acc.w;
+  }
+  if (nrm.part == nullptr) return;
+  // squared norm of this rank's reduced slices: warp -> block -> grid, every level in a fixed order
+  __shared__ double s_part[16];
+  __shared__ bool s_last;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double b = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) b += s_part[w];
+    nrm.part[blockIdx.x] = b;
+    __threadfence();
+    s_last = atomicAdd(nrm.done, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    __threadfence();
+    double tot = 0.0;
+    for (unsigned int i = 0; i < gridDim.x; ++i) tot += reinterpret_cast<volatile double*>(nrm.part)[i];
+    for (int q = 0; q < world; ++q) nrm.slots[q][rank] = tot;   // visible after the next barrier
+    __threadfence_system();
+    *nrm.done = 0u;
   }
 }
 
@@ -129,6 +168,35 @@ __global__ void comm_barrier_kernel(const CommPeers peers, int rank, int world, 
   peer_barrier(peers, rank, world, epoch, status);
 }
 
+struct Seg {          // one parameter inside the arena (same record as the optimizer kernels)
+  long start;
+  long numel;
+  float a;            // 1 - lr wd
+  float b;            // lr * scale
+};
+
+// p <- a p - b Phi (+ EMA) for every Muon parameter; Phi of a parameter is read from the
+// update arena of its owner (start / seg_pad), i.e. over NVLink for the other ranks' segments.
+template <typename UT>
+__global__ void __launch_bounds__(256)
+comm_muon_apply_kernel(const CommPeers peers, int rank, int world, long seg_pad, float* __restrict__ p,
+                       float* __restrict__ ema, const Seg* __restrict__ segs, float ema_w,
+                       const float* __restrict__ clip, int epoch, int* status) {
+  if (!peer_barrier(peers, rank, world, epoch, status)) return;
+  if (clip && clip[1] != 0.f) return;       // skipped step (same decision on every rank)
+  const Seg sg = segs[blockIdx.y];
+  const int owner = (int)(sg.start / seg_pad);
+  const UT* upd = reinterpret_cast<const UT*>(peers.arena[owner]);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < sg.numel;
+       i += (long)gridDim.x * blockDim.x) {
+    const long j = sg.start + i;
+    const float u = static_cast<float>(upd[j]);
+    const float v = p[j] * sg.a - sg.b * u;
+    p[j] = v;
+    if (ema) ema[j] += ema_w * (v - ema[j]);
+  }
+}
+
 static int fill(CommPeers& p, void* const* arena_ptrs, void* const* flag_ptrs, int world) {
   if (world < 1 || world > MAX_RANKS) return -1;
   for (int q = 0; q < MAX_RANKS; ++q) {
@@ -145,11 +213,20 @@ using namespace imf;
 // Mean-reduce this rank's Muon segment and AdamW shard of the fp32 arena.
 // arena_ptrs / flag_ptrs: host arrays of `world` device pointers (peer mapped).
 // mc_arena: NVLS multicast address of the arena or null.
+// norm_ptrs: `world` peer pointers of fp64[MAX_RANKS] arrays (slot r receives rank r's squared
+// norm of its reduced slices), norm_part: local fp64 scratch of >= 296 entries, norm_done: local
+// zeroed counter; all three null to skip the norm.
 extern "C" int imf_comm_reduce(void* const* arena_ptrs, void* const* flag_ptrs, const void* mc_arena,
                                int rank, int world, long seg_pad, long muon_total, long adam_numel,
-                               int epoch, int* status, void* stream) {
+                               int epoch, int* status, void* const* norm_ptrs, double* norm_part,
+                               unsigned int* norm_done, void* stream) {
   CommPeers p;
   if (fill(p, arena_ptrs, flag_ptrs, world)) return -1;
+  NormOut nrm;
+  nrm.part = norm_ptrs ? norm_part : nullptr;
+  nrm.done = norm_done;
+  for (int q = 0; q < MAX_RANKS; ++q)
+    nrm.slots[q] = (norm_ptrs && q < world) ? static_cast<double*>(norm_ptrs[q]) : nullptr;
   if ((seg_pad & 3) || (adam_numel % (4L * world))) return -1;
   const long shard = adam_numel / world;
   const long lo0 = rank * seg_pad, hi0 = lo0 + seg_pad;
@@ -158,7 +235,7 @@ extern "C" int imf_comm_reduce(void* const* arena_ptrs, void* const* flag_ptrs, 
   if (blocks > 148 * 2) blocks = 148 * 2;
   if (blocks < 1) blocks = 1;
   comm_reduce_kernel<<<(unsigned)blocks, 512, 0, (cudaStream_t)stream>>>(
-      p, static_cast<const float*>(mc_arena), rank, world, lo0, hi0, lo1, hi1, epoch, status);
+      p, static_cast<const float*>(mc_arena), rank, world, lo0, hi0, lo1, hi1, epoch, status, nrm);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -188,5 +265,28 @@ extern "C" int imf_comm_barrier(void* const* arena_ptrs, void* const* flag_ptrs,
   CommPeers p;
   if (fill(p, arena_ptrs, flag_ptrs, world)) return -1;
   comm_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(p, rank, world, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Muon weight update with the update all-gather fused in: u_ptrs are the peer pointers of the
+// update arena (bf16 or fp32, owner-major segments of seg_pad elements), segs the device table
+// of nseg parameters {start, numel, 1 - lr wd, lr * scale}.
+extern "C" int imf_comm_muon_apply(void* const* u_ptrs, void* const* flag_ptrs, int rank, int world,
+                                   long seg_pad, float* p, float* ema, const void* segs, int nseg,
+                                   long max_numel, float ema_w, const float* clip, int upd_bf16,
+                                   int epoch, int* status, void* stream) {
+  if (nseg <= 0) return 0;
+  CommPeers peers;
+  if (fill(peers, u_ptrs, flag_ptrs, world)) return -1;
+  long bx = (max_numel + 1023) / 1024;
+  if (bx > 256) bx = 256;
+  if (bx < 1) bx = 1;
+  dim3 grid((unsigned)bx, nseg);
+  if (upd_bf16)
+    comm_muon_apply_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        peers, rank, world, seg_pad, p, ema, (const Seg*)segs, ema_w, clip, epoch, status);
+  else
+    comm_muon_apply_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        peers, rank, world, seg_pad, p, ema, (const Seg*)segs, ema_w, clip, epoch, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

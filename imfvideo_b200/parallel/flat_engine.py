@@ -225,13 +225,16 @@ class FlatEngine(GradSync):
 
     @torch.no_grad()
     def clip_grad_norm_(self, max_norm: float) -> torch.Tensor:
-        own = self.G[self.rank * self.seg_pad:(self.rank + 1) * self.seg_pad]
-        sq = own.double().pow(2).sum()
-        if self.world > 1:
-            sq = sq.reshape(1)
-            dist.all_reduce(sq, op=dist.ReduceOp.SUM)
-            sq = sq[0]
-        sq = sq + self.G[self.muon_total:].double().pow(2).sum()
+        if self.world > 1 and self.comm is not None:
+            sq = self.comm.grad_sq_norm()       # accumulated by the reduce kernel itself
+        else:
+            own = self.G[self.rank * self.seg_pad:(self.rank + 1) * self.seg_pad]
+            sq = own.double().pow(2).sum()
+            if self.world > 1:
+                sq = sq.reshape(1)
+                dist.all_reduce(sq, op=dist.ReduceOp.SUM)
+                sq = sq[0]
+            sq = sq + self.G[self.muon_total:].double().pow(2).sum()
         norm = sq.sqrt().float()
         finite = torch.isfinite(norm)
         coef = (max_norm / (norm + 1e-6)).clamp(max=1.0)
@@ -299,7 +302,8 @@ class FlatEngine(GradSync):
                                                   dtype=g0["ns_dtype"], coeffs=coeffs)
                 own_u[lo:lo + cnt * n * m].view(cnt, n, m).copy_(upd)
                 j = k
-            if self.world > 1:
+            fused_gather = self.world > 1 and self.comm is not None and use_k
+            if self.world > 1 and not fused_gather:
                 if self.comm is not None:
                     self.comm.all_gather_updates()
                 elif dist.get_backend() == "nccl":
@@ -309,7 +313,11 @@ class FlatEngine(GradSync):
                     dist.all_gather(parts, own_u.clone())
                     for q, part in enumerate(parts):
                         self.U[q * self.seg_pad:(q + 1) * self.seg_pad].copy_(part)
-            if use_k:
+            if fused_gather:
+                # the update all-gather happens inside the apply kernel (peer loads)
+                self.comm.apply_muon_updates(self.P, self.E, self._muon_seg_dev, len(self.muon),
+                                             self._max_muon, float(self.ema_w), self.clip)
+            elif use_k:
                 self._K._check(self._lib.imf_muon_apply(
                     self.P.data_ptr(), self.U.data_ptr(), int(self.upd_dtype == torch.bfloat16),
                     self.E.data_ptr() if self.E is not None else None,
