@@ -227,7 +227,7 @@ def load_config_dict(cfg: Config, tree: Dict[str, Any]) -> Config:
 
 
 def parse_cli(argv: Iterable[str], cfg: Optional[Config] = None) -> Config:
-    """``--config file.yaml`` and/or ``group.key=value`` tokens."""
+    """``--config file.yaml``, ``--preset name`` and/or ``group.key=value`` tokens."""
     cfg = config if cfg is None else cfg
     argv = list(argv)
     i = 0
@@ -238,6 +238,10 @@ def parse_cli(argv: Iterable[str], cfg: Optional[Config] = None) -> Config:
 
             with open(argv[i + 1]) as fh:
                 apply_overrides(cfg, yaml.safe_load(fh) or {})
+            i += 2
+            continue
+        if tok == "--preset":
+            load_config_dict(cfg, config_as_dict(preset(argv[i + 1])))
             i += 2
             continue
         if "=" not in tok:

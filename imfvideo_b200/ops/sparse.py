@@ -23,6 +23,47 @@ if K._has("imf_attn_sparse_fwd"):
     _lib.imf_attn_sparse_fwd.argtypes = [vp] * 16 + [ci] * 5 + [vp, c64, c64, c64, cf, ci, ci, vp, vp]
 
 
+if K._has("imf_build_tile_lut"):
+    _lib.imf_build_tile_lut.restype = ci
+    _lib.imf_build_tile_lut.argtypes = [vp] * 5 + [ci] * 7 + [vp]
+    _lib.imf_build_kv_lists.restype = ci
+    _lib.imf_build_kv_lists.argtypes = [vp] * 3 + [ci] * 5 + [vp]
+
+
+def route_tables(sel: torch.Tensor, qblk: int, L: int):
+    """Device-built routing tables from the selection ``sel`` (B, H, Mb, T): the per-tile
+    key-block lists of ``build_tile_lut`` (ascending, -1 padded), their flags, the entry
+    counts, and the (B, H, n_kvt, n_mt) nibble matrix the inverted lists are made from.
+    One launch, no host synchronisation."""
+    B, H, Mb, T = sel.shape
+    sel = sel.to(torch.int32).contiguous()
+    n_mt = -(-L // 128)
+    tmax = T * (128 // qblk)
+    dev = sel.device
+    lut = torch.empty(B, H, n_mt, tmax, dtype=torch.int32, device=dev)
+    flags = torch.empty(B, H, n_mt, tmax, dtype=torch.uint8, device=dev)
+    cnt = torch.empty(B, H, n_mt, dtype=torch.int32, device=dev)
+    fm = torch.empty(B, H, n_mt, n_mt, dtype=torch.uint8, device=dev)
+    K._check(_lib.imf_build_tile_lut(K._ptr(sel), K._ptr(lut), K._ptr(flags), K._ptr(cnt),
+                                     K._ptr(fm), B, H, Mb, T, qblk, L, tmax, K._stream()),
+             "imf_build_tile_lut")
+    K.LAUNCHES.count += 1
+    return lut, flags, cnt, fm
+
+
+def kv_lists(fm: torch.Tensor):
+    """Inverted lists for the backward kernel from the nibble matrix of ``route_tables``:
+    (qlist int32 (B,H,n_kvt,n_mt) padded with -1, qflags uint8).  The list stride is the
+    static bound n_mt, so no host read of the longest list is needed."""
+    B, H, n_kvt, n_mt = fm.shape
+    qlist = torch.empty(B, H, n_kvt, n_mt, dtype=torch.int32, device=fm.device)
+    qflags = torch.empty(B, H, n_kvt, n_mt, dtype=torch.uint8, device=fm.device)
+    K._check(_lib.imf_build_kv_lists(K._ptr(fm), K._ptr(qlist), K._ptr(qflags), B, H, n_kvt, n_mt,
+                                     n_mt, K._stream()), "imf_build_kv_lists")
+    K.LAUNCHES.count += 1
+    return qlist, qflags
+
+
 def quantize_blocks(x: torch.Tensor, block: int, want_q: bool = True, want_fq: bool = False):
     """x: (B, L, H, 64) bf16 -> (int8 (B,L,H,64) | None, scales (B,H,nblk) fp32,
     de-quantised bf16 copy | None)."""
@@ -73,7 +114,8 @@ def build_tile_lut(sel: torch.Tensor, qblk: int) -> Tuple[torch.Tensor, torch.Te
 
 
 def sparse_fwd(q, k, v, dq, dk, dv, lut, flags, qblk: int, int8: bool, quant_p: bool,
-               need_lse: bool = True, scale: Optional[float] = None):
+               need_lse: bool = True, scale: Optional[float] = None,
+               cnt: Optional[torch.Tensor] = None):
     """Block-sparse softmax branch: (o_s, do_s | None, lse | None).
     q, k, v (+ tangents): (B, L, H, 64) bf16, token order = routing order."""
     B, L, H, D = q.shape
@@ -96,8 +138,8 @@ def sparse_fwd(q, k, v, dq, dk, dv, lut, flags, qblk: int, int8: bool, quant_p: 
     do = torch.empty_like(o) if tang else None
     lse = torch.empty(B, H, L, dtype=torch.float32, device=q.device) if need_lse else None
     need_qk = tang or not int8
-    # entries per list = position of the first -1
-    cnt = (lut >= 0).to(torch.int32).cumprod(-1).sum(-1, dtype=torch.int32).contiguous()
+    if cnt is None:     # entries per list = position of the first -1
+        cnt = (lut >= 0).to(torch.int32).cumprod(-1).sum(-1, dtype=torch.int32).contiguous()
     rc = _lib.imf_attn_sparse_fwd(
         K._ptr(q8), K._ptr(k8), K._ptr(qs), K._ptr(ks),
         K._ptr(ts[0]) if need_qk else None, K._ptr(ts[1]) if need_qk else None, K._ptr(ts[2]),

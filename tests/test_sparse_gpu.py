@@ -205,3 +205,33 @@ def test_linear_branch_kernels_match_formulas():
     gk, gv = LA.backward_kv(q, k, v, gnum, gden, sel, zero, zero, blk, blk, n_comp)
     assert rel(gk, gk_r.permute(0, 2, 1, 3)) < 6e-3
     assert rel(gv, gv_r.permute(0, 2, 1, 3)) < 6e-3
+
+
+@pytest.mark.parametrize("qblk", [64, 128])
+def test_device_routing_tables_match_torch_builders(SP, qblk):
+    torch.manual_seed(5)
+    dev = "cuda"
+    B, H, L, T = 2, 3, 1500, 5
+    Mb, Nb = -(-L // qblk), -(-L // 64)
+    sel = torch.stack([torch.stack([torch.stack([torch.randperm(Nb, device=dev)[:T]
+                                                 for _ in range(Mb)]) for _ in range(H)])
+                       for _ in range(B)]).int()
+    lut_r, fl_r = SP.build_tile_lut(sel, qblk)
+    lut, fl, cnt, fm = SP.route_tables(sel, qblk, L)
+    if qblk == 128:     # the torch builder keeps the selection order, the kernel sorts
+        order = lut_r.sort(-1).indices
+        lut_r, fl_r = torch.gather(lut_r, -1, order), torch.gather(fl_r, -1, order)
+    n = lut_r.shape[-1]
+    assert torch.equal(cnt, (lut_r >= 0).sum(-1).int())
+    big = torch.iinfo(torch.int32).max
+    key = lambda t: torch.where(t < 0, torch.full_like(t, big), t).sort(-1).values
+    assert torch.equal(key(lut[..., :n]), key(lut_r))
+    valid = lut[..., :n] >= 0
+    if qblk == 64:
+        assert torch.equal(lut[..., :n][valid], lut_r[lut_r >= 0])
+        assert torch.equal(fl[..., :n][valid], fl_r[lut_r >= 0])
+    ql_r, qf_r = SP.build_kv_lists(lut_r, fl_r, L)
+    ql, qf = SP.kv_lists(fm)
+    m = ql_r.shape[-1]
+    assert bool((ql[..., m:] < 0).all())
+    assert torch.equal(ql[..., :m], ql_r) and torch.equal(qf[..., :m], qf_r)
