@@ -132,7 +132,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   volatile int* abort_flag = &s.abort_flag;
 
   if (warp >= 12) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 13) {
       // ---------------------------------------------------- TMA producer --
       if (elect_one()) {
@@ -232,7 +232,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else if (warp >= 8) {
     // ------------------------------------------ dQ tile -> global reduction --
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
     const int wl = warp & 3;
     const uint32_t tb = tmem_addr(tmem, wl * 32, BC_DQ);
     bool ok = true;
@@ -279,7 +279,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (threadIdx.x == 8 * 32) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
     // ---------------------------------------------------- exp / dS math ----
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
     const int wg = warp >> 2;           // column half: q columns [64 wg, 64 wg + 64)
     const int wl = warp & 3;
     const int row = wl * 32 + lane;     // kv row of this thread (TMEM lane)
