@@ -285,6 +285,7 @@ def preset(name: str) -> Config:
         m.hidden_size, m.depth, m.aux_head_depth, m.num_heads = 1024, 24, 4, 16
         m.kv_lora_rank = 512
         m.max_params = 600_000_000
+        m.grad_checkpoint = False          # activations of all 28 blocks fit in 180 GB
         d.latent_frames, d.latent_size = 21, (60, 104)
         c.loss.autocast_bf16 = True
     elif name == "wan1p3b":
