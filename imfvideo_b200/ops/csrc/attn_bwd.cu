@@ -110,13 +110,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&s.q_empty[i], 1);
     }
     mbar_init(&s.s_full, 1);
-    mbar_init(&s.s_taken, 256);
-    mbar_init(&s.p_ready, 256);
+    mbar_init(&s.s_taken, 8);      // one arrival per exp warp
+    mbar_init(&s.p_ready, 8);
     mbar_init(&s.p_free, 1);
     mbar_init(&s.ds_free[0], 1);
     mbar_init(&s.ds_free[1], 1);
     mbar_init(&s.dq_full, 1);
-    mbar_init(&s.dq_free, 128);
+    mbar_init(&s.dq_free, 4);
     mbar_init(&s.final_bar, 1);
     s.abort_flag = 0;
     fence_barrier_init();
@@ -246,7 +246,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld32(tb + 32, r + 32);
       tc_wait_ld();
       tc_fence_before();
-      mbar_arrive(&s.dq_free);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.dq_free);
       // stage the tile in shared memory (plain [128][64] fp32) and let TMA add it to
       // the fp32 accumulator in global memory: coalesced, asynchronous, rows >= L clipped
       if (i > 0) {
@@ -300,7 +301,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld32(tb + BC_DP + wg * 64 + 32, dp + 32);
       tc_wait_ld();
       tc_fence_before();
-      mbar_arrive(&s.s_taken);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.s_taken);
       // the stats of this q tile arrived with its q_full stage (s_full implies it)
       const float4* lse4 = reinterpret_cast<const float4*>(s.lse2[st] + wg * 64);
       const float4* dl4 = reinterpret_cast<const float4*>(s.delta[st] + wg * 64);
@@ -350,7 +352,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_wait_st();
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&s.p_ready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.p_ready);
     }
     // ---- epilogue: WG0 stores dK (scaled), WG1 stores dV ----
     if (ok && n_q > 0) ok = mbar_wait(&s.final_bar, 0, abort_flag, p.status, STATUS_TIMEOUT_MMA);
