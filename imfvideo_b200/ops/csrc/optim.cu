@@ -51,6 +51,32 @@ __global__ void muon_apply_kernel(float* __restrict__ p, const UT* __restrict__ 
                                   long upd_offset, float ema_w, const float* __restrict__ clip) {
   if (clip && clip[1] != 0.f) return;
   const Seg s = segs[blockIdx.y];
+  if (((s.start | s.numel | upd_offset) & 3) == 0) {   // four elements per thread and access
+    for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < s.numel;
+         i += (long)gridDim.x * blockDim.x * 4) {
+      const long j = s.start + i;
+      float u[4];
+      if constexpr (sizeof(UT) == 2) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(upd + (j - upd_offset));
+        u[0] = __uint_as_float(raw.x << 16); u[1] = __uint_as_float(raw.x & 0xffff0000u);
+        u[2] = __uint_as_float(raw.y << 16); u[3] = __uint_as_float(raw.y & 0xffff0000u);
+      } else {
+        const float4 raw = *reinterpret_cast<const float4*>(upd + (j - upd_offset));
+        u[0] = raw.x; u[1] = raw.y; u[2] = raw.z; u[3] = raw.w;
+      }
+      float4 pv = *reinterpret_cast<float4*>(p + j);
+      pv.x = pv.x * s.a - s.b * u[0]; pv.y = pv.y * s.a - s.b * u[1];
+      pv.z = pv.z * s.a - s.b * u[2]; pv.w = pv.w * s.a - s.b * u[3];
+      *reinterpret_cast<float4*>(p + j) = pv;
+      if (ema) {
+        float4 ev = *reinterpret_cast<float4*>(ema + j);
+        ev.x += ema_w * (pv.x - ev.x); ev.y += ema_w * (pv.y - ev.y);
+        ev.z += ema_w * (pv.z - ev.z); ev.w += ema_w * (pv.w - ev.w);
+        *reinterpret_cast<float4*>(ema + j) = ev;
+      }
+    }
+    return;
+  }
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < s.numel;
        i += (long)gridDim.x * blockDim.x) {
     const long j = s.start + i;
