@@ -11,8 +11,9 @@
 // models/triton_block_jvp.py:228-346) and the FA/SDPA primal forward.
 //
 // Work item = NT 128-row query tiles that share every K/V tile, of one (batch,
-// head): NT = 3 tiles against 64-row K/V tiles in the primal kernel, 2 tiles
-// in the tangent kernel.  Warps 4t .. 4t+3: softmax + O-correction + epilogue
+// head): NT = 3 tiles against 64-row K/V tiles in the primal kernel (2 tiles
+// against 128-row K/V tiles when three would leave SMs without an item), 2
+// tiles in the tangent kernel.  Warps 4t .. 4t+3: softmax + O-correction + epilogue
 // of tile t (one query row per thread, rows live in TMEM lanes); then one warp
 // with the single-thread tcgen05.mma issuer, one TMA producer warp and two
 // warps that only donate registers (setmaxnreg).  The tiles take turns: while
@@ -41,9 +42,6 @@ namespace imf {
 
 constexpr int ATT_HD = 64;
 constexpr int ATT_TILE_M = 128;
-#ifndef IMF_ATT_PRIMAL_NT
-#define IMF_ATT_PRIMAL_NT 3
-#endif
 
 // Work item = NT query tiles of 128 rows that share every K/V tile.
 //   tangent kernel : NT 2, K/V tiles of 64 rows, TMEM per tile S|dS|O|dO
@@ -52,9 +50,9 @@ constexpr int ATT_TILE_M = 128;
 //                    NT 4, K/V tiles of 64 rows, row sum in registers
 // More tiles in flight put more softmax warps on each scheduler (the softmax
 // warps are bound by instruction issue and dependency latency, not by a pipe).
-template <bool TANGENT>
+template <bool TANGENT, int NTP>
 struct AttCfg {
-  static constexpr int NT = TANGENT ? 2 : IMF_ATT_PRIMAL_NT;
+  static constexpr int NT = TANGENT ? 2 : NTP;
   static constexpr int ITEM_M = NT * ATT_TILE_M;
   static constexpr int BN = (TANGENT || NT > 2) ? 64 : 128;
   static constexpr int NQ = TANGENT ? 2 : 1;       // q + dq
@@ -88,14 +86,14 @@ struct AttCfg {
 
 // scratch record of one half of a split item: [ITEM_M][ACC] accumulators,
 // then m, l, mu per row
-template <bool TANGENT>
+template <bool TANGENT, int NTP>
 constexpr size_t att_part_floats() {
-  return (size_t)AttCfg<TANGENT>::ITEM_M * (AttCfg<TANGENT>::ACC + 3);
+  return (size_t)AttCfg<TANGENT, NTP>::ITEM_M * (AttCfg<TANGENT, NTP>::ACC + 3);
 }
 
-template <bool TANGENT>
+template <bool TANGENT, int NTP>
 struct AttSmem {
-  using C = AttCfg<TANGENT>;
+  using C = AttCfg<TANGENT, NTP>;
   alignas(1024) uint8_t q[C::NQ][C::NT][ATT_TILE_M * 128];           // [q|dq][tile]
   alignas(1024) uint8_t kv[C::STAGES][C::NKV][C::BN * 128];          // k, v, dk, dv
   alignas(1024) uint8_t ones[C::ONES ? C::BN * 128 : 1024];          // bf16 1.0 panel
@@ -152,16 +150,16 @@ __device__ __forceinline__ bool get_segment(const AttParams& p, int c, int G, in
   return true;
 }
 
-template <bool TANGENT>
-__global__ void __launch_bounds__(AttCfg<TANGENT>::THREADS, 1)
+template <bool TANGENT, int NTP>
+__global__ void __launch_bounds__(AttCfg<TANGENT, NTP>::THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_dq,
                 const __grid_constant__ CUtensorMap tm_dk,
                 const __grid_constant__ CUtensorMap tm_dv, const AttParams p) {
-  using C = AttCfg<TANGENT>;
+  using C = AttCfg<TANGENT, NTP>;
   constexpr int BN = C::BN;
   extern __shared__ uint8_t smem_raw[];
-  auto& s = *reinterpret_cast<AttSmem<TANGENT>*>(
+  auto& s = *reinterpret_cast<AttSmem<TANGENT, NTP>*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, G = gridDim.x;
@@ -504,7 +502,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           p.lse[((int64_t)b * p.H + h) * p.L + q_row] = m_used * p.scale + __logf(l_tot);
       } else {
         // partial result of a split item: raw accumulators + (m, l, mu)
-        float* part = p.scratch + ((size_t)sg.slot * 2 + sg.part) * att_part_floats<TANGENT>();
+        float* part = p.scratch + ((size_t)sg.slot * 2 + sg.part) * att_part_floats<TANGENT, NTP>();
         float* acc = part + (size_t)row_in_item * C::ACC;
 #pragma unroll
         for (int c = 0; c < C::ACC; c += 32) {
@@ -536,9 +534,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // Merge the two halves of every split item (one CTA per share boundary).
-template <bool TANGENT>
-__global__ void __launch_bounds__(AttCfg<TANGENT>::ITEM_M) attn_fwd_combine_kernel(const AttParams p, int G) {
-  using C = AttCfg<TANGENT>;
+template <bool TANGENT, int NTP>
+__global__ void __launch_bounds__(AttCfg<TANGENT, NTP>::ITEM_M)
+attn_fwd_combine_kernel(const AttParams p, int G) {
+  using C = AttCfg<TANGENT, NTP>;
   const int c = blockIdx.x;              // boundary between CTA c and c + 1
   const long bound = (long)(c + 1) * p.total_iters / G;
   if (bound % p.n_kv == 0) return;       // boundary falls on an item start: nothing was split
@@ -548,8 +547,8 @@ __global__ void __launch_bounds__(AttCfg<TANGENT>::ITEM_M) attn_fwd_combine_kern
   const int r = threadIdx.x;
   const int q_row = qb * C::ITEM_M + r;
   if (q_row >= p.L) return;
-  const float* pa = p.scratch + ((size_t)c * 2 + 0) * att_part_floats<TANGENT>();
-  const float* pb = p.scratch + ((size_t)c * 2 + 1) * att_part_floats<TANGENT>();
+  const float* pa = p.scratch + ((size_t)c * 2 + 0) * att_part_floats<TANGENT, NTP>();
+  const float* pb = p.scratch + ((size_t)c * 2 + 1) * att_part_floats<TANGENT, NTP>();
   const float* sa = pa + (size_t)C::ITEM_M * C::ACC;
   const float* sb = pb + (size_t)C::ITEM_M * C::ACC;
   const float ma = sa[r], mb = sb[r];
@@ -595,11 +594,19 @@ static int att_grid(int n_items) {
   return n_items < sms ? n_items : sms;
 }
 
-template <bool TANGENT>
+// Query tiles per work item of the primal kernel: three, unless that leaves SMs without an
+// item while two tiles per item would not (problems of about one wave).
+static int primal_nt(int B, int L, int H) {
+  const int items3 = ((L + 383) / 384) * H * B, items2 = ((L + 255) / 256) * H * B;
+  const int sms = att_grid(1 << 30);
+  return (items3 < sms && items2 > items3) ? 2 : 3;
+}
+
+template <bool TANGENT, int NTP>
 static int launch_attn_fwd(const void* q, const void* k, const void* v, const void* dq,
                            const void* dk, const void* dv, const int64_t* strides, AttParams prm,
                            size_t scratch_bytes, cudaStream_t stream) {
-  using C = AttCfg<TANGENT>;
+  using C = AttCfg<TANGENT, NTP>;
   CUtensorMap mq, mk, mv, mdq, mdk, mdv;
   int rc;
   const int B = prm.B, L = prm.L, H = prm.H;
@@ -610,7 +617,7 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const vo
   const int G = att_grid(prm.n_items);
   if (G > 1 && prm.n_items > G) {
     if (prm.scratch == nullptr ||
-        scratch_bytes < (size_t)G * 2 * att_part_floats<TANGENT>() * sizeof(float))
+        scratch_bytes < (size_t)G * 2 * att_part_floats<TANGENT, NTP>() * sizeof(float))
       return IMF_ERR_ARG;
   }
   // strides: [q_sb,q_sl,q_sh, k_sb,k_sl,k_sh, v_sb,v_sl,v_sh, dq.., dk.., dv..]
@@ -629,15 +636,15 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const vo
     mdk = mk;
     mdv = mv;
   }
-  auto kern = attn_fwd_kernel<TANGENT>;
-  const size_t smem = sizeof(AttSmem<TANGENT>) + 1024;
+  auto kern = attn_fwd_kernel<TANGENT, NTP>;
+  const size_t smem = sizeof(AttSmem<TANGENT, NTP>) + 1024;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
       cudaSuccess)
     return IMF_ERR_LAUNCH;
   kern<<<G, C::THREADS, smem, stream>>>(mq, mk, mv, mdq, mdk, mdv, prm);
   if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   if (G > 1 && prm.n_items > G) {
-    attn_fwd_combine_kernel<TANGENT><<<G - 1, C::ITEM_M, 0, stream>>>(prm, G);
+    attn_fwd_combine_kernel<TANGENT, NTP><<<G - 1, C::ITEM_M, 0, stream>>>(prm, G);
     if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   }
   return IMF_OK;
@@ -648,11 +655,13 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const vo
 // Bytes of scratch the forward needs for (B, L, H): 0 when no item is split.
 extern "C" long imf_attn_fwd_scratch_bytes(int B, int L, int H, int tangent) {
   using namespace imf;
-  const int item_m = tangent ? AttCfg<true>::ITEM_M : AttCfg<false>::ITEM_M;
+  const int nt = tangent ? 2 : primal_nt(B, L, H);
+  const int item_m = nt * ATT_TILE_M;
   const int n_items = ((L + item_m - 1) / item_m) * H * B;
   const int G = att_grid(n_items);
   if (G <= 1 || n_items <= G) return 0;
-  const size_t per = tangent ? att_part_floats<true>() : att_part_floats<false>();
+  const size_t per = tangent ? att_part_floats<true, 2>()
+                             : (nt == 3 ? att_part_floats<false, 3>() : att_part_floats<false, 2>());
   return (long)((size_t)G * 2 * per * sizeof(float));
 }
 
@@ -686,10 +695,13 @@ extern "C" int imf_attn_fwd(const void* q, const void* k, const void* v, const v
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dq != nullptr) {
     if (dout == nullptr || (reinterpret_cast<uintptr_t>(dout) & 15)) return IMF_ERR_ARG;
-    return launch_attn_fwd<true>(q, k, v, dq, dk, dv, strides, prm, (size_t)scratch_bytes, st);
+    return launch_attn_fwd<true, 2>(q, k, v, dq, dk, dv, strides, prm, (size_t)scratch_bytes, st);
   }
-  return launch_attn_fwd<false>(q, k, v, nullptr, nullptr, nullptr, strides, prm,
-                                (size_t)scratch_bytes, st);
+  if (primal_nt(B, L, H) == 3)
+    return launch_attn_fwd<false, 3>(q, k, v, nullptr, nullptr, nullptr, strides, prm,
+                                     (size_t)scratch_bytes, st);
+  return launch_attn_fwd<false, 2>(q, k, v, nullptr, nullptr, nullptr, strides, prm,
+                                   (size_t)scratch_bytes, st);
 }
 
 // ---------------------------------------------------------------------------
@@ -699,7 +711,7 @@ extern "C" int imf_attn_fwd(const void* q, const void* k, const void* v, const v
 
 namespace imf {
 constexpr size_t NOALLOC_FLOATS =
-    (size_t)IMF_ATTN_NOALLOC_MAX_CTAS * 2 * ((size_t)AttCfg<false>::ITEM_M * (ATT_HD + 3));
+    (size_t)IMF_ATTN_NOALLOC_MAX_CTAS * 2 * ((size_t)AttCfg<false, 3>::ITEM_M * (ATT_HD + 3));
 // Split-item partials of the primal forward.  In host code this name is only a
 // stand-in for the symbol, not a device address: the address comes from
 // cudaGetSymbolAddress below.
@@ -711,7 +723,7 @@ extern "C" int imf_attn_fwd_noalloc(const void* q, const void* k, const void* v,
                                     const int64_t* strides, int64_t o_sb, int64_t o_sl,
                                     int64_t o_sh, float scale, int* status, void* stream) {
   using namespace imf;
-  static_assert(NOALLOC_FLOATS == (size_t)IMF_ATTN_NOALLOC_MAX_CTAS * 2 * att_part_floats<false>(),
+  static_assert(NOALLOC_FLOATS == (size_t)IMF_ATTN_NOALLOC_MAX_CTAS * 2 * att_part_floats<false, 3>(),
                 "scratch array and partial record size disagree");
   constexpr int MAX_DEVICES = 64;
   static float* scratch_of_device[MAX_DEVICES] = {nullptr};
