@@ -71,6 +71,12 @@ struct BwParams {
   const int* qlist;
   const uint8_t* qflags;
   int qmax;
+  // dense mode: the query tiles of a K/V tile are split over `qsplit` CTAs (blockIdx.z =
+  // batch * qsplit + part) to even out the last wave; each writes unscaled fp32 partial
+  // dK / dV to part[r] = (B, L, H, 64) and a second kernel adds them up
+  int qsplit;
+  float* part_dk;
+  float* part_dv;
 };
 
 IMF_DEVICE void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -93,14 +99,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   auto& s = *reinterpret_cast<BwSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                        ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kvb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kvb = blockIdx.x, h = blockIdx.y, b = blockIdx.z / p.qsplit;
+  const int qpart = blockIdx.z % p.qsplit;
   const size_t lrow = (((size_t)b * p.H + h) * gridDim.x + kvb) * (size_t)p.qmax;
   const int* qlist = p.qlist ? p.qlist + lrow : nullptr;
   const uint8_t* qflags = p.qflags ? p.qflags + lrow : nullptr;
-  int n_q = (p.L + BW_T - 1) / BW_T;
+  int n_q = (p.L + BW_T - 1) / BW_T;       // query tiles this CTA walks over
+  int q_first = 0;                          // dense: they are q_first .. q_first + n_q - 1
   if (qlist) {
     n_q = 0;
     while (n_q < p.qmax && qlist[n_q] >= 0) ++n_q;
+  } else {
+    q_first = (int)((long)qpart * n_q / p.qsplit);
+    n_q = (int)((long)(qpart + 1) * n_q / p.qsplit) - q_first;
   }
 
   if (threadIdx.x == 0) {
@@ -151,7 +162,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               !mbar_wait(&s.q_empty[st], (uint32_t)(((i / BW_QSTAGES) - 1) & 1), abort_flag,
                          p.status, STATUS_TIMEOUT_EMPTY))
             break;
-          const int qt = qlist ? qlist[i] : i;
+          const int qt = qlist ? qlist[i] : q_first + i;
           mbar_arrive_expect_tx(&s.q_full[st], 2 * BW_T * 128 + 2 * BW_T * 4);
           tma_load_4d(s.q[st], &tm_q, &s.q_full[st], 0, h, qt * BW_T, b);
           tma_load_4d(s.d_o[st], &tm_do, &s.q_full[st], 0, h, qt * BW_T, b);
@@ -272,7 +283,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               " [%0, {%2, %3, %4, %5}], [%1];"
               ::"l"(reinterpret_cast<uint64_t>(&tm_dq)),
               "r"(smem_u32(stage + pnl * (BW_T * 128))), "r"(pnl * 32), "r"(h),
-              "r"((qlist ? qlist[i] : i) * BW_T), "r"(b)
+              "r"((qlist ? qlist[i] : q_first + i) * BW_T), "r"(b)
               : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
@@ -365,22 +376,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       __nv_bfloat16* base =
           wg == 0 ? p.dk + (int64_t)b * p.dk_sb + (int64_t)kv_row * p.dk_sl + (int64_t)h * p.dk_sh
                   : p.dv + (int64_t)b * p.dv_sb + (int64_t)kv_row * p.dv_sl + (int64_t)h * p.dv_sh;
+      float* pbase = nullptr;
+      if (p.qsplit > 1)
+        pbase = (wg == 0 ? p.part_dk : p.part_dv) +
+                ((((size_t)qpart * p.B + b) * p.L + kv_row) * p.H + h) * BW_HD;
 #pragma unroll
       for (int c = 0; c < BW_HD; c += 32) {
         uint32_t r[32];
         tmem_ld32(tb + (wg == 0 ? BC_DK : BC_DV) + c, r);
         tc_wait_ld();
         if (kv_row < p.L) {
-          uint32_t ob[16];
+          if (pbase) {                       // unscaled fp32 partial of this query range
+            float4* dst = reinterpret_cast<float4*>(pbase + c);
 #pragma unroll
-          for (int e = 0; e < 16; ++e)
-            ob[e] = n_q == 0 ? 0u
-                             : pack_bf16(__uint_as_float(r[2 * e]) * mul,
-                                         __uint_as_float(r[2 * e + 1]) * mul);
-          uint4* dst = reinterpret_cast<uint4*>(base + c);
+            for (int e = 0; e < 8; ++e)
+              dst[e] = n_q == 0 ? make_float4(0.f, 0.f, 0.f, 0.f)
+                                : make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]),
+                                              __uint_as_float(r[4 * e + 2]), __uint_as_float(r[4 * e + 3]));
+          } else {
+            uint32_t ob[16];
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            dst[e] = make_uint4(ob[4 * e], ob[4 * e + 1], ob[4 * e + 2], ob[4 * e + 3]);
+            for (int e = 0; e < 16; ++e)
+              ob[e] = n_q == 0 ? 0u
+                               : pack_bf16(__uint_as_float(r[2 * e]) * mul,
+                                           __uint_as_float(r[2 * e + 1]) * mul);
+            uint4* dst = reinterpret_cast<uint4*>(base + c);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              dst[e] = make_uint4(ob[4 * e], ob[4 * e + 1], ob[4 * e + 2], ob[4 * e + 3]);
+          }
         }
       }
     }
@@ -438,6 +462,62 @@ __global__ void attn_bwd_post_kernel(const float* __restrict__ acc, __nv_bfloat1
   reinterpret_cast<uint2*>(dq)[i] = o;
 }
 
+// dk = scale * sum_r part_dk[r], dv = sum_r part_dv[r] (fixed order), rows of 64 channels.
+__global__ void attn_bwd_combine_kernel(const float* __restrict__ part_dk,
+                                        const float* __restrict__ part_dv,
+                                        __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv,
+                                        int qsplit, int B, int L, int H, int64_t dk_sb, int64_t dk_sl,
+                                        int64_t dk_sh, int64_t dv_sb, int64_t dv_sl, int64_t dv_sh,
+                                        float scale) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;     // one float4 of one row
+  const long rows = (long)B * L * H;
+  if (i >= rows * 16) return;
+  const long row = i >> 4;
+  const int c = (int)(i & 15) * 4;
+  const int h = (int)(row % H), l = (int)((row / H) % L), b = (int)(row / ((long)H * L));
+  const size_t plane = (size_t)rows * 64;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f), v = a;
+  for (int r = 0; r < qsplit; ++r) {
+    const float4 x = *reinterpret_cast<const float4*>(part_dk + r * plane + row * 64 + c);
+    const float4 y = *reinterpret_cast<const float4*>(part_dv + r * plane + row * 64 + c);
+    a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+    v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
+  }
+  uint2 o;
+  o.x = pack_bf16(a.x * scale, a.y * scale);
+  o.y = pack_bf16(a.z * scale, a.w * scale);
+  *reinterpret_cast<uint2*>(dk + b * dk_sb + (int64_t)l * dk_sl + h * dk_sh + c) = o;
+  o.x = pack_bf16(v.x, v.y);
+  o.y = pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(dv + b * dv_sb + (int64_t)l * dv_sl + h * dv_sh + c) = o;
+}
+
+// Number of CTAs the query tiles of one K/V tile are split over (dense mode): the smallest
+// of 1..3 whose last wave wastes less than 6 % on this GPU.
+static int bwd_qsplit(int B, int L, int H) {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  const long n_t = (L + BW_T - 1) / BW_T;
+  const long items = n_t * H * B;
+  int best = 1;
+  double best_w = 1e9;
+  for (int s = 1; s <= 3 && s * 8 <= n_t; ++s) {
+    const double waves = (double)items * s / sms;
+    const double w = (double)((items * s + sms - 1) / sms) / waves;
+    if (w < best_w - 0.02) {
+      best_w = w;
+      best = s;
+    }
+    if (w < 1.06) break;
+  }
+  return best;
+}
+
 static int make_map64(CUtensorMap* m, const void* ptr, int B, int L, int H, int64_t sb, int64_t sl,
                       int64_t sh) {
   uint64_t dims[4] = {(uint64_t)BW_HD, (uint64_t)H, (uint64_t)L, (uint64_t)B};
@@ -448,10 +528,13 @@ static int make_map64(CUtensorMap* m, const void* ptr, int B, int L, int H, int6
 
 }  // namespace imf
 
-// Scratch (bytes) the backward needs: fp32 dQ accumulator + padded lse2/delta.
+// Scratch (bytes) the backward needs: fp32 dQ accumulator + padded lse2/delta + (dense mode,
+// when the query tiles are split) fp32 partial dK / dV.
 extern "C" long imf_attn_bwd_scratch_bytes(int B, int L, int H) {
   const long Lp = ((L + 127) / 128) * 128;
-  return (long)B * L * H * 64 * 4 + 2 * (long)B * H * Lp * 4 + 256;
+  const int qs = imf::bwd_qsplit(B, L, H);
+  const long part = qs > 1 ? 2L * qs * B * L * H * 64 * 4 : 0;
+  return (long)B * L * H * 64 * 4 + 2 * (long)B * H * Lp * 4 + 512 + part;
 }
 
 // All tensors (B, L, H, 64) bf16; strides[0..11]: (batch,row,head) for q,k,v,do;
@@ -478,6 +561,14 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
   const size_t acc_bytes = (size_t)B * L * H * 64 * 4;
   float* lse2 = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + ((acc_bytes + 255) & ~size_t(255)));
   float* delta = lse2 + (size_t)B * H * Lp;
+  const int qsplit = qlist ? 1 : bwd_qsplit(B, L, H);
+  float* part_dk = nullptr;
+  float* part_dv = nullptr;
+  if (qsplit > 1) {
+    const uintptr_t end = (reinterpret_cast<uintptr_t>(delta + (size_t)B * H * Lp) + 255) & ~uintptr_t(255);
+    part_dk = reinterpret_cast<float*>(end);
+    part_dv = part_dk + (size_t)qsplit * B * L * H * 64;
+  }
   if (cudaMemsetAsync(dq_acc, 0, acc_bytes, st) != cudaSuccess) return IMF_ERR_LAUNCH;
   {
     const long warps = (long)B * H * Lp;
@@ -516,13 +607,24 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
   prm.qlist = qlist;
   prm.qflags = qflags;
   prm.qmax = qlist ? qmax : 0;
+  prm.qsplit = qsplit;
+  prm.part_dk = part_dk;
+  prm.part_dv = part_dv;
   const size_t smem = sizeof(BwSmem) + 1024;
   if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem) != cudaSuccess)
     return IMF_ERR_LAUNCH;
-  dim3 grid((L + BW_T - 1) / BW_T, H, B);
+  dim3 grid((L + BW_T - 1) / BW_T, H, B * qsplit);
   attn_bwd_kernel<<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, mdq, prm);
   if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
+  if (qsplit > 1) {
+    const long n = (long)B * L * H * 16;
+    attn_bwd_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+        part_dk, part_dv, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), qsplit,
+        B, L, H, dk_strides[0], dk_strides[1], dk_strides[2], dv_strides[0], dv_strides[1],
+        dv_strides[2], scale);
+    if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
+  }
   const long n4 = (long)B * L * H * 64 / 4;
   attn_bwd_post_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(
       dq_acc, static_cast<__nv_bfloat16*>(dq), n4, scale);

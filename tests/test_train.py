@@ -153,3 +153,13 @@ def test_synthetic_dataset():
     b, lb = ds[3]
     assert a.shape == (16, 4, 16, 16) and torch.equal(a, b) and la == lb == 3
     assert not torch.equal(a, ds[4][0])
+
+
+def test_cli_preset_and_overrides():
+    from imfvideo_b200 import config as C
+
+    cfg = C.parse_cli(["--preset", "d256", "optim.total_steps=7", "model.depth=3"], C.Config())
+    assert cfg.model.hidden_size == 256 and cfg.model.num_heads == 4
+    assert cfg.data.latent_size == (56, 104) and cfg.data.latent_frames == 20
+    assert cfg.optim.total_steps == 7 and cfg.model.depth == 3
+    assert cfg.model.grad_checkpoint is False
