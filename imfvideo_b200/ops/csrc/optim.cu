@@ -157,3 +157,49 @@ extern "C" int imf_adamw(float* p, const float* g, float* m, float* v, float* em
                                                       clip, ema_w);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ---------------------------------------------------------------------------
+// QK-Clip (MuonClip): for every attention module and head whose maximum logit
+// S (log2 units in `stat`) exceeded tau, the rope rows of that head in the q
+// up-projection are scaled by tau / S.  One launch for all modules; the number
+// of clipped heads and the largest logit come back in `summary` (no host
+// round trip inside).  Replaces the per-module loop of the reference
+// (reference train.py:301-350).
+// ---------------------------------------------------------------------------
+namespace imf {
+
+struct ClipMod {
+  float* w;             // (H * hd, cols) row-major weight of q_b_proj
+  const float* stat;    // (H,) max logit in log2 units
+  int H, hd, dn, cols;
+};
+
+__global__ void qk_clip_kernel(const ClipMod* __restrict__ mods, float tau_nat,
+                               float* __restrict__ summary) {
+  const ClipMod m = mods[blockIdx.y];
+  const int h = blockIdx.x;
+  if (h >= m.H) return;
+  const float s_nat = m.stat[h] * 0.6931471805599453f;
+  const float gamma = fminf(1.f, tau_nat / fmaxf(s_nat, 1e-20f));
+  if (threadIdx.x == 0) {
+    // non-negative floats order like their bit patterns
+    atomicMax(reinterpret_cast<int*>(summary + 1), __float_as_int(fmaxf(s_nat, 0.f)));
+    if (gamma < 1.f) atomicAdd(summary, 1.f);
+  }
+  if (gamma >= 1.f) return;
+  const int rows = m.hd - m.dn;
+  float* base = m.w + ((size_t)h * m.hd + m.dn) * m.cols;
+  for (int i = threadIdx.x; i < rows * m.cols; i += blockDim.x) base[i] *= gamma;
+}
+
+}  // namespace imf
+
+// mods: device array of nmod records {float* w, const float* stat, int H, hd, dn, cols};
+// summary: device float[2], zeroed by the caller (count of clipped heads, max logit in nats).
+extern "C" int imf_qk_clip(const void* mods, int nmod, int max_heads, float tau_nat, float* summary,
+                           void* stream) {
+  if (nmod <= 0) return 0;
+  qk_clip_kernel<<<dim3(max_heads, nmod), 256, 0, (cudaStream_t)stream>>>(
+      (const ClipMod*)mods, tau_nat, summary);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -164,6 +164,9 @@ def qk_clip(net, tau: float, world: int = 1) -> Tuple[int, float]:
     stats = torch.stack([m.attn_impl.logit_max_log2.float() for m in mods])   # (n, H)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    fused = _qk_clip_kernel(mods, stats, tau)
+    if fused is not None:
+        return fused
     s_nat = stats * math.log(2.0)
     gamma = (tau / s_nat.clamp_min(1e-20)).clamp(max=1.0)
     for m, g in zip(mods, gamma):
@@ -172,6 +175,47 @@ def qk_clip(net, tau: float, world: int = 1) -> Tuple[int, float]:
         w[:, dn:, :] *= g.to(w.dtype).view(-1, 1, 1)
     summary = torch.stack([(gamma < 1.0).sum().float(), s_nat.max()]).tolist()
     return int(summary[0]), float(summary[1])
+
+
+def _qk_clip_kernel(mods, stats: torch.Tensor, tau: float):
+    """All modules in one launch of the library's kernel (fp32 contiguous weights on a GPU);
+    None when that does not apply."""
+    w0 = mods[0].q_b_proj.weight
+    if not w0.is_cuda or any(m.q_b_proj.weight.dtype != torch.float32
+                             or not m.q_b_proj.weight.is_contiguous() for m in mods):
+        return None
+    try:
+        from .ops import cuda as cu
+        if not cu.available():
+            return None
+        from .ops import kernels as K
+    except Exception:
+        return None
+    if not K._has("imf_qk_clip"):
+        return None
+    import ctypes
+
+    import numpy as np
+
+    rec = np.dtype([("w", "<u8"), ("stat", "<u8"), ("H", "<i4"), ("hd", "<i4"), ("dn", "<i4"),
+                    ("cols", "<i4")])
+    stats = stats.contiguous()
+    host = np.zeros(len(mods), dtype=rec)
+    for i, m in enumerate(mods):
+        w = m.q_b_proj.weight
+        host[i] = (w.data_ptr(), stats[i].data_ptr(), m.num_heads, m.qk_head_dim,
+                   m.qk_nope_head_dim, w.shape[1])
+    table = torch.from_numpy(host.view(np.uint8).reshape(-1).copy()).to(w0.device)
+    summary = torch.zeros(2, dtype=torch.float32, device=w0.device)
+    lib = K._lib
+    lib.imf_qk_clip.restype = ctypes.c_int
+    lib.imf_qk_clip.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_float,
+                                ctypes.c_void_p, ctypes.c_void_p]
+    K._check(lib.imf_qk_clip(K._ptr(table), len(mods), max(m.num_heads for m in mods), float(tau),
+                             K._ptr(summary), K._stream()), "imf_qk_clip")
+    K.LAUNCHES.count += 1
+    n, mx = summary.tolist()
+    return int(n), float(mx)
 
 
 # --------------------------------------------------------------- trainer ---

@@ -110,3 +110,36 @@ def test_fused_block_matches_generic_composition(kernels, bs):
            and rel(g_f[n], g_g[n]) > 6e-2]
     assert not bad, bad
     assert set(g_f) >= set(g_g)
+
+
+def test_qk_clip_kernel_matches_formula():
+    """One-launch QK-Clip over all attention modules against the per-module formula."""
+    import math
+
+    from imfvideo_b200 import train as T
+    from imfvideo_b200.models import imf_dit_video as M
+
+    torch.manual_seed(0)
+    net = M.IMFDiTVideo(input_size=8, num_frames=4, patch_size=(1, 2, 2), in_channels=4,
+                        hidden_size=128, depth=3, aux_head_depth=1, num_heads=2,
+                        num_classes=10).cuda()
+    mods = [m for m in net.modules() if isinstance(m, M.MLAAttention)]
+    before = [m.q_b_proj.weight.detach().clone() for m in mods]
+    tau = 5.0
+    for i, m in enumerate(mods):
+        class _Impl:
+            pass
+        impl = _Impl()
+        impl.logit_max_log2 = torch.tensor([3.0 + 4.0 * i, 12.0 - i], device="cuda")
+        m.attn_impl = impl
+    n, mx = T.qk_clip(net, tau, world=1)
+    exp_n, exp_mx = 0, 0.0
+    for m, w0 in zip(mods, before):
+        s_nat = m.attn_impl.logit_max_log2 * math.log(2.0)
+        gamma = (tau / s_nat).clamp(max=1.0)
+        exp_n += int((gamma < 1).sum())
+        exp_mx = max(exp_mx, float(s_nat.max()))
+        ref = w0.view(m.num_heads, m.qk_head_dim, -1).clone()
+        ref[:, m.qk_nope_head_dim:, :] *= gamma.view(-1, 1, 1)
+        assert torch.allclose(m.q_b_proj.weight.view_as(ref), ref, rtol=1e-6, atol=0)
+    assert n == exp_n and abs(mx - exp_mx) < 1e-4
