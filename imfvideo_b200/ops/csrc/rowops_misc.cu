@@ -340,14 +340,23 @@ __global__ void __launch_bounds__(ROW_THREADS) outgate_bwd_kernel(const EwArgs a
   }
 }
 
-// situ(g) = beta tanh(g/beta) sigmoid(g); up' = lbeta tanh(up/lbeta)
-__device__ __forceinline__ void situ1(float g, float u, float beta, float lbeta, int has_lb,
-                                      float& a, float& da_dg, float& up, float& dup_du) {
-  const float th = tanhf(g / beta), sg = sigmoidf_(g);
+// situ(g) = beta tanh(g/beta) sigmoid(g); up' = lbeta tanh(up/lbeta).  The hyperbolic
+// tangent is the hardware approximation (one MUFU op, error below bf16 resolution) and the
+// sigmoid is written through it, sigmoid(x) = 0.5 tanh(x / 2) + 0.5: three special-function
+// ops per element, so the kernels below stay memory-bound.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void situ1(float g, float u, float beta, float inv_beta, float lbeta,
+                                      float inv_lbeta, int has_lb, float& a, float& da_dg,
+                                      float& up, float& dup_du) {
+  const float th = tanh_fast(g * inv_beta), sg = fmaf(0.5f, tanh_fast(0.5f * g), 0.5f);
   a = beta * th * sg;
   da_dg = (1.f - th * th) * sg + beta * th * sg * (1.f - sg);
   if (has_lb) {
-    const float tu = tanhf(u / lbeta);
+    const float tu = tanh_fast(u * inv_lbeta);
     up = lbeta * tu;
     dup_du = 1.f - tu * tu;
   } else {
@@ -356,57 +365,108 @@ __device__ __forceinline__ void situ1(float g, float u, float beta, float lbeta,
   }
 }
 
-// a0 = [gate | up] rows of width 2*D (up at column offset ld_b), out width D
+__device__ __forceinline__ void unpack8(const uint4 v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// a0 = [gate | up] rows of width 2*D (up at column offset ld_b), out width D.
+// VEC elements per thread and access (8 = 16-byte accesses, 2 = any even layout).
+template <int VEC>
 __global__ void __launch_bounds__(ROW_THREADS) situ_fwd_kernel(const EwArgs a) {
-  const long n2 = (long)a.rows * (a.D / 2);
-  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n2;
-       i += (long)gridDim.x * blockDim.x) {
-    const int row = (int)(i / (a.D / 2)), c = (int)(i % (a.D / 2)) * 2;
-    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(a.a0 + (size_t)row * a.ld_a + c);
-    const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(a.b0 + (size_t)row * a.ld_a + c);
-    const float g[2] = {__low2float(g2), __high2float(g2)}, u[2] = {__low2float(u2), __high2float(u2)};
-    float y[2], dy[2] = {0.f, 0.f};
-    float dg[2] = {0.f, 0.f}, du[2] = {0.f, 0.f};
-    if (a.has_t) {
-      const __nv_bfloat162 dg2 = *reinterpret_cast<const __nv_bfloat162*>(a.da0 + (size_t)row * a.ld_a + c);
-      const __nv_bfloat162 du2 = *reinterpret_cast<const __nv_bfloat162*>(a.db0 + (size_t)row * a.ld_a + c);
-      dg[0] = __low2float(dg2); dg[1] = __high2float(dg2);
-      du[0] = __low2float(du2); du[1] = __high2float(du2);
+  const int per_row = a.D / VEC;
+  const int n = a.rows * per_row;
+  const float inv_beta = 1.f / a.beta, inv_lbeta = a.has_lbeta ? 1.f / a.lbeta : 0.f;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int row = i / per_row, c = (i - row * per_row) * VEC;
+    const size_t ia = (size_t)row * a.ld_a + c, io = (size_t)row * a.ld_o + c;
+    float g[VEC], u[VEC], dg[VEC], du[VEC], y[VEC], dy[VEC];
+    if (VEC == 8) {
+      unpack8(*reinterpret_cast<const uint4*>(a.a0 + ia), g);
+      unpack8(*reinterpret_cast<const uint4*>(a.b0 + ia), u);
+      if (a.has_t) {
+        unpack8(*reinterpret_cast<const uint4*>(a.da0 + ia), dg);
+        unpack8(*reinterpret_cast<const uint4*>(a.db0 + ia), du);
+      }
+    } else {
+      const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(a.a0 + ia);
+      const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(a.b0 + ia);
+      g[0] = __low2float(g2); g[1] = __high2float(g2);
+      u[0] = __low2float(u2); u[1] = __high2float(u2);
+      if (a.has_t) {
+        const __nv_bfloat162 dg2 = *reinterpret_cast<const __nv_bfloat162*>(a.da0 + ia);
+        const __nv_bfloat162 du2 = *reinterpret_cast<const __nv_bfloat162*>(a.db0 + ia);
+        dg[0] = __low2float(dg2); dg[1] = __high2float(dg2);
+        du[0] = __low2float(du2); du[1] = __high2float(du2);
+      }
     }
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
+    for (int e = 0; e < VEC; ++e) {
       float av, dav, up, dup;
-      situ1(g[e], u[e], a.beta, a.lbeta, a.has_lbeta, av, dav, up, dup);
+      situ1(g[e], u[e], a.beta, inv_beta, a.lbeta, inv_lbeta, a.has_lbeta, av, dav, up, dup);
       y[e] = av * up;
-      dy[e] = dav * dg[e] * up + av * dup * du[e];
+      dy[e] = a.has_t ? dav * dg[e] * up + av * dup * du[e] : 0.f;
     }
-    *reinterpret_cast<__nv_bfloat162*>(a.out + (size_t)row * a.ld_o + c) = __floats2bfloat162_rn(y[0], y[1]);
-    if (a.has_t)
-      *reinterpret_cast<__nv_bfloat162*>(a.dout + (size_t)row * a.ld_o + c) =
-          __floats2bfloat162_rn(dy[0], dy[1]);
+    if (VEC == 8) {
+      *reinterpret_cast<uint4*>(a.out + io) = pack8(y);
+      if (a.has_t) *reinterpret_cast<uint4*>(a.dout + io) = pack8(dy);
+    } else {
+      *reinterpret_cast<__nv_bfloat162*>(a.out + io) = __floats2bfloat162_rn(y[0], y[1]);
+      if (a.has_t)
+        *reinterpret_cast<__nv_bfloat162*>(a.dout + io) = __floats2bfloat162_rn(dy[0], dy[1]);
+    }
   }
 }
 
+template <int VEC>
 __global__ void __launch_bounds__(ROW_THREADS) situ_bwd_kernel(const EwArgs a) {
-  const long n2 = (long)a.rows * (a.D / 2);
-  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n2;
-       i += (long)gridDim.x * blockDim.x) {
-    const int row = (int)(i / (a.D / 2)), c = (int)(i % (a.D / 2)) * 2;
-    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(a.a0 + (size_t)row * a.ld_a + c);
-    const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(a.b0 + (size_t)row * a.ld_a + c);
-    const __nv_bfloat162 go2 = *reinterpret_cast<const __nv_bfloat162*>(a.gout + (size_t)row * a.ld_o + c);
-    const float g[2] = {__low2float(g2), __high2float(g2)}, u[2] = {__low2float(u2), __high2float(u2)};
-    const float go[2] = {__low2float(go2), __high2float(go2)};
-    float gg[2], gu[2];
+  const int per_row = a.D / VEC;
+  const int n = a.rows * per_row;
+  const float inv_beta = 1.f / a.beta, inv_lbeta = a.has_lbeta ? 1.f / a.lbeta : 0.f;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int row = i / per_row, c = (i - row * per_row) * VEC;
+    const size_t ia = (size_t)row * a.ld_a + c, io = (size_t)row * a.ld_o + c;
+    const size_t ig = (size_t)row * a.ld_ga + c;
+    float g[VEC], u[VEC], go[VEC], gg[VEC], gu[VEC];
+    if (VEC == 8) {
+      unpack8(*reinterpret_cast<const uint4*>(a.a0 + ia), g);
+      unpack8(*reinterpret_cast<const uint4*>(a.b0 + ia), u);
+      unpack8(*reinterpret_cast<const uint4*>(a.gout + io), go);
+    } else {
+      const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(a.a0 + ia);
+      const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(a.b0 + ia);
+      const __nv_bfloat162 go2 = *reinterpret_cast<const __nv_bfloat162*>(a.gout + io);
+      g[0] = __low2float(g2); g[1] = __high2float(g2);
+      u[0] = __low2float(u2); u[1] = __high2float(u2);
+      go[0] = __low2float(go2); go[1] = __high2float(go2);
+    }
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
+    for (int e = 0; e < VEC; ++e) {
       float av, dav, up, dup;
-      situ1(g[e], u[e], a.beta, a.lbeta, a.has_lbeta, av, dav, up, dup);
+      situ1(g[e], u[e], a.beta, inv_beta, a.lbeta, inv_lbeta, a.has_lbeta, av, dav, up, dup);
       gg[e] = go[e] * dav * up;
       gu[e] = go[e] * av * dup;
     }
-    *reinterpret_cast<__nv_bfloat162*>(a.ga + (size_t)row * a.ld_ga + c) = __floats2bfloat162_rn(gg[0], gg[1]);
-    *reinterpret_cast<__nv_bfloat162*>(a.gb + (size_t)row * a.ld_ga + c) = __floats2bfloat162_rn(gu[0], gu[1]);
+    if (VEC == 8) {
+      *reinterpret_cast<uint4*>(a.ga + ig) = pack8(gg);
+      *reinterpret_cast<uint4*>(a.gb + ig) = pack8(gu);
+    } else {
+      *reinterpret_cast<__nv_bfloat162*>(a.ga + ig) = __floats2bfloat162_rn(gg[0], gg[1]);
+      *reinterpret_cast<__nv_bfloat162*>(a.gb + ig) = __floats2bfloat162_rn(gu[0], gu[1]);
+    }
   }
 }
 
@@ -568,10 +628,20 @@ extern "C" int imf_elementwise(int op, void** p, const int* dims, float beta, fl
       outgate_bwd_kernel<<<grid, ROW_THREADS, 0, st>>>(a);
     }
   } else if (op == 1) {
-    if (a.ld_a % 2 || a.ld_o % 2) return -1;
-    const int grid = ew_grid((long)a.rows * a.D / 2);
-    if (!bwd) situ_fwd_kernel<<<grid, ROW_THREADS, 0, st>>>(a);
-    else situ_bwd_kernel<<<grid, ROW_THREADS, 0, st>>>(a);
+    if (a.ld_a % 2 || a.ld_o % 2 || (long)a.rows * a.D / 2 > 0x7fffffffL) return -1;
+    // 16-byte accesses when every row start and the column split are 16-byte aligned
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    bool v8 = a.D % 8 == 0 && a.ld_a % 8 == 0 && a.ld_o % 8 == 0 && al16(a.a0) && al16(a.b0);
+    if (!bwd) v8 = v8 && al16(a.out) && (!a.has_t || (al16(a.da0) && al16(a.db0) && al16(a.dout)));
+    else v8 = v8 && a.ld_ga % 8 == 0 && al16(a.gout) && al16(a.ga) && al16(a.gb);
+    const int grid = ew_grid((long)a.rows * a.D / (v8 ? 8 : 2));
+    if (!bwd) {
+      if (v8) situ_fwd_kernel<8><<<grid, ROW_THREADS, 0, st>>>(a);
+      else situ_fwd_kernel<2><<<grid, ROW_THREADS, 0, st>>>(a);
+    } else {
+      if (v8) situ_bwd_kernel<8><<<grid, ROW_THREADS, 0, st>>>(a);
+      else situ_bwd_kernel<2><<<grid, ROW_THREADS, 0, st>>>(a);
+    }
   } else if (op == 2) {
     if (!bwd) {
       scale_add_fwd_kernel<<<ew_grid((long)a.rows * a.D / 4), ROW_THREADS, 0, st>>>(a);
