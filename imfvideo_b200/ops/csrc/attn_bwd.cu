@@ -336,21 +336,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         uint32_t pk[16], dk_[16];
+        if (live) {        // warp-uniform: a warp's 32 rows and 64 columns lie in one quadrant
 #pragma unroll
-        for (int c = 0; c < 32; c += 4) {
-          const int cg = hh * 32 + c;
-          const float4 l4 = lse4[cg / 4], d4 = dl4[cg / 4];
-          float p0 = ex2(fmaf(__uint_as_float(sv[cg]), scale_log2, -l4.x));
-          float p1 = ex2(fmaf(__uint_as_float(sv[cg + 1]), scale_log2, -l4.y));
-          float p2 = ex2(fmaf(__uint_as_float(sv[cg + 2]), scale_log2, -l4.z));
-          float p3 = ex2(fmaf(__uint_as_float(sv[cg + 3]), scale_log2, -l4.w));
-          if (!live) p0 = p1 = p2 = p3 = 0.f;
-          pk[c / 2] = pack_bf16(p0, p1);
-          pk[c / 2 + 1] = pack_bf16(p2, p3);
-          dk_[c / 2] = pack_bf16(p0 * (__uint_as_float(dp[cg]) - d4.x),
-                                 p1 * (__uint_as_float(dp[cg + 1]) - d4.y));
-          dk_[c / 2 + 1] = pack_bf16(p2 * (__uint_as_float(dp[cg + 2]) - d4.z),
-                                     p3 * (__uint_as_float(dp[cg + 3]) - d4.w));
+          for (int c = 0; c < 32; c += 4) {
+            const int cg = hh * 32 + c;
+            const float4 l4 = lse4[cg / 4], d4 = dl4[cg / 4];
+            const float p0 = ex2(fmaf(__uint_as_float(sv[cg]), scale_log2, -l4.x));
+            const float p1 = ex2(fmaf(__uint_as_float(sv[cg + 1]), scale_log2, -l4.y));
+            const float p2 = ex2(fmaf(__uint_as_float(sv[cg + 2]), scale_log2, -l4.z));
+            const float p3 = ex2(fmaf(__uint_as_float(sv[cg + 3]), scale_log2, -l4.w));
+            pk[c / 2] = pack_bf16(p0, p1);
+            pk[c / 2 + 1] = pack_bf16(p2, p3);
+            dk_[c / 2] = pack_bf16(p0 * (__uint_as_float(dp[cg]) - d4.x),
+                                   p1 * (__uint_as_float(dp[cg + 1]) - d4.y));
+            dk_[c / 2 + 1] = pack_bf16(p2 * (__uint_as_float(dp[cg + 2]) - d4.z),
+                                       p3 * (__uint_as_float(dp[cg + 3]) - d4.w));
+          }
+        } else {           // block-sparse: this quadrant is not attended
+#pragma unroll
+          for (int c = 0; c < 16; ++c) pk[c] = dk_[c] = 0u;
         }
         tmem_st16(tb + BC_P + wg * 32 + hh * 16, pk);
 #pragma unroll
