@@ -13,9 +13,14 @@ def pytest_configure(config):
 
 
 def reference_dir():
-    """Directory holding the reference sources (for parity tests), or None."""
-    for cand in ("/root/reference", os.path.join(ROOT, "baseline", "_ref")):
-        if os.path.exists(os.path.join(cand, "models", "imf_dit_video.py")):
+    """Directory holding the reference sources (for parity tests), or None: the
+    ``IMF_REFERENCE_DIR`` environment variable, a ``reference`` checkout beside this
+    repository, or the copy installed for the benchmark's reference arm."""
+    cands = [os.environ.get("IMF_REFERENCE_DIR"),
+             os.path.join(os.path.dirname(ROOT), "reference"),
+             os.path.join(ROOT, "baseline", "_ref")]
+    for cand in cands:
+        if cand and os.path.exists(os.path.join(cand, "models", "imf_dit_video.py")):
             return cand
     return None
 
