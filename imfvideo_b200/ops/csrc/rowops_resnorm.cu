@@ -152,6 +152,73 @@ __global__ void __launch_bounds__(ROW_THREADS) resnorm_fwd_kernel(const ResNormA
   }
 }
 
+// Primal-only forward (guidance passes, v branch): the remix is ONE pass over the candidates
+// with a running maximum, flash-softmax style,
+//   h <- h exp(m - m') + exp(s_j - m') v_j,   den likewise,   h /= den at the end,
+// so every snapshot is read once and no tangent registers are carried: twice the occupancy
+// and about half the traffic of the two-pass kernel above.
+template <int NV>
+__global__ void __launch_bounds__(ROW_THREADS, NV <= 4 ? 3 : (NV <= 8 ? 2 : 1)) resnorm_fwd_primal_kernel(const ResNormArgs a) {
+  constexpr int D = NV * 128;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float inv_d = 1.f / D;
+  for (int row = blockIdx.x * ROW_WARPS + warp; row < a.rows; row += gridDim.x * ROW_WARPS) {
+    const size_t base = (size_t)row * D + lane * 4;
+    float4 pf[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const size_t o = base + i * 128;
+      pf[i] = a.res ? ld4(a.res + o) : f4zero();
+      if (a.y) {
+        pf[i] = pf[i] + ld4(a.y + o) * ld4(a.gate + lane * 4 + i * 128);
+        st4(a.pfx + o, pf[i]);
+      }
+    }
+    if (a.w) {
+      // candidate J-1 (the prefix itself) first: it is already in registers
+      float ss = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        ss += dot4(pf[i], pf[i]);
+        s1 += dot4(pf[i], ld4(a.w + lane * 4 + i * 128));
+      }
+      float m = rsqrtf(warp_sum(ss) * inv_d + a.eps) * warp_sum(s1);
+      float den = 1.f;                       // exp(s - m) of the first candidate
+#pragma unroll 1
+      for (int j = 0; j < a.nsnap; ++j) {
+        float4 v[NV];
+        ss = 0.f;
+        s1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          v[i] = ld4(a.snaps[j] + base + i * 128);
+          ss += dot4(v[i], v[i]);
+          s1 += dot4(v[i], ld4(a.w + lane * 4 + i * 128));
+        }
+        const float sc = rsqrtf(warp_sum(ss) * inv_d + a.eps) * warp_sum(s1);
+        const float mn = fmaxf(m, sc);
+        const float al = __expf(m - mn), pj = __expf(sc - mn);
+        den = den * al + pj;
+        m = mn;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) pf[i] = fma4(v[i], pj, pf[i] * al);
+      }
+      const float inv = 1.f / den;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) pf[i] = pf[i] * inv;
+    }
+    float hh = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) hh += dot4(pf[i], pf[i]);
+    const float rh = rsqrtf(warp_sum(hh) * inv_d + a.eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const size_t o = base + i * 128;
+      st4(a.n + o, pf[i] * ld4(a.gain + lane * 4 + i * 128) * rh);
+    }
+  }
+}
+
 template <int NV>
 __global__ void __launch_bounds__(ROW_THREADS) resnorm_bwd_kernel(const ResNormArgs a) {
   constexpr int D = NV * 128;
@@ -292,7 +359,8 @@ template <int NV>
 static int launch_resnorm(const ResNormArgs& a, bool bwd, cudaStream_t st) {
   const int grid = row_grid(a.rows);
   if (!bwd) {
-    resnorm_fwd_kernel<NV><<<grid, ROW_THREADS, 0, st>>>(a);
+    if (a.has_t) resnorm_fwd_kernel<NV><<<grid, ROW_THREADS, 0, st>>>(a);
+    else resnorm_fwd_primal_kernel<NV><<<grid, ROW_THREADS, 0, st>>>(a);
   } else {
     const size_t smem = (size_t)ROW_WARPS * 3 * NV * 128 * sizeof(float);
     if (cudaFuncSetAttribute(resnorm_bwd_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -49,6 +49,8 @@ def main() -> None:
     ap.add_argument("--N", type=int, default=528)
     ap.add_argument("--K", type=int, default=256)
     ap.add_argument("--rows", type=int, default=29140)
+    ap.add_argument("--D", type=int, default=256)
+    ap.add_argument("--snaps", type=int, default=3)
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     from . import cuda as cu
@@ -92,15 +94,15 @@ def main() -> None:
     else:
         from . import rowops as R
 
-        rows, D = args.rows, 256
+        rows, D, ns = args.rows, args.D, args.snaps
         res = torch.randn(rows, D, device=dev)
         y = torch.randn(rows, D, device=dev).bfloat16()
-        snaps = [torch.randn(rows, D, device=dev) for _ in range(3)]
+        snaps = [torch.randn(rows, D, device=dev) for _ in range(ns)]
         gate, w, gain = (torch.randn(D, device=dev) for _ in range(3))
         n, pf = torch.empty(rows, D, dtype=torch.bfloat16, device=dev), torch.empty(rows, D, device=dev)
-        fn = lambda: R.resnorm_fwd(res, None, y, None, gate, snaps, [None] * 3, w, gain, 1e-5, n,
+        fn = lambda: R.resnorm_fwd(res, None, y, None, gate, snaps, [None] * ns, w, gain, 1e-5, n,
                                    None, pf, None)
-        bytes_ = rows * D * (4 * 5 + 2 + 2)
+        bytes_ = rows * D * (4 * (2 + ns) + 2 + 2)
     ms = _time(fn, args.iters, flush)
     K.check_status()
     line = {"kernel": args.kernel, "ms": ms}
