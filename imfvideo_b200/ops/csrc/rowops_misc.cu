@@ -96,6 +96,24 @@ __global__ void __launch_bounds__(ROW_THREADS) rmsnorm_seg_bwd_kernel(const Norm
   }
 }
 
+__device__ __forceinline__ void unpack8(const uint4 v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // ---------------------------------------------------------------------------
 // q / k preparation
 // ---------------------------------------------------------------------------
@@ -190,6 +208,87 @@ __global__ void __launch_bounds__(ROW_THREADS) qkprep_fwd_kernel(const PrepArgs 
       for (int e = 0; e < EPL; e += 2)
         *reinterpret_cast<__nv_bfloat162*>(ddst + e) = __floats2bfloat162_rn(dy[e], dy[e + 1]);
     }
+  }
+}
+
+// Wide variant of the forward: a lane owns 8 consecutive channels (one 16-byte access), so a
+// head is HD / 8 lanes and a warp handles 32 / (HD / 8) (row, head, q|k) units at once; the
+// RMS reduction runs inside the lane group.  Needs dn % 8 == 0 and 16-byte aligned rows.
+template <int HD>
+__global__ void __launch_bounds__(ROW_THREADS) qkprep_fwd_wide_kernel(const PrepArgs a) {
+  constexpr int LPH = HD / 8;            // lanes per head: 8 or 16
+  constexpr int UPW = 32 / LPH;          // units per warp: 4 or 2
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane / LPH, c0 = (lane % LPH) * 8;
+  const bool nope = c0 < a.dn;
+  const int total = a.rows * a.H * 2;
+  const int n_groups = (total + UPW - 1) / UPW;
+  const float inv_dn = 1.f / a.dn;
+  const int kvw = a.H * (a.dn + a.dv);
+  for (int grp = blockIdx.x * ROW_WARPS + warp; grp < n_groups; grp += gridDim.x * ROW_WARPS) {
+    const int wid = grp * UPW + sub;
+    const bool live = wid < total;
+    const int which = wid & 1, h = (wid >> 1) % a.H, row = (wid >> 1) / a.H;
+    float x[8], dx[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = dx[e] = 0.f;
+    if (live) {
+      const bf16 *src, *dsrc;
+      if (which == 0) {
+        src = a.qb + (size_t)row * a.H * HD + h * HD + c0;
+        dsrc = a.dqb ? a.dqb + (size_t)row * a.H * HD + h * HD + c0 : nullptr;
+      } else if (nope) {
+        src = a.kvb + (size_t)row * kvw + h * (a.dn + a.dv) + c0;
+        dsrc = a.dkvb ? a.dkvb + (size_t)row * kvw + h * (a.dn + a.dv) + c0 : nullptr;
+      } else {
+        src = a.kr + (size_t)row * a.ld_kr + (c0 - a.dn);
+        dsrc = a.dkr ? a.dkr + (size_t)row * a.ld_kr + (c0 - a.dn) : nullptr;
+      }
+      unpack8(*reinterpret_cast<const uint4*>(src), x);
+      if (a.has_t && dsrc) unpack8(*reinterpret_cast<const uint4*>(dsrc), dx);
+    }
+    float ss = 0.f, xd = 0.f;
+    if (nope) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        ss += x[e] * x[e];
+        xd += x[e] * dx[e];
+      }
+    }
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) {       // reduction inside the head's lane group
+      ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      xd += __shfl_xor_sync(0xffffffffu, xd, o);
+    }
+    if (!live) continue;
+    float y[8], dy[8];
+    if (nope) {
+      const float r = rsqrtf(ss * inv_dn + a.eps);
+      const float c2 = xd * inv_dn * r * r * r;
+      const float* g = (which == 0 ? a.qg : a.kg) + c0;
+      const float4 g0 = ld4(g), g1 = ld4(g + 4);
+      const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        y[e] = x[e] * r * gg[e];
+        dy[e] = (dx[e] * r - x[e] * c2) * gg[e];
+      }
+    } else {
+      const int pos = row % a.L;
+      const size_t ro = (size_t)pos * (a.dr / 2) + (c0 - a.dn) / 2;
+      const float4 cs4 = ld4(a.cos_ + ro), sn4 = ld4(a.sin_ + ro);
+      const float cs[4] = {cs4.x, cs4.y, cs4.z, cs4.w}, sn[4] = {sn4.x, sn4.y, sn4.z, sn4.w};
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        y[e] = x[e] * cs[e / 2] - x[e + 1] * sn[e / 2];
+        y[e + 1] = x[e] * sn[e / 2] + x[e + 1] * cs[e / 2];
+        dy[e] = dx[e] * cs[e / 2] - dx[e + 1] * sn[e / 2];
+        dy[e + 1] = dx[e] * sn[e / 2] + dx[e + 1] * cs[e / 2];
+      }
+    }
+    const size_t off = ((size_t)row * a.H + h) * HD + c0;
+    *reinterpret_cast<uint4*>((which == 0 ? a.q : a.k) + off) = pack8(y);
+    if (a.has_t) *reinterpret_cast<uint4*>((which == 0 ? a.dq : a.dk) + off) = pack8(dy);
   }
 }
 
@@ -363,24 +462,6 @@ __device__ __forceinline__ void situ1(float g, float u, float beta, float inv_be
     up = u;
     dup_du = 1.f;
   }
-}
-
-__device__ __forceinline__ void unpack8(const uint4 v, float* f) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
-}
-__device__ __forceinline__ uint4 pack8(const float* f) {
-  uint32_t w[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-    w[i] = *reinterpret_cast<const uint32_t*>(&h);
-  }
-  return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
 // a0 = [gate | up] rows of width 2*D (up at column offset ld_b), out width D.
@@ -586,9 +667,21 @@ extern "C" int imf_qkprep(void** p, int rows, int L, int H, int dn, int dr, int 
   a.ld_kr = ld_kr; a.ld_gkr = ld_gkr; a.eps = eps; a.has_t = has_t;
   cudaStream_t st = (cudaStream_t)stream;
   if (!bwd) {
-    const int grid = row_grid(rows * H * 2);
-    if (epl == 2) qkprep_fwd_kernel<2><<<grid, ROW_THREADS, 0, st>>>(a);
-    else qkprep_fwd_kernel<4><<<grid, ROW_THREADS, 0, st>>>(a);
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const bool wide = dn % 8 == 0 && dr % 8 == 0 && (dn + dv) % 8 == 0 && ld_kr % 8 == 0 &&
+                      al16(a.qb) && al16(a.kvb) && al16(a.kr) && al16(a.q) && al16(a.k) &&
+                      al16(a.cos_) && al16(a.sin_) && al16(a.qg) && al16(a.kg) &&
+                      (!has_t || (al16(a.dqb) && al16(a.dkvb) && al16(a.dkr) && al16(a.dq) && al16(a.dk)));
+    if (wide) {
+      const int upw = HD == 64 ? 4 : 2;
+      const int grid = row_grid((rows * H * 2 + upw - 1) / upw);
+      if (HD == 64) qkprep_fwd_wide_kernel<64><<<grid, ROW_THREADS, 0, st>>>(a);
+      else qkprep_fwd_wide_kernel<128><<<grid, ROW_THREADS, 0, st>>>(a);
+    } else {
+      const int grid = row_grid(rows * H * 2);
+      if (epl == 2) qkprep_fwd_kernel<2><<<grid, ROW_THREADS, 0, st>>>(a);
+      else qkprep_fwd_kernel<4><<<grid, ROW_THREADS, 0, st>>>(a);
+    }
   } else {
     const int grid = row_grid(rows);     // partial buffers are sized by imf_row_grid(rows)
     const size_t smem = (size_t)ROW_WARPS * 2 * dn * sizeof(float);
