@@ -653,6 +653,33 @@ class IMFDiTVideo(nn.Module):
                 seq = blk(seq, self.rope_cos, self.rope_sin, self.compute_dtype)
         return seq
 
+    def _fused_out_head_ok(self, pf: Dual, sn) -> bool:
+        """Output re-mix + final RMSNorm in one kernel: bf16 compute on the kernel library,
+        fp32 (B, L, d) streams, d a multiple of 128."""
+        if self.compute_dtype != torch.bfloat16 or not pf.p.is_cuda or pf.p.dtype != torch.float32:
+            return False
+        if pf.p.shape[-1] % 128 or len(sn) + 1 > 8:
+            return False
+        try:
+            from ..ops import cuda as cu
+            return cu.available() and cu.has("block")
+        except Exception:
+            return False
+
+    def _fused_head(self, pf: Dual, sn, gain, pw, final: FinalLayer, keep_tangent: bool):
+        from ..ops.block import out_head
+
+        w = gain.float() * pw.reshape(-1).float()
+        if not keep_tangent:
+            pf, sn = Dual(pf.p, None), [Dual(s.p, None) for s in sn]
+        n, dn = out_head(pf, sn, w, final.norm.weight, final.norm.eps)
+        seq = Dual(n, dn)
+        if self.tile_major:
+            seq = seq.map(lambda z: z[:, self.tm_inv])
+        tok = seq.map(lambda z: z[:, self.prefix_tokens:])
+        y = D.linear(tok, final.linear.weight, final.linear.bias)
+        return y.map(lambda z: self.unpatchify(z.float()))
+
     def _head(self, seq: Dual, final: FinalLayer, keep_tangent: bool):
         if self.tile_major:
             seq = seq.map(lambda z: z[:, self.tm_inv])
@@ -704,6 +731,9 @@ class IMFDiTVideo(nn.Module):
                                                                  self.rmsnorm_eps)
                     s = checkpoint_dual(fn, [pf] + sn)
                 else:
+                    if self._fused_out_head_ok(pf, sn):
+                        out[name] = self._fused_head(pf, sn, gain, pw, final, kt)
+                        continue
                     s = D.attn_res(pf, sn, gain, pw, self.rmsnorm_eps)
                 out[name] = self._head(s, final, kt)
         else:

@@ -263,3 +263,53 @@ def run_block(geom: BlockGeom, core, fresh: bool, use_res: bool, eps: float, bet
     p, t = _BlockFn.apply(geom, core, fresh, use_res, eps, beta, lbeta, cos, sin, nsnap, prefix,
                           dprefix, *args, *params)
     return p, (t if dprefix is not None else None)
+
+
+class _OutHeadFn(torch.autograd.Function):
+    """Output attention-residual re-mix + the final layer's RMSNorm as one kernel:
+        n = RMSNorm(remix(prefix, snaps; w)) * gain            (bf16, + tangent)
+    inputs: eps, nsnap, prefix, dprefix, *snaps, *dsnaps, w, gain.  The tangent is not
+    differentiated.  (reference models/imf_dit_video.py:287-320, :535-549)"""
+
+    @staticmethod
+    def forward(ctx, eps, nsnap, prefix, dprefix, *rest):
+        snaps, dsnaps = list(rest[:nsnap]), list(rest[nsnap:2 * nsnap])
+        w, gain = rest[2 * nsnap:]
+        B, L, d = prefix.shape
+        rows = B * L
+        has_t = dprefix is not None
+        flat = lambda t: None if t is None else t.reshape(rows, d)
+        n = torch.empty(rows, d, dtype=BF16, device=prefix.device)
+        dn = torch.empty_like(n) if has_t else None
+        R.resnorm_fwd(flat(prefix), flat(dprefix), None, None, None, [flat(s) for s in snaps],
+                      [flat(s) if has_t else None for s in dsnaps] if has_t else [None] * nsnap,
+                      w, gain, eps, n, dn, None, None)
+        K.LAUNCHES.count += 1
+        ctx.save_for_backward(prefix, w, gain, *snaps)
+        ctx.meta = (eps, nsnap, B, L, d)
+        ctx.set_materialize_grads(False)
+        return n.view(B, L, d), (dn.view(B, L, d) if has_t else None)
+
+    @staticmethod
+    def backward(ctx, gn, _gdn):
+        eps, nsnap, B, L, d = ctx.meta
+        prefix, w, gain, *snaps = ctx.saved_tensors
+        rows = B * L
+        g_res, _, g_sn, g_gain, g_w, _ = R.resnorm_bwd(
+            prefix.reshape(rows, d), None, None, [s.reshape(rows, d) for s in snaps], w, gain,
+            eps, gn.reshape(rows, d).contiguous(), None)
+        K.LAUNCHES.count += 1
+        grads = (None, None, g_res.view(B, L, d), None) + tuple(g.view(B, L, d) for g in g_sn) + \
+            (None,) * nsnap + (g_w, g_gain)
+        return grads
+
+
+def out_head(prefix, snaps, w: torch.Tensor, gain: torch.Tensor, eps: float):
+    """``prefix`` / ``snaps``: Dual (fp32 (B, L, d)); returns (n, dn) bf16."""
+    ns = len(snaps)
+    has_t = prefix.t is not None
+    dsn = [(s.t if s.t is not None else torch.zeros_like(s.p)) for s in snaps] if has_t else [None] * ns
+    return _OutHeadFn.apply(float(eps), ns, prefix.p.contiguous(),
+                            prefix.t.contiguous() if has_t else None,
+                            *[s.p.contiguous() for s in snaps], *dsn,
+                            w.float().contiguous(), gain.float().contiguous())
