@@ -143,3 +143,73 @@ def test_qk_clip_kernel_matches_formula():
         ref[:, m.qk_nope_head_dim:, :] *= gamma.view(-1, 1, 1)
         assert torch.allclose(m.q_b_proj.weight.view_as(ref), ref, rtol=1e-6, atol=0)
     assert n == exp_n and abs(mx - exp_mx) < 1e-4
+
+
+def test_launches_per_block_are_bounded(kernels):
+    """Launch accounting (the reference checks its fused launch counts the same way): one
+    transformer block of the dual pass is at most 14 launches of this library, a primal-only
+    block at most 13, whatever the sequence length."""
+    from imfvideo_b200.ops.dual import Dual
+
+    net = _net(torch.bfloat16)
+    B = 1
+    x = torch.randn(B, 16, 4, 16, 32, device="cuda")
+    h = torch.rand(B, device="cuda")
+    w, lo, hi = torch.ones(B, device="cuda") * 1.5, torch.zeros(B, device="cuda"), torch.ones(B, device="cuda")
+    y = torch.randint(0, 1000, (B,), device="cuda")
+    n_blocks_u = len(net.shared_blocks) + len(net.u_heads)
+    with torch.no_grad():
+        net.forward_dual(Dual(x, torch.randn_like(x)), Dual(h, torch.ones_like(h)), w, lo, hi, y,
+                         branches=("u",), tangent_branches=("u",))       # warm-up
+        n0 = kernels.LAUNCHES.count
+        net.forward_dual(Dual(x, torch.randn_like(x)), Dual(h, torch.ones_like(h)), w, lo, hi, y,
+                         branches=("u",), tangent_branches=("u",))
+        dual = kernels.LAUNCHES.count - n0
+        n0 = kernels.LAUNCHES.count
+        net.forward_dual(Dual(x), Dual(h), w, lo, hi, y, branches=("u",))
+        primal = kernels.LAUNCHES.count - n0
+    kernels.check_status()
+    assert 0 < dual <= 14 * n_blocks_u + 8, dual
+    assert 0 < primal <= 13 * n_blocks_u + 8, primal
+
+
+def test_attention_kernels_stay_finite_on_large_logits(kernels):
+    """Stress input (scores far outside the usual range, as in the reference's x10-x100
+    battery): forward, tangent and backward stay finite and match the fp32 formulas."""
+    from imfvideo_b200.ops import reference as ref
+
+    torch.manual_seed(1)
+    B, L, H = 1, 700, 2
+    q, k, v, dq, dk, dv, go = (torch.randn(B, L, H, 64, device="cuda") for _ in range(7))
+    q, k = q * 12.0, k * 12.0                 # logits of the order of +-150 after the 1/8 scale
+    bf = lambda t: t.bfloat16()
+    o, do, lse = kernels.attn_fwd(bf(q), bf(k), bf(v), bf(dq), bf(dk), bf(dv))
+    gq, gk, gv = kernels.attn_bwd(bf(q), bf(k), bf(v), o, lse, bf(go))
+    kernels.check_status()
+    for t in (o, do, lse, gq, gk, gv):
+        assert torch.isfinite(t.float()).all()
+    f = lambda t: bf(t).float()
+    o_ref, do_ref = ref.attention_jvp(f(q), f(k), f(v), f(dq), f(dk), f(dv))
+    assert (o.float() - o_ref).abs().max() < 3e-2
+    assert ((do.float() - do_ref).norm() / do_ref.norm()) < 2e-2
+
+
+def test_sla2_trainer_steps_finite(kernels):
+    """Cube SLA2 INT8-QAT model end to end on the kernels: finite loss and gradients over a
+    few seeds (reference tests/test_sla2_e2e.py)."""
+    from imfvideo_b200.config import preset
+    from imfvideo_b200.train import Trainer
+
+    cfg = preset("d256_sla2")
+    cfg.model.depth, cfg.model.aux_head_depth = 3, 1
+    cfg.data.latent_frames, cfg.data.latent_size = 4, (16, 32)
+    cfg.optim.warmup_steps = 0
+    tr = Trainer(cfg, device=torch.device("cuda", 0), verbose=False)
+    for seed in range(3):
+        g = torch.Generator().manual_seed(seed)
+        x = torch.randn(1, 16, 4, 16, 32, generator=g).pin_memory()
+        y = torch.randint(0, 1000, (1,), generator=g)
+        st = tr.train_step(x, y)
+        assert st["loss"] == st["loss"] and not st["skipped"], st
+        assert st["grad_norm"] == st["grad_norm"] and st["grad_norm"] > 0
+    kernels.check_status()
