@@ -99,7 +99,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   auto& s = *reinterpret_cast<BwSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                        ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kvb = blockIdx.x, h = blockIdx.y, b = blockIdx.z / p.qsplit;
+  // block-sparse lists can be very uneven (the always-attended tail tiles are attended by every
+  // query tile and sit at the end): walk the K/V tiles from the back so the long ones start first
+  const int kvb = p.qlist ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z / p.qsplit;
   const int qpart = blockIdx.z % p.qsplit;
   const size_t lrow = (((size_t)b * p.H + h) * gridDim.x + kvb) * (size_t)p.qmax;
   const int* qlist = p.qlist ? p.qlist + lrow : nullptr;
