@@ -52,6 +52,20 @@ def tile_permutation(grid, tile, prefix_len: int, device=None):
     return perm, inv, (T // tt) * (Hh // th) * (Ww // tw)
 
 
+def _router_kernels_ok(q: Tensor, k: Tensor) -> bool:
+    """Pooling + top-k on the kernel library: CUDA bf16 (B, H, L, 64) views with a contiguous
+    last dim and at most 4096 key blocks' worth of candidates."""
+    if not (q.is_cuda and q.dtype == k.dtype == torch.bfloat16 and q.shape[-1] == 64):
+        return False
+    if q.stride(-1) != 1 or k.stride(-1) != 1 or torch._C._are_functorch_transforms_active():
+        return False
+    try:
+        from ..ops import sparse as SP
+        return SP.ROUTER_KERNELS
+    except Exception:
+        return False
+
+
 def block_mean(x: Tensor, block: int) -> Tensor:
     """(B, H, L, D) -> (B, H, ceil(L / block), D) means (ragged last block)."""
     B, H, L, D = x.shape
@@ -106,6 +120,16 @@ class Router(nn.Module):
         return (qb @ kb.transpose(-1, -2)) * (q.shape[-1] ** -0.5)
 
     def forward(self, q, k, k_frac: float, soft: bool = False, need_mask: bool = True):
+        if not soft and not need_mask and _router_kernels_ok(q, k):
+            from ..ops import sparse as SP
+
+            nb = -(-k.shape[2] // self.bk)
+            topk = max(1, min(nb, int(k_frac * nb)))
+            pq, pk = ((self.proj_q.weight, self.proj_k.weight) if self.learnable
+                      else (None, None))
+            lut = SP.route_topk(SP.pool_blocks(q, self.bq), SP.pool_blocks(k, self.bk), topk,
+                                pq, pk)
+            return None, lut, topk, None
         pc = self.scores(q, k)
         nb = pc.shape[-1]
         topk = max(1, min(nb, int(k_frac * nb)))
@@ -118,11 +142,20 @@ class Router(nn.Module):
 
 
 def route_tiles(q: Tensor, k: Tensor, topk_frac: float, Np: int, E: int, prefix_len: int,
-                proj_q: Optional[Tensor] = None, proj_k: Optional[Tensor] = None):
+                proj_q: Optional[Tensor] = None, proj_k: Optional[Tensor] = None,
+                n_tail: int = 0):
     """Hard top-k over pooled (projected) tile scores.  q, k tile-major
-    (B, H, L, D); returns lut (B, H, Mb, T) of VIDEO tile ids and T.  The mean
+    (B, H, L, D); returns lut (B, H, Mb, T + n_tail) of VIDEO tile ids (followed by the
+    always-attended tail blocks Np, Np + 1, ...) and T.  The mean
     key subtraction of the 1-D router is a per-row constant here and cannot
     change a hard top-k, so it is omitted."""
+    T = max(1, min(Np, int(topk_frac * Np)))
+    if _router_kernels_ok(q, k):
+        from ..ops import sparse as SP
+
+        lut = SP.route_topk(SP.pool_blocks(q, E), SP.pool_blocks(k, E, Np), T, proj_q, proj_k,
+                            n_tail=n_tail, tail0=Np)
+        return lut, T
     qb = block_mean(q, E)                                   # (B,H,Mb,D) incl. prefix tail blocks
     kb = block_mean(k[:, :, :Np * E], E)                    # (B,H,Np,D)
     if proj_q is not None:
@@ -130,8 +163,10 @@ def route_tiles(q: Tensor, k: Tensor, topk_frac: float, Np: int, E: int, prefix_
     if proj_k is not None:
         kb = kb @ proj_k.t().to(kb.dtype)
     pc = (qb @ kb.transpose(-1, -2)) * (q.shape[-1] ** -0.5)
-    T = max(1, min(Np, int(topk_frac * Np)))
     lut = torch.topk(pc, T, dim=-1, sorted=False).indices.to(torch.int32)
+    if n_tail:
+        tail = torch.arange(Np, Np + n_tail, device=q.device, dtype=lut.dtype)
+        lut = torch.cat([lut, tail.view(1, 1, 1, -1).expand(*lut.shape[:3], -1)], dim=-1)
     return lut.contiguous(), T
 
 
@@ -375,11 +410,8 @@ class SLA2CubeQATAttentionImpl(nn.Module):
     def route(self, qh: Tensor, kh: Tensor) -> Tuple[Tensor, int]:
         """LUT of routed video tiles plus the prefix tail blocks: (B,H,Mb,T+n_tail)."""
         with torch.no_grad():
-            lut, T = route_tiles(qh, kh, self.topk_frac, self.Np, self.E, self.prefix_len,
-                                 self.proj_q, self.proj_k)
-            tail = torch.arange(self.Np, self.Np + self.n_tail, device=qh.device, dtype=lut.dtype)
-            tail = tail.view(1, 1, 1, -1).expand(*lut.shape[:3], -1)
-            return torch.cat([lut, tail], dim=-1).contiguous(), T
+            return route_tiles(qh, kh, self.topk_frac, self.Np, self.E, self.prefix_len,
+                               self.proj_q, self.proj_k, n_tail=self.n_tail)
 
     def _core(self, q, k, v, lut_aug):
         """(b, l, H, hd) tile-major -> same, given the routing."""

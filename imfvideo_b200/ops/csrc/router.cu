@@ -1,5 +1,7 @@
-// Routing tables of the block-sparse attention kernels, built on the device
-// in two launches and without a host round trip:
+// Router of the block-sparse attention kernels on the device, without a host
+// round trip: pooled block means (pool_blocks), projected block scores with a
+// radix-select top-k (route_topk), and the routing tables built from the
+// selection:
 //
 //   tile lists   : per 128-row query tile the ascending list of 64-row key
 //                  blocks selected by its routing block(s), with 2 flag bits
@@ -12,8 +14,10 @@
 // half); lists come out of the bitmaps in ascending order by a prefix sum over
 // the words, so the result does not depend on the order of the selection.
 // Replaces the reference's `_invert_lut`, the LUT post-processing of
-// `route_*` and the sort / unique passes around them (reference
+// `route_*` and the sort / unique passes around them, and `_colmean`,
+// `_pool_sub`, `_route_pool_kernel` + `torch.topk` (reference
 // models/sla2_vendor/kernel.py, models/sla2_cube.py).
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -137,9 +141,207 @@ kv_lists_kernel(const uint8_t* __restrict__ fm, int* __restrict__ qlist,
   }
 }
 
+// --------------------------------------------------------------------------
+// Block means: x (B, L, H, 64) bf16 with element strides (sb, sl, sh) ->
+// out (B, H, nb, 64) fp32, mean over the valid rows of each block.  Fixed
+// summation order (rows of a warp in sequence, then the warps in sequence).
+// --------------------------------------------------------------------------
+__global__ void __launch_bounds__(RT_THREADS)
+pool_blocks_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out, int64_t sb,
+                   int64_t sl, int64_t sh, int L, int block, int nb) {
+  __shared__ float2 part[RT_THREADS / 32][32];
+  const int n = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r0 = n * block, r1 = min(L, r0 + block);
+  const __nv_bfloat16* base = x + b * sb + h * sh + 2 * lane;
+  float2 acc = make_float2(0.f, 0.f);
+  for (int r = r0 + warp; r < r1; r += RT_THREADS / 32) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(base + r * sl));
+    acc.x += v.x;
+    acc.y += v.y;
+  }
+  part[warp][lane] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    float2 s = part[0][lane];
+#pragma unroll
+    for (int w = 1; w < RT_THREADS / 32; ++w) {
+      s.x += part[w][lane].x;
+      s.y += part[w][lane].y;
+    }
+    const float inv = 1.f / (float)max(1, r1 - r0);
+    float* o = out + ((((size_t)b * gridDim.y + h) * nb + n) << 6) + 2 * lane;
+    *reinterpret_cast<float2*>(o) = make_float2(s.x * inv, s.y * inv);
+  }
+}
+
+// order-preserving map of a float to an unsigned key (larger float <=> larger key)
+__device__ __forceinline__ unsigned int float_key(float f) {
+  const unsigned int u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// --------------------------------------------------------------------------
+// Scores of one pooled query block against the first Nk pooled key blocks and
+// the T best of them:
+//     score[n] = (Pq qb) . (Pk kb[n]) = (Pk^T Pq qb) . kb[n]
+// (a key-side centring would add the same constant to every score of the row
+// and cannot change the selection, so it is not applied).  The T-th largest
+// score is found by a 4-pass radix select on order-preserving keys; the
+// selection is written in ascending block order (scores above the threshold
+// first, then as many equal to it as are still needed, lowest index first),
+// followed by n_tail always-attended blocks tail0, tail0 + 1, ...
+// --------------------------------------------------------------------------
+__global__ void __launch_bounds__(RT_THREADS)
+route_topk_kernel(const float* __restrict__ qb, const float* __restrict__ kb,
+                  const float* __restrict__ Pq, const float* __restrict__ Pk,
+                  int* __restrict__ sel, float* __restrict__ scores_out, int Mb, int Nkb, int Nk,
+                  int T, int n_tail, int tail0, float scale) {
+  extern __shared__ float sc[];                    // Nk scores
+  __shared__ float qv[64], uv[64], wv[64];
+  __shared__ int hist[256];
+  __shared__ unsigned int s_prefix, s_mask;
+  __shared__ int s_remaining;
+  const int m = blockIdx.x, h = blockIdx.y, b = blockIdx.z, H = gridDim.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t bh = (size_t)b * H + h;
+  if (tid < 64) qv[tid] = qb[((bh * Mb + m) << 6) + tid];
+  __syncthreads();
+  if (Pq) {
+    if (tid < 64) {
+      float a = 0.f;
+#pragma unroll 8
+      for (int j = 0; j < 64; ++j) a = fmaf(Pq[tid * 64 + j], qv[j], a);
+      uv[tid] = a;
+    }
+  } else if (tid < 64) {
+    uv[tid] = qv[tid];
+  }
+  __syncthreads();
+  if (Pk) {
+    if (tid < 64) {
+      float a = 0.f;
+#pragma unroll 8
+      for (int i = 0; i < 64; ++i) a = fmaf(Pk[i * 64 + tid], uv[i], a);
+      wv[tid] = a;
+    }
+  } else if (tid < 64) {
+    wv[tid] = uv[tid];
+  }
+  __syncthreads();
+  const float2 w2 = make_float2(wv[2 * lane], wv[2 * lane + 1]);
+  const float* kbase = kb + ((bh * Nkb) << 6) + 2 * lane;
+  for (int n = warp; n < Nk; n += RT_THREADS / 32) {
+    const float2 kv = *reinterpret_cast<const float2*>(kbase + ((size_t)n << 6));
+    float d = fmaf(w2.x, kv.x, w2.y * kv.y);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    if (lane == 0) sc[n] = d * scale;
+  }
+  if (tid == 0) {
+    s_prefix = 0u;
+    s_mask = 0u;
+    s_remaining = T;
+  }
+  __syncthreads();
+  if (scores_out)
+    for (int n = tid; n < Nk; n += RT_THREADS) scores_out[(bh * Mb + m) * Nk + n] = sc[n];
+  // radix select: after the 4 passes s_prefix is the key of the T-th largest score and
+  // s_remaining the number of scores equal to it that belong to the selection
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = tid; i < 256; i += RT_THREADS) hist[i] = 0;
+    __syncthreads();
+    const unsigned int prefix = s_prefix, mask = s_mask;
+    for (int n = tid; n < Nk; n += RT_THREADS) {
+      const unsigned int key = float_key(sc[n]);
+      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // lane l owns bins 255 - 8l ... 248 - 8l (descending)
+      int own = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) own += hist[255 - 8 * lane - i];
+      int incl = own;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += y;
+      }
+      const int remaining = s_remaining;
+      const int before = incl - own;
+      if (before < remaining && remaining <= incl) {
+        int cum = before;
+        for (int i = 0; i < 8; ++i) {
+          const int bin = 255 - 8 * lane - i;
+          const int c = hist[bin];
+          if (cum + c >= remaining) {
+            s_prefix = prefix | ((unsigned int)bin << shift);
+            s_mask = mask | (255u << shift);
+            s_remaining = remaining - cum;
+            break;
+          }
+          cum += c;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const unsigned int thr = s_prefix;
+  const int n_eq_take = s_remaining;
+  const int per = (Nk + RT_THREADS - 1) / RT_THREADS;
+  const int lo = tid * per, hi = min(Nk, lo + per);
+  int cg = 0, ce = 0;
+  for (int n = lo; n < hi; ++n) {
+    const unsigned int key = float_key(sc[n]);
+    cg += key > thr;
+    ce += key == thr;
+  }
+  int total;
+  const int packed = block_excl_scan(cg | (ce << 16), &total);
+  int pg = packed & 0xffff, pe = packed >> 16;
+  const int n_gt = total & 0xffff;
+  int* row = sel + (bh * Mb + m) * (size_t)(T + n_tail);
+  for (int n = lo; n < hi; ++n) {
+    const unsigned int key = float_key(sc[n]);
+    if (key > thr) {
+      row[pg++] = n;
+    } else if (key == thr) {
+      if (pe < n_eq_take) row[n_gt + pe] = n;
+      ++pe;
+    }
+  }
+  for (int j = tid; j < n_tail; j += RT_THREADS) row[T + j] = tail0 + j;
+}
+
 }  // namespace imf
 
 using namespace imf;
+
+extern "C" int imf_pool_blocks(const void* x, float* out, int B, int L, int H, int block, int nb,
+                               int64_t sb, int64_t sl, int64_t sh, void* stream) {
+  if (B <= 0 || H <= 0 || L <= 0 || block <= 0 || nb <= 0 || (int64_t)(nb - 1) * block >= L)
+    return -1;
+  if ((reinterpret_cast<uintptr_t>(x) & 3) || ((sb | sl | sh) & 1)) return -2;
+  pool_blocks_kernel<<<dim3(nb, H, B), RT_THREADS, 0, (cudaStream_t)stream>>>(
+      static_cast<const __nv_bfloat16*>(x), out, sb, sl, sh, L, block, nb);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// qb (B, H, Mb, 64), kb (B, H, Nkb, 64) fp32 pooled blocks; the first Nk key blocks are
+// candidates.  sel (B, H, Mb, T + n_tail) int32.  Pq / Pk: 64 x 64 fp32 row-major projections
+// (nn.Linear weights) or null.  scores_out (B, H, Mb, Nk) fp32 or null.
+extern "C" int imf_route_topk(const float* qb, const float* kb, const float* Pq, const float* Pk,
+                              int* sel, float* scores_out, int B, int H, int Mb, int Nkb, int Nk,
+                              int T, int n_tail, int tail0, float scale, void* stream) {
+  if (B <= 0 || H <= 0 || Mb <= 0 || Nk <= 0 || Nk > Nkb || T < 1 || T > Nk || n_tail < 0)
+    return -1;
+  if (Nk > RT_MAX_WORDS * 32) return -4;           // also keeps the packed 16-bit counts exact
+  route_topk_kernel<<<dim3(Mb, H, B), RT_THREADS, (size_t)Nk * sizeof(float),
+                      (cudaStream_t)stream>>>(qb, kb, Pq, Pk, sel, scores_out, Mb, Nkb, Nk, T,
+                                              n_tail, tail0, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
 
 extern "C" int imf_build_tile_lut(const int* sel, int* lut, uint8_t* flags, int* cnt, uint8_t* fm,
                                   int B, int H, int Mb, int T, int qblk, int L, int tmax,

@@ -30,6 +30,52 @@ if K._has("imf_build_tile_lut"):
     _lib.imf_build_kv_lists.argtypes = [vp] * 3 + [ci] * 5 + [vp]
 
 
+ROUTER_KERNELS = K._has("imf_route_topk")
+if ROUTER_KERNELS:
+    _lib.imf_pool_blocks.restype = ci
+    _lib.imf_pool_blocks.argtypes = [vp, vp] + [ci] * 5 + [c64] * 3 + [vp]
+    _lib.imf_route_topk.restype = ci
+    _lib.imf_route_topk.argtypes = [vp] * 6 + [ci] * 8 + [cf, vp]
+
+
+def pool_blocks(x: torch.Tensor, block: int, nb: Optional[int] = None) -> torch.Tensor:
+    """Means of the first ``nb`` blocks of ``block`` rows (ragged last block: mean of its
+    valid rows).  x: (B, H, L, 64) bf16 view with a contiguous last dim -> (B, H, nb, 64) fp32."""
+    B, H, L, D = x.shape
+    assert D == 64 and x.dtype == torch.bfloat16 and x.stride(3) == 1
+    nb = -(-L // block) if nb is None else nb
+    out = torch.empty(B, H, nb, D, dtype=torch.float32, device=x.device)
+    K._check(_lib.imf_pool_blocks(K._ptr(x), K._ptr(out), B, min(L, nb * block), H, block, nb,
+                                  x.stride(0), x.stride(2), x.stride(1), K._stream()),
+             "imf_pool_blocks")
+    K.LAUNCHES.count += 1
+    return out
+
+
+def route_topk(qb: torch.Tensor, kb: torch.Tensor, T: int, proj_q: Optional[torch.Tensor] = None,
+               proj_k: Optional[torch.Tensor] = None, n_keys: Optional[int] = None,
+               n_tail: int = 0, tail0: int = 0, want_scores: bool = False):
+    """Hard top-``T`` of the projected block scores (one launch).  qb (B, H, Mb, 64), kb
+    (B, H, Nkb, 64) fp32 pooled blocks; the first ``n_keys`` key blocks are candidates;
+    ``n_tail`` always-attended block ids ``tail0, tail0 + 1, ...`` are appended to every row.
+    Returns sel (B, H, Mb, T + n_tail) int32 (ascending within the two groups of the
+    selection) and, on request, the scores (B, H, Mb, n_keys) fp32."""
+    B, H, Mb, D = qb.shape
+    Nkb = kb.shape[2]
+    Nk = Nkb if n_keys is None else n_keys
+    assert D == 64 and qb.dtype == kb.dtype == torch.float32
+    qb, kb = qb.contiguous(), kb.contiguous()
+    pq = None if proj_q is None else proj_q.detach().float().contiguous()
+    pk = None if proj_k is None else proj_k.detach().float().contiguous()
+    sel = torch.empty(B, H, Mb, T + n_tail, dtype=torch.int32, device=qb.device)
+    sc = torch.empty(B, H, Mb, Nk, dtype=torch.float32, device=qb.device) if want_scores else None
+    K._check(_lib.imf_route_topk(K._ptr(qb), K._ptr(kb), K._ptr(pq), K._ptr(pk), K._ptr(sel),
+                                 K._ptr(sc), B, H, Mb, Nkb, Nk, T, n_tail, tail0,
+                                 float(D) ** -0.5, K._stream()), "imf_route_topk")
+    K.LAUNCHES.count += 1
+    return (sel, sc) if want_scores else sel
+
+
 def route_tables(sel: torch.Tensor, qblk: int, L: int):
     """Device-built routing tables from the selection ``sel`` (B, H, Mb, T): the per-tile
     key-block lists of ``build_tile_lut`` (ascending, -1 padded), their flags, the entry

@@ -235,3 +235,70 @@ def test_device_routing_tables_match_torch_builders(SP, qblk):
     m = ql_r.shape[-1]
     assert bool((ql[..., m:] < 0).all())
     assert torch.equal(ql[..., :m], ql_r) and torch.equal(qf[..., :m], qf_r)
+
+
+@pytest.mark.parametrize("L,bq,bk,n_keys,n_tail,proj", [
+    (29140, 64, 64, 455, 1, True),        # cube shape: 455 video tiles + 1 prefix tail block
+    (1000, 128, 64, None, 0, True),       # 1-D router, ragged last blocks
+    (700, 64, 64, None, 0, False),
+])
+def test_router_pool_and_topk_kernels(SP, L, bq, bk, n_keys, n_tail, proj):
+    """Pooled block means and the radix-select top-k against torch: the means and scores
+    match the fp32 formulas; the selection is an exact top-T of the kernel's own scores
+    (so a rounding-level difference of two near-equal scores cannot fail the test)."""
+    from imfvideo_b200.models import sla2 as S
+
+    torch.manual_seed(5)
+    B, H = 2, 3
+    q = torch.randn(B, L, H, 64, device="cuda").bfloat16().permute(0, 2, 1, 3)
+    k = torch.randn(B, L, H, 64, device="cuda").bfloat16().permute(0, 2, 1, 3)
+    qb = SP.pool_blocks(q, bq)
+    nkb = n_keys if n_keys is not None else -(-L // bk)
+    kb = SP.pool_blocks(k, bk, nkb)
+    assert torch.allclose(qb, S.block_mean(q, bq), atol=1e-5)
+    assert torch.allclose(kb, S.block_mean(k, bk)[:, :, :nkb], atol=1e-5)
+    pq = pk = None
+    if proj:
+        pq = torch.eye(64, device="cuda") + 0.3 * torch.randn(64, 64, device="cuda")
+        pk = torch.eye(64, device="cuda") + 0.3 * torch.randn(64, 64, device="cuda")
+    T = max(1, int(0.05 * nkb))
+    sel, sc = SP.route_topk(qb, kb, T, pq, pk, n_tail=n_tail, tail0=nkb, want_scores=True)
+    qp = qb if pq is None else qb @ pq.t()
+    kp = kb if pk is None else kb @ pk.t()
+    ref = (qp @ kp.transpose(-1, -2)) * 64 ** -0.5
+    assert torch.allclose(sc, ref, atol=2e-5, rtol=1e-4)
+    top = sel[..., :T].long()
+    assert int(top.min()) >= 0 and int(top.max()) < nkb
+    assert bool((top[..., 1:] != top[..., :-1]).all())
+    picked = torch.zeros_like(sc, dtype=torch.bool).scatter_(-1, top, True)
+    assert int(picked.sum(-1).min()) == T                       # no duplicates
+    lo_in = sc.masked_fill(~picked, float("inf")).amin(-1)
+    hi_out = sc.masked_fill(picked, float("-inf")).amax(-1)
+    assert bool((lo_in >= hi_out).all())
+    want = torch.topk(sc, T, dim=-1).indices.sort(-1).values
+    assert (top.sort(-1).values == want).float().mean() > 0.999
+    if n_tail:
+        assert bool((sel[..., T:] == torch.arange(nkb, nkb + n_tail, device="cuda")).all())
+
+
+def test_router_modules_use_the_kernels(SP):
+    """Router.forward (1-D) and route_tiles (cube) on the kernels agree with their torch paths."""
+    from imfvideo_b200.models import sla2 as S
+
+    torch.manual_seed(6)
+    B, H, L = 1, 2, 64 * 40 + 20
+    q = torch.randn(B, L, H, 64, device="cuda").bfloat16().permute(0, 2, 1, 3)
+    k = torch.randn(B, L, H, 64, device="cuda").bfloat16().permute(0, 2, 1, 3)
+    r = S.Router(64, bq=128, bk=64).cuda()
+    with torch.no_grad():
+        r.proj_q.weight.add_(0.2 * torch.randn_like(r.proj_q.weight))
+    _, lut_k, tk, _ = r(q, k, 0.1, need_mask=False)
+    _, lut_t, tt, _ = r(q.float(), k.float(), 0.1, need_mask=False)
+    assert tk == tt and lut_k.shape == lut_t.shape
+    same = (lut_k.sort(-1).values == lut_t.sort(-1).values.to(lut_k.dtype)).float().mean()
+    assert same > 0.99
+    lut_c, T = S.route_tiles(q, k, 0.1, 40, 64, 20, n_tail=1)
+    lut_r, T2 = S.route_tiles(q.float(), k.float(), 0.1, 40, 64, 20, n_tail=1)
+    assert T == T2 and lut_c.shape == lut_r.shape == (B, H, 41, T + 1)
+    same = (lut_c.sort(-1).values == lut_r.sort(-1).values.to(lut_c.dtype)).float().mean()
+    assert same > 0.99
