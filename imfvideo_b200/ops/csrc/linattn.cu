@@ -148,13 +148,22 @@ __global__ void __launch_bounds__(256) lin_states_kernel(const StatesArgs a) {
     dst[base + d * LW + e] = hi;
     dst[base + lo_off + d * LW + e] = __float2bfloat16(v - __bfloat162float(hi));
   };
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
+  // four columns at a time: one 8-byte store of the hi parts and one of the lo parts
+  auto put4 = [&](__nv_bfloat16* dst, int d, int e, const float (&v)[4]) {
+    __align__(8) __nv_bfloat16 hi[4], lo[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      put(a.out, d0 + i, e0 + j, acc[i][j]);
-      if (TANGENT) put(a.dout, d0 + i, e0 + j, dacc[i][j]);
+      hi[j] = __float2bfloat16(v[j]);
+      lo[j] = __float2bfloat16(v[j] - __bfloat162float(hi[j]));
     }
+    *reinterpret_cast<uint2*>(dst + base + d * LW + e) = *reinterpret_cast<const uint2*>(hi);
+    *reinterpret_cast<uint2*>(dst + base + lo_off + d * LW + e) = *reinterpret_cast<const uint2*>(lo);
+  };
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    put4(a.out, d0 + i, e0, acc[i]);
+    if (TANGENT) put4(a.dout, d0 + i, e0, dacc[i]);
+  }
   if (tid < 64) {
     put(a.out, tid, 64, zacc);
     if (TANGENT) put(a.dout, tid, 64, dzacc);
@@ -164,6 +173,75 @@ __global__ void __launch_bounds__(256) lin_states_kernel(const StatesArgs a) {
       if (TANGENT) put(a.dout, tid, e, 0.f);
     }
   }
+}
+
+// --------------------------------------------------------------------------
+// 64 x 64 x 64 products in shared memory.  All matrices have pitch LP = 68
+// floats (rows 16-byte aligned; rows four apart sit 16 banks apart).  The 256
+// threads form a 16 x 16 grid, each with a 4 x 4 tile of the result:
+//     acc[i][j] += sum_k A[r0 + i][k] * Bm[k][c0 + j]
+// Per four k: four 16-byte loads of A (two addresses per warp, broadcast) and
+// four of Bm (256 contiguous bytes per half warp) feed 64 FMAs.
+// --------------------------------------------------------------------------
+constexpr int LP = LW;
+
+__device__ __forceinline__ void tile_mm(const float* __restrict__ A, const float* __restrict__ Bm,
+                                        int r0, int c0, float (&acc)[4][4]) {
+#pragma unroll 2
+  for (int k = 0; k < 64; k += 4) {
+    float4 av[4], bv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) av[i] = *reinterpret_cast<const float4*>(A + (r0 + i) * LP + k);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) bv[j] = *reinterpret_cast<const float4*>(Bm + (k + j) * LP + c0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float as[4] = {av[i].x, av[i].y, av[i].z, av[i].w};
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        acc[i][0] = fmaf(as[kk], bv[kk].x, acc[i][0]);
+        acc[i][1] = fmaf(as[kk], bv[kk].y, acc[i][1]);
+        acc[i][2] = fmaf(as[kk], bv[kk].z, acc[i][2]);
+        acc[i][3] = fmaf(as[kk], bv[kk].w, acc[i][3]);
+      }
+    }
+  }
+}
+
+// sum over the 16 lanes that share a row group (lanes 0-15 / 16-31 of a warp)
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void load_state(float* dst, const float* src, int tid) {
+  for (int i = tid * 4; i < LSTATE; i += 256 * 4)
+    *reinterpret_cast<float4*>(dst + i) = *reinterpret_cast<const float4*>(src + i);
+}
+
+// dst[e][d] = src[d][e] for d, e < 64 (both pitch LP, both in shared memory)
+__device__ __forceinline__ void transpose_state(float* dst, const float* src, int tid) {
+  const int d = tid & 63;
+  for (int e = tid >> 6; e < 64; e += 4) dst[e * LP + d] = src[d * LP + e];
+}
+
+__device__ __forceinline__ __nv_bfloat16* row_at(const RowPtr& t, int b, int row, int h) {
+  return static_cast<__nv_bfloat16*>(const_cast<void*>(t.p)) + b * t.sb + (int64_t)row * t.sl +
+         h * t.sh;
+}
+__device__ __forceinline__ void ld_bf16x4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void st_bf16x4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 u;
+  u.x = *reinterpret_cast<const unsigned int*>(&lo);
+  u.y = *reinterpret_cast<const unsigned int*>(&hi);
+  *reinterpret_cast<uint2*>(p) = u;
 }
 
 // --------------------------------------------------------------------------
@@ -179,98 +257,73 @@ struct ApplyArgs {
   int L, H, Mb, qblk;
 };
 
-__device__ __forceinline__ void load_state(float* dst, const float* src, int tid) {
-  for (int i = tid * 4; i < LSTATE; i += 256 * 4)
-    *reinterpret_cast<float4*>(dst + i) = *reinterpret_cast<const float4*>(src + i);
-}
-
 template <bool TANGENT>
 __global__ void __launch_bounds__(256) lin_apply_kernel(const ApplyArgs a) {
-  extern __shared__ float sm[];
-  float* C = sm;                      // [64][68]
-  float* P = C + LSTATE;              // phi rows [64][65]
-  float* dC = P + 64 * 65;
+  extern __shared__ __align__(16) float sm[];
+  float* C = sm;                      // [64][LP]: H | z
+  float* P = C + LSTATE;              // phi rows [64][LP]
+  float* dC = P + 64 * LP;            // tangent only
   float* dP = dC + LSTATE;
+  __shared__ float Den[64], dDen[64];
   const int m = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t sidx = (((int64_t)b * a.H + h) * a.Mb + m) * LSTATE;
   load_state(C, a.C + sidx, tid);
   if (TANGENT) load_state(dC, a.dC + sidx, tid);
-  const int r = tid >> 2, e0 = (tid & 3) * 16;
-  for (int c0 = 0; c0 < a.qblk; c0 += 64) {
-    __syncthreads();
+  __syncthreads();
+  const float z0 = C[(2 * lane) * LP + 64], z1 = C[(2 * lane + 1) * LP + 64];
+  const float dz0 = TANGENT ? dC[(2 * lane) * LP + 64] : 0.f;
+  const float dz1 = TANGENT ? dC[(2 * lane + 1) * LP + 64] : 0.f;
+  const int r0 = (tid >> 4) * 4, c0 = (tid & 15) * 4;
+  for (int ch = 0; ch < a.qblk; ch += 64) {
+    if (ch) __syncthreads();
     for (int rr = warp; rr < 64; rr += 8) {
-      const int row = m * a.qblk + c0 + rr;
+      const int row = m * a.qblk + ch + rr;
       float2 phi = make_float2(0.f, 0.f), dphi = phi;
       if (row < a.L) {
         softmax_row(ld_bf16x2(a.q, b, row, h, 2 * lane), phi);
         if (TANGENT) softmax_row_jvp(phi, ld_bf16x2(a.dq, b, row, h, 2 * lane), dphi);
       }
-      P[rr * 65 + 2 * lane] = phi.x;
-      P[rr * 65 + 2 * lane + 1] = phi.y;
+      *reinterpret_cast<float2*>(P + rr * LP + 2 * lane) = phi;
+      const float den = warp_sum(fmaf(phi.x, z0, phi.y * z1));
       if (TANGENT) {
-        dP[rr * 65 + 2 * lane] = dphi.x;
-        dP[rr * 65 + 2 * lane + 1] = dphi.y;
+        *reinterpret_cast<float2*>(dP + rr * LP + 2 * lane) = dphi;
+        const float dd = warp_sum(fmaf(dphi.x, z0, dphi.y * z1) + fmaf(phi.x, dz0, phi.y * dz1));
+        if (lane == 0) dDen[rr] = dd;
       }
+      if (lane == 0) Den[rr] = den + LIN_EPS;
     }
     __syncthreads();
-    const int row = m * a.qblk + c0 + r;
-    float num[16] = {}, dnum[16] = {};
-    float den = LIN_EPS, dden = 0.f;
-#pragma unroll 2
-    for (int d = 0; d < 64; ++d) {
-      const float f = P[r * 65 + d];
-      const float df = TANGENT ? dP[r * 65 + d] : 0.f;
-      den = fmaf(f, C[d * LW + 64], den);
-      if (TANGENT) dden = fmaf(df, C[d * LW + 64], fmaf(f, dC[d * LW + 64], dden));
-#pragma unroll
-      for (int j = 0; j < 16; j += 4) {
-        const float4 c4 = *reinterpret_cast<const float4*>(C + d * LW + e0 + j);
-        num[j] = fmaf(f, c4.x, num[j]);
-        num[j + 1] = fmaf(f, c4.y, num[j + 1]);
-        num[j + 2] = fmaf(f, c4.z, num[j + 2]);
-        num[j + 3] = fmaf(f, c4.w, num[j + 3]);
-        if (TANGENT) {
-          const float4 t4 = *reinterpret_cast<const float4*>(dC + d * LW + e0 + j);
-          dnum[j] = fmaf(df, c4.x, fmaf(f, t4.x, dnum[j]));
-          dnum[j + 1] = fmaf(df, c4.y, fmaf(f, t4.y, dnum[j + 1]));
-          dnum[j + 2] = fmaf(df, c4.z, fmaf(f, t4.z, dnum[j + 2]));
-          dnum[j + 3] = fmaf(df, c4.w, fmaf(f, t4.w, dnum[j + 3]));
-        }
-      }
+    float num[4][4] = {}, dnum[4][4] = {};
+    tile_mm(P, C, r0, c0, num);
+    if (TANGENT) {
+      tile_mm(dP, C, r0, c0, dnum);
+      tile_mm(P, dC, r0, c0, dnum);
     }
-    if (row < a.L) {
-      const float inv = 1.f / den;
-      const float al = a.a_rows[(int64_t)h * a.L + row], bl = 1.f - al;
-      const __nv_bfloat16* os = static_cast<const __nv_bfloat16*>(a.os.p) + b * a.os.sb +
-                                (int64_t)row * a.os.sl + h * a.os.sh + e0;
-      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(const_cast<void*>(a.o.p)) + b * a.o.sb +
-                         (int64_t)row * a.o.sl + h * a.o.sh + e0;
-      const __nv_bfloat16* dos = nullptr;
-      __nv_bfloat16* dout = nullptr;
-      if (TANGENT) {
-        dos = static_cast<const __nv_bfloat16*>(a.dos.p) + b * a.dos.sb + (int64_t)row * a.dos.sl +
-              h * a.dos.sh + e0;
-        dout = static_cast<__nv_bfloat16*>(const_cast<void*>(a.dout.p)) + b * a.dout.sb +
-               (int64_t)row * a.dout.sl + h * a.dout.sh + e0;
-      }
 #pragma unroll
-      for (int j = 0; j < 16; j += 2) {
-        const float2 s2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(os + j));
-        const float l0 = num[j] * inv, l1 = num[j + 1] * inv;
-        *reinterpret_cast<__nv_bfloat162*>(o + j) =
-            __floats2bfloat162_rn(al * s2.x + bl * l0, al * s2.y + bl * l1);
-        if (TANGENT) {
-          const float2 t2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dos + j));
-          const float g0 = (dnum[j] - l0 * dden) * inv, g1 = (dnum[j + 1] - l1 * dden) * inv;
-          *reinterpret_cast<__nv_bfloat162*>(dout + j) =
-              __floats2bfloat162_rn(al * t2.x + bl * g0, al * t2.y + bl * g1);
-        }
+    for (int i = 0; i < 4; ++i) {
+      const int row = m * a.qblk + ch + r0 + i;
+      if (row >= a.L) continue;
+      const float inv = 1.f / Den[r0 + i];
+      const float al = a.a_rows[(int64_t)h * a.L + row], bl = 1.f - al;
+      float s[4], l[4];
+      ld_bf16x4(row_at(a.os, b, row, h) + c0, s);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) l[j] = num[i][j] * inv;
+      st_bf16x4(row_at(a.o, b, row, h) + c0, al * s[0] + bl * l[0], al * s[1] + bl * l[1],
+                al * s[2] + bl * l[2], al * s[3] + bl * l[3]);
+      if (TANGENT) {
+        const float dden = dDen[r0 + i];
+        float t[4], g[4];
+        ld_bf16x4(row_at(a.dos, b, row, h) + c0, t);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) g[j] = (dnum[i][j] - l[j] * dden) * inv;
+        st_bf16x4(row_at(a.dout, b, row, h) + c0, al * t[0] + bl * g[0], al * t[1] + bl * g[1],
+                  al * t[2] + bl * g[2], al * t[3] + bl * g[3]);
       }
     }
   }
 }
-
 
 // --------------------------------------------------------------------------
 // Reverse mode, row side.  Per query row with upstream gradient go of the mixed
@@ -279,6 +332,7 @@ __global__ void __launch_bounds__(256) lin_apply_kernel(const ApplyArgs a) {
 // Writes g_q (fp32, into the dQ accumulator of the sparse backward), g_num /
 // g_den rows (inputs of the dL/dC state build), a go (bf16, upstream gradient of
 // the sparse branch) and the per-row alpha-logit gradient a (1 - a) go . (o_s - o_l).
+// Two tile products per 64 rows: phi H (num) and g_num H^T (g_phi).
 // --------------------------------------------------------------------------
 struct BwdRowsArgs {
   RowPtr q, os, go;
@@ -293,103 +347,92 @@ struct BwdRowsArgs {
 };
 
 __global__ void __launch_bounds__(256) lin_bwd_rows_kernel(const BwdRowsArgs a) {
-  extern __shared__ float sm[];
-  float* C = sm;                      // [64][69]: odd pitch, rows are read with stride 4 below
-  float* P = C + 64 * 69;             // phi rows [64][65]
-  float* G = P + 64 * 65;             // g_num rows [64][65]
+  extern __shared__ __align__(16) float sm[];
+  float* C = sm;                      // [64 d][LP]: H | z
+  float* Ct = C + LSTATE;             // [64 e][LP]: H^T
+  float* P = Ct + 64 * LP;            // phi rows
+  float* G = P + 64 * LP;             // g_num rows
+  __shared__ float Den[64], GD[64];
   const int m = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const float* src = a.C + (((int64_t)b * a.H + h) * a.Mb + m) * LSTATE;
-  for (int i = tid; i < 64 * LW; i += 256) {
-    const int d = i / LW, e = i - d * LW;
-    C[d * 69 + e] = src[i];
-  }
-  const int r = tid >> 2, qd = tid & 3, e0 = qd * 16;
-  for (int c0 = 0; c0 < a.qblk; c0 += 64) {
-    __syncthreads();
+  load_state(C, a.C + (((int64_t)b * a.H + h) * a.Mb + m) * LSTATE, tid);
+  __syncthreads();
+  transpose_state(Ct, C, tid);
+  const float z0 = C[(2 * lane) * LP + 64], z1 = C[(2 * lane + 1) * LP + 64];
+  const int r0 = (tid >> 4) * 4, c0 = (tid & 15) * 4, tx = tid & 15;
+  float zc[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) zc[j] = C[(c0 + j) * LP + 64];
+  for (int ch = 0; ch < a.qblk; ch += 64) {
+    if (ch) __syncthreads();
     for (int rr = warp; rr < 64; rr += 8) {
-      const int row = m * a.qblk + c0 + rr;
+      const int row = m * a.qblk + ch + rr;
       float2 phi = make_float2(0.f, 0.f);
       if (row < a.L) softmax_row(ld_bf16x2(a.q, b, row, h, 2 * lane), phi);
-      P[rr * 65 + 2 * lane] = phi.x;
-      P[rr * 65 + 2 * lane + 1] = phi.y;
+      *reinterpret_cast<float2*>(P + rr * LP + 2 * lane) = phi;
+      const float den = warp_sum(fmaf(phi.x, z0, phi.y * z1));
+      if (lane == 0) Den[rr] = den + LIN_EPS;
     }
-    __syncthreads();
-    const int row = m * a.qblk + c0 + r;
-    const bool live = row < a.L;
-    float num[16] = {};
-    float den = LIN_EPS;
-    for (int d = 0; d < 64; ++d) {
-      const float f = P[r * 65 + d];
-      den = fmaf(f, C[d * 69 + 64], den);
+    __syncthreads();                  // also orders the writes of Ct before its first use
+    float num[4][4] = {};
+    tile_mm(P, C, r0, c0, num);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) num[j] = fmaf(f, C[d * 69 + e0 + j], num[j]);
-    }
-    const float inv = 1.f / den;
-    float al = 0.f, uo = 0.f, ga = 0.f;
-    float gn[16];
-    const int64_t roff = (((int64_t)b * a.L + row) * a.H + h) * 64 + e0;
-    if (live) {
-      al = a.a_rows[(int64_t)h * a.L + row];
-      const __nv_bfloat16* go = static_cast<const __nv_bfloat16*>(a.go.p) + b * a.go.sb +
-                                (int64_t)row * a.go.sl + h * a.go.sh + e0;
-      const __nv_bfloat16* os = static_cast<const __nv_bfloat16*>(a.os.p) + b * a.os.sb +
-                                (int64_t)row * a.os.sl + h * a.os.sh + e0;
-      __nv_bfloat16* gos = static_cast<__nv_bfloat16*>(const_cast<void*>(a.gos.p)) + b * a.gos.sb +
-                           (int64_t)row * a.gos.sl + h * a.gos.sh + e0;
+    for (int i = 0; i < 4; ++i) {
+      const int row = m * a.qblk + ch + r0 + i;
+      const bool live = row < a.L;    // no early exit: the shuffles below need every lane
+      const float inv = 1.f / Den[r0 + i];
+      float gn[4] = {0.f, 0.f, 0.f, 0.f};
+      float uo = 0.f, ga = 0.f, al = 0.f;
+      if (live) {
+        al = a.a_rows[(int64_t)h * a.L + row];
+        float g[4], s[4];
+        ld_bf16x4(row_at(a.go, b, row, h) + c0, g);
+        ld_bf16x4(row_at(a.os, b, row, h) + c0, s);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float g = __bfloat162float(go[j]);
-        const float ol = num[j] * inv;
-        const float u = (1.f - al) * g;
-        uo = fmaf(u, ol, uo);
-        ga = fmaf(g, __bfloat162float(os[j]) - ol, ga);
-        gn[j] = u * inv;
-        gos[j] = __float2bfloat16(al * g);
+        for (int j = 0; j < 4; ++j) {
+          const float ol = num[i][j] * inv;
+          const float u = (1.f - al) * g[j];
+          uo = fmaf(u, ol, uo);
+          ga = fmaf(g[j], s[j] - ol, ga);
+          gn[j] = u * inv;
+        }
+        st_bf16x4(row_at(a.gos, b, row, h) + c0, al * g[0], al * g[1], al * g[2], al * g[3]);
+        *reinterpret_cast<float4*>(a.gnum + (((int64_t)b * a.L + row) * a.H + h) * 64 + c0) =
+            make_float4(gn[0], gn[1], gn[2], gn[3]);
       }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) gn[j] = 0.f;
-    }
-    // the four threads of a row hold 16 columns each
-    uo += __shfl_xor_sync(0xffffffffu, uo, 1);
-    uo += __shfl_xor_sync(0xffffffffu, uo, 2);
-    ga += __shfl_xor_sync(0xffffffffu, ga, 1);
-    ga += __shfl_xor_sync(0xffffffffu, ga, 2);
-    const float g_den = -uo * inv;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) G[r * 65 + e0 + j] = gn[j];
-    if (live) {
-#pragma unroll
-      for (int j = 0; j < 16; j += 4)
-        *reinterpret_cast<float4*>(a.gnum + roff + j) = make_float4(gn[j], gn[j + 1], gn[j + 2], gn[j + 3]);
-      if (qd == 0) {
-        const int64_t so = ((int64_t)b * a.H + h) * a.L + row;
-        a.gden[so] = g_den;
-        a.ga_row[so] = al * (1.f - al) * ga;
+      *reinterpret_cast<float4*>(G + (r0 + i) * LP + c0) = make_float4(gn[0], gn[1], gn[2], gn[3]);
+      uo = half_warp_sum(uo);
+      ga = half_warp_sum(ga);
+      if (tx == 0) {
+        const float g_den = -uo * inv;
+        GD[r0 + i] = g_den;
+        if (live) {
+          const int64_t so = ((int64_t)b * a.H + h) * a.L + row;
+          a.gden[so] = g_den;
+          a.ga_row[so] = al * (1.f - al) * ga;
+        }
       }
     }
     __syncthreads();
-    // g_phi for d = qd + 4 i
-    float gp[16];
-    float dot = 0.f;
+    float gp[4][4] = {};
+    tile_mm(G, Ct, r0, c0, gp);       // columns are d here
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int d = qd + 4 * i;
-      float acc = g_den * C[d * 69 + 64];
-      for (int e = 0; e < 64; ++e) acc = fmaf(C[d * 69 + e], G[r * 65 + e], acc);
-      gp[i] = acc;
-      dot = fmaf(P[r * 65 + d], acc, dot);
-    }
-    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-    if (live) {
-      float* gq = a.gq + (((int64_t)b * a.L + row) * a.H + h) * 64;
+    for (int i = 0; i < 4; ++i) {
+      const int row = m * a.qblk + ch + r0 + i;
+      const float g_den = GD[r0 + i];
+      const float4 p4 = *reinterpret_cast<const float4*>(P + (r0 + i) * LP + c0);
+      const float ps[4] = {p4.x, p4.y, p4.z, p4.w};
+      float dot = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const int d = qd + 4 * i;
-        gq[d] = P[r * 65 + d] * (gp[i] - dot);
+      for (int j = 0; j < 4; ++j) {
+        gp[i][j] = fmaf(g_den, zc[j], gp[i][j]);
+        dot = fmaf(ps[j], gp[i][j], dot);
       }
+      dot = half_warp_sum(dot);
+      if (row < a.L)
+        *reinterpret_cast<float4*>(a.gq + (((int64_t)b * a.L + row) * a.H + h) * 64 + c0) =
+            make_float4(ps[0] * (gp[i][0] - dot), ps[1] * (gp[i][1] - dot),
+                        ps[2] * (gp[i][2] - dot), ps[3] * (gp[i][3] - dot));
     }
   }
 }
@@ -406,17 +449,14 @@ struct BwdKvArgs {
 };
 
 __global__ void __launch_bounds__(256) lin_bwd_kv_kernel(const BwdKvArgs a) {
-  extern __shared__ float sm[];
-  float* C = sm;                      // [64][69]
-  float* P = C + 64 * 69;             // phi(k) rows [64][65]
-  float* V = P + 64 * 65;             // v rows [64][65]
+  extern __shared__ __align__(16) float sm[];
+  float* C = sm;                      // [64 d][LP]: gH | gz
+  float* Ct = C + LSTATE;             // [64 e][LP]: gH^T
+  float* P = Ct + 64 * LP;            // phi(k) rows
+  float* V = P + 64 * LP;             // v rows
   const int n = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const float* src = a.gS + (((int64_t)b * a.H + h) * a.Nb + n) * LSTATE;
-  for (int i = tid; i < 64 * LW; i += 256) {
-    const int d = i / LW, e = i - d * LW;
-    C[d * 69 + e] = src[i];
-  }
+  load_state(C, a.gS + (((int64_t)b * a.H + h) * a.Nb + n) * LSTATE, tid);
   for (int rr = warp; rr < 64; rr += 8) {
     const int row = n * 64 + rr;
     float2 phi = make_float2(0.f, 0.f), vv = phi;
@@ -424,50 +464,54 @@ __global__ void __launch_bounds__(256) lin_bwd_kv_kernel(const BwdKvArgs a) {
       softmax_row(ld_bf16x2(a.k, b, row, h, 2 * lane), phi);
       vv = ld_bf16x2(a.v, b, row, h, 2 * lane);
     }
-    P[rr * 65 + 2 * lane] = phi.x;
-    P[rr * 65 + 2 * lane + 1] = phi.y;
-    V[rr * 65 + 2 * lane] = vv.x;
-    V[rr * 65 + 2 * lane + 1] = vv.y;
+    *reinterpret_cast<float2*>(P + rr * LP + 2 * lane) = phi;
+    *reinterpret_cast<float2*>(V + rr * LP + 2 * lane) = vv;
   }
   __syncthreads();
-  const int r = tid >> 2, qd = tid & 3, e0 = qd * 16;
-  const int row = n * 64 + r;
-  const bool live = row < a.L;       // no early return: the shuffles below need every lane
-  // g_v for columns e0 .. e0 + 15
-  float gv[16] = {};
-  for (int d = 0; d < 64; ++d) {
-    const float f = P[r * 65 + d];
+  transpose_state(Ct, C, tid);
+  const int r0 = (tid >> 4) * 4, c0 = (tid & 15) * 4;
+  float gv[4][4] = {};
+  tile_mm(P, C, r0, c0, gv);          // g_v, columns e
+  __syncthreads();
+  float gp[4][4] = {};
+  tile_mm(V, Ct, r0, c0, gp);         // g_phi, columns d
+  float gz[4];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) gv[j] = fmaf(f, C[d * 69 + e0 + j], gv[j]);
+  for (int j = 0; j < 4; ++j) gz[j] = C[(c0 + j) * LP + 64];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = n * 64 + r0 + i;
+    const float4 p4 = *reinterpret_cast<const float4*>(P + (r0 + i) * LP + c0);
+    const float ps[4] = {p4.x, p4.y, p4.z, p4.w};
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      gp[i][j] += gz[j];
+      dot = fmaf(ps[j], gp[i][j], dot);
+    }
+    dot = half_warp_sum(dot);         // every lane takes part; rows past L only skip the stores
+    if (row >= a.L) continue;
+    float s[4];
+    ld_bf16x4(row_at(a.gvs, b, row, h) + c0, s);
+    st_bf16x4(row_at(a.gv, b, row, h) + c0, s[0] + gv[i][0], s[1] + gv[i][1], s[2] + gv[i][2],
+              s[3] + gv[i][3]);
+    ld_bf16x4(row_at(a.gks, b, row, h) + c0, s);
+    st_bf16x4(row_at(a.gk, b, row, h) + c0, s[0] + ps[0] * (gp[i][0] - dot),
+              s[1] + ps[1] * (gp[i][1] - dot), s[2] + ps[2] * (gp[i][2] - dot),
+              s[3] + ps[3] * (gp[i][3] - dot));
   }
-  // g_phi for d = qd + 4 i
-  float gp[16];
-  float dot = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int d = qd + 4 * i;
-    float acc = C[d * 69 + 64];
-    for (int e = 0; e < 64; ++e) acc = fmaf(C[d * 69 + e], V[r * 65 + e], acc);
-    gp[i] = acc;
-    dot = fmaf(P[r * 65 + d], acc, dot);
+}
+
+
+// 8-byte accesses of four bf16: base pointers 8-byte aligned, strides multiples of 4 elements
+static bool rows_vec4_ok(const void* const* ptrs, int n, const int64_t* strides) {
+  for (int i = 0; i < n; ++i) {
+    if (!ptrs[i]) continue;
+    if (reinterpret_cast<uintptr_t>(ptrs[i]) & 7) return false;
+    for (int j = 0; j < 3; ++j)
+      if (strides[3 * i + j] & 3) return false;
   }
-  dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-  dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-  if (!live) return;
-  auto at = [&](const RowPtr& t) {
-    return static_cast<__nv_bfloat16*>(const_cast<void*>(t.p)) + b * t.sb + (int64_t)row * t.sl +
-           h * t.sh;
-  };
-  const __nv_bfloat16 *gks = at(a.gks), *gvs = at(a.gvs);
-  __nv_bfloat16 *gk = at(a.gk), *gvo = at(a.gv);
-#pragma unroll
-  for (int j = 0; j < 16; ++j)
-    gvo[e0 + j] = __float2bfloat16(__bfloat162float(gvs[e0 + j]) + gv[j]);
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const int d = qd + 4 * i;
-    gk[d] = __float2bfloat16(__bfloat162float(gks[d]) + P[r * 65 + d] * (gp[i] - dot));
-  }
+  return true;
 }
 
 static RowPtr row_ptr(const void* p, const int64_t* st) {
@@ -526,6 +570,8 @@ extern "C" int imf_lin_apply(const void* q, const void* dq, const void* os, cons
                              void* dout, int B, int L, int H, int Mb, int qblk,
                              const int64_t* strides, void* stream) {
   if (qblk % 64 || B <= 0) return -1;
+  const void* ptrs[6] = {q, dq, os, dos, o, dout};
+  if (!rows_vec4_ok(ptrs, 6, strides)) return -2;
   ApplyArgs a;
   a.q = row_ptr(q, strides);
   a.dq = row_ptr(dq, strides + 3);
@@ -536,7 +582,7 @@ extern "C" int imf_lin_apply(const void* q, const void* dq, const void* os, cons
   a.C = C; a.dC = dC; a.a_rows = a_rows;
   a.L = L; a.H = H; a.Mb = Mb; a.qblk = qblk;
   const dim3 grid(Mb, H, B);
-  const size_t base = (size_t)(LSTATE + 64 * 65) * sizeof(float);
+  const size_t base = (size_t)(LSTATE + 64 * LP) * sizeof(float);
   if (dq) {
     if (set_smem(lin_apply_kernel<true>, 2 * base)) return -3;
     lin_apply_kernel<true><<<grid, 256, 2 * base, (cudaStream_t)stream>>>(a);
@@ -552,6 +598,8 @@ extern "C" int imf_lin_bwd_rows(const void* q, const void* os, const void* go, c
                                 float* ga_row, void* gos, int B, int L, int H, int Mb, int qblk,
                                 const int64_t* strides, void* stream) {
   if (qblk % 64 || B <= 0) return -1;
+  const void* ptrs[4] = {q, os, go, gos};
+  if (!rows_vec4_ok(ptrs, 4, strides)) return -2;
   BwdRowsArgs a;
   a.q = row_ptr(q, strides);
   a.os = row_ptr(os, strides + 3);
@@ -559,7 +607,7 @@ extern "C" int imf_lin_bwd_rows(const void* q, const void* os, const void* go, c
   a.gos = row_ptr(gos, strides + 9);
   a.C = C; a.a_rows = a_rows; a.gq = gq; a.gnum = gnum; a.gden = gden; a.ga_row = ga_row;
   a.L = L; a.H = H; a.Mb = Mb; a.qblk = qblk;
-  const size_t smem = (size_t)(64 * 69 + 2 * 64 * 65) * sizeof(float);
+  const size_t smem = (size_t)(LSTATE + 3 * 64 * LP) * sizeof(float);
   if (set_smem(lin_bwd_rows_kernel, smem)) return -3;
   lin_bwd_rows_kernel<<<dim3(Mb, H, B), 256, smem, (cudaStream_t)stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
@@ -570,6 +618,8 @@ extern "C" int imf_lin_bwd_kv(const void* k, const void* v, const void* gks, con
                               const float* gS, void* gk, void* gv, int B, int L, int H, int Nb,
                               int lim, const int64_t* strides, void* stream) {
   if (B <= 0) return -1;
+  const void* ptrs[6] = {k, v, gks, gvs, gk, gv};
+  if (!rows_vec4_ok(ptrs, 6, strides)) return -2;
   BwdKvArgs a;
   a.k = row_ptr(k, strides);
   a.v = row_ptr(v, strides + 3);
@@ -578,7 +628,7 @@ extern "C" int imf_lin_bwd_kv(const void* k, const void* v, const void* gks, con
   a.gk = row_ptr(gk, strides + 12);
   a.gv = row_ptr(gv, strides + 15);
   a.gS = gS; a.L = L; a.H = H; a.Nb = Nb; a.lim = lim < L ? lim : L;
-  const size_t smem = (size_t)(64 * 69 + 2 * 64 * 65) * sizeof(float);
+  const size_t smem = (size_t)(LSTATE + 3 * 64 * LP) * sizeof(float);
   if (set_smem(lin_bwd_kv_kernel, smem)) return -3;
   lin_bwd_kv_kernel<<<dim3(Nb, H, B), 256, smem, (cudaStream_t)stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;

@@ -229,14 +229,19 @@ route_topk_kernel(const float* __restrict__ qb, const float* __restrict__ kb,
     wv[tid] = uv[tid];
   }
   __syncthreads();
-  const float2 w2 = make_float2(wv[2 * lane], wv[2 * lane + 1]);
-  const float* kbase = kb + ((bh * Nkb) << 6) + 2 * lane;
-  for (int n = warp; n < Nk; n += RT_THREADS / 32) {
-    const float2 kv = *reinterpret_cast<const float2*>(kbase + ((size_t)n << 6));
-    float d = fmaf(w2.x, kv.x, w2.y * kv.y);
+  // one key block per thread: 16 independent 16-byte loads per score
+  for (int n = tid; n < Nk; n += RT_THREADS) {
+    const float4* kr = reinterpret_cast<const float4*>(kb + ((bh * Nkb + n) << 6));
+    float d = 0.f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-    if (lane == 0) sc[n] = d * scale;
+    for (int j = 0; j < 16; ++j) {
+      const float4 kv = __ldg(kr + j);
+      d = fmaf(wv[4 * j], kv.x, d);
+      d = fmaf(wv[4 * j + 1], kv.y, d);
+      d = fmaf(wv[4 * j + 2], kv.z, d);
+      d = fmaf(wv[4 * j + 3], kv.w, d);
+    }
+    sc[n] = d * scale;
   }
   if (tid == 0) {
     s_prefix = 0u;

@@ -7,6 +7,8 @@ under ``ncu`` (or for a quick CUDA-event timing without it).
     python -m imfvideo_b200.ops.profile_kernels gemm      --M 58280 --N 528 --K 256
     python -m imfvideo_b200.ops.profile_kernels sparse    --L 9472
     python -m imfvideo_b200.ops.profile_kernels resnorm   --rows 29140
+    python -m imfvideo_b200.ops.profile_kernels lin       --L 29140      # linear-branch kernels, one line each
+    python -m imfvideo_b200.ops.profile_kernels route     --L 29140      # block means + top-k
 
 Prints the CUDA-event time per launch (after warm-up, inputs larger than L2
 or L2 flushed between launches) and the achieved fraction of the measured
@@ -41,7 +43,7 @@ def _time(fn, iters: int, flush) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["attn_fwd", "attn_jvp", "attn_bwd", "gemm", "sparse",
-                                       "sparse_jvp", "resnorm"])
+                                       "sparse_jvp", "resnorm", "lin", "route"])
     ap.add_argument("--L", type=int, default=9472)
     ap.add_argument("--B", type=int, default=1)
     ap.add_argument("--H", type=int, default=4)
@@ -91,6 +93,42 @@ def main() -> None:
         tang = args.kernel == "sparse_jvp"
         fn = lambda: SP.sparse_fwd(q, k, v, dq if tang else None, dk if tang else None,
                                    dv if tang else None, lut, flags, 64, True, True)
+    elif args.kernel in ("lin", "route"):
+        from . import linattn as LA
+        from . import sparse as SP
+
+        q, k, v, o_s, go = (mk() for _ in range(5))
+        Mb = Nb = -(-L // 64)
+        T = max(1, Nb // 10)
+        qh, kh = q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3)
+        if args.kernel == "route":
+            qb, kb = SP.pool_blocks(qh, 64), SP.pool_blocks(kh, 64)
+            eye = torch.eye(64, device=dev)
+            for name, f in (("pool_blocks", lambda: SP.pool_blocks(qh, 64)),
+                            ("route_topk", lambda: SP.route_topk(qb, kb, T, eye, eye))):
+                print(json.dumps({"kernel": name, "ms": _time(f, args.iters, flush)}))
+            K.check_status()
+            return
+        sel = SP.route_topk(SP.pool_blocks(qh, 64), SP.pool_blocks(kh, 64), T)
+        a_rows = torch.full((H, L), 0.9, device=dev)
+        S2, _ = LA.states(k, None, v, None, None, 64, L)
+        cm2 = LA.comp_mask(sel, Mb, Nb)
+        o, _, C = LA.forward(q, k, v, None, None, None, o_s, None, sel, a_rows, 64, 64, None)
+        gq, gnum, gden, ga, g_os = LA.backward_rows(q, o_s, go, C, a_rows, 64)
+        steps = (
+            ("lin_states", lambda: LA.states(k, None, v, None, None, 64, L)),
+            ("comp_mask (torch)", lambda: LA.comp_mask(sel, Mb, Nb)),
+            ("mask gemm", lambda: K.gemm_batched(cm2, S2, b_mn=True, out_dtype=torch.float32)),
+            ("forward (states + mask + gemm + apply)",
+             lambda: LA.forward(q, k, v, None, None, None, o_s, None, sel, a_rows, 64, 64, None)),
+            ("lin_bwd_rows", lambda: LA.backward_rows(q, o_s, go, C, a_rows, 64)),
+            ("backward_kv (states + mask + gemm + kv)",
+             lambda: LA.backward_kv(q, k, v, gnum, gden, sel, g_os, g_os, 64, 64, None)),
+        )
+        for name, f in steps:
+            print(json.dumps({"kernel": name, "ms": _time(f, args.iters, flush)}))
+        K.check_status()
+        return
     else:
         from . import rowops as R
 
