@@ -198,7 +198,7 @@ route_topk_kernel(const float* __restrict__ qb, const float* __restrict__ kb,
                   int* __restrict__ sel, float* __restrict__ scores_out, int Mb, int Nkb, int Nk,
                   int T, int n_tail, int tail0, float scale) {
   extern __shared__ float sc[];                    // Nk scores
-  __shared__ float qv[64], uv[64], wv[64];
+  __shared__ __align__(16) float qv[64], uv[64], wv[64];
   __shared__ int hist[256];
   __shared__ unsigned int s_prefix, s_mask;
   __shared__ int s_remaining;
@@ -207,41 +207,64 @@ route_topk_kernel(const float* __restrict__ qb, const float* __restrict__ kb,
   const size_t bh = (size_t)b * H + h;
   if (tid < 64) qv[tid] = qb[((bh * Mb + m) << 6) + tid];
   __syncthreads();
-  if (Pq) {
-    if (tid < 64) {
-      float a = 0.f;
-#pragma unroll 8
-      for (int j = 0; j < 64; ++j) a = fmaf(Pq[tid * 64 + j], qv[j], a);
-      uv[tid] = a;
+  // every global access below is a whole 256-byte row per (half) warp: a divergent
+  // row-per-thread access costs one L1 tag look-up per lane
+  if (Pq) {                                        // u = Pq q: one row per warp, four in flight
+    const float2 q2 = make_float2(qv[2 * lane], qv[2 * lane + 1]);
+    for (int i0 = warp * 16; i0 < warp * 16 + 16; i0 += 4) {
+      float part[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float2 p2 = __ldg(reinterpret_cast<const float2*>(Pq + (i0 + r) * 64) + lane);
+        part[r] = fmaf(p2.x, q2.x, p2.y * q2.y);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) part[r] += __shfl_xor_sync(0xffffffffu, part[r], o);
+      if (lane < 4) uv[i0 + lane] = part[lane == 0 ? 0 : lane == 1 ? 1 : lane == 2 ? 2 : 3];
     }
   } else if (tid < 64) {
     uv[tid] = qv[tid];
   }
   __syncthreads();
-  if (Pk) {
-    if (tid < 64) {
-      float a = 0.f;
+  if (Pk) {                                        // w = Pk^T u: column per thread, rows split in two
+    const int j = tid & 63, half = tid >> 6;
+    float acc = 0.f;
 #pragma unroll 8
-      for (int i = 0; i < 64; ++i) a = fmaf(Pk[i * 64 + tid], uv[i], a);
-      wv[tid] = a;
-    }
+    for (int i = half * 32; i < half * 32 + 32; ++i) acc = fmaf(__ldg(Pk + i * 64 + j), uv[i], acc);
+    if (half) qv[j] = acc;                         // qv is free after the first product
+    __syncthreads();
+    if (!half) wv[j] = acc + qv[j];
   } else if (tid < 64) {
     wv[tid] = uv[tid];
   }
   __syncthreads();
-  // one key block per thread: 16 independent 16-byte loads per score
-  for (int n = tid; n < Nk; n += RT_THREADS) {
-    const float4* kr = reinterpret_cast<const float4*>(kb + ((bh * Nkb + n) << 6));
-    float d = 0.f;
+  {                                                // scores: half a warp per key, eight keys in flight
+    const int hl = lane & 15, sub = lane >> 4;
+    const float4 w4 = *reinterpret_cast<const float4*>(wv + 4 * hl);
+    const float4* kbase = reinterpret_cast<const float4*>(kb + ((bh * Nkb) << 6)) + hl;
+    for (int n0 = warp * 8; n0 < Nk; n0 += (RT_THREADS / 32) * 8) {
+      float part[4];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float4 kv = __ldg(kr + j);
-      d = fmaf(wv[4 * j], kv.x, d);
-      d = fmaf(wv[4 * j + 1], kv.y, d);
-      d = fmaf(wv[4 * j + 2], kv.z, d);
-      d = fmaf(wv[4 * j + 3], kv.w, d);
+      for (int r = 0; r < 4; ++r) {
+        const int n = n0 + 2 * r + sub;
+        float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (n < Nk) kv = __ldg(kbase + ((size_t)n << 4));
+        part[r] = fmaf(w4.x, kv.x, fmaf(w4.y, kv.y, fmaf(w4.z, kv.z, w4.w * kv.w)));
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) part[r] += __shfl_xor_sync(0xffffffffu, part[r], o);
+      if (hl == 0) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int n = n0 + 2 * r + sub;
+          if (n < Nk) sc[n] = part[r] * scale;
+        }
+      }
     }
-    sc[n] = d * scale;
   }
   if (tid == 0) {
     s_prefix = 0u;

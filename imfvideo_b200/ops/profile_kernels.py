@@ -8,7 +8,7 @@ under ``ncu`` (or for a quick CUDA-event timing without it).
     python -m imfvideo_b200.ops.profile_kernels sparse    --L 9472
     python -m imfvideo_b200.ops.profile_kernels resnorm   --rows 29140
     python -m imfvideo_b200.ops.profile_kernels lin       --L 29140      # linear-branch kernels, one line each
-    python -m imfvideo_b200.ops.profile_kernels route     --L 29140      # block means + top-k
+    python -m imfvideo_b200.ops.profile_kernels route     --L 29140      # block means, top-k, INT8 quantiser
 
 Prints the CUDA-event time per launch (after warm-up, inputs larger than L2
 or L2 flushed between launches) and the achieved fraction of the measured
@@ -105,7 +105,8 @@ def main() -> None:
             qb, kb = SP.pool_blocks(qh, 64), SP.pool_blocks(kh, 64)
             eye = torch.eye(64, device=dev)
             for name, f in (("pool_blocks", lambda: SP.pool_blocks(qh, 64)),
-                            ("route_topk", lambda: SP.route_topk(qb, kb, T, eye, eye))):
+                            ("route_topk", lambda: SP.route_topk(qb, kb, T, eye, eye)),
+                            ("quantize_blocks", lambda: SP.quantize_blocks(q, 64, want_fq=True))):
                 print(json.dumps({"kernel": name, "ms": _time(f, args.iters, flush)}))
             K.check_status()
             return
