@@ -23,6 +23,7 @@ import torch.nn as nn
 
 from ..ops import dual as D
 from ..ops.dual import Dual
+from ..ops.patch import permute_rows
 
 Tensor = torch.Tensor
 
@@ -97,6 +98,11 @@ class SwiGLUMlp(nn.Module):
 
 def sinusoid(t: Tensor, dim: int, max_period: float = 10000.0) -> Tuple[Tensor, Tensor]:
     """cos|sin features of a scalar and their derivative w.r.t. the scalar."""
+    if t.is_cuda and not t.requires_grad and t.dim() == 1:
+        from ..ops import patch as PK
+
+        if PK.AVAILABLE and not torch._C._are_functorch_transforms_active():
+            return PK.sinusoid(t, dim, max_period)
     half = dim // 2
     freqs = torch.exp(-math.log(max_period)
                       * torch.arange(half, dtype=torch.float32, device=t.device) / half)
@@ -165,11 +171,10 @@ class VideoPatchEmbedder(nn.Module):
                 self.proj.bias.zero_()
 
     def patches(self, x: Tensor) -> Tensor:
-        b, c, t, h, w = x.shape
-        pt, ph, pw = self.patch_size
-        x = x.reshape(b, c, t // pt, pt, h // ph, ph, w // pw, pw)
-        x = x.permute(0, 2, 4, 6, 1, 3, 5, 7)          # b, gt, gh, gw, c, pt, ph, pw
-        return x.reshape(b, (t // pt) * (h // ph) * (w // pw), c * pt * ph * pw)
+        """(b, c, t, h, w) -> (b, gt*gh*gw, c*pt*ph*pw): one gather kernel on CUDA."""
+        from ..ops.patch import patch_rows
+
+        return patch_rows(x, self.patch_size, c_last=False)
 
     def forward(self, x) -> Dual:
         x = D.lift(x).map(self.patches)
@@ -570,14 +575,14 @@ class IMFDiTVideo(nn.Module):
                 and not torch._C._are_functorch_transforms_active())
 
     def unpatchify(self, x: Tensor) -> Tensor:
-        """(B, N, pt*ph*pw*C) -> (B, C, T, H, W)."""
-        b = x.shape[0]
-        c = self.out_channels
+        """(B, N, pt*ph*pw*C) bf16 / fp32 -> (B, C, T, H, W) fp32 (one scatter kernel on CUDA)."""
+        from ..ops.patch import unpatch_rows
+
         pt, ph, pw = self.patch_size
         gt, gh, gw = self.grid_size
         assert gt * gh * gw == x.shape[1]
-        x = x.reshape(b, gt, gh, gw, pt, ph, pw, c).permute(0, 7, 1, 4, 2, 5, 3, 6)
-        return x.reshape(b, c, gt * pt, gh * ph, gw * pw)
+        shape = (x.shape[0], self.out_channels, gt * pt, gh * ph, gw * pw)
+        return unpatch_rows(x, shape, self.patch_size, c_last=True)
 
     def _build_sequence(self, x, h, w, t_min, t_max, y) -> Dual:
         """[class | omega | t_min | t_max | time | patches]; omega enters as
@@ -675,18 +680,18 @@ class IMFDiTVideo(nn.Module):
         n, dn = out_head(pf, sn, w, final.norm.weight, final.norm.eps)
         seq = Dual(n, dn)
         if self.tile_major:
-            seq = seq.map(lambda z: z[:, self.tm_inv])
+            seq = seq.map(lambda z: permute_rows(z, self.tm_inv, self.tm_perm))
         tok = seq.map(lambda z: z[:, self.prefix_tokens:])
         y = D.linear(tok, final.linear.weight, final.linear.bias)
-        return y.map(lambda z: self.unpatchify(z.float()))
+        return y.map(self.unpatchify)
 
     def _head(self, seq: Dual, final: FinalLayer, keep_tangent: bool):
         if self.tile_major:
-            seq = seq.map(lambda z: z[:, self.tm_inv])
+            seq = seq.map(lambda z: permute_rows(z, self.tm_inv, self.tm_perm))
         tok = seq.map(lambda z: z[:, self.prefix_tokens:])
         if not keep_tangent:
             tok = Dual(tok.p, None)
-        out = final(tok, self.compute_dtype).map(lambda z: self.unpatchify(z.float()))
+        out = final(tok, self.compute_dtype).map(self.unpatchify)
         return out
 
     # ----------------------------------------------------------- forward ---
@@ -708,7 +713,7 @@ class IMFDiTVideo(nn.Module):
             branches = [b for b in branches if b == "u"] or ["u"]
         seq = self._build_sequence(x, h, w, t_min, t_max, y)
         if self.tile_major:
-            seq = seq.map(lambda z: z[:, self.tm_perm])
+            seq = seq.map(lambda z: permute_rows(z, self.tm_perm, self.tm_inv))
         need_t = seq.t is not None and any(b in tangent_branches for b in branches)
         if not need_t:
             seq = Dual(seq.p, None)

@@ -277,6 +277,7 @@ __global__ void __launch_bounds__(256) lin_apply_kernel(const ApplyArgs a) {
   const int r0 = (tid >> 4) * 4, c0 = (tid & 15) * 4;
   for (int ch = 0; ch < a.qblk; ch += 64) {
     if (ch) __syncthreads();
+#pragma unroll 4
     for (int rr = warp; rr < 64; rr += 8) {
       const int row = m * a.qblk + ch + rr;
       float2 phi = make_float2(0.f, 0.f), dphi = phi;
@@ -365,6 +366,7 @@ __global__ void __launch_bounds__(256) lin_bwd_rows_kernel(const BwdRowsArgs a) 
   for (int j = 0; j < 4; ++j) zc[j] = C[(c0 + j) * LP + 64];
   for (int ch = 0; ch < a.qblk; ch += 64) {
     if (ch) __syncthreads();
+#pragma unroll 4
     for (int rr = warp; rr < 64; rr += 8) {
       const int row = m * a.qblk + ch + rr;
       float2 phi = make_float2(0.f, 0.f);
@@ -457,6 +459,7 @@ __global__ void __launch_bounds__(256) lin_bwd_kv_kernel(const BwdKvArgs a) {
   const int n = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   load_state(C, a.gS + (((int64_t)b * a.H + h) * a.Nb + n) * LSTATE, tid);
+#pragma unroll 4
   for (int rr = warp; rr < 64; rr += 8) {
     const int row = n * 64 + rr;
     float2 phi = make_float2(0.f, 0.f), vv = phi;
