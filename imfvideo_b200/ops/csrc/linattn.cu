@@ -517,6 +517,60 @@ static bool rows_vec4_ok(const void* const* ptrs, int n, const int64_t* strides)
   return true;
 }
 
+// --------------------------------------------------------------------------
+// 0/1 complement masks of the selection, duplicated for the (hi, lo) halves of
+// the states: cm[(b,h)][m][n] = cm[(b,h)][m][cp + n] = 1 unless key block n is
+// selected by query block m (n < Nb; pads are 0).  `transposed` writes the
+// [(b,h)][n][2 * pad4(Mb)] form instead, in two launches (fill, then clear).
+// --------------------------------------------------------------------------
+__global__ void comp_mask_rows_kernel(const int* __restrict__ sel, __nv_bfloat16* __restrict__ cm,
+                                      int Mb, int Nb, int T, int cp) {
+  const int m = blockIdx.x;
+  const size_t bh = blockIdx.y;
+  __nv_bfloat16* row = cm + (bh * Mb + m) * (size_t)(2 * cp);
+  const __nv_bfloat16 one = __float2bfloat16(1.f), zero = __float2bfloat16(0.f);
+  for (int i = threadIdx.x; i < 2 * cp; i += blockDim.x) {
+    const int n = i < cp ? i : i - cp;
+    row[i] = n < Nb ? one : zero;
+  }
+  __syncthreads();
+  const int* s = sel + (bh * Mb + m) * (size_t)T;
+  for (int t = threadIdx.x; t < T; t += blockDim.x) {
+    const int n = s[t];
+    if (n >= 0 && n < Nb) {
+      row[n] = zero;
+      row[cp + n] = zero;
+    }
+  }
+}
+
+__global__ void comp_mask_fill_t_kernel(__nv_bfloat16* __restrict__ cm, int Mb, int cp) {
+  const size_t rowi = (size_t)blockIdx.y * gridDim.x + blockIdx.x;     // (bh, n)
+  __nv_bfloat16* row = cm + rowi * (size_t)(2 * cp);
+  const __nv_bfloat16 one = __float2bfloat16(1.f), zero = __float2bfloat16(0.f);
+  for (int i = threadIdx.x; i < 2 * cp; i += blockDim.x) {
+    const int m = i < cp ? i : i - cp;
+    row[i] = m < Mb ? one : zero;
+  }
+}
+
+__global__ void comp_mask_clear_t_kernel(const int* __restrict__ sel,
+                                         __nv_bfloat16* __restrict__ cm, int Mb, int Nb, int T,
+                                         int cp) {
+  const int m = blockIdx.x;
+  const size_t bh = blockIdx.y;
+  const int* s = sel + (bh * Mb + m) * (size_t)T;
+  const __nv_bfloat16 zero = __float2bfloat16(0.f);
+  for (int t = threadIdx.x; t < T; t += blockDim.x) {
+    const int n = s[t];
+    if (n >= 0 && n < Nb) {
+      __nv_bfloat16* row = cm + (bh * Nb + n) * (size_t)(2 * cp);
+      row[m] = zero;
+      row[cp + m] = zero;
+    }
+  }
+}
+
 static RowPtr row_ptr(const void* p, const int64_t* st) {
   RowPtr r;
   r.p = p;
@@ -539,6 +593,23 @@ static int set_smem(K kern, size_t bytes) {
 using namespace imf;
 
 extern "C" int imf_lin_state_elems() { return LSTATE; }
+
+// sel (BH, Mb, T) int32 -> cm (BH, Mb, 2 * pad4(Nb)) bf16, or with `transposed`
+// (BH, Nb, 2 * pad4(Mb)).
+extern "C" int imf_comp_mask(const int* sel, void* cm, int BH, int Mb, int Nb, int T,
+                             int transposed, void* stream) {
+  if (BH <= 0 || Mb <= 0 || Nb <= 0 || T <= 0) return -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(cm);
+  if (!transposed) {
+    comp_mask_rows_kernel<<<dim3(Mb, BH), 128, 0, st>>>(sel, out, Mb, Nb, T, (Nb + 3) / 4 * 4);
+  } else {
+    const int cp = (Mb + 3) / 4 * 4;
+    comp_mask_fill_t_kernel<<<dim3(Nb, BH), 128, 0, st>>>(out, Mb, cp);
+    comp_mask_clear_t_kernel<<<dim3(Mb, BH), 64, 0, st>>>(sel, out, Mb, Nb, T, cp);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
 
 // strides: x(3), dx(3), y(3), dy(3) element strides (batch, row, head).
 extern "C" int imf_lin_states(const void* x, const void* dx, const void* y, const void* dy,

@@ -34,6 +34,9 @@ if AVAILABLE:
     _lib.imf_lin_bwd_rows.argtypes = [vp] * 10 + [ci] * 5 + [vp, vp]
     _lib.imf_lin_bwd_kv.restype = ci
     _lib.imf_lin_bwd_kv.argtypes = [vp] * 7 + [ci] * 5 + [vp, vp]
+    if K._has("imf_comp_mask"):
+        _lib.imf_comp_mask.restype = ci
+        _lib.imf_comp_mask.argtypes = [vp, vp] + [ci] * 5 + [vp]
 else:
     LSTATE = 64 * 68
 
@@ -57,6 +60,15 @@ def comp_mask(sel: torch.Tensor, Mb: int, Nb: int, transpose: bool = False) -> t
     """0/1 complement of the selection, duplicated for the (hi, lo) halves of the states:
     ``(B*H, Mb, 2*pad4(Nb))`` bf16, or the transposed ``(B*H, Nb, 2*pad4(Mb))``."""
     B, H = sel.shape[:2]
+    if AVAILABLE and sel.is_cuda and sel.dtype == torch.int32 and K._has("imf_comp_mask"):
+        sel = sel.contiguous()
+        rows, cols = (Nb, Mb) if transpose else (Mb, Nb)
+        out = torch.empty(B * H, rows, 2 * _pad4(cols), dtype=torch.bfloat16, device=sel.device)
+        rc = _lib.imf_comp_mask(K._ptr(sel), K._ptr(out), B * H, Mb, Nb, sel.shape[-1],
+                                int(transpose), K._stream())
+        K._check(rc, "imf_comp_mask")
+        K.LAUNCHES.count += 2 if transpose else 1
+        return out
     cm = torch.ones(B, H, Mb, Nb, dtype=torch.bfloat16, device=sel.device)
     cm.scatter_(-1, sel.long(), 0.0)
     if transpose:

@@ -302,3 +302,23 @@ def test_router_modules_use_the_kernels(SP):
     assert T == T2 and lut_c.shape == lut_r.shape == (B, H, 41, T + 1)
     same = (lut_c.sort(-1).values == lut_r.sort(-1).values.to(lut_c.dtype)).float().mean()
     assert same > 0.99
+
+
+def test_complement_mask_kernel_matches_scatter(SP):
+    from imfvideo_b200.ops import linattn as LA
+
+    torch.manual_seed(7)
+    B, H, Mb, Nb, T = 2, 3, 37, 41, 6
+    sel = torch.stack([torch.randperm(Nb, device="cuda")[:T] for _ in range(B * H * Mb)])
+    sel = sel.view(B, H, Mb, T).to(torch.int32)
+    for transpose in (False, True):
+        got = LA.comp_mask(sel, Mb, Nb, transpose)
+        cm = torch.ones(B, H, Mb, Nb, device="cuda").scatter_(-1, sel.long(), 0.0)
+        if transpose:
+            cm = cm.transpose(-1, -2)
+        rows, cols = cm.shape[-2:]
+        cp = (cols + 3) // 4 * 4
+        want = torch.zeros(B * H, rows, 2 * cp, device="cuda")
+        want[:, :, :cols] = cm.reshape(B * H, rows, cols)
+        want[:, :, cp:cp + cols] = cm.reshape(B * H, rows, cols)
+        assert got.dtype == torch.bfloat16 and torch.equal(got.float(), want)
