@@ -157,3 +157,33 @@ def test_sampling_laws():
     lm2 = IMFVideoLoss(_net(), 1000, strat_group=8)
     us = torch.cat([lm2._strat_uniform(1, "cpu", "s") for _ in range(8)])
     assert sorted((us * 8).floor().int().tolist()) == list(range(8))
+
+
+def test_layout_formulas_are_adjoint_and_match_conv3d():
+    """CPU path of the layout ops: patch rows x flattened Conv3d weight equals the
+    convolution, scatter inverts gather in both feature orders, gather / scatter are
+    adjoint (the autograd rules of the CUDA kernels rely on it), and a row permutation
+    falls back to plain indexing."""
+    from imfvideo_b200.ops import patch as PK
+
+    torch.manual_seed(0)
+    B, C, T, H, W, patch = 2, 4, 4, 6, 8, (2, 2, 2)
+    x = torch.randn(B, C, T, H, W)
+    conv = torch.nn.Conv3d(C, 10, kernel_size=patch, stride=patch)
+    rows = PK.patch_rows(x, patch, c_last=False)
+    y = rows @ conv.weight.reshape(10, -1).t() + conv.bias
+    ref = conv(x).flatten(2).transpose(1, 2)
+    assert torch.allclose(y, ref, atol=1e-5)
+    for c_last in (False, True):
+        r = PK.patch_rows(x, patch, c_last)
+        assert torch.equal(PK.unpatch_rows(r, x.shape, patch, c_last), x)
+        g = torch.randn_like(r)
+        lhs = (r * g).sum()
+        rhs = (x * PK.scatter_formula(g, x.shape, patch, c_last)).sum()
+        assert torch.allclose(lhs, rhs, rtol=1e-5)
+    z = torch.randn(2, 12, 8)
+    perm = torch.randperm(12)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(12)
+    assert torch.equal(PK.permute_rows(z, perm, inv), z[:, perm])
+    assert torch.equal(PK.permute_rows(PK.permute_rows(z, perm, inv), inv, perm), z)
