@@ -116,6 +116,7 @@ class OptimConfig:
     min_lr_ratio: float = 0.1
     grad_accum: int = 1
     fused_adamw: bool = True
+    ns_cuda_graph: bool = False      # replay the Newton-Schulz phase of the optimizer as one CUDA graph
 
 
 @dataclass

@@ -52,8 +52,11 @@ class FlatEngine(GradSync):
     handles_ema = True
 
     def __init__(self, optimizer: Moonlight, net: torch.nn.Module, ema: Optional[torch.nn.Module],
-                 rank: int, world: int, ema_decay: float = 0.0, mode: str = "fused_p2p"):
+                 rank: int, world: int, ema_decay: float = 0.0, mode: str = "fused_p2p",
+                 ns_cuda_graph: bool = False):
         self.opt, self.net, self.ema = optimizer, net, ema
+        self.ns_cuda_graph = bool(ns_cuda_graph)
+        self._ns_graph, self._ns_graph_launches, self._ns_eager_steps = None, 0, 0
         self.rank, self.world, self.mode = rank, world, mode
         self.ema_w = (1.0 - ema_decay) if ema is not None else 0.0
         name_of = {id(p): n for n, p in net.named_parameters()}
@@ -283,25 +286,8 @@ class FlatEngine(GradSync):
                 new_m = own_m * mu + gc
                 own_m.copy_(torch.where(skip.bool(), own_m, new_m))
                 self.Dir.copy_(gc + mu * own_m if nest else own_m)
-            # batched Newton-Schulz per contiguous same-shape run of the owned segment
-            items = self.seg_items[r]
-            j = 0
+            self._newton_schulz_phase(opt, g0, use_k)
             own_u = self.U[r * self.seg_pad:(r + 1) * self.seg_pad]
-            while j < len(items):
-                shp = self.shapes[items[j]]
-                k = j
-                while k < len(items) and self.shapes[items[k]] == shp:
-                    k += 1
-                lo = self.muon_off[items[j]] - r * self.seg_pad
-                cnt = k - j
-                n, m = shp
-                batch = self.Dir[lo:lo + cnt * n * m].view(cnt, n, m)
-                coeffs = get_ns_coefficients(n, m, steps=g0["ns_steps"], mode=g0["coeff_mode"],
-                                             **opt._solve_kw)
-                upd = zeropower_via_newtonschulz5(batch, steps=g0["ns_steps"],
-                                                  dtype=g0["ns_dtype"], coeffs=coeffs)
-                own_u[lo:lo + cnt * n * m].view(cnt, n, m).copy_(upd)
-                j = k
             fused_gather = self.world > 1 and self.comm is not None and use_k
             if self.world > 1 and not fused_gather:
                 if self.comm is not None:
@@ -370,6 +356,53 @@ class FlatEngine(GradSync):
             lerp = self.E + self.ema_w * (self.P - self.E)
             self.E.copy_(torch.where(skip.bool(), self.E, lerp))
 
+    def _newton_schulz_eager(self, opt: Moonlight, g0) -> None:
+        """Batched Newton-Schulz per contiguous same-shape run of the owned segment:
+        ``Dir`` (momentum direction) -> the owned slice of ``U``."""
+        r = self.rank
+        items = self.seg_items[r]
+        j = 0
+        own_u = self.U[r * self.seg_pad:(r + 1) * self.seg_pad]
+        while j < len(items):
+            shp = self.shapes[items[j]]
+            k = j
+            while k < len(items) and self.shapes[items[k]] == shp:
+                k += 1
+            lo = self.muon_off[items[j]] - r * self.seg_pad
+            cnt = k - j
+            n, m = shp
+            batch = self.Dir[lo:lo + cnt * n * m].view(cnt, n, m)
+            coeffs = get_ns_coefficients(n, m, steps=g0["ns_steps"], mode=g0["coeff_mode"],
+                                         **opt._solve_kw)
+            upd = zeropower_via_newtonschulz5(batch, steps=g0["ns_steps"],
+                                              dtype=g0["ns_dtype"], coeffs=coeffs)
+            own_u[lo:lo + cnt * n * m].view(cnt, n, m).copy_(upd)
+            j = k
+
+    def _newton_schulz_phase(self, opt: Moonlight, g0, use_k: bool) -> None:
+        """The phase is a fixed sequence of launches on fixed buffers (arena slices in, arena
+        slices out, constant coefficients, no collective and no host read), so with
+        ``ns_cuda_graph`` it is captured once, after one eager step has warmed every cache,
+        and replayed as one graph launch afterwards."""
+        if not (self.ns_cuda_graph and use_k and self.P.is_cuda):
+            return self._newton_schulz_eager(opt, g0)
+        if self._ns_graph is not None:
+            self._ns_graph.replay()
+            self._K.LAUNCHES.count += self._ns_graph_launches
+            return
+        if self._ns_eager_steps < 1:
+            self._ns_eager_steps += 1
+            return self._newton_schulz_eager(opt, g0)
+        graph = torch.cuda.CUDAGraph()
+        n0 = self._K.LAUNCHES.count
+        with torch.cuda.graph(graph):
+            self._newton_schulz_eager(opt, g0)
+        self._ns_graph_launches = self._K.LAUNCHES.count - n0
+        self._K.LAUNCHES.count = n0
+        self._ns_graph = graph
+        self._ns_graph.replay()
+        self._K.LAUNCHES.count += self._ns_graph_launches
+
     def undo_step_count(self) -> None:
         """Called by the trainer when it learns (from the device skip flag) that
         the last step was skipped, so AdamW's bias-correction count stays exact."""
@@ -401,4 +434,5 @@ class FlatEngine(GradSync):
 
 def attach_engine(trainer, mode: str) -> FlatEngine:
     return FlatEngine(trainer.optimizer, trainer.net, trainer.ema, trainer.rank, trainer.world,
-                      trainer.cfg.run.ema_decay, mode)
+                      trainer.cfg.run.ema_decay, mode,
+                      ns_cuda_graph=getattr(trainer.cfg.optim, "ns_cuda_graph", False))

@@ -264,3 +264,37 @@ def test_layout_kernels_match_formulas(kernels):
     assert torch.allclose(demb, torch.cat([-arg.sin() * freqs, arg.cos() * freqs], -1), atol=1e-5)
     e2, d2 = sinusoid(t, 256)
     assert torch.equal(e2, emb) and torch.equal(d2, demb)
+
+
+def test_newton_schulz_cuda_graph_matches_eager(kernels):
+    """The optimizer's Newton-Schulz phase replayed as a CUDA graph (captured on the second
+    step) writes exactly the updates of the eager launches, and training steps through it."""
+    from imfvideo_b200.config import preset
+    from imfvideo_b200.train import Trainer
+
+    cfg = preset("d256")
+    cfg.model.depth, cfg.model.aux_head_depth = 2, 1
+    cfg.data.latent_frames, cfg.data.latent_size = 4, (16, 32)
+    cfg.optim.warmup_steps = 0
+    cfg.optim.ns_cuda_graph = True
+    tr = Trainer(cfg, device=torch.device("cuda", 0), verbose=False)
+    eng = tr.grad_sync
+    for seed in range(4):
+        g = torch.Generator().manual_seed(100 + seed)
+        x = torch.randn(1, 16, 4, 16, 32, generator=g)
+        y = torch.randint(0, 1000, (1,), generator=g)
+        st = tr.train_step(x, y)
+        assert st["loss"] == st["loss"] and not st["skipped"], st
+        assert (eng._ns_graph is not None) == (seed >= 1)
+    assert eng._ns_graph_launches > 0
+    g0 = next(g for g, _ in eng.muon)
+    n0 = kernels.LAUNCHES.count
+    eng.U.zero_()
+    eng._ns_graph.replay()
+    u_graph = eng.U.clone()
+    eng.U.zero_()
+    eng._newton_schulz_eager(tr.optimizer, g0)
+    assert kernels.LAUNCHES.count - n0 == eng._ns_graph_launches
+    kernels.check_status()
+    assert u_graph.float().abs().sum() > 0
+    assert torch.equal(u_graph, eng.U)
