@@ -140,6 +140,10 @@ def run_ours(args):
     cfg.optim.warmup_steps = 0          # non-zero lr from the first step
     if args.grad_sync:
         cfg.parallel.grad_sync = args.grad_sync
+    if args.override:
+        from imfvideo_b200.config import parse_cli
+
+        parse_cli(args.override, cfg)
     if device.type != "cuda":
         cfg.loss.autocast_bf16 = False
     trainer = Trainer(cfg, rank, world, device, verbose=False)
@@ -261,6 +265,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="d256", choices=sorted(TOKENS))
     ap.add_argument("--grad-sync", default="")
+    ap.add_argument("--override", action="append", default=[], metavar="group.key=value",
+                    help="config override of the measured arm, e.g. optim.ns_cuda_graph=true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     _rank, world, _lr = _dist_env()
