@@ -64,72 +64,63 @@ __global__ void __launch_bounds__(ROW_THREADS) resnorm_fwd_kernel(const ResNormA
       }
     }
     if (a.w) {
-      const int J = a.nsnap + 1;
-      float r[MAX_CANDS], vw[MAX_CANDS], dvw[MAX_CANDS], vdv[MAX_CANDS];
-#pragma unroll 1
-      for (int j = 0; j < J; ++j) {
+      // One pass over the candidates with a running maximum, for the value and its tangent:
+      //   s_j = r_j <v_j, w>,  ds_j = r_j <dv_j, w> - r_j^3 <v_j, w> <v_j, dv_j> / D,
+      //   e_j = exp(s_j - m):  H = sum e_j v_j,  Hd = sum e_j (ds_j v_j + dv_j),
+      //   S = sum e_j,  Sd = sum e_j ds_j;   h = H / S,  dh = Hd / S - (Sd / S) h.
+      // The running prefix (already in registers) is the first candidate, so pf / dpf turn
+      // into H / Hd and every snapshot and snapshot tangent is read exactly once.
+      auto score = [&](const float4(&v)[NV], const float4(&dv)[NV], float& sc, float& dsc) {
         float ss = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
-          const size_t o = base + i * 128;
           const float4 w4 = ld4(a.w + lane * 4 + i * 128);
-          const float4 v = j < a.nsnap ? ld4(a.snaps[j] + o) : pf[i];
-          ss += dot4(v, v);
-          s1 += dot4(v, w4);
-          if (a.has_t) {
-            const float4 dv = j < a.nsnap ? (a.dsnaps[j] ? ld4(a.dsnaps[j] + o) : f4zero()) : dpf[i];
-            s2 += dot4(dv, w4);
-            s3 += dot4(v, dv);
-          }
+          ss += dot4(v[i], v[i]);
+          s1 += dot4(v[i], w4);
+          s2 += dot4(dv[i], w4);
+          s3 += dot4(v[i], dv[i]);
         }
         ss = warp_sum(ss);
         s1 = warp_sum(s1);
-        r[j] = rsqrtf(ss * inv_d + a.eps);
-        vw[j] = s1;
-        if (a.has_t) {
-          dvw[j] = warp_sum(s2);
-          vdv[j] = warp_sum(s3) * inv_d;
-        }
-      }
-      float p[MAX_CANDS], dp[MAX_CANDS];
-      float mx = -INFINITY;
-      for (int j = 0; j < J; ++j) {
-        p[j] = r[j] * vw[j];
-        mx = fmaxf(mx, p[j]);
-      }
-      float den = 0.f;
-      for (int j = 0; j < J; ++j) {
-        p[j] = __expf(p[j] - mx);
-        den += p[j];
-      }
-      float pds = 0.f;
-      for (int j = 0; j < J; ++j) {
-        p[j] /= den;
-        if (a.has_t) {
-          dp[j] = r[j] * dvw[j] - r[j] * r[j] * r[j] * vw[j] * vdv[j];
-          pds += p[j] * dp[j];
-        }
-      }
-      if (a.has_t)
-        for (int j = 0; j < J; ++j) dp[j] = p[j] * (dp[j] - pds);
-        // h = sum p_j v_j, dh = sum dp_j v_j + p_j dv_j  (in place over pf / dpf)
+        s2 = warp_sum(s2);
+        s3 = warp_sum(s3) * inv_d;
+        const float r = rsqrtf(ss * inv_d + a.eps);
+        sc = r * s1;
+        dsc = r * s2 - r * r * r * s1 * s3;
+      };
+      float m, ds0;
+      score(pf, dpf, m, ds0);
+      float S = 1.f, Sd = ds0;
 #pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        if (a.has_t) dpf[i] = fma4(pf[i], dp[J - 1], dpf[i] * p[J - 1]);
-        pf[i] = pf[i] * p[J - 1];
-      }
+      for (int i = 0; i < NV; ++i) dpf[i] = fma4(pf[i], ds0, dpf[i]);
 #pragma unroll 1
       for (int j = 0; j < a.nsnap; ++j) {
+        float4 v[NV], dv[NV];
+        const bool has_dv = a.has_t && a.dsnaps[j];
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
           const size_t o = base + i * 128;
-          const float4 v = ld4(a.snaps[j] + o);
-          pf[i] = fma4(v, p[j], pf[i]);
-          if (a.has_t) {
-            dpf[i] = fma4(v, dp[j], dpf[i]);
-            if (a.dsnaps[j]) dpf[i] = fma4(ld4(a.dsnaps[j] + o), p[j], dpf[i]);
-          }
+          v[i] = ld4(a.snaps[j] + o);
+          dv[i] = has_dv ? ld4(a.dsnaps[j] + o) : f4zero();
         }
+        float sc, dsc;
+        score(v, dv, sc, dsc);
+        const float mn = fmaxf(m, sc);
+        const float al = __expf(m - mn), e = __expf(sc - mn);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          pf[i] = fma4(v[i], e, pf[i] * al);
+          dpf[i] = fma4(fma4(v[i], dsc, dv[i]), e, dpf[i] * al);
+        }
+        S = S * al + e;
+        Sd = Sd * al + e * dsc;
+        m = mn;
+      }
+      const float inv = 1.f / S, sd = Sd * inv;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        pf[i] = pf[i] * inv;
+        dpf[i] = fma4(pf[i], -sd, dpf[i] * inv);
       }
     }
     float hh = 0.f, hdh = 0.f;
