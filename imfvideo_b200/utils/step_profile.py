@@ -1,0 +1,74 @@
+"""Where one training step spends its device time: runs a few warm-up steps of a
+preset on synthetic latents, records one step with ``torch.profiler`` and prints
+the device time per kernel / operator, largest first.
+
+    python -m imfvideo_b200.utils.step_profile --preset d256
+    python -m imfvideo_b200.utils.step_profile --preset d256_sla2 --top 30
+    python -m imfvideo_b200.utils.step_profile --preset d1024 optim.ns_cuda_graph=true
+
+Times taken under the profiler are for comparing shares, not for quoting a step
+time (use ``bench.py`` for that).  The reference has no profiling entry point
+(only wall-clock prints in its train loop, reference train.py); this one is an
+addition.
+"""
+
+from __future__ import annotations
+
+import argparse
+from typing import List, Tuple
+
+import torch
+
+
+def profile_step(cfg, warmup: int = 2, device: int = 0):
+    """Returns (rows, step_wall_ms): rows = [(device_us, count, name)], largest first, for one
+    training step after ``warmup`` un-profiled steps."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from ..train import Trainer
+
+    cfg.optim.warmup_steps = 0
+    tr = Trainer(cfg, device=torch.device("cuda", device), verbose=False)
+    x = torch.randn(1, cfg.model.in_channels,
+                    cfg.data.latent_frames, *cfg.data.latent_size, device="cuda")
+    y = torch.randint(0, 1000, (1,), device="cuda")
+    for _ in range(warmup):
+        tr.train_step(x, y)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+        a.record()
+        tr.train_step(x, y)
+        b.record()
+        torch.cuda.synchronize()
+    rows: List[Tuple[float, int, str]] = []
+    for e in prof.key_averages():
+        if (e.self_device_time_total > 0 and e.device_type == torch.autograd.DeviceType.CUDA
+                and not e.key.startswith("Optimizer.step")):      # a span, not a kernel
+            rows.append((e.self_device_time_total, e.count, e.key))
+    rows.sort(reverse=True)
+    return rows, a.elapsed_time(b)
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--preset", default="d256")
+    ap.add_argument("--top", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("overrides", nargs="*", help="group.key=value config overrides")
+    args = ap.parse_args(argv)
+    from ..config import parse_cli, preset
+
+    cfg = preset(args.preset)
+    if args.overrides:
+        parse_cli(args.overrides, cfg)
+    rows, wall = profile_step(cfg, args.warmup)
+    total = sum(r[0] for r in rows)
+    print(f"preset {args.preset}: step {wall:.1f} ms under the profiler, "
+          f"kernels {total / 1000:.1f} ms in {sum(r[1] for r in rows)} launches")
+    for us, n, name in rows[:args.top]:
+        print(f"{us / 1000:9.2f} ms {100 * us / total:5.1f} %  x{n:<5d} {name[:100]}")
+
+
+if __name__ == "__main__":
+    main()
