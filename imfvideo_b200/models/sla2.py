@@ -59,6 +59,8 @@ def _router_kernels_ok(q: Tensor, k: Tensor) -> bool:
         return False
     if q.stride(-1) != 1 or k.stride(-1) != 1 or torch._C._are_functorch_transforms_active():
         return False
+    if k.shape[2] > 4096 * 64:          # the top-k kernel holds one score per key block in smem
+        return False
     try:
         from ..ops import sparse as SP
         return SP.ROUTER_KERNELS
