@@ -43,7 +43,7 @@ struct ResNormArgs {
 };
 
 template <int NV>
-__global__ void __launch_bounds__(ROW_THREADS) resnorm_fwd_kernel(const ResNormArgs a) {
+__global__ void __launch_bounds__(ROW_THREADS, NV <= 2 ? 4 : 1) resnorm_fwd_kernel(const ResNormArgs a) {
   constexpr int D = NV * 128;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float inv_d = 1.f / D;
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(ROW_THREADS) resnorm_fwd_kernel(const ResNormA
 // so every snapshot is read once and no tangent registers are carried: twice the occupancy
 // and about half the traffic of the two-pass kernel above.
 template <int NV>
-__global__ void __launch_bounds__(ROW_THREADS, NV <= 4 ? 3 : (NV <= 8 ? 2 : 1)) resnorm_fwd_primal_kernel(const ResNormArgs a) {
+__global__ void __launch_bounds__(ROW_THREADS, NV <= 2 ? 4 : (NV <= 4 ? 3 : (NV <= 8 ? 2 : 1))) resnorm_fwd_primal_kernel(const ResNormArgs a) {
   constexpr int D = NV * 128;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float inv_d = 1.f / D;
@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(ROW_THREADS, NV <= 4 ? 3 : (NV <= 8 ? 2 : 1)) 
 }
 
 template <int NV>
-__global__ void __launch_bounds__(ROW_THREADS) resnorm_bwd_kernel(const ResNormArgs a) {
+__global__ void __launch_bounds__(ROW_THREADS, NV <= 2 ? 4 : 1) resnorm_bwd_kernel(const ResNormArgs a) {
   constexpr int D = NV * 128;
   extern __shared__ float smem_acc[];  // [ROW_WARPS][3][D]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

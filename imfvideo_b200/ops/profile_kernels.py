@@ -7,6 +7,7 @@ under ``ncu`` (or for a quick CUDA-event timing without it).
     python -m imfvideo_b200.ops.profile_kernels gemm      --M 58280 --N 528 --K 256
     python -m imfvideo_b200.ops.profile_kernels sparse    --L 9472
     python -m imfvideo_b200.ops.profile_kernels resnorm   --rows 29140
+    python -m imfvideo_b200.ops.profile_kernels resnorm_bwd --rows 29140 --D 256
     python -m imfvideo_b200.ops.profile_kernels lin       --L 29140      # linear-branch kernels, one line each
     python -m imfvideo_b200.ops.profile_kernels route     --L 29140      # block means, top-k, INT8 quantiser
 
@@ -43,7 +44,7 @@ def _time(fn, iters: int, flush) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["attn_fwd", "attn_jvp", "attn_bwd", "gemm", "sparse",
-                                       "sparse_jvp", "resnorm", "lin", "route"])
+                                       "sparse_jvp", "resnorm", "resnorm_bwd", "lin", "route"])
     ap.add_argument("--L", type=int, default=9472)
     ap.add_argument("--B", type=int, default=1)
     ap.add_argument("--H", type=int, default=4)
@@ -130,6 +131,19 @@ def main() -> None:
             print(json.dumps({"kernel": name, "ms": _time(f, args.iters, flush)}))
         K.check_status()
         return
+    elif args.kernel == "resnorm_bwd":
+        from . import rowops as R
+
+        rows, D, ns = args.rows, args.D, args.snaps
+        res = torch.randn(rows, D, device=dev)
+        y = torch.randn(rows, D, device=dev).bfloat16()
+        gn = torch.randn(rows, D, device=dev).bfloat16()
+        gext = torch.randn(rows, D, device=dev)
+        snaps = [torch.randn(rows, D, device=dev) for _ in range(ns)]
+        gate, w, gain = (torch.randn(D, device=dev) for _ in range(3))
+        fn = lambda: R.resnorm_bwd(res, y, gate, snaps, w, gain, 1e-5, gn, gext)
+        # reads: res, y, gn, g_pfx_ext, snaps; writes: g_res, g_y, g_snaps
+        bytes_ = rows * D * (4 + 2 + 2 + 4 + 4 * ns + 4 + 2 + 4 * ns)
     else:
         from . import rowops as R
 
