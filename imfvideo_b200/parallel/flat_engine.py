@@ -395,8 +395,16 @@ class FlatEngine(GradSync):
             return self._newton_schulz_eager(opt, g0)
         graph = torch.cuda.CUDAGraph()
         n0 = self._K.LAUNCHES.count
-        with torch.cuda.graph(graph):
-            self._newton_schulz_eager(opt, g0)
+        try:
+            # thread-local error mode: a pinned-memory allocation by a loader thread during
+            # the capture must not invalidate it
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self._newton_schulz_eager(opt, g0)
+        except RuntimeError:
+            # nothing captured has run: do this step eagerly and stay eager from now on
+            self._K.LAUNCHES.count = n0
+            self.ns_cuda_graph = False
+            return self._newton_schulz_eager(opt, g0)
         self._ns_graph_launches = self._K.LAUNCHES.count - n0
         self._K.LAUNCHES.count = n0
         self._ns_graph = graph
