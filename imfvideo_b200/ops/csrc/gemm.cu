@@ -375,9 +375,12 @@ extern "C" int imf_gemm_bf16(const void* A, const void* B, void* C, const float*
   if (M <= 0 || N <= 0 || K <= 0) return IMF_ERR_ARG;
   if ((lda & 7) || (ldb & 7)) return IMF_ERR_ARG;  // TMA strides are multiples of 16 B
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+// fp32 output: the 64 KB staging tile leaves room for one CTA per SM only, so the operand
+// pipeline is four stages deep there; bf16 output: two CTAs per SM with two stages each.
+#define IMF_GEMM_STAGES(OT) (sizeof(OT) == 4 ? 4 : 2)
 #define IMF_GEMM_CASE(AM, BM_, OT)                                                          \
-  return launch_gemm<128, 2, AM, BM_, OT>(A, B, C, bias, M, N, K, lda, ldb, ldc, bias_rows, \
-                                          alpha, accumulate_out, status, st)
+  return launch_gemm<128, IMF_GEMM_STAGES(OT), AM, BM_, OT>(                                \
+      A, B, C, bias, M, N, K, lda, ldb, ldc, bias_rows, alpha, accumulate_out, status, st)
   if (out_fp32) {
     if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, float);
     if (!a_mn && b_mn) IMF_GEMM_CASE(false, true, float);
@@ -405,8 +408,8 @@ extern "C" int imf_gemm_bf16_batched(const void* A, const void* B, void* C, cons
   if ((lda & 7) || (ldb & 7) || (batch > 1 && ((sa & 7) || (sb & 7)))) return IMF_ERR_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define IMF_GEMM_CASE(AM, BM_, OT)                                                              \
-  return launch_gemm<128, 2, AM, BM_, OT>(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, alpha, 0, \
-                                          status, st, batch, sa, sb, sc, Cin, beta)
+  return launch_gemm<128, IMF_GEMM_STAGES(OT), AM, BM_, OT>(                                    \
+      A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, alpha, 0, status, st, batch, sa, sb, sc, Cin, beta)
   if (out_fp32) {
     if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, float);
     if (!a_mn && b_mn) IMF_GEMM_CASE(false, true, float);
