@@ -171,7 +171,7 @@ def run_ours(args):
 
     def step_device(i):
         loss, _parts = trainer.micro_step(dev_lat[i % n_host], dev_lab[i % n_host])
-        trainer.optimizer_step_async()
+        trainer.optimizer_step()
         return loss
 
     for i in range(args.warmup):

@@ -155,6 +155,9 @@ class ParallelConfig:
     distributed_moonlight: bool = True
     wire_dtype: str = "bfloat16"
     broadcast_init: bool = True
+    # bound (seconds) of every device-side wait on another rank's flag; when it runs out the
+    # kernel returns without touching data and the trainer raises at its per-step host read
+    peer_wait_s: float = 2.0
 
 
 @dataclass

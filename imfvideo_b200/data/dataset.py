@@ -55,22 +55,50 @@ def build_loader(data_cfg, model_cfg, rank: int, world: int, cuda: bool, seed: i
 
 
 class InfiniteLoader:
-    """Endless iterator over a DataLoader that advances the sampler epoch."""
+    """Endless iterator over a DataLoader that advances the sampler epoch.
+
+    ``state()`` / ``restore()`` give the sampler position (epoch, batches already
+    handed out in it) that checkpoints carry: after ``restore`` the iterator starts
+    the saved epoch and drops the batches that were consumed before the save."""
 
     def __init__(self, loader, sampler=None, epoch: int = 0):
         self.loader, self.sampler, self.epoch = loader, sampler, epoch
         self._it: Optional[Iterator] = None
+        self.batch = 0            # batches handed out in the current epoch
+        self._skip = 0
 
     def __iter__(self):
         return self
+
+    def state(self, prefetched: int = 0):
+        """Position as seen by the consumer; ``prefetched`` = batches taken from this
+        iterator that the consumer has not used yet (a prefetcher holds one)."""
+        epoch, batch = self.epoch, self.batch - prefetched
+        if batch < 0:                       # the prefetched batch closed the previous epoch
+            epoch, batch = max(0, epoch - 1), max(0, len(self.loader) + batch)
+        return {"epoch": epoch, "batch": batch}
+
+    def restore(self, state) -> None:
+        self.epoch, self._skip = int(state.get("epoch", 0)), int(state.get("batch", 0))
+        self._it, self.batch = None, 0
 
     def __next__(self):
         if self._it is None:
             if self.sampler is not None:
                 self.sampler.set_epoch(self.epoch)
             self._it = iter(self.loader)
+            self.batch = 0
+            while self._skip > 0:
+                self._skip -= 1
+                try:
+                    next(self._it)
+                    self.batch += 1
+                except StopIteration:
+                    break
         try:
-            return next(self._it)
+            out = next(self._it)
+            self.batch += 1
+            return out
         except StopIteration:
             self.epoch += 1
             self._it = None

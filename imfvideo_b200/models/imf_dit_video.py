@@ -183,17 +183,25 @@ class VideoPatchEmbedder(nn.Module):
 
 
 # ------------------------------------------------- attention plug-ins -----
-def flash_jvp_attention(q: Dual, k: Dual, v: Dual) -> Dual:
+def _plug(q, k, v, impl: str):
+    """Plug-ins take duals inside the model; called with plain (b, l, H, d) tensors (the
+    reference's ``attn_impl(q, k, v)`` protocol) they return a plain tensor."""
+    plain = not isinstance(q, Dual)
+    out = D.dense_attention(D.lift(q), D.lift(k), D.lift(v), impl=impl)
+    return out.p if plain else out
+
+
+def flash_jvp_attention(q, k, v):
     """Fused primal+tangent dense attention (sm_100a kernel on CUDA)."""
-    return D.dense_attention(q, k, v, impl="auto")
+    return _plug(q, k, v, "auto")
 
 
-def sdpa_math_attention(q: Dual, k: Dual, v: Dual) -> Dual:
-    return D.dense_attention(q, k, v, impl="math")
+def sdpa_math_attention(q, k, v):
+    return _plug(q, k, v, "math")
 
 
-def sdpa_flash_attention(q: Dual, k: Dual, v: Dual) -> Dual:
-    return D.dense_attention(q, k, v, impl="sdpa")
+def sdpa_flash_attention(q, k, v):
+    return _plug(q, k, v, "sdpa")
 
 
 eager_math_attention = sdpa_math_attention

@@ -27,6 +27,13 @@ if K._has("imf_comm_reduce"):
     _lib.imf_comm_muon_apply.restype = ci
     _lib.imf_comm_muon_apply.argtypes = [vp, vp, ci, ci, cl, vp, vp, vp, ci, cl, ctypes.c_float, vp,
                                          ci, ci, vp, vp]
+    _lib.imf_comm_set_wait_ns.restype = ctypes.c_ulonglong
+    _lib.imf_comm_set_wait_ns.argtypes = [ctypes.c_ulonglong]
+
+
+def set_peer_wait(seconds: float) -> float:
+    """Bound of every later device-side wait on a peer's flag; returns the previous bound."""
+    return _lib.imf_comm_set_wait_ns(int(max(1e-6, seconds) * 1e9)) / 1e9
 
 
 def _ptr_array(ptrs: List[int]):

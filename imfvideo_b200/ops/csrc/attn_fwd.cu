@@ -583,13 +583,18 @@ static int make_qkv_map(CUtensorMap* m, const void* ptr, int B, int L, int H, in
   return make_tmap(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, str, box);
 }
 
+// SM count of the CURRENT device (cached per device index: a host may hold GPUs of
+// different sizes, and a persistent grid larger than the device would not be co-resident).
 static int att_grid(int n_items) {
-  static int sms = 0;
+  constexpr int MAX_DEVICES = 64;
+  static int sms_of_device[MAX_DEVICES] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int sms = (dev >= 0 && dev < MAX_DEVICES) ? sms_of_device[dev] : 0;
   if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       sms = 148;
+    if (dev >= 0 && dev < MAX_DEVICES) sms_of_device[dev] = sms;   // same value from every thread
   }
   return n_items < sms ? n_items : sms;
 }

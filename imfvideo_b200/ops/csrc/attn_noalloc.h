@@ -22,7 +22,9 @@
 //    partial slot per SM, is rejected with IMF_ERR_TOO_LARGE (-4);
 //  * the first call on each device looks up the device address of the array
 //    (cudaGetSymbolAddress, with that device current).  Make that first call
-//    outside of any stream capture;
+//    outside of any stream capture.  First calls made at the same time from
+//    several host threads are safe: each of them looks up and stores the same
+//    address for that device;
 //  * all calls on a device share the one array and it keeps the previous
 //    call's contents.  Nothing in it needs to start at zero: every slot that a
 //    launch reads was written earlier in the same launch sequence.  Two calls

@@ -18,8 +18,12 @@
 //
 // Barriers are epoch flags in symmetric memory: rank r writes flag[r] = epoch
 // into every peer's flag array (st.release.sys) and every CTA polls its LOCAL
-// copy (ld.acquire.sys) with a wall-clock bound; on expiry the kernel records
-// STATUS_TIMEOUT_PEER and returns, the host raises.  No TMA multicast, no
+// copy (ld.acquire.sys) with a wall-clock bound (2 s unless imf_comm_set_wait_ns
+// changed it); on expiry the kernel records STATUS_TIMEOUT_PEER and returns
+// without touching data, and the host raises when it next reads the status word
+// (the trainer does so once per step).  The signal is sent by whichever CTA of
+// the grid gets there first (a ticket in the local flag array), so it does not
+// depend on the order in which the hardware schedules the CTAs.  No TMA multicast, no
 // library kernel touches peer memory.  Replaces the reference's flat NCCL
 // all-reduce (reference train.py:353-371).
 #include <cuda_bf16.h>
@@ -29,11 +33,13 @@
 namespace imf {
 
 constexpr int MAX_RANKS = 16;
-constexpr unsigned long long PEER_WAIT_NS = 2000000000ull;
+constexpr int TICKET_SLOT = 2 * MAX_RANKS;     // local "someone has signalled epoch e" word
+static unsigned long long g_peer_wait_ns = 2000000000ull;
 
 struct CommPeers {
   float* arena[MAX_RANKS];      // peer base pointers of the fp32 arena
-  int* flags[MAX_RANKS];        // peer base pointers of the flag arrays [MAX_RANKS]
+  int* flags[MAX_RANKS];        // peer base pointers of the flag arrays [4 * MAX_RANKS]
+  unsigned long long wait_ns;   // bound of every wait on a peer
 };
 
 __device__ __forceinline__ unsigned long long gtime() {
@@ -50,12 +56,12 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   return v;
 }
 
-// Signal (first block) and wait (every block).  Returns false on timeout.
+// Signal (first block to arrive) and wait (every block).  Returns false on timeout.
 __device__ __forceinline__ bool peer_barrier(const CommPeers& peers, int rank, int world, int epoch,
                                              int* status) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
-    if (blockIdx.x == 0 && blockIdx.y == 0) {
+    if (atomicMax(peers.flags[rank] + TICKET_SLOT, epoch) < epoch) {
       __threadfence_system();
       for (int q = 0; q < world; ++q) st_release_sys(peers.flags[q] + rank, epoch);
     }
@@ -63,7 +69,7 @@ __device__ __forceinline__ bool peer_barrier(const CommPeers& peers, int rank, i
     const unsigned long long t0 = gtime();
     for (int q = 0; q < world && ok; ++q) {
       while (ld_acquire_sys(peers.flags[rank] + q) < epoch) {
-        if (gtime() - t0 > PEER_WAIT_NS) {
+        if (gtime() - t0 > peers.wait_ns) {
           ok = 0;
           if (status) atomicCAS(status, 0, 6);
           break;
@@ -229,12 +235,21 @@ static int fill(CommPeers& p, void* const* arena_ptrs, void* const* flag_ptrs, i
     p.arena[q] = q < world ? static_cast<float*>(arena_ptrs[q]) : nullptr;
     p.flags[q] = q < world ? static_cast<int*>(flag_ptrs[q]) : nullptr;
   }
+  p.wait_ns = g_peer_wait_ns;
   return 0;
 }
 
 }  // namespace imf
 
 using namespace imf;
+
+// Bound (nanoseconds) of every later wait on a peer's flag; returns the previous value.
+// A launcher-side setting: kernels already in flight keep the bound they were launched with.
+extern "C" unsigned long long imf_comm_set_wait_ns(unsigned long long ns) {
+  const unsigned long long old = g_peer_wait_ns;
+  if (ns > 0) g_peer_wait_ns = ns;
+  return old;
+}
 
 // Mean-reduce this rank's Muon segment and AdamW shard of the fp32 arena.
 // arena_ptrs / flag_ptrs: host arrays of `world` device pointers (peer mapped).

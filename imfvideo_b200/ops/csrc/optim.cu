@@ -87,16 +87,31 @@ __global__ void muon_apply_kernel(float* __restrict__ p, const UT* __restrict__ 
   }
 }
 
+// `t_dev` (optional): device count of applied steps, this one included; the bias
+// corrections are then computed here, so a step skipped by the device-side flag never
+// needs the host to roll a counter back.  [lo, hi) (absolute arena offsets, hi > lo)
+// restricts the update to one rank's shard of the AdamW slice.
 __global__ void adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
                              float* __restrict__ m, float* __restrict__ v,
                              float* __restrict__ ema, const Seg* __restrict__ segs, long state_offset,
                              float b1, float b2, float eps, float bias1, float bias2,
-                             const float* __restrict__ clip, float ema_w) {
+                             const float* __restrict__ clip, float ema_w,
+                             const float* __restrict__ t_dev, long lo, long hi) {
   if (clip && clip[1] != 0.f) return;
   const Seg s = segs[blockIdx.y];
   const float c = clip ? clip[0] : 1.f;
+  if (t_dev) {
+    const double t = (double)t_dev[0];
+    bias1 = (float)(1.0 - pow((double)b1, t));
+    bias2 = (float)(1.0 - pow((double)b2, t));
+  }
   const float inv_b1 = 1.f / bias1, inv_b2 = 1.f / bias2;
-  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < s.numel;
+  long i0 = 0, i1 = s.numel;
+  if (hi > lo) {
+    i0 = lo > s.start ? lo - s.start : 0;
+    i1 = hi - s.start < s.numel ? hi - s.start : s.numel;
+  }
+  for (long i = i0 + (long)blockIdx.x * blockDim.x + threadIdx.x; i < i1;
        i += (long)gridDim.x * blockDim.x) {
     const long j = s.start + i, k = j - state_offset;
     const float gv = g[j] * c;
@@ -146,7 +161,7 @@ extern "C" int imf_muon_apply(float* p, const void* upd, int upd_bf16, float* em
 extern "C" int imf_adamw(float* p, const float* g, float* m, float* v, float* ema,
                          const void* segs, int nseg, long max_numel, long state_offset, float b1,
                          float b2, float eps, float bias1, float bias2, const float* clip,
-                         float ema_w, void* stream) {
+                         float ema_w, const float* t_dev, long lo, long hi, void* stream) {
   if (nseg <= 0) return 0;
   long bx = (max_numel + 1023) / 1024;
   if (bx > 256) bx = 256;
@@ -154,7 +169,7 @@ extern "C" int imf_adamw(float* p, const float* g, float* m, float* v, float* em
   dim3 grid((unsigned)bx, nseg);
   adamw_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p, g, m, v, ema, (const Seg*)segs,
                                                       state_offset, b1, b2, eps, bias1, bias2,
-                                                      clip, ema_w);
+                                                      clip, ema_w, t_dev, lo, hi);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -172,14 +187,22 @@ struct ClipMod {
   float* w;             // (H * hd, cols) row-major weight of q_b_proj
   const float* stat;    // (H,) max logit in log2 units
   int H, hd, dn, cols;
+  float* ema;           // the same weight in the EMA model, or null
 };
 
+// `clip` (optional) is the optimizer's [factor, skip flag] word: a skipped step leaves
+// the weights alone here too.  A non-finite statistic clips nothing.  The optimizer
+// kernels have already folded the un-clipped weight into the EMA, so for a clipped row
+// the EMA is corrected to what lerp(ema, gamma * w) would have given.
 __global__ void qk_clip_kernel(const ClipMod* __restrict__ mods, float tau_nat,
-                               float* __restrict__ summary) {
+                               float* __restrict__ summary, const float* __restrict__ clip,
+                               float ema_w) {
+  if (clip && clip[1] != 0.f) return;
   const ClipMod m = mods[blockIdx.y];
   const int h = blockIdx.x;
   if (h >= m.H) return;
   const float s_nat = m.stat[h] * 0.6931471805599453f;
+  if (!isfinite(s_nat)) return;
   const float gamma = fminf(1.f, tau_nat / fmaxf(s_nat, 1e-20f));
   if (threadIdx.x == 0) {
     // non-negative floats order like their bit patterns
@@ -188,18 +211,25 @@ __global__ void qk_clip_kernel(const ClipMod* __restrict__ mods, float tau_nat,
   }
   if (gamma >= 1.f) return;
   const int rows = m.hd - m.dn;
-  float* base = m.w + ((size_t)h * m.hd + m.dn) * m.cols;
-  for (int i = threadIdx.x; i < rows * m.cols; i += blockDim.x) base[i] *= gamma;
+  const size_t off = ((size_t)h * m.hd + m.dn) * m.cols;
+  float* base = m.w + off;
+  float* eb = m.ema ? m.ema + off : nullptr;
+  for (int i = threadIdx.x; i < rows * m.cols; i += blockDim.x) {
+    const float w = base[i];
+    base[i] = w * gamma;
+    if (eb) eb[i] += ema_w * (gamma - 1.f) * w;
+  }
 }
 
 }  // namespace imf
 
-// mods: device array of nmod records {float* w, const float* stat, int H, hd, dn, cols};
-// summary: device float[2], zeroed by the caller (count of clipped heads, max logit in nats).
+// mods: device array of nmod records {float* w, const float* stat, int H, hd, dn, cols, float* ema};
+// summary: device float[2], zeroed by the caller (count of clipped heads, max logit in nats);
+// clip: the optimizer's device word [factor, skip flag] or null; ema_w = 1 - ema decay.
 extern "C" int imf_qk_clip(const void* mods, int nmod, int max_heads, float tau_nat, float* summary,
-                           void* stream) {
+                           const float* clip, float ema_w, void* stream) {
   if (nmod <= 0) return 0;
   qk_clip_kernel<<<dim3(max_heads, nmod), 256, 0, (cudaStream_t)stream>>>(
-      (const ClipMod*)mods, tau_nat, summary);
+      (const ClipMod*)mods, tau_nat, summary, clip, ema_w);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

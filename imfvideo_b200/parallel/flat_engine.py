@@ -23,6 +23,12 @@ Per step:
   * owner: momentum + batched Newton-Schulz on its segment; update all-gather;
     every rank applies ``p <- p (1 - lr wd) - lr s Phi`` (+ EMA) to all Muon
     parameters and AdamW (+ EMA) to the rest -> replicas stay bit-identical.
+
+Deliberate difference from the reference optimizer (``moonlight.py`` ``_muon_step`` /
+``_adamw_step`` skip parameters whose ``grad is None``): every parameter owns a
+permanent, zero-filled gradient view in the arena, so a parameter that received no
+gradient in a step is updated with a zero gradient (weight decay, moment decay).
+All AdamW parameters share one step count (kept on the device, ``tcount``).
 """
 
 from __future__ import annotations
@@ -113,6 +119,9 @@ class FlatEngine(GradSync):
                   else z(self.muon_total, self.upd_dtype))
         self.clip = z(2)                                  # [coef, skip flag]
         self.norm = z(1)
+        # AdamW steps actually applied (skipped steps do not count); the kernels read the
+        # bias corrections from here, the Python ints in ``state[p]["step"]`` follow it
+        self.tcount = z(1)
         self._repoint(name_of, ema_of)
         self._muon_seg_host = np.zeros(len(self.muon), dtype=SEG_DTYPE)
         self._adam_seg_host = np.zeros(len(self.adam), dtype=SEG_DTYPE)
@@ -181,13 +190,12 @@ class FlatEngine(GradSync):
         L.imf_muon_apply.restype = ci
         L.imf_muon_apply.argtypes = [vp, vp, ci, vp, vp, ci, cl, cl, cf, vp, vp]
         L.imf_adamw.restype = ci
-        L.imf_adamw.argtypes = [vp, vp, vp, vp, vp, vp, ci, cl, cl, cf, cf, cf, cf, cf, vp, cf, vp]
+        L.imf_adamw.argtypes = [vp, vp, vp, vp, vp, vp, ci, cl, cl, cf, cf, cf, cf, cf, vp, cf, vp,
+                                cl, cl, vp]
 
     # ---------------------------------------------------------------- grads --
     def zero_grad(self) -> None:
         self.G.zero_()
-        for _, p in self.muon + self.adam:      # autograd may have replaced a view
-            pass
 
     def _check_grad_views(self) -> None:
         """Autograd accumulates in place into existing ``.grad`` views; a grad
@@ -247,6 +255,16 @@ class FlatEngine(GradSync):
         return norm
 
     # ----------------------------------------------------------------- step --
+    def _refresh_groups(self) -> None:
+        """Re-read which param-group dict each parameter belongs to.
+        ``Optimizer.load_state_dict`` replaces ``param_groups`` with new dicts, and the
+        trainer writes the scheduled learning rate into the current ones, so group
+        references taken at construction go stale after a resume.  The parameter
+        order (and with it every arena offset) never changes."""
+        group_of = {id(p): g for g in self.opt.param_groups for p in g["params"]}
+        self.muon = [(group_of[id(p)], p) for _, p in self.muon]
+        self.adam = [(group_of[id(p)], p) for _, p in self.adam]
+
     def _upload_segments(self) -> None:
         wd_of = lambda g: g["weight_decay"]
         for i, (g, p) in enumerate(self.muon):
@@ -265,6 +283,7 @@ class FlatEngine(GradSync):
 
     @torch.no_grad()
     def step(self, opt: Moonlight) -> None:
+        self._refresh_groups()
         use_k = self._lib is not None
         if use_k:
             self._upload_segments()
@@ -325,18 +344,23 @@ class FlatEngine(GradSync):
             eps = g0["adamw_eps"]
             for _, p in self.adam:
                 opt.state[p]["step"] += 1
-            t = opt.state[self.adam[0][1]]["step"]
-            bias1, bias2 = 1 - b1 ** t, 1 - b2 ** t
+            # the count on the device moves only when the step is applied (skip flag = 0),
+            # so it stays exact even if the host never learns that a step was skipped
+            self.tcount += 1.0 - skip
             if use_k:
                 self._K._check(self._lib.imf_adamw(
                     self.P.data_ptr(), self.G.data_ptr(), self.A1.data_ptr(), self.A2.data_ptr(),
                     self.E.data_ptr() if self.E is not None else None,
                     self._adam_seg_dev.data_ptr(), len(self.adam), self._max_adam,
-                    self.muon_total, float(b1), float(b2), float(eps), float(bias1), float(bias2),
-                    self.clip.data_ptr(), float(self.ema_w), stream), "imf_adamw")
+                    self.muon_total, float(b1), float(b2), float(eps), 1.0, 1.0,
+                    self.clip.data_ptr(), float(self.ema_w), self.tcount.data_ptr(), 0, 0,
+                    stream), "imf_adamw")
                 self._K.LAUNCHES.count += 1
             else:
                 keep = skip.bool()
+                t = self.tcount.double().clamp_min(1.0)
+                bias1 = (1 - torch.tensor(b1, dtype=torch.float64) ** t).float()
+                bias2 = (1 - torch.tensor(b2, dtype=torch.float64) ** t).float()
                 sl = slice(self.muon_total, self.total)
                 g = self.G[sl] * self.clip[0]
                 m_new = self.A1 * b1 + (1 - b1) * g
@@ -412,14 +436,23 @@ class FlatEngine(GradSync):
         self._K.LAUNCHES.count += self._ns_graph_launches
 
     def undo_step_count(self) -> None:
-        """Called by the trainer when it learns (from the device skip flag) that
-        the last step was skipped, so AdamW's bias-correction count stays exact."""
+        """Called by the trainer when it learns (from the device skip flag) that the last
+        step was skipped: brings the Python ``step`` ints back in line with the device
+        count, which is the one the update itself uses."""
         for _, p in self.adam:
             self.opt.state[p]["step"] -= 1
+
+    def sync_step_count(self) -> None:
+        """Host read of the device count into ``state[p]["step"]`` (before a checkpoint)."""
+        if self.adam:
+            t = int(round(float(self.tcount.item())))
+            for _, p in self.adam:
+                self.opt.state[p]["step"] = t
 
     # ---------------------------------------------------------- checkpoints --
     @torch.no_grad()
     def gather_state(self) -> None:
+        self.sync_step_count()
         if self.world == 1 or not self.muon:
             return
         own = self.M[self.rank * self.seg_pad:(self.rank + 1) * self.seg_pad].clone()
@@ -435,6 +468,9 @@ class FlatEngine(GradSync):
         name_of = {id(p): n for n, p in self.net.named_parameters()}
         ema_of = dict(self.ema.named_parameters()) if self.ema is not None else {}
         self._repoint(name_of, ema_of)
+        self._refresh_groups()
+        if self.adam:
+            self.tcount.fill_(float(self.opt.state[self.adam[0][1]].get("step", 0)))
 
     def owner_table(self) -> List[int]:
         return list(self.owner)

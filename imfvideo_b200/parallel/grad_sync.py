@@ -2,9 +2,10 @@
 
 ``FlatAllReduce`` is the reference's scheme (one flat fp32 all-reduce after
 the whole backward, ``train.py:353-371``) and serves as the baseline arm.
-The NVLink-native path (bucketed reduce-scatter overlapped with backward,
-owner-partitioned Moonlight, fused update + all-gather) lives in
-``parallel/flat_engine.py`` and ``ops/comm_impl.py``.
+The NVLink-native path (reduce-scatter of the flat gradient arena to the Muon
+owners and AdamW shards over peer memory, owner-partitioned Moonlight, update
+all-gather fused into the weight update) lives in ``parallel/flat_engine.py``
+and ``ops/comm_impl.py``.
 """
 
 from __future__ import annotations

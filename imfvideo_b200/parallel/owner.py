@@ -8,7 +8,9 @@ ranks, which apply the same fp32 update so replicas stay bit-identical.
 
 ``assign_owners`` is a deterministic longest-processing-time bin packing over
 the Newton-Schulz FLOP cost, so the map is a pure function of (shapes, world)
-and is stable across resume; it is also written into checkpoints.
+and is stable across resume; ``Trainer.save`` writes it into the checkpoint's
+``extra["muon_owner"]`` and ``Trainer.load`` refuses a file whose map differs
+at the same world size.
 """
 
 from __future__ import annotations

@@ -151,35 +151,65 @@ def lr_at(step: int, cfg: Optional[Config] = None) -> float:
 
 
 @torch.no_grad()
-def qk_clip(net, tau: float, world: int = 1) -> Tuple[int, float]:
+def qk_clip(net, tau: float, world: int = 1, skip: Optional[torch.Tensor] = None,
+            ema=None, ema_w: float = 0.0, as_tensors: bool = False):
     """MuonClip: heads whose max logit exceeded ``tau`` (nats) get the rope
     rows of ``q_b_proj`` scaled by tau / S_max.  All modules' per-head stats
-    are reduced in ONE batched MAX all-reduce and ONE host read (the
-    reference does an all-reduce and two host syncs per module,
-    ``train.py:301-350``).  Returns (#clipped heads, global max logit)."""
-    mods = [m for m in net.modules() if isinstance(m, M.MLAAttention)
+    are reduced in ONE batched MAX all-reduce (the reference does an
+    all-reduce and two host syncs per module, ``train.py:301-350``).
+
+    ``skip``: the optimizer's device word [clip factor, skip flag]; when the
+    flag is set (non-finite gradient norm) nothing is rescaled, as in the
+    reference, which clips only inside its finite branch (``train.py:583-592``).
+    A non-finite statistic clips nothing either.  ``ema`` / ``ema_w``: when the
+    optimizer already folded the un-clipped weights into the EMA model (fused
+    update kernels), the clipped rows of the EMA copy are corrected so the result
+    equals the reference order step -> clip -> EMA.
+
+    Returns (#clipped heads, global max logit) as Python numbers, or as two
+    device scalars with ``as_tensors`` (no host read)."""
+    mods = [(n, m) for n, m in net.named_modules() if isinstance(m, M.MLAAttention)
             and getattr(m.attn_impl, "logit_max_log2", None) is not None]
     if not mods:
+        if as_tensors:
+            z = torch.zeros((), device=next(net.parameters()).device)
+            return z, z
         return 0, 0.0
+    ema_mods = dict(ema.named_modules()) if (ema is not None and ema_w > 0) else {}
+    emas = [ema_mods.get(n) for n, _ in mods]
+    mods = [m for _, m in mods]
     stats = torch.stack([m.attn_impl.logit_max_log2.float() for m in mods])   # (n, H)
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    fused = _qk_clip_kernel(mods, stats, tau)
+    fused = _qk_clip_kernel(mods, emas, stats, tau, skip, ema_w)
     if fused is not None:
-        return fused
-    s_nat = stats * math.log(2.0)
-    gamma = (tau / s_nat.clamp_min(1e-20)).clamp(max=1.0)
-    for m, g in zip(mods, gamma):
-        dn = m.qk_nope_head_dim
-        w = m.q_b_proj.weight.view(m.num_heads, m.qk_head_dim, -1)
-        w[:, dn:, :] *= g.to(w.dtype).view(-1, 1, 1)
-    summary = torch.stack([(gamma < 1.0).sum().float(), s_nat.max()]).tolist()
-    return int(summary[0]), float(summary[1])
+        n_hot, s_max = fused
+    else:
+        s_nat = stats * math.log(2.0)
+        finite = torch.isfinite(s_nat)
+        gamma = (tau / s_nat.clamp_min(1e-20)).clamp(max=1.0)
+        gamma = torch.where(finite, gamma, torch.ones_like(gamma))
+        if skip is not None:
+            gamma = torch.where(skip[1].to(gamma.device) != 0, torch.ones_like(gamma), gamma)
+        for m, e, g in zip(mods, emas, gamma):
+            dn = m.qk_nope_head_dim
+            w = m.q_b_proj.weight.view(m.num_heads, m.qk_head_dim, -1)
+            gg = g.to(w.dtype).view(-1, 1, 1)
+            if e is not None:
+                ew = e.q_b_proj.weight.view(m.num_heads, m.qk_head_dim, -1)
+                ew[:, dn:, :] += ema_w * (gg - 1.0) * w[:, dn:, :]
+            w[:, dn:, :] *= gg
+        n_hot = (gamma < 1.0).sum().float()
+        s_max = torch.where(finite, s_nat, torch.zeros_like(s_nat)).max()
+    if as_tensors:
+        return n_hot, s_max
+    n, mx = torch.stack([n_hot.float(), s_max.float()]).tolist()
+    return int(n), float(mx)
 
 
-def _qk_clip_kernel(mods, stats: torch.Tensor, tau: float):
+def _qk_clip_kernel(mods, emas, stats: torch.Tensor, tau: float, skip, ema_w: float):
     """All modules in one launch of the library's kernel (fp32 contiguous weights on a GPU);
-    None when that does not apply."""
+    None when that does not apply.  Returns two device scalars."""
     w0 = mods[0].q_b_proj.weight
     if not w0.is_cuda or any(m.q_b_proj.weight.dtype != torch.float32
                              or not m.q_b_proj.weight.is_contiguous() for m in mods):
@@ -198,24 +228,29 @@ def _qk_clip_kernel(mods, stats: torch.Tensor, tau: float):
     import numpy as np
 
     rec = np.dtype([("w", "<u8"), ("stat", "<u8"), ("H", "<i4"), ("hd", "<i4"), ("dn", "<i4"),
-                    ("cols", "<i4")])
+                    ("cols", "<i4"), ("ema", "<u8")])
     stats = stats.contiguous()
     host = np.zeros(len(mods), dtype=rec)
-    for i, m in enumerate(mods):
+    for i, (m, e) in enumerate(zip(mods, emas)):
         w = m.q_b_proj.weight
+        ew = 0
+        if e is not None and e.q_b_proj.weight.dtype == torch.float32 \
+                and e.q_b_proj.weight.is_contiguous():
+            ew = e.q_b_proj.weight.data_ptr()
         host[i] = (w.data_ptr(), stats[i].data_ptr(), m.num_heads, m.qk_head_dim,
-                   m.qk_nope_head_dim, w.shape[1])
+                   m.qk_nope_head_dim, w.shape[1], ew)
     table = torch.from_numpy(host.view(np.uint8).reshape(-1).copy()).to(w0.device)
     summary = torch.zeros(2, dtype=torch.float32, device=w0.device)
     lib = K._lib
     lib.imf_qk_clip.restype = ctypes.c_int
     lib.imf_qk_clip.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_float,
-                                ctypes.c_void_p, ctypes.c_void_p]
+                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_float,
+                                ctypes.c_void_p]
     K._check(lib.imf_qk_clip(K._ptr(table), len(mods), max(m.num_heads for m in mods), float(tau),
-                             K._ptr(summary), K._stream()), "imf_qk_clip")
+                             K._ptr(summary), K._ptr(skip), float(ema_w), K._stream()),
+             "imf_qk_clip")
     K.LAUNCHES.count += 1
-    n, mx = summary.tolist()
-    return int(n), float(mx)
+    return summary[0], summary[1]
 
 
 # --------------------------------------------------------------- trainer ---
@@ -322,7 +357,10 @@ class Trainer:
             if eng is not None:
                 self.optimizer.step()
                 skipped = eng.clip[1]
-                n_hot, s_max = qk_clip(self.net, o.qk_clip_tau, self.world)
+                # the fused update kernels have already folded the new weights into the
+                # EMA; the clip corrects the EMA rows it rescales and honours the skip flag
+                n_hot, s_max = qk_clip(self.net, o.qk_clip_tau, self.world, skip=eng.clip,
+                                       ema=self.ema, ema_w=eng.ema_w, as_tensors=True)
             else:
                 finite = bool(torch.isfinite(grad_norm))
                 skipped = torch.tensor(float(not finite))
@@ -341,11 +379,6 @@ class Trainer:
         self.step += 1
         return {"lr": lr, "grad_norm": grad_norm, "skipped": skipped,
                 "qk_hot": n_hot, "qk_smax": s_max}
-
-    def optimizer_step_async(self) -> Dict[str, Any]:
-        """``optimizer_step`` without converting statistics to Python floats
-        (the only host read left is the finite-gradient check)."""
-        return self.optimizer_step()
 
     def _report_bad_grads(self) -> None:
         if not self.verbose:
@@ -378,10 +411,16 @@ class Trainer:
             loss, parts = self.micro_step(lat, lab)
             losses.append(loss)
         stats = self.optimizer_step()
-        dt = losses[0].dtype
+        dt, dev = losses[0].dtype, losses[0].device
+        as_t = lambda v: (v if torch.is_tensor(v) else torch.tensor(float(v))).to(dt).to(dev) \
+            .reshape(())
+        # ONE device -> host read per step: losses, norm, skip flag, QK-clip statistics and
+        # the kernel status word (a bounded wait that ran out inside any kernel of this step)
         vec = torch.stack([torch.stack(losses).mean(), parts["loss_u"], parts["loss_v"],
-                           stats["grad_norm"].to(dt).reshape(()),
-                           stats["skipped"].to(dt).to(losses[0].device).reshape(())]).tolist()
+                           as_t(stats["grad_norm"]), as_t(stats["skipped"]),
+                           as_t(stats["qk_hot"]), as_t(stats["qk_smax"]),
+                           as_t(self._status_scalar())]).tolist()
+        self._raise_on_status(int(vec[7]))
         if not math.isfinite(vec[0]):
             self._dump_nan_batch(parts["_latents"], parts["_labels"])
         skipped = bool(vec[4])
@@ -389,28 +428,75 @@ class Trainer:
             if hasattr(self.grad_sync, "undo_step_count"):
                 self.grad_sync.undo_step_count()
                 self._report_bad_grads()
-        stats.update(loss=vec[0], loss_u=vec[1], loss_v=vec[2], grad_norm=vec[3], skipped=skipped)
+        stats.update(loss=vec[0], loss_u=vec[1], loss_v=vec[2], grad_norm=vec[3], skipped=skipped,
+                     qk_hot=int(vec[5]), qk_smax=vec[6])
         self.last = stats
         return stats
 
+    def _status_scalar(self):
+        """The device status word of this rank's GPU (0 on CPU or before any kernel ran)."""
+        if self.device.type != "cuda":
+            return 0.0
+        try:
+            from .ops import cuda as cu
+            if not cu.available():
+                return 0.0
+            from .ops import kernels as K
+        except Exception:
+            return 0.0
+        return K.status_word(self.device)[0]
+
+    def _raise_on_status(self, code: int) -> None:
+        """A kernel of this step gave up on a bounded wait (a peer rank that never
+        arrived, a TMA load or MMA that never completed): its output is not valid, so
+        the step must not be trusted.  The CUDA context itself stays usable."""
+        if code == 0:
+            return
+        from .ops import kernels as K
+
+        K.status_word(self.device).zero_()
+        raise RuntimeError(
+            f"rank {self.rank}: imf_b200 kernel status {code} "
+            f"({K.STATUS_NAMES.get(code, 'unknown')}) at step {self.step}; gradients or "
+            "weights of this step are not valid on this rank")
+
     # -------------------------------------------------------- checkpoints --
-    def save(self, path: Optional[str] = None) -> Optional[str]:
-        extra = {"rng": ckpt_mod.rng_state(), "world": self.world}
+    def save(self, path: Optional[str] = None, sampler_state: Optional[Dict[str, int]] = None
+             ) -> Optional[str]:
+        """Collective: every rank calls it.  Rank 0 writes; all ranks leave together, so no
+        rank runs ahead into the next step's peer barrier while rank 0 is still in fsync.
+        ``extra`` carries the RNG state, the world size, the Muon owner map and the
+        sampler position (epoch, batches consumed) for an exact resume."""
+        extra: Dict[str, Any] = {"rng": ckpt_mod.rng_state(), "world": self.world}
+        if hasattr(self.grad_sync, "owner_table"):
+            extra["muon_owner"] = list(self.grad_sync.owner_table())
+        if sampler_state:
+            extra["sampler"] = {k: int(v) for k, v in sampler_state.items()}
         if hasattr(self.grad_sync, "gather_state"):
             self.grad_sync.gather_state()     # collective: every rank calls save()
-        if self.rank != 0:
-            return None
-        path = path or ckpt_mod.checkpoint_path(self.cfg.run.out_dir, self.step)
-        ckpt_mod.save_checkpoint(path, self.net, self.optimizer, self.ema, self.step,
-                                 config_as_dict(self.cfg), extra)
-        if self.verbose:
-            print(f"saved {path}", flush=True)
-        return path
+        out = None
+        if self.rank == 0:
+            out = path or ckpt_mod.checkpoint_path(self.cfg.run.out_dir, self.step)
+            ckpt_mod.save_checkpoint(out, self.net, self.optimizer, self.ema, self.step,
+                                     config_as_dict(self.cfg), extra)
+            if self.verbose:
+                print(f"saved {out}", flush=True)
+        if self.world > 1:
+            pdist.barrier()
+        return out
 
     def load(self, path: str, restore_rng: bool = False) -> None:
         info = ckpt_mod.load_checkpoint(path, self.net, self.optimizer, self.ema, self.rank,
                                         self.world, barrier=pdist.barrier)
         self.step = info["step"]
+        extra = info.get("extra", {}) or {}
+        saved_owner = extra.get("muon_owner")
+        if saved_owner is not None and hasattr(self.grad_sync, "owner_table") \
+                and extra.get("world") == self.world \
+                and list(saved_owner) != list(self.grad_sync.owner_table()):
+            raise RuntimeError("checkpoint was written with a different Muon owner map for the "
+                               "same world size; momentum segments would not line up")
+        self.resume_sampler = extra.get("sampler")
         if restore_rng and "rng" in info.get("extra", {}) and self.world == 1:
             ckpt_mod.set_rng_state(info["extra"]["rng"])
         if hasattr(self.grad_sync, "after_load"):
@@ -439,7 +525,10 @@ def main(argv=None) -> None:
 
         wandb.init(project=cfg.run.wandb_project, config=config_as_dict(cfg))
     os.makedirs(cfg.run.out_dir, exist_ok=True)
-    batches = DevicePrefetcher(InfiniteLoader(loader, sampler), device)
+    inf = InfiniteLoader(loader, sampler)
+    if cfg.run.resume and getattr(trainer, "resume_sampler", None):
+        inf.restore(trainer.resume_sampler)
+    batches = DevicePrefetcher(inf, device)
     o = cfg.optim
     loss_u_ema, t_log = None, time.time()
     while trainer.step < o.total_steps:
@@ -469,7 +558,7 @@ def main(argv=None) -> None:
                            "samples_per_s": sps}, step=step)
             t_log = time.time()
         if step % cfg.run.ckpt_every == 0:
-            trainer.save()
+            trainer.save(sampler_state=inf.state(prefetched=1))
     if hb is not None:
         hb.stop()
     pdist.shutdown()

@@ -5,8 +5,8 @@ step_{step:07d}.pt`` holding ``{"model", "optimizer", "ema", "step",
 "config"}`` of tensors, numbers, strings, tuples and dicts only, so it loads
 under ``torch.load(weights_only=True)``.  Added here: the write is atomic
 (temp file + fsync + rename; a kill in mid-save corrupted a reference run),
-an ``extra`` dict carries RNG state / Muon owner map / sampler position for
-exact resume, and loading is serialised over ranks to bound host memory
+an ``extra`` dict carries RNG state, world size, Muon owner map and sampler
+position (``Trainer.save`` fills it), and loading is serialised over ranks to bound host memory
 (reference ``train.py:500-519``).
 """
 

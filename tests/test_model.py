@@ -187,3 +187,33 @@ def test_layout_formulas_are_adjoint_and_match_conv3d():
     inv[perm] = torch.arange(12)
     assert torch.equal(PK.permute_rows(z, perm, inv), z[:, perm])
     assert torch.equal(PK.permute_rows(PK.permute_rows(z, perm, inv), inv, perm), z)
+
+
+def test_reference_import_names_and_fast_engine():
+    """The reference's module paths resolve, plug-ins accept plain tensors, and
+    ``model_du_dt_fast`` equals ``torch.func.jvp`` of the u output."""
+    import importlib
+
+    for mod, names in {"models.attention_op": ["flash_jvp_attention"],
+                       "models.mla_jvp_fast": ["build_fast_jvp_state", "model_du_dt_fast"],
+                       "models.sla2_attention": ["SLA2AttentionImpl"],
+                       "models.sla2_cube_qat": ["SLA2CubeQATAttentionImpl"],
+                       "models.imf_dit_video": ["eager_math_attention", "IMFDiTVideo"]}.items():
+        m = importlib.import_module(mod)
+        assert all(hasattr(m, n) for n in names), mod
+    from models.attention_op import flash_jvp_attention
+    from models.mla_jvp_fast import build_fast_jvp_state, model_du_dt_fast
+
+    q, k, v = (torch.randn(1, 20, 2, 16) for _ in range(3))
+    o = flash_jvp_attention(q, k, v)
+    assert torch.is_tensor(o) and o.shape == (1, 20, 2, 16)
+    net = _net(attn_res_block_size=1)
+    b = 2
+    x, v_c = torch.randn(b, 16, 4, 16, 16), torch.randn(b, 16, 4, 16, 16)
+    t, r = torch.rand(b) * 0.5 + 0.5, torch.rand(b) * 0.5
+    w, t0, t1 = torch.ones(b) * 1.5, torch.zeros(b), torch.ones(b)
+    y = torch.randint(0, 1000, (b,))
+    du = model_du_dt_fast(net, build_fast_jvp_state(net), x, t, t - r, w, t0, t1, y, v_c)
+    fn = lambda z, tt: net(z, tt, tt - r, w, t0, t1, y)[0]
+    _, want = torch.func.jvp(fn, (x, t), (v_c, torch.ones_like(t)))
+    assert (du - want).abs().max() < 1e-4 * max(1.0, want.abs().max().item())

@@ -133,6 +133,7 @@ def test_sla2_model_fused_core_vs_torch_formulas(SP, kind):
     assert al and all(torch.isfinite(g_f[n]).all() for n in g_f)
     bad = [(n, _rel(g_f[n], g_g[n])) for n in g_g if n in g_f and g_g[n].norm() > 0
            and _rel(g_f[n], g_g[n]) > 0.15]
+    print("sla2 gradient outliers (> 15 %):", bad)
     assert len(bad) <= 2, bad
 
 

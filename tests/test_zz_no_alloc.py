@@ -6,8 +6,8 @@ they run, or no allocator of their own) and so cannot provide the scratch
 buffer that the regular entry point takes.  The library keeps that scratch in
 a built-in device array instead.  This test checks, on two calls in a row
 (the array keeps the first call's contents), that the result equals the
-regular entry point's, and that an oversized request is refused with an error
-code rather than launched.  The file name sorts last so every other test has
+regular entry point's and the plain fp32 formula, and that an oversized request
+is refused with an error code rather than launched.  The file name sorts last so every other test has
 already run if this one fails under ``-x``.
 """
 import ctypes
@@ -60,6 +60,16 @@ def test_noalloc_entry_matches_regular_entry_twice():
         assert (o.float() - o_ref.float()).abs().max() < 2e-2
         assert ((o.float() - o_ref.float()).norm() / o_ref.float().norm()) < 1e-2
         assert (lse - lse_ref).abs().max() < 1e-3
+        if seed == 0:
+            # and against the plain fp32 formula (one (batch, head) pair at a time: the score
+            # matrix of the whole problem would not be small)
+            from imfvideo_b200.ops import reference as ref
+
+            for h in (0, H // 2, H - 1):
+                ro = ref.attention(q[:, :, h:h + 1].float(), k[:, :, h:h + 1].float(),
+                                   v[:, :, h:h + 1].float())
+                assert (o[:, :, h:h + 1].float() - ro).abs().max() < 2e-2
+                assert ((o[:, :, h:h + 1].float() - ro).norm() / ro.norm()) < 1e-2
 
 
 def test_noalloc_entry_rejects_oversize_request():
