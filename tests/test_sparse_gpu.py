@@ -133,8 +133,11 @@ def test_sla2_model_fused_core_vs_torch_formulas(SP, kind):
     assert al and all(torch.isfinite(g_f[n]).all() for n in g_f)
     bad = [(n, _rel(g_f[n], g_g[n])) for n in g_g if n in g_f and g_g[n].norm() > 0
            and _rel(g_f[n], g_g[n]) > 0.15]
-    print("sla2 gradient outliers (> 15 %):", bad)
-    assert len(bad) <= 2, bad
+    # The only gradients that leave the 15 % band are gains of the attention-residual score
+    # heads (``*_res_norm.weight``): their gradient is the small difference of large
+    # per-candidate terms of a softmax over 2-3 candidates, so the bf16 rounding of the mixed
+    # stream shows up in it (17 % on one such gain with the 1-D SLA2 blocks, none with cubes).
+    assert all("_res_norm" in n and r < 0.25 for n, r in bad) and len(bad) <= 1, bad
 
 
 @pytest.mark.parametrize("qblk,L", [(128, 640), (64, 583)])
