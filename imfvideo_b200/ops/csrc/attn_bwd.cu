@@ -23,6 +23,7 @@
 // warps 8-11: dQ tile TMEM -> global reduction; warp 12: tcgen05.mma issuer;
 // warp 13: TMA producer.  S^T/dP^T of tile i+1 are issued as soon as tile i
 // has been pulled into registers, so the tensor core overlaps the exp math.
+#include "attn_bwd128.h"
 #include "common.cuh"
 #include "host_util.h"
 
@@ -544,7 +545,13 @@ extern "C" long imf_attn_bwd_scratch_bytes(int B, int L, int H) {
   return (long)B * L * H * 64 * 4 + 2 * (long)B * H * Lp * 4 + 512 + part;
 }
 
-// All tensors (B, L, H, 64) bf16; strides[0..11]: (batch,row,head) for q,k,v,do;
+// Same for either head_dim (64 or 128).
+extern "C" long imf_attn_bwd_scratch_bytes_hd(int B, int L, int H, int head_dim) {
+  if (head_dim == 128) return imf::attn_bwd128_scratch_bytes(B, L, H);
+  return imf_attn_bwd_scratch_bytes(B, L, H);
+}
+
+// All tensors (B, L, H, head_dim) bf16, head_dim 64 or 128 (128: dense only); strides[0..11]: (batch,row,head) for q,k,v,do;
 // o contiguous-like with its own strides; dq contiguous (B, L, H, 64);
 // dk/dv with given strides (dv may point into a wider buffer).
 extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const void* o,
@@ -555,7 +562,19 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
                             long scratch_bytes, const int* qlist, const uint8_t* qflags, int qmax,
                             int* status, void* stream) {
   using namespace imf;
-  if (head_dim != BW_HD || B <= 0 || L <= 0 || H <= 0) return IMF_ERR_ARG;
+  if ((head_dim != BW_HD && head_dim != 128) || B <= 0 || L <= 0 || H <= 0) return IMF_ERR_ARG;
+  if (head_dim == 128) {
+    if (qlist != nullptr) return IMF_ERR_ARG;       // block-sparse lists: head_dim 64 only
+    if ((reinterpret_cast<uintptr_t>(scratch) & 255) || (reinterpret_cast<uintptr_t>(dq) & 15) ||
+        (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15))
+      return IMF_ERR_ARG;
+    for (int i = 0; i < 3; ++i)
+      if ((dk_strides[i] & 7) || (dv_strides[i] & 7) || (o_strides[i] & 3) || (strides[9 + i] & 3))
+        return IMF_ERR_ARG;
+    Bwd128Args a{q, k, v, o, d_o, lse, dq, dk, dv, B, L, H, strides, o_strides, dk_strides,
+                 dv_strides, scale, scratch, scratch_bytes, status, stream};
+    return attn_bwd128_launch(a);
+  }
   if (scratch == nullptr || scratch_bytes < imf_attn_bwd_scratch_bytes(B, L, H)) return IMF_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(scratch) & 255) || (reinterpret_cast<uintptr_t>(dq) & 15) ||
       (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15))

@@ -35,6 +35,7 @@
 //
 // Tensors are (B, L, H, 64) bf16 with arbitrary 16-byte-aligned strides;
 // ragged L is handled by TMA zero fill + masking of the last K/V tile.
+#include "attn_fwd128.h"
 #include "common.cuh"
 #include "host_util.h"
 
@@ -670,8 +671,14 @@ extern "C" long imf_attn_fwd_scratch_bytes(int B, int L, int H, int tangent) {
   return (long)((size_t)G * 2 * per * sizeof(float));
 }
 
-// Dense attention forward (+ optional tangent).  All tensors (B, L, H, 64)
-// bf16; `strides` holds (batch, row, head) element strides for q, k, v and,
+// Same for either head_dim (64 or 128).
+extern "C" long imf_attn_fwd_scratch_bytes_hd(int B, int L, int H, int tangent, int head_dim) {
+  if (head_dim == 128) return imf::attn_fwd128_scratch_bytes(B, L, H, tangent);
+  return imf_attn_fwd_scratch_bytes(B, L, H, tangent);
+}
+
+// Dense attention forward (+ optional tangent).  All tensors (B, L, H, head_dim)
+// bf16, head_dim 64 or 128; `strides` holds (batch, row, head) element strides for q, k, v and,
 // when tangents are given, dq, dk, dv.  o/dout contiguous-in-last-dim with
 // strides (o_sb, o_sl, o_sh).  lse: (B, H, L) fp32 or null.  scratch: device
 // buffer of at least imf_attn_fwd_scratch_bytes() bytes (may be null if 0).
@@ -681,9 +688,16 @@ extern "C" int imf_attn_fwd(const void* q, const void* k, const void* v, const v
                             int64_t o_sb, int64_t o_sl, int64_t o_sh, float scale, void* scratch,
                             long scratch_bytes, int* status, void* stream) {
   using namespace imf;
-  if (head_dim != ATT_HD || B <= 0 || L <= 0 || H <= 0) return IMF_ERR_ARG;
+  if ((head_dim != ATT_HD && head_dim != 128) || B <= 0 || L <= 0 || H <= 0) return IMF_ERR_ARG;
   if ((o_sl & 7) || (o_sh & 7) || (o_sb & 7) || (reinterpret_cast<uintptr_t>(o) & 15))
     return IMF_ERR_ARG;
+  if (head_dim == 128) {
+    if (dq != nullptr && (dout == nullptr || (reinterpret_cast<uintptr_t>(dout) & 15)))
+      return IMF_ERR_ARG;
+    Fwd128Args a{q, k, v, dq, dk, dv, o, dout, lse, B, L, H, strides, o_sb, o_sl, o_sh, scale,
+                 scratch, scratch_bytes, status, stream};
+    return attn_fwd128_launch(a);
+  }
   AttParams prm;
   prm.o = static_cast<__nv_bfloat16*>(o);
   prm.dout = static_cast<__nv_bfloat16*>(dout);
@@ -743,6 +757,7 @@ extern "C" int imf_attn_fwd_noalloc(const void* q, const void* k, const void* v,
     }
     scratch_of_device[dev] = static_cast<float*>(ptr);
   }
+  if (head_dim != ATT_HD) return IMF_ERR_ARG;     // the built-in scratch is sized for head_dim 64
   const long need = imf_attn_fwd_scratch_bytes(B, L, H, 0);
   if (need > (long)(NOALLOC_FLOATS * sizeof(float))) {
     fprintf(stderr,

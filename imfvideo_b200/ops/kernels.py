@@ -116,6 +116,10 @@ if _has("imf_attn_fwd"):
                                                    ctypes.c_long, c_void_p, c_void_p]
     _lib.imf_attn_fwd_scratch_bytes.restype = ctypes.c_long
     _lib.imf_attn_fwd_scratch_bytes.argtypes = [c_int, c_int, c_int, c_int]
+    _lib.imf_attn_fwd_scratch_bytes_hd.restype = ctypes.c_long
+    _lib.imf_attn_fwd_scratch_bytes_hd.argtypes = [c_int, c_int, c_int, c_int, c_int]
+
+ATTN_HEAD_DIMS = (64, 128)
 
 _scratch: Dict[Tuple[int, str], torch.Tensor] = {}
 
@@ -147,7 +151,7 @@ def _tma_ok(t: torch.Tensor) -> torch.Tensor:
 
 def attn_fwd(q, k, v, dq=None, dk=None, dv=None, scale: Optional[float] = None,
              need_lse: bool = True):
-    """(o, do | None, lse | None) for (B, L, H, 64) bf16 tensors."""
+    """(o, do | None, lse | None) for (B, L, H, head_dim) bf16 tensors, head_dim 64 or 128."""
     B, L, H, hd = q.shape
     scale = 1.0 / math.sqrt(hd) if scale is None else scale
     ts = [_tma_ok(t) for t in (q, k, v)]
@@ -161,7 +165,7 @@ def attn_fwd(q, k, v, dq=None, dk=None, dv=None, scale: Optional[float] = None,
     o = torch.empty(B, L, H, hd, dtype=torch.bfloat16, device=q.device)
     do = torch.empty_like(o) if tang else None
     lse = torch.empty(B, H, L, dtype=torch.float32, device=q.device) if need_lse else None
-    nscr = int(_lib.imf_attn_fwd_scratch_bytes(B, L, H, int(tang)))
+    nscr = int(_lib.imf_attn_fwd_scratch_bytes_hd(B, L, H, int(tang), hd))
     scr = _scratch_buf(q.device, nscr, "attn_fwd")
     rc = _lib.imf_attn_fwd(_ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]),
                            _ptr(ts[3]) if tang else None, _ptr(ts[4]) if tang else None,
@@ -179,6 +183,8 @@ if _has("imf_attn_bwd"):
         [c_float, c_void_p, ctypes.c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
     _lib.imf_attn_bwd_scratch_bytes.restype = ctypes.c_long
     _lib.imf_attn_bwd_scratch_bytes.argtypes = [c_int, c_int, c_int]
+    _lib.imf_attn_bwd_scratch_bytes_hd.restype = ctypes.c_long
+    _lib.imf_attn_bwd_scratch_bytes_hd.argtypes = [c_int, c_int, c_int, c_int]
 
 
 def attn_bwd(q, k, v, o, lse, go, scale: Optional[float] = None,
@@ -204,7 +210,7 @@ def attn_bwd(q, k, v, o, lse, go, scale: Optional[float] = None,
     if dv.stride(3) != 1 or dv.data_ptr() % 16 or any(s_ % 8 for s_ in dv.stride()[:3]):
         raise ValueError("dv output needs 16-byte aligned rows")
     i3 = lambda t: (c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
-    nscr = int(_lib.imf_attn_bwd_scratch_bytes(B, L, H))
+    nscr = int(_lib.imf_attn_bwd_scratch_bytes_hd(B, L, H, hd))
     scr = _scratch_buf(q.device, nscr, "attn_bwd")
     rc = _lib.imf_attn_bwd(_ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]), _ptr(o), _ptr(ts[3]),
                            _ptr(lse), _ptr(dq), _ptr(dk), _ptr(dv), B, L, H, hd,
@@ -255,8 +261,9 @@ class _AttnFn(torch.autograd.Function):
 
 
 def attention_dual(q: Dual, k: Dual, v: Dual) -> Dual:
-    if q.p.dtype != torch.bfloat16 or q.p.shape[-1] != 64 or v.p.shape[-1] != 64:
-        raise ValueError("attention kernel needs bf16 tensors with head_dim 64; got "
+    if q.p.dtype != torch.bfloat16 or q.p.shape[-1] not in ATTN_HEAD_DIMS \
+            or v.p.shape[-1] != q.p.shape[-1]:
+        raise ValueError("attention kernel needs bf16 tensors with head_dim 64 or 128; got "
                          f"{q.p.dtype}, qk {q.p.shape[-1]}, v {v.p.shape[-1]}")
     if q.t is not None:
         o, do = _AttnFn.apply(q.p, k.p, v.p, q.t, k.t, v.t)

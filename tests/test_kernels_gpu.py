@@ -79,6 +79,46 @@ def test_attention_forward_tangent(K, B, L, H):
     K.check_status()
 
 
+@pytest.mark.parametrize("B,L,H", [(1, 256, 1), (1, 300, 3), (2, 1000, 3), (1, 64, 1), (1, 2049, 2),
+                                   (2, 2100, 12)])
+def test_attention_forward_hd128(K, B, L, H):
+    """head_dim 128, head counts that are not powers of two, ragged lengths, and (last case)
+    more work items than SMs, so items are split between CTAs and merged."""
+    from imfvideo_b200.ops import reference as ref
+
+    g = torch.Generator(device="cuda").manual_seed(L)
+    q, k, v = (torch.randn(B, L, H, 128, device="cuda", generator=g).bfloat16() for _ in range(3))
+    o, _, lse = K.attn_fwd(q, k, v)
+    for h in sorted({0, H // 2, H - 1}):
+        sl = slice(h, h + 1)
+        ro = ref.attention(q[:, :, sl].float(), k[:, :, sl].float(), v[:, :, sl].float())
+        assert (o[:, :, sl].float() - ro).abs().max() < 2e-2 and _rel(o[:, :, sl], ro) < 1e-2
+        rl = ref.attention_lse(q[:, :, sl].float(), k[:, :, sl].float())
+        assert (lse[:, sl] - rl).abs().max() < 1e-3
+    K.check_status()
+
+
+@pytest.mark.parametrize("B,L,H", [(1, 128, 1), (1, 212, 3), (2, 1000, 3), (1, 2049, 2), (1, 2100, 12)])
+def test_attention_forward_tangent_hd128(K, B, L, H):
+    from imfvideo_b200.ops import reference as ref
+
+    g = torch.Generator(device="cuda").manual_seed(L)
+    mk = lambda s: (torch.randn(B, L, H, 128, device="cuda", generator=g) * s).bfloat16()
+    q, k, v, dq, dk, dv = mk(1), mk(1), mk(1), mk(.5), mk(.5), mk(.5)
+    o, do, lse = K.attn_fwd(q, k, v, dq, dk, dv)
+    for h in sorted({0, H // 2, H - 1}):
+        sl = slice(h, h + 1)
+        ro, rdo = ref.attention_jvp(*(t[:, :, sl].float() for t in (q, k, v, dq, dk, dv)))
+        assert (o[:, :, sl].float() - ro).abs().max() < 2e-2 and _rel(o[:, :, sl], ro) < 1e-2
+        assert (do[:, :, sl].float() - rdo).abs().max() < 3e-2 and _rel(do[:, :, sl], rdo) < 1e-2
+    o2, _, lse2 = K.attn_fwd(q, k, v)
+    assert _rel(o2, o) < 5e-3            # primal-only and fused kernels agree
+    assert (lse - lse2).abs().max() < 1e-3
+    o3, do3, _ = K.attn_fwd(q, k, v, dq, dk, dv)
+    assert torch.equal(o, o3) and torch.equal(do, do3)       # run twice: same bits
+    K.check_status()
+
+
 def test_attention_strided_views_and_run_twice(K):
     """v as a slice of a wider kv tensor (as in MLA); two runs are bit-equal."""
     torch.manual_seed(0)
@@ -129,6 +169,30 @@ def test_attention_backward(K, B, L, H):
     dq2, dk2, dv2 = K.attn_bwd(q, k, v, o, lse, go)
     assert torch.equal(dk, dk2) and torch.equal(dv2, dv.contiguous())   # deterministic parts
     assert _rel(dq2, dq) < 1e-3              # dQ uses fp32 atomics: order may differ
+    K.check_status()
+
+
+@pytest.mark.parametrize("B,L,H", [(1, 128, 1), (1, 300, 3), (2, 1000, 3), (1, 2049, 2), (1, 2100, 12)])
+def test_attention_backward_hd128(K, B, L, H):
+    """head_dim 128 reverse mode (64-row query steps, transposed dQ tiles); the last case
+    splits the query range of each K/V tile over several CTAs."""
+    from imfvideo_b200.ops import reference as ref
+
+    g = torch.Generator(device="cuda").manual_seed(L)
+    q, k, v, go = (torch.randn(B, L, H, 128, device="cuda", generator=g).bfloat16() for _ in range(4))
+    o, _, lse = K.attn_fwd(q, k, v)
+    kvbuf = torch.zeros(B, L, H, 224, dtype=torch.bfloat16, device="cuda")
+    dq, dk, dv = K.attn_bwd(q, k, v, o, lse, go, gv_out=kvbuf[..., 96:])
+    for h in sorted({0, H // 2, H - 1}):
+        sl = slice(h, h + 1)
+        qf, kf, vf = (t[:, :, sl].float().requires_grad_(True) for t in (q, k, v))
+        ref.attention(qf, kf, vf).backward(go[:, :, sl].float())
+        for name, a, b in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+            assert _rel(a[:, :, sl], b) < 1.5e-2, (name, h, _rel(a[:, :, sl], b))
+    assert (kvbuf[..., :96] == 0).all()        # only the value band was written
+    dq2, dk2, dv2 = K.attn_bwd(q, k, v, o, lse, go)
+    assert torch.equal(dk, dk2) and torch.equal(dv2, dv.contiguous())
+    assert _rel(dq2, dq) < 1e-3
     K.check_status()
 
 
