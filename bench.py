@@ -30,7 +30,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-TOKENS = {"d256": 29120, "d256_sla2": 29120, "d1024": 32760, "wan1p3b": 32760, "tiny": 256}
+TOKENS = {"d256": 29120, "d256_sla2": 29120, "d1024": 32760, "wan1p3b": 32760,
+          "wan1p3b_dense": 32760, "tiny": 256}
 PUBLISHED = None      # the reference publishes no B200 tokens/s figure
 
 

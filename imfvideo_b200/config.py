@@ -263,7 +263,9 @@ def preset(name: str) -> Config:
     ``d256``   d=256, depth 12, 4 heads, 29,140 tokens (headline benchmark).
     ``d256_sla2``  same with cube SLA2 INT8-QAT attention.
     ``d1024``  d=1024, depth 24, 16 heads, 32,780 tokens.
-    ``wan1p3b`` d=1536, 30 layers, 12 heads (head_dim 128), FFN 8960.
+    ``wan1p3b`` d=1536, 30 layers, 12 heads (head_dim 128), FFN 8960, SLA2 cube attention.
+    ``wan1p3b_dense`` the same geometry with dense attention (the fused primal+tangent
+    kernels cover head_dim 128 for dense attention).
     """
     c = copy.deepcopy(Config())
     m, d = c.model, c.data
@@ -292,12 +294,16 @@ def preset(name: str) -> Config:
         m.grad_checkpoint = False          # activations of all 28 blocks fit in 180 GB
         d.latent_frames, d.latent_size = 21, (60, 104)
         c.loss.autocast_bf16 = True
-    elif name == "wan1p3b":
+    elif name in ("wan1p3b", "wan1p3b_dense"):
         m.hidden_size, m.depth, m.aux_head_depth, m.num_heads = 1536, 30, 4, 12
         m.mlp_ratio = 8960 / 1536
-        m.attn_impl = "sla2_cube_qat"
-        m.sla2_topk = 0.10
+        if name == "wan1p3b":
+            m.attn_impl = "sla2_cube_qat"
+            m.sla2_topk = 0.10
         m.max_params = 2_000_000_000
+        # 34 blocks x 32,780 rows x ~106 KB of saved activations per row would leave no room
+        # beside 1.7 B parameters with their optimizer state: recompute each block in backward
+        m.grad_checkpoint = True
         d.latent_frames, d.latent_size = 21, (60, 104)
         c.loss.autocast_bf16 = True
     else:

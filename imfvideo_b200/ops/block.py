@@ -65,7 +65,7 @@ class BlockGeom:
 
 
 def supported(g: BlockGeom) -> bool:
-    return (g.d % 128 == 0 and g.hd in (64,) and g.dv == g.hd and g.dq % 8 == 0 and g.dc % 8 == 0
+    return (g.d % 128 == 0 and g.hd in (64, 128) and g.dv == g.hd and g.dq % 8 == 0 and g.dc % 8 == 0
             and g.dr % 2 == 0 and g.dn % (g.hd // 32) == 0 and (g.H * g.dv) % 8 == 0
             and (g.dq + g.dc) % 4 == 0 and g.fp % 8 == 0)
 

@@ -12,7 +12,7 @@ namespace imf {
 
 constexpr int ROW_THREADS = 256;
 constexpr int ROW_WARPS = ROW_THREADS / 32;
-constexpr int MAX_CANDS = 8;
+constexpr int MAX_CANDS = 16;     // candidates of the attention-residual re-mix (snapshots + prefix)
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

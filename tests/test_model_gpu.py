@@ -19,13 +19,17 @@ def kernels():
     return K
 
 
-def _net(dtype=None, bs=2):
+def _net(dtype=None, bs=2, wide=False):
+    """``wide``: 3 heads of 128 (not a power of two, the Wan2.1-1.3B head shape) and an MLP
+    width that is not a multiple of 128."""
     from imfvideo_b200.models import IMFDiTVideo, flash_jvp_attention
 
     torch.manual_seed(0)
-    net = IMFDiTVideo(input_size=(16, 32), num_frames=4, hidden_size=256, depth=3, num_heads=4,
-                      aux_head_depth=1, kv_lora_rank=128, attn_res_block_size=bs,
-                      attn_impl=flash_jvp_attention, compute_dtype=dtype)
+    geo = dict(hidden_size=384, num_heads=3, mlp_ratio=8960 / 1536) if wide else \
+        dict(hidden_size=256, num_heads=4, kv_lora_rank=128)
+    net = IMFDiTVideo(input_size=(16, 32), num_frames=4, depth=3, aux_head_depth=1,
+                      attn_res_block_size=bs, attn_impl=flash_jvp_attention, compute_dtype=dtype,
+                      **geo)
     with torch.no_grad():
         for p in net.parameters():
             p.add_(torch.randn_like(p) * 0.03)
@@ -75,14 +79,18 @@ def test_trainer_steps_on_gpu(kernels):
     assert st[-1]["grad_norm"] > 0
 
 
-@pytest.mark.parametrize("bs", [0, 2])
-def test_fused_block_matches_generic_composition(kernels, bs):
+@pytest.mark.parametrize("bs,wide", [(0, False), (2, False), (2, True)])
+def test_fused_block_matches_generic_composition(kernels, bs, wide):
     """Same bf16 kernels for GEMM/attention; fused block node vs op-by-op path:
     outputs, tangent and every parameter gradient."""
     from imfvideo_b200.ops import cuda as cu
     from imfvideo_b200.ops.dual import Dual
 
-    net = _net(torch.bfloat16, bs=bs)
+    net = _net(torch.bfloat16, bs=bs, wide=wide)
+    if wide:
+        blk = net.shared_blocks[0]
+        assert blk.attn.qk_head_dim == 128 and blk.fused_ok(torch.zeros(1, device="cuda"),
+                                                            torch.bfloat16)
     B = 2
     g = torch.Generator(device="cuda").manual_seed(3)
     x = torch.randn(B, 16, 4, 16, 32, device="cuda", generator=g)
