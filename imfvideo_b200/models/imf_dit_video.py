@@ -365,6 +365,31 @@ class TransformerBlock(nn.Module):
                 a.kv_a_layernorm.weight, a.q_norm.weight, a.k_norm.weight, self.attn_scale,
                 self.mlp_scale) + mats
 
+    def fused_sinks(self):
+        """Which parameter each row band of the six fused bf16 matrices comes from (same
+        order as ``fused_params`` concatenates them), for direct weight-gradient writes."""
+        sk = getattr(self, "_sinks", None)
+        if sk is None:
+            from ..ops.block import GradSinks
+
+            a, mlp = self.attn, self.mlp
+            ws = [a.q_a_proj.weight, a.kv_a_proj.weight] + \
+                ([a.g_proj.weight] if a.use_output_gate else [])
+            wa, r = [], 0
+            for w in ws:
+                wa.append((w, r, w.shape[0], w.shape[1]))
+                r += w.shape[0]
+            one = lambda w: [(w, 0, w.shape[0], w.shape[1])]
+            f = mlp.w1.out_features
+            fp = f + (-f) % 8
+            sk = self._sinks = GradSinks({
+                "W_a": wa, "W_qb": one(a.q_b_proj.weight), "W_kvb": one(a.kv_b_proj.weight),
+                "W_out": one(a.out_proj.weight),
+                "W13": [(mlp.w1.weight, 0, f, mlp.w1.weight.shape[1]),
+                        (mlp.w3.weight, fp, f, mlp.w3.weight.shape[1])],
+                "W2": [(mlp.w2.weight, 0, mlp.w2.weight.shape[0], f)]})
+        return sk
+
     def fused_forward(self, prefix: Dual, snaps, fresh: bool, use_res: bool, rope_cos, rope_sin,
                       eps: float) -> Dual:
         from ..ops.block import DENSE_CORE, run_block
@@ -375,7 +400,8 @@ class TransformerBlock(nn.Module):
         p, t = run_block(self.fused_geom(), core, fresh, use_res, eps, act.beta, act.linear_beta,
                          rope_cos, rope_sin, prefix.p, prefix.t, [s.p for s in snaps],
                          [s.t for s in snaps] if has_t else [None] * len(snaps),
-                         self.fused_params(use_res))
+                         self.fused_params(use_res),
+                         self.fused_sinks() if torch.is_grad_enabled() else None)
         return Dual(p, t)
 
     def forward(self, x, rope_cos, rope_sin, compute_dtype=None):

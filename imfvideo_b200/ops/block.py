@@ -50,6 +50,37 @@ class DenseCore:
 DENSE_CORE = DenseCore()
 
 
+class GradSinks:
+    """Where the weight gradients of one block go.  The six bf16 matrices the node works on
+    are casts / concatenations of fp32 parameters; ``pieces[name]`` lists, for matrix
+    ``name``, the parameters it was built from as (param, first_row, n_rows, n_cols).
+
+    When every such parameter already owns an fp32 ``.grad`` buffer (the flat gradient
+    arena of the optimizer engine, or a previous micro-batch's gradient), the backward
+    pass writes each product dY^T X straight into it with accumulation and returns no
+    gradient for the matrices: no bf16 gradient tensors, no casts, no splits, no adds."""
+
+    ORDER = ("W_a", "W_qb", "W_kvb", "W_out", "W13", "W2")
+
+    def __init__(self, pieces):
+        self.pieces = pieces
+
+    def direct(self) -> bool:
+        for name in self.ORDER:
+            for p, r0, _n, _c in self.pieces[name]:
+                g = p.grad
+                if (not p.requires_grad or g is None or g.dtype != F32 or not g.is_contiguous()
+                        or g.shape != p.shape or r0 % 8 or g.data_ptr() % 16):
+                    return False       # r0: the TMA view of dY[:, r0:] must start 16-byte aligned
+        return True
+
+    def accumulate(self, name: str, dy: torch.Tensor, x: torch.Tensor) -> None:
+        """grad(piece) += dy[:, rows of the piece]^T x[:, :cols of the piece]"""
+        for p, r0, n, c in self.pieces[name]:
+            K.gemm_wgrad(dy[:, r0:r0 + n], x[:, :c] if c != x.shape[1] else x,
+                         out=p.grad.view(n, c), accumulate=True)
+
+
 class BlockGeom:
     """Static geometry of a block (python ints only)."""
 
@@ -81,6 +112,7 @@ class _BlockFn(torch.autograd.Function):
     def forward(ctx, geom, core, fresh, use_res, eps, beta, lbeta, cos, sin, nsnap, prefix,
                 dprefix, *rest):
         g: BlockGeom = geom
+        core, sinks = core if isinstance(core, tuple) else (core, None)
         snaps = list(rest[:nsnap])
         dsnaps = list(rest[nsnap:2 * nsnap])
         (w1, w2, g_n1, g_n2, g_qa, g_kva, g_qn, g_kn, a_scale, m_scale,
@@ -165,6 +197,7 @@ class _BlockFn(torch.autograd.Function):
                                   q[0], k[0], o, og[0], a_out[:rows], p2[0], n2[0], gu[:rows],
                                   act[:rows], m[:rows], *core_saved)
             ctx.meta = (g, core, fresh, use_res, eps, beta, lbeta, nsnap, B, L, len(core_saved))
+            ctx.sinks = sinks
         new_p = out[0].view(B, L, d)
         new_t = out[1].view(B, L, d) if has_t else out.new_empty(0)
         ctx.mark_non_differentiable(new_t)
@@ -191,20 +224,27 @@ class _BlockFn(torch.autograd.Function):
         # 11'. out = p2 + m * mlp_scale
         g_m, g_mscale = R.scale_add_bwd(m, m_scale, g_out, rows, d)
         # 10'. MLP
-        g_act = g_m @ W2                                            # [rows, fp]
-        gW2 = g_m.t() @ act
+        # data gradients dY W: W is [n_out, n_in] = [K, N], consumed MN-major as it is.
+        # weight gradients dY^T X: split-K products (K = token rows), written straight into the
+        # parameters' gradient buffers when they exist (`direct`), else returned to autograd.
+        sinks = getattr(ctx, "sinks", None)
+        direct = sinks is not None and sinks.direct()
+        wgrad = (lambda name, dy, x: sinks.accumulate(name, dy, x)) if direct else \
+            (lambda name, dy, x: K.gemm_wgrad(dy, x).to(BF16))
+        g_act = K.gemm(g_m, W2, b_mn=True)                          # [rows, fp]
+        gW2 = wgrad("W2", g_m, act)
         g_gu = new(rows, 2 * g.fp)
         R.situ_bwd(gu, g_act, g_gu, rows, g.fp, beta, lbeta)
-        g_n2v = g_gu @ W13
-        gW13 = g_gu.t() @ n2
+        g_n2v = K.gemm(g_gu, W13, b_mn=True)
+        gW13 = wgrad("W13", g_gu, n2)
         # 9'. residual + remix + norm2
         sn2 = sn + [pfx] if fresh else sn
         g_res2, g_aout, g_sn2, gg_n2, g_w2, g_ascale = R.resnorm_bwd(
             None if fresh else pfx, a_out, a_scale, sn2, w2 if use_res else None, g_n2, eps,
             g_n2v, g_out, want_g_res=not fresh)
         # 8'. output projection
-        g_og = g_aout @ W_out                                       # [rows, hv]
-        gW_out = g_aout.t() @ og
+        g_og = K.gemm(g_aout, W_out, b_mn=True)                     # [rows, hv]
+        gW_out = wgrad("W_out", g_aout, og)
         # 7'. output gate (gate gradient goes straight into its band of g_a_)
         g_a = new(rows, na)
         o2 = o.view(rows, hv)
@@ -226,17 +266,17 @@ class _BlockFn(torch.autograd.Function):
                                     gk.contiguous(), g_qb, g_kvb, g_a[:, g.dq + g.dc:], rows, L,
                                     g.H, g.dn, g.dr, g.dv, na, eps)
         # 4'. up-projections
-        g_qlat = g_qb @ W_qb
-        gW_qb = g_qb.t() @ qlat
-        g_kvlat = g_kvb @ W_kvb
-        gW_kvb = g_kvb.t() @ kvlat
+        g_qlat = K.gemm(g_qb, W_qb, b_mn=True)
+        gW_qb = wgrad("W_qb", g_qb, qlat)
+        g_kvlat = K.gemm(g_kvb, W_kvb, b_mn=True)
+        gW_kvb = wgrad("W_kvb", g_kvb, kvlat)
         # 3'. latent norms (write into the q / kv bands of g_a_)
         gg_qa, gg_kva = R.rmsnorm_seg_bwd(
             [(a_, g_qa, g_qlat, g_a, g.dq, na, g.dq),
              (a_[:, g.dq:], g_kva, g_kvlat, g_a[:, g.dq:], g.dc, na, g.dc)], rows, eps)
         # 2'. fused projection
-        g_n1v = g_a @ W_a
-        gW_a = g_a.t() @ n1
+        g_n1v = K.gemm(g_a, W_a, b_mn=True)
+        gW_a = wgrad("W_a", g_a, n1)
         # 1'. remix + norm1; the prefix gradient of step 9' rides in as g_pfx_ext
         ext = g_sn2[-1] if fresh else g_res2
         g_pfx, _, g_sn1, gg_n1, g_w1, _ = R.resnorm_bwd(
@@ -255,10 +295,14 @@ class _BlockFn(torch.autograd.Function):
 
 
 def run_block(geom: BlockGeom, core, fresh: bool, use_res: bool, eps: float, beta: float,
-              lbeta: Optional[float], cos, sin, prefix, dprefix, snaps, dsnaps, params):
+              lbeta: Optional[float], cos, sin, prefix, dprefix, snaps, dsnaps, params,
+              sinks: Optional[GradSinks] = None):
     """params: (w1, w2, g_norm1, g_norm2, g_qa, g_kva, g_qn, g_kn, attn_scale, mlp_scale,
-    W_a, W_qb, W_kvb, W_out, W13, W2) with bf16 weight matrices."""
+    W_a, W_qb, W_kvb, W_out, W13, W2) with bf16 weight matrices; ``sinks`` says which
+    parameters those matrices were built from (see ``GradSinks``)."""
     nsnap = len(snaps)
+    if sinks is not None:
+        core = (core, sinks)
     args = list(snaps) + ([s for s in dsnaps] if dprefix is not None else [None] * nsnap)
     p, t = _BlockFn.apply(geom, core, fresh, use_res, eps, beta, lbeta, cos, sin, nsnap, prefix,
                           dprefix, *args, *params)

@@ -42,7 +42,9 @@ struct GemmSmem {
 };
 
 struct GemmTiles {
-  int n_m, n_n, total;     // tiles along M, N; total = n_m * n_n * batch
+  int n_m, n_n, total;     // tiles along M, N; total = n_m * n_n * batch * splits
+  int splits, kb_per;      // split-K: slice z of the K loop covers k-blocks [z kb_per, (z+1) kb_per)
+                           // and writes plane z of C (batch must be 1 then)
 };
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT>
@@ -80,10 +82,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   tc_fence_after();
   const uint32_t tmem = s.tmem_base;
   volatile int* abort_flag = &s.abort_flag;
-  auto tile_coords = [&](int tile, int& n0, int& m0, int& bz) {
+  // bz: batch index of the operands; cz: plane of C (batch index, or K slice under split-K)
+  auto tile_coords = [&](int tile, int& n0, int& m0, int& bz, int& cz, int& kb0, int& kb1) {
     n0 = (tile % tiles.n_n) * BN;
     m0 = ((tile / tiles.n_n) % tiles.n_m) * GEMM_BM;
-    bz = tile / (tiles.n_n * tiles.n_m);
+    cz = tile / (tiles.n_n * tiles.n_m);
+    if (tiles.splits > 1) {
+      bz = 0;
+      kb0 = cz * tiles.kb_per;
+      kb1 = kb0 + tiles.kb_per < num_kb ? kb0 + tiles.kb_per : num_kb;
+    } else {
+      bz = cz;
+      kb0 = 0;
+      kb1 = num_kb;
+    }
   };
 
   if (warp == 4) {
@@ -95,9 +107,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles.total && ok; tile += gridDim.x) {
-        int n0, m0, bz;
-        tile_coords(tile, n0, m0, bz);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        int n0, m0, bz, cz, kb0, kb1;
+        tile_coords(tile, n0, m0, bz, cz, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int st = it % STAGES;
           if (it >= STAGES && !mbar_wait(&s.empty[st], ((it / STAGES) & 1) ^ 1, abort_flag, status,
                                          STATUS_TIMEOUT_EMPTY)) {
@@ -136,7 +148,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         if (!ok) break;
         tc_fence_after();
         const uint32_t acc = tmem + buf * BN;
-        for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+        int n0_, m0_, bz_, cz_, kb0, kb1;
+        tile_coords(tile, n0_, m0_, bz_, cz_, kb0, kb1);
+        for (int kb = kb0; kb < kb1 && ok; ++kb, ++it) {
           const int st = it % STAGES;
           ok = mbar_wait(&s.full[st], (it / STAGES) & 1, abort_flag, status, STATUS_TIMEOUT_TMA);
           if (!ok) break;
@@ -148,7 +162,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                                      : sdesc_kmajor(a_base + ks * 32);
             const uint64_t db = B_MN ? sdesc_mnmajor(b_base + ks * 2048, 64 * 128)
                                      : sdesc_kmajor(b_base + ks * 32);
-            mma_ss(acc, da, db, idesc, (kb | ks) != 0);
+            mma_ss(acc, da, db, idesc, kb != kb0 || ks != 0);
           }
           tc_commit(&s.empty[st]);
         }
@@ -161,11 +175,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     bool dead = false;     // a wait gave up: keep walking (the named barriers below are
                            // counted per tile by all four warps) but touch nothing
     for (int tile = blockIdx.x; tile < tiles.total; tile += gridDim.x, ++tn) {
-      int n0, m0, bz;
-      tile_coords(tile, n0, m0, bz);
+      int n0, m0, bz, cz, kb0_, kb1_;
+      tile_coords(tile, n0, m0, bz, cz, kb0_, kb1_);
       const uint32_t buf = tn & 1;
-      OutT* C = Cbase + (int64_t)bz * batch_stride_c;
-      const OutT* Cin = Cin_base ? Cin_base + (int64_t)bz * batch_stride_c : nullptr;
+      OutT* C = Cbase + (int64_t)cz * batch_stride_c;
+      const OutT* Cin = Cin_base ? Cin_base + (int64_t)cz * batch_stride_c : nullptr;
       if (!dead)
         dead = !__all_sync(0xffffffffu, mbar_wait(&s.acc_full[buf], (tn >> 1) & 1, abort_flag,
                                                   status, STATUS_TIMEOUT_MMA));
@@ -277,7 +291,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 #pragma unroll
           for (int pn = 0; pn < BN / PANEL_COLS; ++pn)
             if (n0 + pn * PANEL_COLS < N)
-              tma_store_3d(&tm_c, s.c + pn * (GEMM_BM * 128), n0 + pn * PANEL_COLS, m0, bz);
+              tma_store_3d(&tm_c, s.c + pn * (GEMM_BM * 128), n0 + pn * PANEL_COLS, m0, cz);
           tma_store_commit();
         }
       }
@@ -297,9 +311,11 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
                        int K, int64_t lda, int64_t ldb, int64_t ldc, int bias_rows, float alpha,
                        int accumulate_out, int* status, cudaStream_t stream, int batch = 1,
                        int64_t sa = 0, int64_t sb = 0, int64_t sc = 0, const void* Cin = nullptr,
-                       float beta = 0.f) {
+                       float beta = 0.f, int splits = 1) {
   CUtensorMap ta, tb, tc;
   int rc;
+  if (splits > 1 && batch != 1) return IMF_ERR_ARG;
+  const int c_planes = splits > 1 ? splits : batch;
   {
     // K-major: dims (K, M), box (64, 128).  MN-major: dims (M, K), box (64, 64).
     uint64_t dims[3] = {A_MN ? (uint64_t)M : (uint64_t)K, A_MN ? (uint64_t)K : (uint64_t)M,
@@ -320,12 +336,12 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
   // C through TMA when its pitch, batch stride and base are 16-byte multiples
   constexpr int ES = (int)sizeof(OutT);
   int tma_store = ((ldc * ES) % 16 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0) &&
-                  (batch == 1 || (sc * ES) % 16 == 0) && !accumulate_out;
+                  (c_planes == 1 || (sc * ES) % 16 == 0) && !accumulate_out;
   tc = ta;
   if (tma_store) {
-    uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)c_planes};
     uint64_t str[3] = {(uint64_t)ES, (uint64_t)ldc * ES,
-                       (uint64_t)(batch > 1 ? sc : ldc * (int64_t)M) * ES};
+                       (uint64_t)(c_planes > 1 ? sc : ldc * (int64_t)M) * ES};
     uint32_t box[3] = {(uint32_t)(128 / ES), (uint32_t)GEMM_BM, 1};
     if (make_tmap(&tc, ES == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                         3, C, dims, str, box))
@@ -343,7 +359,11 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
   GemmTiles tiles;
   tiles.n_n = (N + BN - 1) / BN;
   tiles.n_m = (M + GEMM_BM - 1) / GEMM_BM;
-  tiles.total = tiles.n_n * tiles.n_m * batch;
+  const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  tiles.kb_per = splits > 1 ? (num_kb + splits - 1) / splits : num_kb;
+  tiles.splits = splits > 1 ? (num_kb + tiles.kb_per - 1) / tiles.kb_per : 1;   // no empty slice
+  if (splits > 1 && tiles.splits != splits) return IMF_ERR_ARG;
+  tiles.total = tiles.n_n * tiles.n_m * (splits > 1 ? tiles.splits : batch);
   static int sms = 0;
   if (!sms) {
     int dev = 0;
@@ -393,6 +413,63 @@ extern "C" int imf_gemm_bf16(const void* A, const void* B, void* C, const float*
     IMF_GEMM_CASE(true, true, __nv_bfloat16);
   }
 #undef IMF_GEMM_CASE
+}
+
+// Split-K product for long-K / small-output shapes (weight gradients dY^T X with K = tokens):
+// slice z of `splits` equal K ranges writes plane z of `partial` ([splits][M][N] fp32); the
+// slices are summed in a fixed order by imf_splitk_reduce, so the result does not depend on
+// which CTA finishes first.  `splits` must satisfy ceil(nkb / ceil(nkb / splits)) == splits for
+// nkb = ceil(K / 64) (imf_gemm_splitk_count returns such a value).
+extern "C" int imf_gemm_splitk_count(int M, int N, int K, int target_tiles) {
+  const int tiles_mn = ((M + 127) / 128) * ((N + 127) / 128);
+  const int nkb = (K + imf::GEMM_BK - 1) / imf::GEMM_BK;
+  int want = (target_tiles + tiles_mn - 1) / tiles_mn;
+  if (want > nkb / 4) want = nkb / 4;          // at least four k-blocks per slice
+  if (want < 1) want = 1;
+  const int per = (nkb + want - 1) / want;
+  return (nkb + per - 1) / per;
+}
+
+extern "C" int imf_gemm_bf16_splitk(const void* A, const void* B, float* partial, int M, int N,
+                                    int K, int64_t lda, int64_t ldb, int a_mn, int b_mn,
+                                    int splits, int* status, void* stream) {
+  using namespace imf;
+  if (M <= 0 || N <= 0 || K <= 0 || splits < 2) return IMF_ERR_ARG;
+  if ((lda & 7) || (ldb & 7)) return IMF_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t plane = (int64_t)M * N;
+#define IMF_GEMM_CASE(AM, BM_)                                                                  \
+  return launch_gemm<128, 4, AM, BM_, float>(A, B, partial, nullptr, M, N, K, lda, ldb, N, 0,   \
+                                             1.f, 0, status, st, 1, 0, 0, plane, nullptr, 0.f,  \
+                                             splits)
+  if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false);
+  if (!a_mn && b_mn) IMF_GEMM_CASE(false, true);
+  if (a_mn && !b_mn) IMF_GEMM_CASE(true, false);
+  IMF_GEMM_CASE(true, true);
+#undef IMF_GEMM_CASE
+}
+
+namespace imf {
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, long plane,
+                                     int N, float* __restrict__ out, int64_t ldo, float alpha,
+                                     int accumulate) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= plane) return;
+  float acc = 0.f;
+  for (int z = 0; z < splits; ++z) acc += partial[z * plane + i];     // fixed order
+  float* dst = out + (i / N) * ldo + (i % N);
+  *dst = accumulate ? *dst + alpha * acc : alpha * acc;
+}
+}  // namespace imf
+
+// out[M, N] (row pitch ldo) (+)= alpha * sum_z partial[z]
+extern "C" int imf_splitk_reduce(const float* partial, int splits, int M, int N, float* out,
+                                 int64_t ldo, float alpha, int accumulate, void* stream) {
+  if (splits < 1 || M <= 0 || N <= 0) return imf::IMF_ERR_ARG;
+  const long plane = (long)M * N;
+  imf::splitk_reduce_kernel<<<(unsigned)((plane + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      partial, splits, plane, N, out, ldo, alpha, accumulate);
+  return cudaGetLastError() == cudaSuccess ? imf::IMF_OK : imf::IMF_ERR_LAUNCH;
 }
 
 // Batched form with an additive source: C[z] = alpha * op(A[z]) op(B[z])^T + beta * Cin[z].

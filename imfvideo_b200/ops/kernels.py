@@ -108,6 +108,56 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+if _has("imf_gemm_bf16_splitk"):
+    _lib.imf_gemm_splitk_count.restype = c_int
+    _lib.imf_gemm_splitk_count.argtypes = [c_int] * 4
+    _lib.imf_gemm_bf16_splitk.restype = c_int
+    _lib.imf_gemm_bf16_splitk.argtypes = [c_void_p] * 3 + [c_int] * 3 + [c_int64] * 2 + \
+        [c_int] * 3 + [c_void_p, c_void_p]
+    _lib.imf_splitk_reduce.restype = c_int
+    _lib.imf_splitk_reduce.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_float,
+                                       c_int, c_void_p]
+
+SPLITK_TARGET_TILES = 296      # two CTAs per SM on 148 SMs
+
+
+def gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+               accumulate: bool = False) -> torch.Tensor:
+    """Weight gradient ``out[n_out, n_in] (+)= dy^T x`` for ``dy`` [rows, n_out] and ``x``
+    [rows, n_in] (bf16, row-major views with 16-byte row pitch), fp32 result.
+
+    The contraction runs over the token rows, so the output is small and K is long: the K
+    range is cut into slices that run as separate tiles (split-K) and are summed in a
+    fixed order, straight into ``out`` -- with ``accumulate`` into a gradient buffer that
+    already holds other micro-batches' contributions.  Both operands are consumed as they
+    are (MN-major), no transposed copy."""
+    assert dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+    assert dy.dim() == 2 and x.dim() == 2 and dy.stride(1) == 1 and x.stride(1) == 1
+    rows, M = dy.shape
+    N = x.shape[1]
+    assert x.shape[0] == rows
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32, device=dy.device)
+        accumulate = False
+    assert out.dtype == torch.float32 and out.shape == (M, N) and out.stride(1) == 1
+    splits = int(_lib.imf_gemm_splitk_count(M, N, rows, SPLITK_TARGET_TILES))
+    st = _ptr(status_word(dy.device))
+    if splits < 2:
+        _check(_lib.imf_gemm_bf16(_ptr(dy), _ptr(x), _ptr(out), None, M, N, rows, dy.stride(0),
+                                  x.stride(0), out.stride(0), 1, 1, 1, 0, 1.0, int(accumulate),
+                                  st, _stream()), "imf_gemm_bf16 (weight gradient)")
+        LAUNCHES.count += 1
+        return out
+    part = _scratch_buf(dy.device, splits * M * N * 4, "wgrad")
+    _check(_lib.imf_gemm_bf16_splitk(_ptr(dy), _ptr(x), _ptr(part), M, N, rows, dy.stride(0),
+                                     x.stride(0), 1, 1, splits, st, _stream()),
+           "imf_gemm_bf16_splitk")
+    _check(_lib.imf_splitk_reduce(_ptr(part), splits, M, N, _ptr(out), out.stride(0), 1.0,
+                                  int(accumulate), _stream()), "imf_splitk_reduce")
+    LAUNCHES.count += 2
+    return out
+
+
 # ------------------------------------------------------------- attention ---
 if _has("imf_attn_fwd"):
     _lib.imf_attn_fwd.restype = c_int

@@ -44,6 +44,27 @@ def test_gemm(K, M, N, Kd, a_mn, b_mn):
     K.check_status()
 
 
+@pytest.mark.parametrize("rows,M,N", [(29140, 528, 256), (1000, 144, 256), (4100, 256, 682),
+                                      (333, 64, 72), (20000, 1364, 256)])
+def test_gemm_weight_gradient_splitk(K, rows, M, N):
+    """dY^T X over many token rows: split-K slices summed in a fixed order; strided operand
+    views (a band of a wider dY, the first columns of a wider X); accumulation into an
+    existing fp32 buffer; two runs give the same bits."""
+    torch.manual_seed(rows)
+    dy_full = torch.randn(rows, (M + 23) // 8 * 8, device="cuda").bfloat16()
+    x_full = torch.randn(rows, (N + 15) // 8 * 8, device="cuda").bfloat16()   # 16-byte row pitch
+    dy, x = dy_full[:, 8:8 + M], x_full[:, :N]
+    ref = dy.float().t() @ x.float()
+    out = K.gemm_wgrad(dy, x)
+    assert out.dtype == torch.float32 and _rel(out, ref) < 1e-5
+    base = torch.randn(M, N, device="cuda")
+    acc = base.clone()
+    K.gemm_wgrad(dy, x, out=acc, accumulate=True)
+    assert _rel(acc, base + ref) < 1e-5
+    assert torch.equal(K.gemm_wgrad(dy, x), out)
+    K.check_status()
+
+
 def test_gemm_rejects_bad_stride(K):
     A = torch.randn(64, 12, device="cuda").bfloat16()      # K = 12: stride not 16-byte multiple
     with pytest.raises(ValueError):

@@ -122,6 +122,43 @@ def test_fused_block_matches_generic_composition(kernels, bs, wide):
     assert set(g_f) >= set(g_g)
 
 
+def test_weight_gradients_written_straight_into_existing_grad_buffers(kernels):
+    """With fp32 ``.grad`` buffers already attached (the optimizer engine's arena views), the
+    block node accumulates dY^T X into them itself and hands autograd nothing for the
+    matrices; the result equals the autograd route and accumulates over two backward passes."""
+    from imfvideo_b200.ops.dual import Dual
+
+    net = _net(torch.bfloat16, bs=2)
+    B = 1
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(B, 16, 4, 16, 32, device="cuda", generator=g)
+    dx = torch.randn(B, 16, 4, 16, 32, device="cuda", generator=g)
+    h = torch.rand(B, device="cuda", generator=g)
+    w = 1 + torch.rand(B, device="cuda", generator=g)
+    lo, hi = torch.zeros(B, device="cuda"), torch.ones(B, device="cuda")
+    y = torch.randint(0, 1000, (B,), device="cuda")
+
+    def backward_once():
+        out = net.forward_dual(Dual(x, dx), Dual(h, torch.ones_like(h)), w, lo, hi, y)
+        (out["u"].p.square().sum() + out["v"].p.square().sum()).backward()
+
+    net.zero_grad()                       # grads None: gradients travel through autograd
+    backward_once()
+    via_autograd = {n: p.grad.clone() for n, p in net.named_parameters()}
+    for p in net.parameters():            # attached buffers: direct accumulation
+        p.grad = torch.zeros_like(p)
+    assert net.shared_blocks[0].fused_sinks().direct()
+    n0 = kernels.LAUNCHES.count
+    backward_once()
+    backward_once()
+    assert kernels.LAUNCHES.count > n0
+    kernels.check_status()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+    bad = [(n, rel(p.grad, 2 * via_autograd[n])) for n, p in net.named_parameters()
+           if via_autograd[n].norm() > 0 and rel(p.grad, 2 * via_autograd[n]) > 1e-2]
+    assert not bad, bad
+
+
 def test_qk_clip_kernel_matches_formula():
     """One-launch QK-Clip over all attention modules against the per-module formula."""
     import math
