@@ -153,7 +153,11 @@ class ParallelConfig:
     bucket_mb: float = 32.0
     # give every Muon matrix one owner rank; the others receive the update
     distributed_moonlight: bool = True
+    # what the peers' gradient contributions travel as ("bfloat16": bucketed reduce with fp32
+    # accumulation and sharded AdamW; "float32": one whole-arena fp32 reduce after backward)
     wire_dtype: str = "bfloat16"
+    # launch each block's gradient bucket on a side stream as soon as backward has produced it
+    overlap_backward: bool = True
     broadcast_init: bool = True
     # bound (seconds) of every device-side wait on another rank's flag; when it runs out the
     # kernel returns without touching data and the trainer raises at its per-step host read

@@ -64,6 +64,7 @@ class GradSinks:
 
     def __init__(self, pieces):
         self.pieces = pieces
+        self.on_backward = None       # optional callable: this block's backward has begun
 
     def direct(self) -> bool:
         for name in self.ORDER:
@@ -220,6 +221,8 @@ class _BlockFn(torch.autograd.Function):
         sn = [s.reshape(rows, d) for s in snaps]
         g_out = g_out.reshape(rows, d).contiguous()
         new = lambda *shape, dt=BF16: torch.empty(*shape, dtype=dt, device=dev)
+        if getattr(ctx, "sinks", None) is not None and ctx.sinks.on_backward is not None:
+            ctx.sinks.on_backward()
 
         # 11'. out = p2 + m * mlp_scale
         g_m, g_mscale = R.scale_add_bwd(m, m_scale, g_out, rows, d)

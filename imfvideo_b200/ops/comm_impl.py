@@ -29,6 +29,20 @@ if K._has("imf_comm_reduce"):
                                          ci, ci, vp, vp]
     _lib.imf_comm_set_wait_ns.restype = ctypes.c_ulonglong
     _lib.imf_comm_set_wait_ns.argtypes = [ctypes.c_ulonglong]
+    _lib.imf_comm_bucket_pack.restype = ci
+    _lib.imf_comm_bucket_pack.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp]
+    _lib.imf_comm_bucket_reduce.restype = ci
+    _lib.imf_comm_bucket_reduce.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp, vp]
+    _lib.imf_comm_norm_finish.restype = ci
+    _lib.imf_comm_norm_finish.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp, vp]
+    _lib.imf_comm_param_gather.restype = ci
+    _lib.imf_comm_param_gather.argtypes = [vp, vp, vp, vp, ci, ci, cl, cl, ctypes.c_float, vp, ci,
+                                           vp, vp]
+
+MAX_BUCKETS = 64
+BUCKET_BX = 8
+FLAG_INTS = 4 * 16 + MAX_BUCKETS * 16
+RANGE_DTYPE = [("start", "<i8"), ("numel", "<i8"), ("owner", "<i4"), ("pad", "<i4")]
 
 
 def set_peer_wait(seconds: float) -> float:
@@ -58,7 +72,7 @@ class PeerComm:
         self.grad_arena = symm.empty(total, dtype=torch.float32, device=device)
         self.grad_arena.zero_()
         self._hG = symm.rendezvous(self.grad_arena, group)
-        self._flags = symm.empty(self.MAX_RANKS * 4, dtype=torch.int32, device=device)
+        self._flags = symm.empty(FLAG_INTS, dtype=torch.int32, device=device)
         self._flags.zero_()
         self._hF = symm.rendezvous(self._flags, group)
         self._g_ptrs = _ptr_array(list(self._hG.buffer_ptrs))
@@ -73,6 +87,11 @@ class PeerComm:
         self._U: Optional[torch.Tensor] = None
         self._u_ptrs = None
         self.epoch = 0
+        # bucketed bf16 path (set up by ``set_buckets``)
+        self.wire: Optional[torch.Tensor] = None
+        self.param_arena: Optional[torch.Tensor] = None
+        self.bucket_step = 0
+        self.side_stream = torch.cuda.Stream(device)
         # NVLS in-switch reduction (multimem.ld_reduce) is opt-in
         self.use_multimem = (os.environ.get("IMF_B200_MULTIMEM", "0") == "1"
                              and bool(getattr(self._hG, "multicast_ptr", 0)))
@@ -130,6 +149,90 @@ class PeerComm:
                                           max_numel, float(ema_w), K._ptr(clip),
                                           int(self._U.dtype == torch.bfloat16), self._next(),
                                           self._status(), K._stream()), "imf_comm_muon_apply")
+        K.LAUNCHES.count += 1
+
+    # ------------------------------------------------------- bucketed bf16 path --
+    def make_param_arena(self) -> torch.Tensor:
+        """fp32 parameter arena in symmetric memory: after the sharded AdamW the other ranks
+        read this rank's updated shard from it."""
+        import torch.distributed._symmetric_memory as symm
+
+        self.param_arena = symm.empty(self.total, dtype=torch.float32, device=self.device)
+        self.param_arena.zero_()
+        self._hP = symm.rendezvous(self.param_arena, dist.group.WORLD)
+        self._p_ptrs = _ptr_array(list(self._hP.buffer_ptrs))
+        return self.param_arena
+
+    def set_buckets(self, buckets) -> None:
+        """``buckets``: list (one entry per bucket, same on every rank) of lists of
+        (start, numel, owner) arena ranges.  Allocates the bf16 wire arena."""
+        import numpy as np
+        import torch.distributed._symmetric_memory as symm
+
+        if len(buckets) > MAX_BUCKETS:
+            raise RuntimeError(f"at most {MAX_BUCKETS} gradient buckets")
+        self.wire = symm.empty(self.total, dtype=torch.bfloat16, device=self.device)
+        self.wire.zero_()
+        self._hW = symm.rendezvous(self.wire, dist.group.WORLD)
+        self._w_ptrs = _ptr_array(list(self._hW.buffer_ptrs))
+        rows, self._bk = [], []
+        for b in buckets:
+            self._bk.append((len(rows), len(b)))
+            rows += [(int(s), int(n), int(o), 0) for s, n, o in b]
+        host = np.array(rows, dtype=np.dtype(RANGE_DTYPE)) if rows else \
+            np.zeros(0, dtype=np.dtype(RANGE_DTYPE))
+        self._ranges = torch.from_numpy(host.view(np.uint8).reshape(-1).copy()).to(self.device)
+        self._range_bytes = np.dtype(RANGE_DTYPE).itemsize
+        self._parts = torch.zeros(max(1, len(rows)) * BUCKET_BX, dtype=torch.float64,
+                                  device=self.device)
+        self._pack_done = torch.zeros(MAX_BUCKETS, dtype=torch.int32, device=self.device)
+        self._n_parts = len(rows) * BUCKET_BX
+        torch.cuda.synchronize(self.device)
+        dist.barrier()
+
+    def begin_step(self) -> None:
+        self.bucket_step += 1
+
+    def reduce_bucket(self, b: int, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Pack + reduce bucket ``b`` of the current step on ``stream`` (default: the side
+        stream, ordered after everything queued so far on the current stream)."""
+        first, n = self._bk[b]
+        if n == 0:
+            return
+        st = stream or self.side_stream
+        if st != torch.cuda.current_stream(self.device):
+            st.wait_stream(torch.cuda.current_stream(self.device))
+        sp = vp(st.cuda_stream)
+        rng = vp(self._ranges.data_ptr() + first * self._range_bytes)
+        K._check(_lib.imf_comm_bucket_pack(self._f_ptrs, K._ptr(self.grad_arena), K._ptr(self.wire),
+                                           rng, n, self.rank, self.world, b, self.bucket_step,
+                                           vp(self._pack_done.data_ptr() + 4 * b), sp),
+                 "imf_comm_bucket_pack")
+        K._check(_lib.imf_comm_bucket_reduce(self._f_ptrs, self._w_ptrs, K._ptr(self.grad_arena),
+                                             rng, n, self.rank, self.world, b, self.bucket_step,
+                                             self._status(),
+                                             vp(self._parts.data_ptr() + 8 * first * BUCKET_BX),
+                                             sp), "imf_comm_bucket_reduce")
+        K.LAUNCHES.count += 2
+
+    def finish_norm(self) -> None:
+        """Join the side stream, publish this rank's squared-norm share, barrier."""
+        cur = torch.cuda.current_stream(self.device)
+        cur.wait_stream(self.side_stream)
+        K._check(_lib.imf_comm_norm_finish(self._f_ptrs, self._n_ptrs, K._ptr(self._parts),
+                                           self._n_parts, self.rank, self.world, self._next(),
+                                           self._status(), K._stream()), "imf_comm_norm_finish")
+        K.LAUNCHES.count += 1
+
+    def gather_params(self, P: torch.Tensor, E: Optional[torch.Tensor], ema_w: float,
+                      clip: torch.Tensor) -> None:
+        """Every rank's updated AdamW shard -> every rank's parameter arena (+ EMA)."""
+        assert P.data_ptr() == self.param_arena.data_ptr()
+        shard = self.adam_numel // self.world
+        K._check(_lib.imf_comm_param_gather(self._f_ptrs, self._p_ptrs, K._ptr(P), K._ptr(E),
+                                            self.rank, self.world, self.muon_total, shard,
+                                            float(ema_w), K._ptr(clip), self._next(),
+                                            self._status(), K._stream()), "imf_comm_param_gather")
         K.LAUNCHES.count += 1
 
     def barrier(self) -> None:

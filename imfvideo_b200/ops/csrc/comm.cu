@@ -331,3 +331,291 @@ extern "C" int imf_comm_muon_apply(void* const* u_ptrs, void* const* flag_ptrs, 
         peers, rank, world, seg_pad, p, ema, (const Seg*)segs, ema_w, clip, epoch, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ---------------------------------------------------------------------------
+// Bucketed gradient reduce-scatter with a bf16 wire format, launched bucket by
+// bucket on a side stream while the backward pass is still producing the later
+// buckets (a bucket = the parameters of one transformer block).  Two launches per
+// bucket, neither of which makes one rank's kernel wait for a kernel that another
+// rank has not launched yet for longer than the ranks' skew:
+//   pack   : this rank's fp32 gradients of the bucket that OTHER ranks own are
+//            written as bf16 into its wire arena; the last CTA to finish publishes
+//            "bucket b of step e is packed" to every peer (no waiting at all);
+//   reduce : waits (bounded) until every peer has published the bucket, then, for
+//            the ranges this rank owns: own fp32 gradient + the peers' bf16 copies,
+//            summed in rank order in fp32, times 1/W, written back in place, and
+//            the squared norm of the result as per-CTA fp64 partials.
+// finish_norm adds up all partials in a fixed order, publishes the rank's share of
+// the squared gradient norm to every rank and ends with a barrier, so the clip
+// factor is known everywhere without a collective.  AdamW then runs on this rank's
+// shard only and param_gather pulls the updated parameters (not gradients) from
+// their owners, updating the local EMA copy on the way.
+// Replaces the reference's blocking flat all-reduce after backward (reference
+// train.py:353-371) and its replicated AdamW (reference moonlight.py:439-469).
+// ---------------------------------------------------------------------------
+namespace imf {
+
+constexpr int BUCKET_FLAG_BASE = 4 * MAX_RANKS;     // flags[BASE + bucket * MAX_RANKS + rank]
+constexpr int MAX_BUCKETS = 64;
+constexpr int BUCKET_BX = 8;                        // CTAs per range
+
+struct Range {       // one contiguous piece of the arena with a single owner
+  long start;
+  long numel;
+  int owner;
+  int pad;
+};
+
+__device__ __forceinline__ uint2 pack4_bf16(float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a);
+  u.y = *reinterpret_cast<uint32_t*>(&b);
+  return u;
+}
+
+__global__ void __launch_bounds__(256)
+comm_bucket_pack_kernel(const CommPeers peers, const float* __restrict__ g,
+                        __nv_bfloat16* __restrict__ wire, const Range* __restrict__ ranges,
+                        int rank, int world, int bucket, int epoch, unsigned int* done) {
+  const Range r = ranges[blockIdx.y];
+  if (r.owner != rank) {
+    if (((r.start | r.numel) & 3) == 0) {
+      for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < r.numel;
+           i += (long)gridDim.x * blockDim.x * 4)
+        *reinterpret_cast<uint2*>(wire + r.start + i) =
+            pack4_bf16(*reinterpret_cast<const float4*>(g + r.start + i));
+    } else {
+      for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < r.numel;
+           i += (long)gridDim.x * blockDim.x)
+        wire[r.start + i] = __float2bfloat16_rn(g[r.start + i]);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int total = gridDim.x * gridDim.y;
+    if (atomicAdd(done, 1u) == total - 1) {          // every CTA's stores are fenced
+      *done = 0u;
+      __threadfence_system();
+      for (int q = 0; q < world; ++q)
+        if (q != rank)
+          st_release_sys(peers.flags[q] + BUCKET_FLAG_BASE + bucket * MAX_RANKS + rank, epoch);
+    }
+  }
+}
+
+struct WirePeers {
+  const __nv_bfloat16* wire[MAX_RANKS];
+};
+
+__global__ void __launch_bounds__(256)
+comm_bucket_reduce_kernel(const CommPeers peers, const WirePeers wp, float* __restrict__ g,
+                          const Range* __restrict__ ranges, int rank, int world, int bucket,
+                          int epoch, int* status, double* __restrict__ part) {
+  const Range r = ranges[blockIdx.y];
+  double ss = 0.0;
+  __shared__ int s_ok;
+  if (r.owner == rank) {
+    if (threadIdx.x == 0) {
+      int ok = 1;
+      const unsigned long long t0 = gtime();
+      const int* mine = peers.flags[rank] + BUCKET_FLAG_BASE + bucket * MAX_RANKS;
+      for (int q = 0; q < world && ok; ++q) {
+        if (q == rank) continue;
+        while (ld_acquire_sys(mine + q) < epoch) {
+          if (gtime() - t0 > peers.wait_ns) {
+            ok = 0;
+            if (status) atomicCAS(status, 0, 6);
+            break;
+          }
+        }
+      }
+      s_ok = ok;
+    }
+    __syncthreads();
+    if (s_ok) {
+      const float inv = 1.f / world;
+      if (((r.start | r.numel) & 3) == 0) {
+        for (long i = ((long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < r.numel;
+             i += (long)gridDim.x * blockDim.x * 4) {
+          const long j = r.start + i;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int q = 0; q < world; ++q) {            // rank order: same bits on every run
+            float4 v;
+            if (q == rank) {
+              v = *reinterpret_cast<const float4*>(g + j);
+            } else {
+              const uint2 u = *reinterpret_cast<const uint2*>(wp.wire[q] + j);
+              v.x = __uint_as_float(u.x << 16); v.y = __uint_as_float(u.x & 0xffff0000u);
+              v.z = __uint_as_float(u.y << 16); v.w = __uint_as_float(u.y & 0xffff0000u);
+            }
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+          acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+          *reinterpret_cast<float4*>(g + j) = acc;
+          ss += (double)acc.x * acc.x + (double)acc.y * acc.y + (double)acc.z * acc.z +
+                (double)acc.w * acc.w;
+        }
+      } else {
+        for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < r.numel;
+             i += (long)gridDim.x * blockDim.x) {
+          const long j = r.start + i;
+          float acc = 0.f;
+          for (int q = 0; q < world; ++q)
+            acc += q == rank ? g[j] : __bfloat162float(wp.wire[q][j]);
+          acc *= inv;
+          g[j] = acc;
+          ss += (double)acc * acc;
+        }
+      }
+    }
+  }
+  // per-CTA partial of the squared norm (zero for ranges of other owners), fixed order
+  __shared__ double s_part[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double b = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) b += s_part[w];
+    part[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = b;
+  }
+}
+
+// One CTA: total = sum of `n` partials in a fixed order; publish to slot `rank` of every rank's
+// norm array; barrier, after which every rank's slot array is complete.
+__global__ void __launch_bounds__(256)
+comm_norm_finish_kernel(const CommPeers peers, const NormOut nrm, const double* __restrict__ part,
+                        int n, int rank, int world, int epoch, int* status) {
+  __shared__ double s_sum[256];
+  double acc = 0.0;
+  for (int i = threadIdx.x; i < n; i += 256) acc += part[i];
+  s_sum[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) s_sum[threadIdx.x] += s_sum[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    for (int q = 0; q < world; ++q) nrm.slots[q][rank] = s_sum[0];
+    __threadfence_system();
+  }
+  __syncthreads();
+  peer_barrier(peers, rank, world, epoch, status);
+}
+
+struct ParamPeers {
+  const float* p[MAX_RANKS];
+};
+
+// Pull the AdamW shard of every other rank from that rank's parameter arena (it holds the
+// updated values), and fold them into the local EMA copy.
+__global__ void __launch_bounds__(512)
+comm_param_gather_kernel(const CommPeers peers, const ParamPeers pp, float* __restrict__ p,
+                         float* __restrict__ ema, int rank, int world, long base, long shard,
+                         float ema_w, const float* __restrict__ clip, int epoch, int* status) {
+  if (!peer_barrier(peers, rank, world, epoch, status)) return;
+  if (clip && clip[1] != 0.f) return;       // skipped step: nothing changed anywhere
+  const long nv = shard / 4;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nv * (world - 1);
+       i += (long)gridDim.x * blockDim.x) {
+    int q = (int)(i / nv);
+    if (q >= rank) ++q;
+    const long off = base + (long)q * shard + (i % nv) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(pp.p[q] + off);
+    *reinterpret_cast<float4*>(p + off) = v;
+    if (ema) {
+      float4 e = *reinterpret_cast<float4*>(ema + off);
+      e.x += ema_w * (v.x - e.x); e.y += ema_w * (v.y - e.y);
+      e.z += ema_w * (v.z - e.z); e.w += ema_w * (v.w - e.w);
+      *reinterpret_cast<float4*>(ema + off) = e;
+    }
+  }
+}
+
+}  // namespace imf
+
+// Pack bucket `bucket` (device table `ranges`, `nranges` entries) of this rank's gradients `g`
+// into its bf16 wire arena and publish it.  `done`: local zeroed counter.  No waits.
+extern "C" int imf_comm_bucket_pack(void* const* flag_ptrs, const float* g, void* wire,
+                                    const void* ranges, int nranges, int rank, int world,
+                                    int bucket, int epoch, unsigned int* done, void* stream) {
+  if (nranges <= 0) return 0;
+  if (bucket < 0 || bucket >= MAX_BUCKETS || world < 1 || world > MAX_RANKS) return -1;
+  CommPeers p;
+  for (int q = 0; q < MAX_RANKS; ++q) {
+    p.arena[q] = nullptr;
+    p.flags[q] = q < world ? static_cast<int*>(flag_ptrs[q]) : nullptr;
+  }
+  p.wait_ns = g_peer_wait_ns;
+  comm_bucket_pack_kernel<<<dim3(BUCKET_BX, nranges), 256, 0, (cudaStream_t)stream>>>(
+      p, g, static_cast<__nv_bfloat16*>(wire), static_cast<const Range*>(ranges), rank, world,
+      bucket, epoch, done);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Reduce the ranges of bucket `bucket` that this rank owns: g (fp32, in place) = mean over ranks
+// of own fp32 + peers' bf16 wire copies.  part: fp64[nranges * 8] partial squared norms.
+extern "C" int imf_comm_bucket_reduce(void* const* flag_ptrs, void* const* wire_ptrs, float* g,
+                                      const void* ranges, int nranges, int rank, int world,
+                                      int bucket, int epoch, int* status, double* part,
+                                      void* stream) {
+  if (nranges <= 0) return 0;
+  if (bucket < 0 || bucket >= MAX_BUCKETS || world < 1 || world > MAX_RANKS) return -1;
+  CommPeers p;
+  WirePeers wp;
+  for (int q = 0; q < MAX_RANKS; ++q) {
+    p.arena[q] = nullptr;
+    p.flags[q] = q < world ? static_cast<int*>(flag_ptrs[q]) : nullptr;
+    wp.wire[q] = q < world ? static_cast<const __nv_bfloat16*>(wire_ptrs[q]) : nullptr;
+  }
+  p.wait_ns = g_peer_wait_ns;
+  comm_bucket_reduce_kernel<<<dim3(BUCKET_BX, nranges), 256, 0, (cudaStream_t)stream>>>(
+      p, wp, g, static_cast<const Range*>(ranges), rank, world, bucket, epoch, status, part);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Sum `n` fp64 partials, publish to slot `rank` of every rank's norm array, barrier.
+extern "C" int imf_comm_norm_finish(void* const* flag_ptrs, void* const* norm_ptrs,
+                                    const double* part, int n, int rank, int world, int epoch,
+                                    int* status, void* stream) {
+  if (world < 1 || world > MAX_RANKS || n < 0) return -1;
+  CommPeers p;
+  NormOut nrm;
+  nrm.part = nullptr;
+  nrm.done = nullptr;
+  for (int q = 0; q < MAX_RANKS; ++q) {
+    p.arena[q] = nullptr;
+    p.flags[q] = q < world ? static_cast<int*>(flag_ptrs[q]) : nullptr;
+    nrm.slots[q] = q < world ? static_cast<double*>(norm_ptrs[q]) : nullptr;
+  }
+  p.wait_ns = g_peer_wait_ns;
+  comm_norm_finish_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(p, nrm, part, n, rank, world,
+                                                              epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// All-gather of updated parameters: shard q ([base + q * shard, + shard), shard % 4 == 0) is read
+// from rank q's parameter arena into the local one; ema (optional) follows with weight ema_w.
+extern "C" int imf_comm_param_gather(void* const* flag_ptrs, void* const* param_ptrs, float* p,
+                                     float* ema, int rank, int world, long base, long shard,
+                                     float ema_w, const float* clip, int epoch, int* status,
+                                     void* stream) {
+  if (world < 1 || world > MAX_RANKS || (shard & 3) || (base & 3)) return -1;
+  CommPeers peers;
+  ParamPeers pp;
+  for (int q = 0; q < MAX_RANKS; ++q) {
+    peers.arena[q] = nullptr;
+    peers.flags[q] = q < world ? static_cast<int*>(flag_ptrs[q]) : nullptr;
+    pp.p[q] = q < world ? static_cast<const float*>(param_ptrs[q]) : nullptr;
+  }
+  peers.wait_ns = g_peer_wait_ns;
+  long blocks = (shard / 4 * (world - 1) + 511) / 512;
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  if (blocks < 1) blocks = 1;
+  comm_param_gather_kernel<<<(unsigned)blocks, 512, 0, (cudaStream_t)stream>>>(
+      peers, pp, p, ema, rank, world, base, shard, ema_w, clip, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}

@@ -16,9 +16,12 @@ matrices are sorted by shape so every shape is one contiguous (k, n, m) batch
 for Newton-Schulz.  The AdamW slice is padded to a multiple of 256 * W.
 
 Per step:
-  * gradient mean: Muon segment r is reduced onto rank r only, the AdamW
-    slice on every rank (own peer-memory kernels when available, else NCCL /
-    gloo on the same contiguous slices);
+  * gradient mean: Muon segment r is reduced onto rank r only, AdamW shard r
+    likewise.  With peer memory this happens bucket by bucket (one bucket per
+    transformer block) on a side stream while backward is still running, peers'
+    contributions travel as bf16 and are summed in fp32; AdamW then runs on the
+    shard and the updated parameters are gathered.  Without peer memory: NCCL /
+    gloo on the same contiguous slices, AdamW replicated;
   * global norm -> device-side clip factor and skip flag (no host sync);
   * owner: momentum + batched Newton-Schulz on its segment; update all-gather;
     every rank applies ``p <- p (1 - lr wd) - lr s Phi`` (+ EMA) to all Muon
@@ -59,8 +62,14 @@ class FlatEngine(GradSync):
 
     def __init__(self, optimizer: Moonlight, net: torch.nn.Module, ema: Optional[torch.nn.Module],
                  rank: int, world: int, ema_decay: float = 0.0, mode: str = "fused_p2p",
-                 ns_cuda_graph: bool = False):
+                 ns_cuda_graph: bool = False, wire_dtype: str = "bfloat16",
+                 overlap: bool = True):
         self.opt, self.net, self.ema = optimizer, net, ema
+        self.wire_dtype, self.overlap = wire_dtype, bool(overlap)
+        self.bucketed = False          # bucketed bf16 reduce + sharded AdamW (needs peer memory)
+        self.armed = True              # False during all but the last micro-batch of a step
+        self._launched: set = set()
+        self._last_started: Optional[int] = None
         self.ns_cuda_graph = bool(ns_cuda_graph)
         self._ns_graph, self._ns_graph_launches, self._ns_eager_steps = None, 0, 0
         self.rank, self.world, self.mode = rank, world, mode
@@ -102,12 +111,13 @@ class FlatEngine(GradSync):
         self.total = self.muon_total + self.adam_numel
         # ---- arenas ---------------------------------------------------------
         z = lambda n, dt=torch.float32: torch.zeros(n, dtype=dt, device=dev)
-        self.P = z(self.total)
         self.comm = None
         if world > 1 and mode == "fused_p2p" and self.cuda:
             from ..ops import comm as comm_mod
 
             self.comm = comm_mod.try_create(world, rank, dev, self.total, self.seg_pad)
+        self.bucketed = self.comm is not None and wire_dtype in ("bfloat16", "bf16")
+        self.P = self.comm.make_param_arena() if self.bucketed else z(self.total)
         self.G = self.comm.grad_arena if self.comm is not None else z(self.total)
         self.E = z(self.total) if ema is not None else None
         self.M = z(self.muon_total)                       # momentum (own segment is live)
@@ -150,6 +160,66 @@ class FlatEngine(GradSync):
                     self._bind()
         optimizer.distributed = self
         self.skipped_last = False
+        self.buckets = self._build_buckets()
+        if self.bucketed:
+            self.comm.set_buckets(self.buckets)
+
+    # -------------------------------------------------------------- buckets ---
+    def _blocks(self):
+        net = self.net
+        return [b for name in ("shared_blocks", "u_heads", "v_heads")
+                for b in getattr(net, name, [])]
+
+    def _build_buckets(self):
+        """One gradient bucket per transformer block (in forward order; backward finishes
+        them in reverse) plus one for everything else.  A bucket is a list of arena ranges
+        (start, numel, owner): a Muon matrix belongs to its owner rank, an AdamW range to
+        the rank whose shard of the AdamW slice it falls in (ranges are cut at shard
+        boundaries).  Every rank builds the same table."""
+        blocks = self._blocks()
+        bucket_of = {}
+        for bi, blk in enumerate(blocks):
+            for p in blk.parameters():
+                bucket_of[id(p)] = bi
+        nb = len(blocks) + 1
+        buckets = [[] for _ in range(nb)]
+        for i, (_, p) in enumerate(self.muon):
+            buckets[bucket_of.get(id(p), nb - 1)].append(
+                (self.muon_off[i], p.numel(), self.owner[i]))
+        shard = self.adam_numel // self.world
+        for i, (_, p) in enumerate(self.adam):
+            lo, hi = self.adam_off[i], self.adam_off[i] + p.numel()
+            while lo < hi:
+                q = (lo - self.muon_total) // shard
+                cut = min(hi, self.muon_total + (q + 1) * shard)
+                buckets[bucket_of.get(id(p), nb - 1)].append((lo, cut - lo, int(q)))
+                lo = cut
+        if self.bucketed and self.overlap:
+            from functools import partial
+
+            for bi, blk in enumerate(blocks):
+                if hasattr(blk, "fused_sinks"):
+                    blk.fused_sinks().on_backward = partial(self._block_backward_started, bi)
+        return buckets
+
+    def _block_backward_started(self, bi: int) -> None:
+        """Called by block ``bi``'s autograd node when its backward begins: the block whose
+        backward ran before it has all its gradients in the arena by now (leaf accumulation
+        runs before any other ready node), so its bucket goes out on the side stream while
+        this block's backward computes."""
+        if not (self.armed and self.bucketed):
+            return
+        prev, self._last_started = self._last_started, bi
+        if prev is not None and prev != bi:
+            self._launch_bucket(prev)
+
+    def _launch_bucket(self, b: int) -> None:
+        if b in self._launched:
+            return
+        if not self._launched:
+            self.comm.begin_step()
+        self._launched.add(b)
+        self.comm.reduce_bucket(b)
 
     # ------------------------------------------------------------- set-up ---
     def _repoint(self, name_of, ema_of) -> None:
@@ -218,6 +288,15 @@ class FlatEngine(GradSync):
         self._check_grad_views()
         w = self.world
         if w == 1:
+            return
+        if self.bucketed:
+            # whatever the backward pass has not sent yet (at least the last block and the
+            # non-block parameters), then this rank's share of the squared norm + barrier
+            for b in range(len(self.buckets)):
+                self._launch_bucket(b)
+            self.comm.finish_norm()
+            self._launched.clear()
+            self._last_started = None
             return
         if self.comm is not None:
             self.comm.reduce_grads()            # own kernels: Muon segment -> owner, AdamW -> all
@@ -348,14 +427,21 @@ class FlatEngine(GradSync):
             # so it stays exact even if the host never learns that a step was skipped
             self.tcount += 1.0 - skip
             if use_k:
+                lo = hi = 0
+                if self.bucketed:       # this rank's shard only; the others' arrive by gather
+                    shard = self.adam_numel // self.world
+                    lo = self.muon_total + r * shard
+                    hi = lo + shard
                 self._K._check(self._lib.imf_adamw(
                     self.P.data_ptr(), self.G.data_ptr(), self.A1.data_ptr(), self.A2.data_ptr(),
                     self.E.data_ptr() if self.E is not None else None,
                     self._adam_seg_dev.data_ptr(), len(self.adam), self._max_adam,
                     self.muon_total, float(b1), float(b2), float(eps), 1.0, 1.0,
-                    self.clip.data_ptr(), float(self.ema_w), self.tcount.data_ptr(), 0, 0,
+                    self.clip.data_ptr(), float(self.ema_w), self.tcount.data_ptr(), lo, hi,
                     stream), "imf_adamw")
                 self._K.LAUNCHES.count += 1
+                if self.bucketed:
+                    self.comm.gather_params(self.P, self.E, float(self.ema_w), self.clip)
             else:
                 keep = skip.bool()
                 t = self.tcount.double().clamp_min(1.0)
@@ -460,6 +546,14 @@ class FlatEngine(GradSync):
         dist.all_gather(parts, own)
         for q, part in enumerate(parts):
             self.M[q * self.seg_pad:(q + 1) * self.seg_pad].copy_(part)
+        if self.bucketed:               # AdamW moments live on the shard owners
+            shard = self.adam_numel // self.world
+            for arena in (self.A1, self.A2):
+                own = arena[self.rank * shard:(self.rank + 1) * shard].clone()
+                parts = [torch.empty_like(own) for _ in range(self.world)]
+                dist.all_gather(parts, own)
+                for q, part in enumerate(parts):
+                    arena[q * shard:(q + 1) * shard].copy_(part)
 
     @torch.no_grad()
     def after_load(self) -> None:
@@ -477,6 +571,15 @@ class FlatEngine(GradSync):
 
 
 def attach_engine(trainer, mode: str) -> FlatEngine:
+    par = trainer.cfg.parallel
+    if trainer.world > 1 and trainer.device.type == "cuda":
+        try:
+            from ..ops.comm_impl import set_peer_wait
+
+            set_peer_wait(float(par.peer_wait_s))
+        except Exception:
+            pass
     return FlatEngine(trainer.optimizer, trainer.net, trainer.ema, trainer.rank, trainer.world,
                       trainer.cfg.run.ema_decay, mode,
-                      ns_cuda_graph=getattr(trainer.cfg.optim, "ns_cuda_graph", False))
+                      ns_cuda_graph=getattr(trainer.cfg.optim, "ns_cuda_graph", False),
+                      wire_dtype=par.wire_dtype, overlap=par.overlap_backward)

@@ -407,7 +407,10 @@ class Trainer:
         (latents, labels) micro-batches for grad_accum > 1."""
         micro = list(batches) if batches is not None else [(latents, labels)]
         losses, parts = [], {}
-        for lat, lab in micro:
+        for i, (lat, lab) in enumerate(micro):
+            if hasattr(self.grad_sync, "armed"):
+                # gradient buckets may leave for their owners during the LAST backward only
+                self.grad_sync.armed = i == len(micro) - 1
             loss, parts = self.micro_step(lat, lab)
             losses.append(loss)
         stats = self.optimizer_step()

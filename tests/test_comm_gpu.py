@@ -169,3 +169,84 @@ def test_bounded_wait_runs_out_and_context_survives(C):
         assert int(flags[1][0].item()) == 3        # rank 0's signal reached the peer's array
     finally:
         C.set_peer_wait(old)
+
+
+def test_bucketed_bf16_reduce_norm_and_param_gather_virtual_ranks(C):
+    """The bucket path end to end on one GPU: pack (publishes the bucket), reduce (own fp32 +
+    peers' bf16, rank order), norm finish, sharded parameters gathered with EMA."""
+    import numpy as np
+
+    K = C.K
+    W, total = 4, 8192
+    g = torch.Generator(device="cuda").manual_seed(7)
+    G = [torch.randn(total, device="cuda", generator=g) for _ in range(W)]
+    G0 = [x.clone() for x in G]
+    wire = [torch.zeros(total, dtype=torch.bfloat16, device="cuda") for _ in range(W)]
+    flags = [torch.zeros(C.FLAG_INTS, dtype=torch.int32, device="cuda") for _ in range(W)]
+    # two buckets; ranges with every owner, one of odd length and odd start (scalar path)
+    buckets = [[(0, 1024, 0), (1024, 1000, 1), (2024, 1001, 2), (3025, 71, 3)],
+               [(4096, 2048, 3), (6144, 1024, 0), (7168, 1024, 1)]]
+    rows = [(s, n, o, 0) for b in buckets for s, n, o in b]
+    table = torch.from_numpy(np.array(rows, dtype=np.dtype(C.RANGE_DTYPE)).view(np.uint8)
+                             .reshape(-1).copy()).cuda()
+    rb = np.dtype(C.RANGE_DTYPE).itemsize
+    parts = [torch.zeros(len(rows) * C.BUCKET_BX, dtype=torch.float64, device="cuda")
+             for _ in range(W)]
+    done = torch.zeros(C.MAX_BUCKETS, dtype=torch.int32, device="cuda")
+    status = K.status_word(torch.device("cuda", 0))
+    fp, wp = _ptrs(flags), _ptrs(wire)
+    vp = ctypes.c_void_p
+    first = 0
+    for b, bk in enumerate(buckets):
+        rng = vp(table.data_ptr() + first * rb)
+        for r in range(W):          # every rank packs (and publishes) before any rank reduces
+            K._check(C._lib.imf_comm_bucket_pack(fp, K._ptr(G[r]), K._ptr(wire[r]), rng, len(bk), r,
+                                                 W, b, 1, vp(done.data_ptr() + 4 * b), K._stream()),
+                     "pack")
+        for r in range(W):
+            K._check(C._lib.imf_comm_bucket_reduce(
+                fp, wp, K._ptr(G[r]), rng, len(bk), r, W, b, 1, K._ptr(status),
+                vp(parts[r].data_ptr() + 8 * first * C.BUCKET_BX), K._stream()), "reduce")
+        first += len(bk)
+    sq = [0.0] * W
+    for s, n, o in [x for b in buckets for x in b]:
+        want = G0[o][s:s + n].clone()
+        for q in range(W):
+            if q != o:
+                want += G0[q][s:s + n].bfloat16().float()
+        want /= W
+        assert torch.allclose(G[o][s:s + n], want, atol=1e-6), (s, n, o)
+        for q in range(W):          # the other ranks' copies of the range are untouched
+            if q != o:
+                assert torch.equal(G[q][s:s + n], G0[q][s:s + n])
+        sq[o] += float(G[o][s:s + n].double().pow(2).sum())     # of what the kernel wrote
+    norms = [torch.zeros(MAXR, dtype=torch.float64, device="cuda") for _ in range(W)]
+    _preset(flags, W, 1)
+    for r in range(W):
+        K._check(C._lib.imf_comm_norm_finish(fp, _ptrs(norms), K._ptr(parts[r]), len(rows) * C.BUCKET_BX,
+                                             r, W, 1, K._ptr(status), K._stream()), "norm_finish")
+    for r in range(W):
+        for q in range(W):
+            assert abs(float(norms[r][q]) - sq[q]) < 1e-9 * max(1.0, sq[q])
+    # sharded parameters: rank q's shard of the AdamW slice is authoritative on rank q
+    base, shard, ema_w = 4096, 1024, 0.25
+    P = [torch.randn(total, device="cuda", generator=g) for _ in range(W)]
+    E0 = torch.randn(total, device="cuda", generator=g)
+    truth = P[0].clone()
+    for q in range(W):
+        truth[base + q * shard: base + (q + 1) * shard] = P[q][base + q * shard: base + (q + 1) * shard]
+    clip = torch.tensor([1.0, 0.0], device="cuda")
+    _preset(flags, W, 2)
+    for r in range(W):
+        Pr, Er = P[r].clone(), E0.clone()
+        ptrs = _ptrs([Pr if q == r else P[q] for q in range(W)])
+        K._check(C._lib.imf_comm_param_gather(fp, ptrs, K._ptr(Pr), K._ptr(Er), r, W, base, shard,
+                                              ema_w, K._ptr(clip), 2, K._ptr(status), K._stream()),
+                 "param_gather")
+        assert torch.equal(Pr[base:], truth[base:]) and torch.equal(Pr[:base], P[r][:base])
+        own = slice(base + r * shard, base + (r + 1) * shard)
+        want_e = E0 + ema_w * (truth - E0)
+        want_e[:base] = E0[:base]
+        want_e[own] = E0[own]                   # the owner's EMA is updated by its AdamW kernel
+        assert torch.allclose(Er, want_e, atol=1e-7)
+    K.check_status()
