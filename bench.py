@@ -177,6 +177,7 @@ def run_ours(args):
 
     for i in range(args.warmup):
         step_device(i)
+    trainer.timer.summary()          # drop the warm-up phases (no-op unless run.profile_phases)
     _barrier_sync(device)
     sampler = ClockSampler(local_rank).start() if device.type == "cuda" and rank == 0 else None
     n0 = launches.count if launches is not None else 0
@@ -195,6 +196,12 @@ def run_ours(args):
     n_launch = (launches.count - n0) if launches is not None else 0
     clocks = sampler.stop() if sampler is not None else None
     ms = _max_over_ranks(ms, device)
+    phases = None
+    if cfg.run.profile_phases:       # per-phase device time per step, maximum over ranks
+        from imfvideo_b200.utils.timers import PhaseTimer
+
+        phases = {k: v / args.steps
+                  for k, v in PhaseTimer.reduce_max(trainer.timer.summary()).items()}
     if device.type == "cuda":
         from imfvideo_b200.ops import kernels
 
@@ -236,6 +243,8 @@ def run_ours(args):
                     "loss": last.get("loss")},
             "gpu_launches": n_launch,
         }
+        if phases is not None:
+            out["phases_ms_max_over_ranks"] = phases
         print(json.dumps(out), flush=True)
     pdist.shutdown()
 

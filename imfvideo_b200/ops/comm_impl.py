@@ -39,6 +39,9 @@ if K._has("imf_comm_reduce"):
     _lib.imf_comm_param_gather.argtypes = [vp, vp, vp, vp, ci, ci, cl, cl, ctypes.c_float, vp, ci,
                                            vp, vp]
 
+    _lib.imf_comm_max.restype = ci
+    _lib.imf_comm_max.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp, vp]
+
 MAX_BUCKETS = 64
 BUCKET_BX = 8
 FLAG_INTS = 4 * 16 + MAX_BUCKETS * 16
@@ -234,6 +237,29 @@ class PeerComm:
                                             float(ema_w), K._ptr(clip), self._next(),
                                             self._status(), K._stream()), "imf_comm_param_gather")
         K.LAUNCHES.count += 1
+
+    MAX_STATS = 4096
+
+    def max_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Element-wise maximum over ranks of a small fp32 tensor, by this library's kernel
+        over peer memory (no NCCL, no host read).  Returns a new tensor of x's shape."""
+        n = x.numel()
+        if n > self.MAX_STATS:
+            raise ValueError(f"max_reduce holds at most {self.MAX_STATS} values")
+        if getattr(self, "_stat_in", None) is None:
+            import torch.distributed._symmetric_memory as symm
+
+            self._stat_in = symm.empty(self.MAX_STATS, dtype=torch.float32, device=self.device)
+            self._stat_in.zero_()
+            self._hS = symm.rendezvous(self._stat_in, dist.group.WORLD)
+            self._s_ptrs = _ptr_array(list(self._hS.buffer_ptrs))
+        self._stat_in[:n].copy_(x.reshape(-1).float())
+        out = torch.empty(n, dtype=torch.float32, device=self.device)
+        K._check(_lib.imf_comm_max(self._s_ptrs, self._f_ptrs, K._ptr(out), n, self.rank,
+                                   self.world, self._next(), self._status(), K._stream()),
+                 "imf_comm_max")
+        K.LAUNCHES.count += 1
+        return out.view(x.shape)
 
     def barrier(self) -> None:
         K._check(_lib.imf_comm_barrier(self._g_ptrs, self._f_ptrs, self.rank, self.world,

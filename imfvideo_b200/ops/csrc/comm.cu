@@ -619,3 +619,36 @@ extern "C" int imf_comm_param_gather(void* const* flag_ptrs, void* const* param_
       peers, pp, p, ema, rank, world, base, shard, ema_w, clip, epoch, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ---------------------------------------------------------------------------
+// Element-wise MAX over ranks of a small fp32 vector (the per-head logit maxima of
+// every attention module, for QK-clip): every rank reads every rank's copy over
+// peer memory after a barrier and writes the maximum to a LOCAL output, so no rank
+// overwrites what another is still reading.  One launch, no host read.  Replaces
+// the per-module all_reduce(MAX) of the reference (reference train.py:336).
+// ---------------------------------------------------------------------------
+namespace imf {
+__global__ void __launch_bounds__(256)
+comm_max_kernel(const CommPeers peers, float* __restrict__ out, int n, int rank, int world,
+                int epoch, int* status) {
+  if (!peer_barrier(peers, rank, world, epoch, status)) return;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    float m = peers.arena[0][i];
+    for (int q = 1; q < world; ++q) m = fmaxf(m, peers.arena[q][i]);   // NaN-ignoring, like MAX
+    out[i] = m;
+  }
+}
+}  // namespace imf
+
+// in_ptrs: `world` peer pointers of fp32[n] buffers; out: local fp32[n].
+extern "C" int imf_comm_max(void* const* in_ptrs, void* const* flag_ptrs, float* out, int n,
+                            int rank, int world, int epoch, int* status, void* stream) {
+  if (n <= 0) return 0;
+  CommPeers p;
+  if (fill(p, in_ptrs, flag_ptrs, world)) return -1;
+  int blocks = (n + 255) / 256;
+  if (blocks > 64) blocks = 64;
+  comm_max_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p, out, n, rank, world, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+

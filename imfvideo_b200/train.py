@@ -152,7 +152,7 @@ def lr_at(step: int, cfg: Optional[Config] = None) -> float:
 
 @torch.no_grad()
 def qk_clip(net, tau: float, world: int = 1, skip: Optional[torch.Tensor] = None,
-            ema=None, ema_w: float = 0.0, as_tensors: bool = False):
+            ema=None, ema_w: float = 0.0, as_tensors: bool = False, max_reduce=None):
     """MuonClip: heads whose max logit exceeded ``tau`` (nats) get the rope
     rows of ``q_b_proj`` scaled by tau / S_max.  All modules' per-head stats
     are reduced in ONE batched MAX all-reduce (the reference does an
@@ -165,6 +165,9 @@ def qk_clip(net, tau: float, world: int = 1, skip: Optional[torch.Tensor] = None
     optimizer already folded the un-clipped weights into the EMA model (fused
     update kernels), the clipped rows of the EMA copy are corrected so the result
     equals the reference order step -> clip -> EMA.
+
+    ``max_reduce``: callable doing the element-wise MAX over ranks (the peer-memory
+    kernel of the optimizer engine); default ``torch.distributed.all_reduce``.
 
     Returns (#clipped heads, global max logit) as Python numbers, or as two
     device scalars with ``as_tensors`` (no host read)."""
@@ -180,7 +183,10 @@ def qk_clip(net, tau: float, world: int = 1, skip: Optional[torch.Tensor] = None
     mods = [m for _, m in mods]
     stats = torch.stack([m.attn_impl.logit_max_log2.float() for m in mods])   # (n, H)
     if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        if max_reduce is not None:
+            stats = max_reduce(stats)
+        else:
+            dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     fused = _qk_clip_kernel(mods, emas, stats, tau, skip, ema_w)
     if fused is not None:
         n_hot, s_max = fused
@@ -359,8 +365,10 @@ class Trainer:
                 skipped = eng.clip[1]
                 # the fused update kernels have already folded the new weights into the
                 # EMA; the clip corrects the EMA rows it rescales and honours the skip flag
+                comm = getattr(eng, "comm", None)
                 n_hot, s_max = qk_clip(self.net, o.qk_clip_tau, self.world, skip=eng.clip,
-                                       ema=self.ema, ema_w=eng.ema_w, as_tensors=True)
+                                       ema=self.ema, ema_w=eng.ema_w, as_tensors=True,
+                                       max_reduce=comm.max_reduce if comm is not None else None)
             else:
                 finite = bool(torch.isfinite(grad_norm))
                 skipped = torch.tensor(float(not finite))

@@ -250,3 +250,21 @@ def test_bucketed_bf16_reduce_norm_and_param_gather_virtual_ranks(C):
         want_e[own] = E0[own]                   # the owner's EMA is updated by its AdamW kernel
         assert torch.allclose(Er, want_e, atol=1e-7)
     K.check_status()
+
+
+def test_max_reduce_virtual_ranks(C):
+    K = C.K
+    W, n = 4, 300
+    g = torch.Generator(device="cuda").manual_seed(9)
+    ins = [torch.randn(n, device="cuda", generator=g) for _ in range(W)]
+    ins[2][5] = float("nan")                      # MAX ignores a NaN when another rank is finite
+    flags = [torch.zeros(C.FLAG_INTS, dtype=torch.int32, device="cuda") for _ in range(W)]
+    status = K.status_word(torch.device("cuda", 0))
+    _preset(flags, W, 1)
+    want = torch.stack([torch.nan_to_num(x, nan=float("-inf")) for x in ins]).amax(0)
+    for r in range(W):
+        out = torch.empty(n, device="cuda")
+        K._check(C._lib.imf_comm_max(_ptrs(ins), _ptrs(flags), K._ptr(out), n, r, W, 1,
+                                     K._ptr(status), K._stream()), "max")
+        assert torch.equal(out, want)
+    K.check_status()

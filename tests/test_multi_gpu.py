@@ -21,9 +21,14 @@ from imfvideo_b200.parallel import dist as pdist
 from imfvideo_b200.train import Trainer
 mode = sys.argv[1]
 rank, world, local, device = pdist.init_distributed(timeout_s=120)
-cfg = preset("d256")
+sla2 = mode.endswith("_sla2")
+mode = mode[:-5] if sla2 else mode
+cfg = preset("d256_sla2" if sla2 else "d256")
 cfg.model.depth, cfg.model.aux_head_depth = 3, 1
-cfg.data.latent_frames, cfg.data.latent_size = 4, (16, 32)
+cfg.data.latent_frames, cfg.data.latent_size = (8, (16, 32)) if sla2 else (4, (16, 32))
+if sla2:
+    cfg.model.sla2_topk = 0.25
+    cfg.optim.qk_clip_tau = 1e-3           # every head is over the threshold: the clip runs
 cfg.optim.warmup_steps = 0
 cfg.run.ema_decay = 0.9
 cfg.parallel.grad_sync = "fused_p2p" if mode.startswith("fused_p2p") else mode
@@ -35,7 +40,7 @@ if mode.startswith("fused_p2p"):
     assert tr.grad_sync.bucketed == (mode == "fused_p2p")
 g = torch.Generator().manual_seed(10 + rank)
 for s in range(3):
-    x = torch.randn(1, 16, 4, 16, 32, generator=g)
+    x = torch.randn(1, 16, cfg.data.latent_frames, 16, 32, generator=g)
     y = torch.randint(0, 1000, (1,), generator=g)
     torch.manual_seed(100 * s + rank)
     st = tr.train_step(x, y)
@@ -48,8 +53,11 @@ dist.broadcast(ref, src=0)
 same = bool(torch.equal(flat, ref))
 if rank == 0:
     torch.save({"w": flat.cpu(), "gn": st["grad_norm"]}, sys.argv[2])
-print(f"rank {rank} replicas_identical={same} loss={st['loss']:.5f}", flush=True)
+print(f"rank {rank} replicas_identical={same} loss={st['loss']:.5f} qk={st['qk_hot']}/{st['qk_smax']:.3f}",
+      flush=True)
 assert same
+if sla2:        # the per-head maxima went through the peer-memory MAX kernel and clipped heads
+    assert st["qk_hot"] > 0 and st["qk_smax"] > 0
 pdist.shutdown()
 '''
 
@@ -81,3 +89,4 @@ def test_peer_memory_collectives_match_nccl(tmp_path):
         rel = ((a["w"] - b["w"]).norm() / b["w"].norm()).item()
         assert rel < 2e-3, (mode, rel)       # bf16 model: same update up to summation order
         assert abs(a["gn"] - b["gn"]) / b["gn"] < 2e-2, mode
+    _run("fused_p2p_sla2", str(tmp_path / "c.pt"))     # SLA2 blocks + QK-clip statistics over ranks
