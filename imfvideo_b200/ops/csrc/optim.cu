@@ -233,3 +233,67 @@ extern "C" int imf_qk_clip(const void* mods, int nmod, int max_heads, float tau_
       (const ClipMod*)mods, tau_nat, summary, clip, ema_w);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ---------------------------------------------------------------------------
+// Newton-Schulz input preparation: X[z] = bf16(G[z] / (||G[z]||_F + eps)) for a batch of
+// fp32 matrices (n x m, contiguous) into bf16 matrices with row pitch mp >= m (the pad
+// columns are zeroed), in two launches with fixed-order sums.  Replaces the norm / divide /
+// cast / pad sequence of the reference (reference moonlight.py:228-236).
+// ---------------------------------------------------------------------------
+namespace imf {
+
+constexpr int NS_CHUNKS = 32;
+
+__global__ void __launch_bounds__(256)
+ns_sumsq_kernel(const float* __restrict__ g, long numel, double* __restrict__ part) {
+  const float* src = g + (long)blockIdx.y * numel;
+  const long per = (numel + NS_CHUNKS - 1) / NS_CHUNKS;
+  const long lo = blockIdx.x * per, hi = lo + per < numel ? lo + per : numel;
+  double ss = 0.0;
+  for (long i = lo + threadIdx.x; i < hi; i += 256) {
+    const float v = src[i];
+    ss += (double)v * v;
+  }
+  __shared__ double s_part[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double b = 0.0;
+    for (int w = 0; w < 8; ++w) b += s_part[w];
+    part[blockIdx.y * NS_CHUNKS + blockIdx.x] = b;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+ns_scale_kernel(const float* __restrict__ g, __nv_bfloat16* __restrict__ x, int n, int m, int mp,
+                const double* __restrict__ part, float eps) {
+  const int z = blockIdx.y;
+  double tot = 0.0;
+  for (int c = 0; c < NS_CHUNKS; ++c) tot += part[z * NS_CHUNKS + c];    // same order everywhere
+  const float inv = 1.f / ((float)sqrt(tot) + eps);
+  const float* src = g + (long)z * n * m;
+  __nv_bfloat16* dst = x + (long)z * n * mp;
+  const long total = (long)n * mp;
+  for (long i = (long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long)gridDim.x * 256) {
+    const int r = (int)(i / mp), c = (int)(i % mp);
+    dst[i] = __float2bfloat16_rn(c < m ? src[(long)r * m + c] * inv : 0.f);
+  }
+}
+
+}  // namespace imf
+
+// g: (k, n, m) fp32 contiguous; x: (k, n, mp) bf16; part: fp64 scratch of k * 32 entries.
+extern "C" int imf_ns_prepare(const float* g, void* x, int k, int n, int m, int mp, double* part,
+                              float eps, void* stream) {
+  if (k <= 0 || n <= 0 || m <= 0 || mp < m) return -1;
+  const long numel = (long)n * m;
+  ns_sumsq_kernel<<<dim3(NS_CHUNKS, k), 256, 0, (cudaStream_t)stream>>>(g, numel, part);
+  long bx = ((long)n * mp + 255) / 256;
+  if (bx > 128) bx = 128;
+  ns_scale_kernel<<<dim3((unsigned)bx, k), 256, 0, (cudaStream_t)stream>>>(
+      g, static_cast<__nv_bfloat16*>(x), n, m, mp, part, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+

@@ -413,38 +413,76 @@ def gemm_batched(a, b, *, a_mn=False, b_mn=False, cin=None, alpha=1.0, beta=0.0,
     return out
 
 
-def newton_schulz(G: torch.Tensor, coeffs, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
+if _has("imf_ns_prepare"):
+    _lib.imf_ns_prepare.restype = c_int
+    _lib.imf_ns_prepare.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                    c_float, c_void_p]
+
+_ns_ws: Dict[Tuple[int, int, int, int], Tuple[torch.Tensor, ...]] = {}
+
+
+def _ns_workspace(dev: torch.device, k: int, n: int, mp: int, g: int):
+    """X, Y (k, n, mp), A, B (k, g, g) bf16 and the norm partials, allocated once per shape
+    batch and reused by every later step (the optimizer calls with the same shapes)."""
+    key = (dev.index or 0, k, n, mp)
+    ws = _ns_ws.get(key)
+    if ws is None:
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        ws = (torch.zeros(k, n, mp, **bf), torch.zeros(k, n, mp, **bf),
+              torch.empty(k, g, g, **bf), torch.empty(k, g, g, **bf),
+              torch.empty(k * 32, dtype=torch.float64, device=dev))
+        _ns_ws[key] = ws
+    return ws
+
+
+def newton_schulz(G: torch.Tensor, coeffs, steps: int = 5, eps: float = 1e-7,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Quintic Newton-Schulz on a batch (k, n, m) with the tcgen05 GEMM:
     per iteration A = X X^T (or X^T X when n > m), B = b A + c A A,
     X <- a X + B X (or X B), three launches for the whole batch.  The Gram
-    side is chosen by operand major flags, so no transposed copy is made."""
+    side is chosen by operand major flags, so no transposed copy is made.
+    Normalisation, cast and padding are one two-launch kernel; the iterates live in
+    a workspace kept between calls; with ``out`` (bf16 (k, n, m), m a multiple of 8)
+    the last iteration writes the result there."""
     a_, b_, c_ = coeffs
     k, n, m = G.shape
     if min(n, m) < 8 or (n > m and m % 8):
         return None                 # tiny / odd Gram side: the caller uses the torch path
     mp = (m + 7) // 8 * 8
-    Gf = G.float()
-    nrm = Gf.flatten(1).norm(dim=1).view(k, 1, 1) + eps
-    X = torch.zeros(k, n, mp, dtype=torch.bfloat16, device=G.device)
-    X[:, :, :m] = (Gf / nrm).to(torch.bfloat16)
-    Y = torch.empty_like(X)
     small_rows = n <= m
     g = n if small_rows else mp
-    if (not small_rows) and mp != m:
-        Y.zero_()
-    A = torch.empty(k, g, g, dtype=torch.bfloat16, device=G.device)
-    B = torch.empty_like(A)
-    for _ in range(steps):
+    X, Y, A, B, part = _ns_workspace(G.device, k, n, mp, g)
+    Gf = G if (G.dtype == torch.float32 and G.is_contiguous()) else G.float().contiguous()
+    if _has("imf_ns_prepare"):
+        _check(_lib.imf_ns_prepare(_ptr(Gf), _ptr(X), k, n, m, mp, _ptr(part), float(eps),
+                                   _stream()), "imf_ns_prepare")
+        LAUNCHES.count += 2
+    else:
+        nrm = Gf.flatten(1).norm(dim=1).view(k, 1, 1) + eps
+        X.zero_()
+        X[:, :, :m] = (Gf / nrm).to(torch.bfloat16)
+    if mp != m:
+        Y.zero_()        # the pad columns of the other iterate stay zero through a X + B X
+    direct = (out is not None and mp == m and out.dtype == torch.bfloat16 and out.is_contiguous()
+              and out.shape == (k, n, m))
+    for it in range(steps):
+        dst = out if (direct and it == steps - 1) else Y
         if small_rows:
             gemm_batched(X, X, out=A)                                        # X X^T
             gemm_batched(A, A, cin=A, alpha=c_, beta=b_, out=B)              # b A + c A A
-            gemm_batched(B, X, b_mn=True, cin=X, alpha=1.0, beta=a_, out=Y)  # a X + B X
+            gemm_batched(B, X, b_mn=True, cin=X, alpha=1.0, beta=a_, out=dst)  # a X + B X
         else:
             gemm_batched(X, X, a_mn=True, b_mn=True, out=A)                  # X^T X
             gemm_batched(A, A, cin=A, alpha=c_, beta=b_, out=B)
-            gemm_batched(X, B, cin=X, alpha=1.0, beta=a_, out=Y)             # a X + X B
-        X, Y = Y, X
-    return X[:, :, :m]
+            gemm_batched(X, B, cin=X, alpha=1.0, beta=a_, out=dst)           # a X + X B
+        X, Y = dst, X
+    if direct:
+        return out
+    res = X[:, :, :m]
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res.clone()      # the workspace is reused by the next call
 
 
 if _has("imf_gemm_bf16_batched"):

@@ -126,8 +126,8 @@ def get_ns_coefficients(n, m, steps, mode="per_shape", verbose=False, **solve_kw
 
 
 # ------------------------------------------------------- Newton-Schulz -----
-def zeropower_via_newtonschulz5(G: Tensor, steps=5, eps=1e-7, dtype=None, coeffs=None
-                                ) -> Tensor:
+def zeropower_via_newtonschulz5(G: Tensor, steps=5, eps=1e-7, dtype=None, coeffs=None,
+                                out: Optional[Tensor] = None) -> Tensor:
     """Approximate U V^T of G = U S V^T.  Accepts (n, m) or a batch (k, n, m).
     X = G / (||G||_F + eps); transposed when n > m so the Gram matrix is the
     small one; ``steps`` x {A = X X^T; B = bA + cA^2; X = aX + BX}.
@@ -140,9 +140,9 @@ def zeropower_via_newtonschulz5(G: Tensor, steps=5, eps=1e-7, dtype=None, coeffs
         from ..ops import cuda as cu
 
         if cu.available() and cu.has("newton_schulz") and dtype == torch.bfloat16:
-            out = cu.newton_schulz(G, (a, b, c), steps, eps)
-            if out is not None:
-                return out
+            res = cu.newton_schulz(G, (a, b, c), steps, eps, out=out)
+            if res is not None:
+                return res
     X = G.to(dtype)
     nrm = X.flatten(-2).norm(dim=-1)
     X = X / (nrm.reshape(nrm.shape + (1, 1)) + eps)
@@ -153,7 +153,11 @@ def zeropower_via_newtonschulz5(G: Tensor, steps=5, eps=1e-7, dtype=None, coeffs
         A = X @ X.transpose(-1, -2)
         B = b * A + c * (A @ A)
         X = a * X + B @ X
-    return X.transpose(-1, -2) if tr else X
+    X = X.transpose(-1, -2) if tr else X
+    if out is not None:
+        out.copy_(X)
+        return out
+    return X
 
 
 # ----------------------------------------------------------- optimizer -----

@@ -484,9 +484,10 @@ class FlatEngine(GradSync):
             batch = self.Dir[lo:lo + cnt * n * m].view(cnt, n, m)
             coeffs = get_ns_coefficients(n, m, steps=g0["ns_steps"], mode=g0["coeff_mode"],
                                          **opt._solve_kw)
-            upd = zeropower_via_newtonschulz5(batch, steps=g0["ns_steps"],
-                                              dtype=g0["ns_dtype"], coeffs=coeffs)
-            own_u[lo:lo + cnt * n * m].view(cnt, n, m).copy_(upd)
+            # the last iteration writes straight into the owned slice of the update arena
+            zeropower_via_newtonschulz5(batch, steps=g0["ns_steps"], dtype=g0["ns_dtype"],
+                                        coeffs=coeffs,
+                                        out=own_u[lo:lo + cnt * n * m].view(cnt, n, m))
             j = k
 
     def _newton_schulz_phase(self, opt: Moonlight, g0, use_k: bool) -> None:
