@@ -19,6 +19,13 @@
 // are added to an fp32 accumulator in global memory (red.global.add.v4.f32),
 // converted to bf16 by a small epilogue kernel.
 //
+// The per-query constants ride on the tensor core: the query tile carries Q * scale*log2e
+// and 16 extra K columns [-lse2_hi, -lse2_lo, 0 ...] (bf16 pair = fp32 to 2^-17), the K tile
+// 16 columns of ones, so the S^T accumulator already holds the exponent S*scale*log2e - lse2;
+// dO / V likewise carry -delta, so the dP^T accumulator holds dP - delta.  The math warps are
+// left with one ex2, one multiply and two packs per pair of elements (they, not the tensor
+// pipe, set the pace of this kernel), and read no per-row statistics at all.
+//
 // Warps 0-3 / 4-7: exp / dS math for columns 0-63 / 64-127 of the S^T tile;
 // warps 8-11: dQ tile TMEM -> global reduction; warp 12: tcgen05.mma issuer;
 // warp 13: TMA producer.  S^T/dP^T of tile i+1 are issued as soon as tile i
@@ -44,8 +51,9 @@ struct BwSmem {
   alignas(1024) uint8_t d_o[BW_QSTAGES][BW_T * 128];
   alignas(1024) uint8_t ds[2][2 * BW_T * 128];       // dS^T: [kv 128][q 128] as two 64-col panels
   alignas(1024) float dq_stage[BW_T * BW_HD];        // dQ tile staged for the TMA reduce-add
-  alignas(16) float lse2[BW_QSTAGES][BW_T];
-  alignas(16) float delta[BW_QSTAGES][BW_T];
+  alignas(1024) uint8_t ones[BW_T * 32];             // [128][16] bf16 1.0, 32-byte rows (SWIZZLE_32B)
+  alignas(1024) uint8_t augq[BW_QSTAGES][BW_T * 32]; // [q 128][16]: -lse2 as (hi, lo), zeros
+  alignas(1024) uint8_t augd[BW_QSTAGES][BW_T * 32]; // [q 128][16]: -delta as (hi, lo), zeros
   uint64_t kv_full;
   uint64_t q_full[BW_QSTAGES], q_empty[BW_QSTAGES];
   uint64_t s_full, s_taken, p_ready, p_free;
@@ -57,8 +65,6 @@ struct BwSmem {
 };
 
 struct BwParams {
-  const float* lse2;      // (B, H, Lp) log2-domain LSE, +inf on padding rows
-  const float* delta;     // (B, H, Lp) rowsum(dO .* O), 0 on padding rows
   float* dq_acc;          // (B, L, H, 64) fp32, zeroed
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
@@ -86,6 +92,17 @@ IMF_DEVICE void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// K-major operand with 32-byte rows (16 bf16 along K = one MMA K-step), SWIZZLE_32B:
+// 8-row groups are 256 B apart
+IMF_DEVICE uint64_t sdesc_kmajor_sw32(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(256 >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 6ull << 61;                               // SWIZZLE_32B
+  return d;
+}
 IMF_DEVICE void red_add_v4(float* gptr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gptr), "f"(a), "f"(b),
                "f"(c), "f"(d)
@@ -95,7 +112,8 @@ IMF_DEVICE void red_add_v4(float* gptr, float a, float b, float c, float d) {
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const __grid_constant__ CUtensorMap tm_dq, const BwParams p) {
+                const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_augq,
+                const __grid_constant__ CUtensorMap tm_augd, const BwParams p) {
   extern __shared__ uint8_t smem_raw[];
   auto& s = *reinterpret_cast<BwSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                        ~uintptr_t(1023));
@@ -136,6 +154,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     s.abort_flag = 0;
     fence_barrier_init();
   }
+  {
+    uint32_t* o32 = reinterpret_cast<uint32_t*>(s.ones);       // every element 1.0: the swizzle
+    for (int i = threadIdx.x; i < BW_T * 32 / 4; i += BW_THREADS) o32[i] = 0x3f803f80u;   // is moot
+    fence_proxy_async_smem();
+  }
   if (warp == 12) {
     tmem_alloc(&s.tmem_base, 512);
     tmem_relinquish();
@@ -158,8 +181,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_arrive_expect_tx(&s.kv_full, 2 * BW_T * 128);
         tma_load_4d(s.k, &tm_k, &s.kv_full, 0, h, kvb * BW_T, b);
         tma_load_4d(s.v, &tm_v, &s.kv_full, 0, h, kvb * BW_T, b);
-        const float* lse_row = p.lse2 + ((size_t)b * p.H + h) * p.Lp;
-        const float* dl_row = p.delta + ((size_t)b * p.H + h) * p.Lp;
+        const int bh = b * p.H + h;
         for (int i = 0; i < n_q; ++i) {
           const int st = i % BW_QSTAGES;
           if (i >= BW_QSTAGES &&
@@ -167,11 +189,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                          p.status, STATUS_TIMEOUT_EMPTY))
             break;
           const int qt = qlist ? qlist[i] : q_first + i;
-          mbar_arrive_expect_tx(&s.q_full[st], 2 * BW_T * 128 + 2 * BW_T * 4);
+          mbar_arrive_expect_tx(&s.q_full[st], 2 * BW_T * 128 + 2 * BW_T * 32);
           tma_load_4d(s.q[st], &tm_q, &s.q_full[st], 0, h, qt * BW_T, b);
           tma_load_4d(s.d_o[st], &tm_do, &s.q_full[st], 0, h, qt * BW_T, b);
-          bulk_load_1d(s.lse2[st], lse_row + (size_t)qt * BW_T, BW_T * 4, &s.q_full[st]);
-          bulk_load_1d(s.delta[st], dl_row + (size_t)qt * BW_T, BW_T * 4, &s.q_full[st]);
+          tma_load_3d(s.augq[st], &tm_augq, &s.q_full[st], 0, qt * BW_T, bh);
+          tma_load_3d(s.augd[st], &tm_augd, &s.q_full[st], 0, qt * BW_T, bh);
         }
       }
     } else if (warp == 12) {
@@ -181,14 +203,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         constexpr uint32_t id_kn = idesc_bf16(BW_T, BW_HD, 0, 1);    // dV (TS), dK (SS, A K-major)
         constexpr uint32_t id_mn = idesc_bf16(BW_T, BW_HD, 1, 1);    // dQ (A MN-major)
         const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v);
+        const uint64_t ones_d = sdesc_kmajor_sw32(smem_u32(s.ones));
         auto issue_s = [&](int st) {
           const uint32_t qa = smem_u32(s.q[st]), doa = smem_u32(s.d_o[st]);
 #pragma unroll
           for (int ks = 0; ks < BW_HD / 16; ++ks)
             mma_ss(tmem + BC_S, sdesc_kmajor(ka + ks * 32), sdesc_kmajor(qa + ks * 32), id_st, ks != 0);
+          // + ones[kv] x (-lse2[q])  ->  the accumulator holds the exponent itself
+          mma_ss(tmem + BC_S, ones_d, sdesc_kmajor_sw32(smem_u32(s.augq[st])), id_st, 1);
 #pragma unroll
           for (int ks = 0; ks < BW_HD / 16; ++ks)
             mma_ss(tmem + BC_DP, sdesc_kmajor(va + ks * 32), sdesc_kmajor(doa + ks * 32), id_st, ks != 0);
+          // + ones[kv] x (-delta[q])  ->  dP - delta
+          mma_ss(tmem + BC_DP, ones_d, sdesc_kmajor_sw32(smem_u32(s.augd[st])), id_st, 1);
           tc_commit(&s.s_full);
         };
         bool ok = n_q > 0 &&      // a K/V tile that no query tile attends has zero gradients
@@ -300,10 +327,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int wl = warp & 3;
     const int row = wl * 32 + lane;     // kv row of this thread (TMEM lane)
     const uint32_t tb = tmem_addr(tmem, wl * 32, 0);
-    const float scale_log2 = p.scale * 1.4426950408889634f;
     bool ok = true;
     for (int i = 0; i < n_q && ok; ++i) {
-      const int st = i % BW_QSTAGES;
       const uint32_t par = (uint32_t)(i & 1);
       ok = __all_sync(0xffffffffu,
                       mbar_wait(&s.s_full, par, abort_flag, p.status, STATUS_TIMEOUT_MMA));
@@ -318,9 +343,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.s_taken);
-      // the stats of this q tile arrived with its q_full stage (s_full implies it)
-      const float4* lse4 = reinterpret_cast<const float4*>(s.lse2[st] + wg * 64);
-      const float4* dl4 = reinterpret_cast<const float4*>(s.delta[st] + wg * 64);
       // P^T goes to TMEM (A operand of the dV GEMM): dV of tile i-1 must have read it;
       // dS^T goes to smem buffer i&1: the GEMMs of tile i-2 must have read it
       if (i > 0) {
@@ -342,19 +364,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t pk[16], dk_[16];
         if (live) {        // warp-uniform: a warp's 32 rows and 64 columns lie in one quadrant
 #pragma unroll
-          for (int c = 0; c < 32; c += 4) {
+          for (int c = 0; c < 32; c += 2) {
             const int cg = hh * 32 + c;
-            const float4 l4 = lse4[cg / 4], d4 = dl4[cg / 4];
-            const float p0 = ex2(fmaf(__uint_as_float(sv[cg]), scale_log2, -l4.x));
-            const float p1 = ex2(fmaf(__uint_as_float(sv[cg + 1]), scale_log2, -l4.y));
-            const float p2 = ex2(fmaf(__uint_as_float(sv[cg + 2]), scale_log2, -l4.z));
-            const float p3 = ex2(fmaf(__uint_as_float(sv[cg + 3]), scale_log2, -l4.w));
+            // sv = S scale log2e - lse2 and dp = dP - delta, straight from the tensor core
+            const float p0 = ex2(__uint_as_float(sv[cg]));
+            const float p1 = ex2(__uint_as_float(sv[cg + 1]));
             pk[c / 2] = pack_bf16(p0, p1);
-            pk[c / 2 + 1] = pack_bf16(p2, p3);
-            dk_[c / 2] = pack_bf16(p0 * (__uint_as_float(dp[cg]) - d4.x),
-                                   p1 * (__uint_as_float(dp[cg + 1]) - d4.y));
-            dk_[c / 2 + 1] = pack_bf16(p2 * (__uint_as_float(dp[cg + 2]) - d4.z),
-                                       p3 * (__uint_as_float(dp[cg + 3]) - d4.w));
+            dk_[c / 2] = pack_bf16(p0 * __uint_as_float(dp[cg]), p1 * __uint_as_float(dp[cg + 1]));
           }
         } else {           // block-sparse: this quadrant is not attended
 #pragma unroll
@@ -380,7 +396,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (ok) {
       tc_fence_after();
       const int kv_row = kvb * BW_T + row;
-      const float mul = n_q == 0 ? 0.f : (wg == 0 ? p.scale : 1.f);
+      // Q in shared memory is Q * scale * log2(e): dK = scale dS^T Q = ln(2) dS^T Q_scaled
+      const float mul = n_q == 0 ? 0.f : (wg == 0 ? 0.6931471805599453f : 1.f);
       __nv_bfloat16* base =
           wg == 0 ? p.dk + (int64_t)b * p.dk_sb + (int64_t)kv_row * p.dk_sl + (int64_t)h * p.dk_sh
                   : p.dv + (int64_t)b * p.dv_sb + (int64_t)kv_row * p.dv_sl + (int64_t)h * p.dv_sh;
@@ -426,36 +443,48 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
 }
 
-// delta = rowsum(dO .* O), lse2 = lse * log2(e), both padded to Lp rows per
-// (b, h); one warp per (b, l, h) row of 64 channels.
-__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o,
+// Per (b, l, h) row, one warp:  delta = rowsum(dO .* O) and lse2 = lse * log2(e) as the bf16
+// (hi, lo) pairs the main kernel feeds to the tensor core (16 columns per row, the rest zero;
+// rows l >= L of the padded length Lp get lse2 = 30000, i.e. P = 0), and Q * scale*log2e as bf16.
+__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ q,
+                                     const __nv_bfloat16* __restrict__ o,
                                      const __nv_bfloat16* __restrict__ d_o,
-                                     const float* __restrict__ lse, float* __restrict__ lse2,
-                                     float* __restrict__ delta, int B, int L, int H, int Lp,
+                                     const float* __restrict__ lse, __nv_bfloat16* __restrict__ qs,
+                                     uint32_t* __restrict__ augq, uint32_t* __restrict__ augd, int B,
+                                     int L, int H, int Lp, int64_t q_sb, int64_t q_sl, int64_t q_sh,
                                      int64_t o_sb, int64_t o_sl, int64_t o_sh, int64_t g_sb,
-                                     int64_t g_sl, int64_t g_sh) {
+                                     int64_t g_sl, int64_t g_sh, float scale_log2) {
   const int lane = threadIdx.x & 31;
   const long wid = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long total = (long)B * H * Lp;
   if (wid >= total) return;
   const int l = (int)(wid % Lp), h = (int)((wid / Lp) % H), b = (int)(wid / ((long)Lp * H));
-  if (l >= L) {
-    if (lane == 0) {
-      lse2[wid] = INFINITY;
-      delta[wid] = 0.f;
-    }
-    return;
-  }
-  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(
-      o + b * o_sb + (int64_t)l * o_sl + h * o_sh + lane * 2);
-  const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(
-      d_o + b * g_sb + (int64_t)l * g_sl + h * g_sh + lane * 2);
-  float v = __low2float(a) * __low2float(g) + __high2float(a) * __high2float(g);
+  float x = 30000.f, dl = 0.f;          // padding rows: exp2(S - 30000) = 0
+  if (l < L) {
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(
+        o + b * o_sb + (int64_t)l * o_sl + h * o_sh + lane * 2);
+    const __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(
+        d_o + b * g_sb + (int64_t)l * g_sl + h * g_sh + lane * 2);
+    float v = __low2float(a) * __low2float(g) + __high2float(a) * __high2float(g);
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-  if (lane == 0) {
-    delta[wid] = v;
-    lse2[wid] = lse[((long)b * H + h) * L + l] * 1.4426950408889634f;
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    dl = v;
+    x = lse[((long)b * H + h) * L + l] * 1.4426950408889634f;
+    x = fminf(fmaxf(x, -30000.f), 30000.f);
+    const __nv_bfloat162 qq = *reinterpret_cast<const __nv_bfloat162*>(
+        q + b * q_sb + (int64_t)l * q_sl + h * q_sh + lane * 2);
+    *reinterpret_cast<uint32_t*>(qs + (((int64_t)b * L + l) * H + h) * 64 + lane * 2) =
+        pack_bf16(__low2float(qq) * scale_log2, __high2float(qq) * scale_log2);
+  }
+  if (lane < 8) {                        // 16 bf16 = 8 words per row
+    uint32_t wq = 0u, wd = 0u;
+    if (lane == 0) {
+      const float xh = bf16_lo(pack_bf16(-x, 0.f)), dh = bf16_lo(pack_bf16(-dl, 0.f));
+      wq = pack_bf16(xh, -x - xh);
+      wd = pack_bf16(dh, -dl - dh);
+    }
+    augq[wid * 8 + lane] = wq;
+    augd[wid * 8 + lane] = wd;
   }
 }
 
@@ -536,13 +565,15 @@ static int make_map64(CUtensorMap* m, const void* ptr, int B, int L, int H, int6
 
 }  // namespace imf
 
-// Scratch (bytes) the backward needs: fp32 dQ accumulator + padded lse2/delta + (dense mode,
-// when the query tiles are split) fp32 partial dK / dV.
+// Scratch (bytes) the backward needs: fp32 dQ accumulator + the two 16-column operand bands
+// (-lse2, -delta; padded to Lp rows) + the scaled copy of Q + (dense mode, when the query tiles
+// are split) fp32 partial dK / dV.
 extern "C" long imf_attn_bwd_scratch_bytes(int B, int L, int H) {
   const long Lp = ((L + 127) / 128) * 128;
   const int qs = imf::bwd_qsplit(B, L, H);
   const long part = qs > 1 ? 2L * qs * B * L * H * 64 * 4 : 0;
-  return (long)B * L * H * 64 * 4 + 2 * (long)B * H * Lp * 4 + 512 + part;
+  return (long)B * L * H * 64 * 4 + 2 * (long)B * H * Lp * 32 + (long)B * L * H * 64 * 2 + 1024 +
+         part;
 }
 
 // Same for either head_dim (64 or 128).
@@ -585,14 +616,18 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
   const int Lp = ((L + 127) / 128) * 128;
   float* dq_acc = static_cast<float*>(scratch);
   const size_t acc_bytes = (size_t)B * L * H * 64 * 4;
-  float* lse2 = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + ((acc_bytes + 255) & ~size_t(255)));
-  float* delta = lse2 + (size_t)B * H * Lp;
+  uint8_t* cur = static_cast<uint8_t*>(scratch) + ((acc_bytes + 255) & ~size_t(255));
+  uint32_t* augq = reinterpret_cast<uint32_t*>(cur);
+  cur += (size_t)B * H * Lp * 32;
+  uint32_t* augd = reinterpret_cast<uint32_t*>(cur);
+  cur += (size_t)B * H * Lp * 32;
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(cur);
+  cur += ((size_t)B * L * H * 64 * 2 + 255) & ~size_t(255);
   const int qsplit = qlist ? 1 : bwd_qsplit(B, L, H);
   float* part_dk = nullptr;
   float* part_dv = nullptr;
   if (qsplit > 1) {
-    const uintptr_t end = (reinterpret_cast<uintptr_t>(delta + (size_t)B * H * Lp) + 255) & ~uintptr_t(255);
-    part_dk = reinterpret_cast<float*>(end);
+    part_dk = reinterpret_cast<float*>(cur);
     part_dv = part_dk + (size_t)qsplit * B * L * H * 64;
   }
   if (cudaMemsetAsync(dq_acc, 0, acc_bytes, st) != cudaSuccess) return IMF_ERR_LAUNCH;
@@ -601,14 +636,25 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
     const int threads = 256;
     const long blocks = (warps * 32 + threads - 1) / threads;
     attn_bwd_prep_kernel<<<(unsigned)blocks, threads, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), lse, lse2,
-        delta, B, L, H, Lp, o_strides[0], o_strides[1], o_strides[2], strides[9], strides[10],
-        strides[11]);
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(o),
+        static_cast<const __nv_bfloat16*>(d_o), lse, qs, augq, augd, B, L, H, Lp, strides[0],
+        strides[1], strides[2], o_strides[0], o_strides[1], o_strides[2], strides[9], strides[10],
+        strides[11], scale * 1.4426950408889634f);
     if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   }
-  CUtensorMap mq, mk, mv, mdo, mdq;
+  CUtensorMap mq, mk, mv, mdo, mdq, maq, mad;
   int rc;
-  if ((rc = make_map64(&mq, q, B, L, H, strides[0], strides[1], strides[2]))) return rc;
+  // the query operand is the scaled copy (contiguous (B, L, H, 64))
+  if ((rc = make_map64(&mq, qs, B, L, H, (int64_t)L * H * 64, (int64_t)H * 64, 64))) return rc;
+  for (int which = 0; which < 2; ++which) {      // (B*H, Lp, 16) bf16, 32-byte rows
+    uint64_t dims[3] = {16, (uint64_t)Lp, (uint64_t)B * H};
+    uint64_t str[3] = {2, 32, (uint64_t)Lp * 32};
+    uint32_t box[3] = {16, (uint32_t)BW_T, 1};
+    if ((rc = make_tmap(which ? &mad : &maq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                        which ? (void*)augd : (void*)augq, dims, str, box,
+                        CU_TENSOR_MAP_SWIZZLE_32B)))
+      return rc;
+  }
   if ((rc = make_map64(&mk, k, B, L, H, strides[3], strides[4], strides[5]))) return rc;
   if ((rc = make_map64(&mv, v, B, L, H, strides[6], strides[7], strides[8]))) return rc;
   if ((rc = make_map64(&mdo, d_o, B, L, H, strides[9], strides[10], strides[11]))) return rc;
@@ -620,8 +666,6 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
       return rc;
   }
   BwParams prm;
-  prm.lse2 = lse2;
-  prm.delta = delta;
   prm.dq_acc = dq_acc;
   prm.dk = static_cast<__nv_bfloat16*>(dk);
   prm.dv = static_cast<__nv_bfloat16*>(dv);
@@ -641,14 +685,14 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
                            (int)smem) != cudaSuccess)
     return IMF_ERR_LAUNCH;
   dim3 grid((L + BW_T - 1) / BW_T, H, B * qsplit);
-  attn_bwd_kernel<<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, mdq, prm);
+  attn_bwd_kernel<<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, mdq, maq, mad, prm);
   if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   if (qsplit > 1) {
     const long n = (long)B * L * H * 16;
     attn_bwd_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
         part_dk, part_dv, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), qsplit,
         B, L, H, dk_strides[0], dk_strides[1], dk_strides[2], dv_strides[0], dv_strides[1],
-        dv_strides[2], scale);
+        dv_strides[2], 0.6931471805599453f);      // partial dK = dS^T (Q scale log2e)
     if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   }
   const long n4 = (long)B * L * H * 64 / 4;

@@ -4,6 +4,7 @@ under ``ncu`` (or for a quick CUDA-event timing without it).
     python -m imfvideo_b200.ops.profile_kernels attn_fwd  --L 9472
     python -m imfvideo_b200.ops.profile_kernels attn_jvp  --L 9472
     python -m imfvideo_b200.ops.profile_kernels attn_bwd  --L 4736
+    python -m imfvideo_b200.ops.profile_kernels attn_jvp  --L 32780 --H 12 --hd 128
     python -m imfvideo_b200.ops.profile_kernels gemm      --M 58280 --N 528 --K 256
     python -m imfvideo_b200.ops.profile_kernels sparse    --L 9472
     python -m imfvideo_b200.ops.profile_kernels resnorm   --rows 29140
@@ -48,6 +49,7 @@ def main() -> None:
     ap.add_argument("--L", type=int, default=9472)
     ap.add_argument("--B", type=int, default=1)
     ap.add_argument("--H", type=int, default=4)
+    ap.add_argument("--hd", type=int, default=64, help="head dimension of the attention kernels")
     ap.add_argument("--M", type=int, default=58280)
     ap.add_argument("--N", type=int, default=528)
     ap.add_argument("--K", type=int, default=256)
@@ -68,8 +70,9 @@ def main() -> None:
     mk = lambda: torch.randn(B, L, H, 64, device=dev).bfloat16()
     flops = bytes_ = None
     if args.kernel in ("attn_fwd", "attn_jvp", "attn_bwd"):
-        q, k, v, dq, dk, dv = (mk() for _ in range(6))
-        base = 4.0 * B * H * L * L * 64
+        mkd = lambda: torch.randn(B, L, H, args.hd, device=dev).bfloat16()
+        q, k, v, dq, dk, dv = (mkd() for _ in range(6))
+        base = 4.0 * B * H * L * L * args.hd
         if args.kernel == "attn_fwd":
             fn, flops = (lambda: K.attn_fwd(q, k, v)), base
         elif args.kernel == "attn_jvp":
