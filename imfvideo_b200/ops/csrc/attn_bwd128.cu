@@ -302,20 +302,8 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (lane == 0) mbar_arrive(&s.s_taken);
       const float4* lse4 = reinterpret_cast<const float4*>(s.lse2[st] + wg * 32);
       const float4* dl4 = reinterpret_cast<const float4*>(s.delta[st] + wg * 32);
-      // P^T goes to TMEM (A operand of the dV GEMM): dV of tile i-1 must have read it;
-      // dS^T goes to smem buffer i&1: the GEMMs of tile i-2 must have read it
-      if (i > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&s.p_free, (uint32_t)((i - 1) & 1), abort_flag,
-                                               p.status, STATUS_TIMEOUT_MMA));
-        if (!ok) break;
-      }
-      if (i >= 2) {
-        ok = __all_sync(0xffffffffu,
-                        mbar_wait(&s.ds_free[i & 1], (uint32_t)(((i / 2) - 1) & 1), abort_flag,
-                                  p.status, STATUS_TIMEOUT_MMA));
-        if (!ok) break;
-      }
-      uint8_t* dsb = s.ds[i & 1] + row * 128;
+      // all of the tile's math first, from registers only: it overlaps the dV / dK / dQ MMAs
+      // of the previous tile, which still read P^T (TMEM) and dS^T (shared memory)
       uint32_t pk[16], dk_[16];
 #pragma unroll
       for (int c = 0; c < 32; c += 4) {
@@ -331,7 +319,21 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         dk_[c / 2 + 1] = pack_bf16(p2 * (__uint_as_float(dp[c + 2]) - d4.z),
                                    p3 * (__uint_as_float(dp[c + 3]) - d4.w));
       }
+      // P^T goes to TMEM (A operand of the dV GEMM): dV of tile i-1 must have read it;
+      // dS^T goes to smem buffer i&1: the GEMMs of tile i-2 must have read it
+      if (i > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&s.p_free, (uint32_t)((i - 1) & 1), abort_flag,
+                                               p.status, STATUS_TIMEOUT_MMA));
+        if (!ok) break;
+      }
       tmem_st16(tb + BC_P + wg * 16, pk);
+      if (i >= 2) {
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait(&s.ds_free[i & 1], (uint32_t)(((i / 2) - 1) & 1), abort_flag,
+                                  p.status, STATUS_TIMEOUT_MMA));
+        if (!ok) break;
+      }
+      uint8_t* dsb = s.ds[i & 1] + row * 128;
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
         const int chunk = wg * 4 + cc;
