@@ -92,17 +92,6 @@ IMF_DEVICE void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
-// K-major operand with 32-byte rows (16 bf16 along K = one MMA K-step), SWIZZLE_32B:
-// 8-row groups are 256 B apart
-IMF_DEVICE uint64_t sdesc_kmajor_sw32(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>(1) << 16;
-  d |= static_cast<uint64_t>(256 >> 4) << 32;
-  d |= 1ull << 46;
-  d |= 6ull << 61;                               // SWIZZLE_32B
-  return d;
-}
 IMF_DEVICE void red_add_v4(float* gptr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gptr), "f"(a), "f"(b),
                "f"(c), "f"(d)

@@ -263,6 +263,20 @@ IMF_DEVICE uint64_t sdesc_mnmajor(uint32_t smem_addr, uint32_t panel_bytes) {
   return make_sdesc(smem_addr, panel_bytes, 1024);
 }
 
+// K-major operand with 32-byte rows (16 x 16-bit along K = one MMA K-step), SWIZZLE_32B:
+// 8-row groups are 256 B apart.  Used for the narrow "constant" operand bands that let the
+// tensor core add a per-row term to an accumulator (rows of ones on one side, the term as a
+// bf16 (hi, lo) pair on the other).
+IMF_DEVICE uint64_t sdesc_kmajor_sw32(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(256 >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 6ull << 61;                               // SWIZZLE_32B
+  return d;
+}
+
 // TMEM address helpers: bits [16,32) lane, [0,16) column
 IMF_DEVICE uint32_t tmem_addr(uint32_t base, uint32_t lane, uint32_t col) {
   return base + (lane << 16) + col;
