@@ -213,6 +213,16 @@ IMF_DEVICE void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// fp8 (e4m3 / e5m2, chosen by the instruction descriptor) x fp8 -> fp32; K = 32 per instruction
+IMF_DEVICE void mma_ss_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // int8 x int8 -> int32
 IMF_DEVICE void mma_ss_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                           uint32_t accumulate) {
@@ -229,6 +239,7 @@ IMF_DEVICE void mma_ss_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uin
 //   [15] A major (0 = K)   [16] B major (0 = K, 1 = MN)
 //   [17,23) N >> 3   [24,29) M >> 4
 constexpr uint32_t FMT_F16 = 0, FMT_BF16 = 1, FMT_S8 = 1;
+constexpr uint32_t FMT_E4M3 = 0, FMT_E5M2 = 1;      // kind::f8f6f4
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t m, uint32_t n, uint32_t a_fmt,
                                                   uint32_t b_fmt, uint32_t d_fmt,
                                                   uint32_t a_mn_major, uint32_t b_mn_major) {

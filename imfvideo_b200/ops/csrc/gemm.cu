@@ -47,18 +47,26 @@ struct GemmTiles {
                            // and writes plane z of C (batch must be 1 then)
 };
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT>
+// FP8: operands are e4m3 bytes (K-major only); a 128-byte shared-memory row then holds 128
+// K elements and one instruction covers 32 of them, so the byte geometry of the pipeline is
+// the one of the bf16 kernel.  `alpha_dev` (optional): two device floats whose product scales
+// the result (the de-quantisation scales of the two fp8 operands).
+template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT, bool FP8 = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 2)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_c, OutT* __restrict__ Cbase,
             const float* __restrict__ bias, int M, int N, int K, int64_t ldc, int bias_rows,
             float alpha, int accumulate_out, int* status, const OutT* __restrict__ Cin_base,
-            float beta, int64_t batch_stride_c, GemmTiles tiles, int tma_store) {
+            float beta, int64_t batch_stride_c, GemmTiles tiles, int tma_store,
+            const float* __restrict__ alpha_dev = nullptr) {
+  static_assert(!FP8 || (!A_MN && !B_MN), "fp8 operands are K-major");
+  constexpr int KB_ELEMS = FP8 ? 2 * GEMM_BK : GEMM_BK;      // K elements per 128-byte row
+  if (alpha_dev) alpha *= alpha_dev[0] * alpha_dev[1];
   extern __shared__ uint8_t smem_raw[];
   auto& s = *reinterpret_cast<GemmSmem<BN, STAGES, OutT>*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  const int num_kb = (K + KB_ELEMS - 1) / KB_ELEMS;
   constexpr int PANEL_COLS = 128 / (int)sizeof(OutT);      // 64 bf16 or 32 fp32 columns
 
   if (threadIdx.x == 0) {
@@ -117,7 +125,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             break;
           }
           mbar_arrive_expect_tx(&s.full[st], bytes);
-          const int k0 = kb * GEMM_BK;
+          const int k0 = kb * KB_ELEMS;
           if (!A_MN) {
             tma_load_3d(s.a[st], &tm_a, &s.full[st], k0, m0, bz);
           } else {
@@ -137,7 +145,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   } else if (warp == 5) {
     // -------------------------------------------------------- MMA issuer --
     if (elect_one()) {
-      constexpr uint32_t idesc = idesc_bf16(GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = FP8 ? make_idesc(GEMM_BM, BN, FMT_E4M3, FMT_E4M3, 1, 0, 0)
+                                     : idesc_bf16(GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t it = 0, tn = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles.total && ok; tile += gridDim.x, ++tn) {
@@ -162,7 +171,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                                      : sdesc_kmajor(a_base + ks * 32);
             const uint64_t db = B_MN ? sdesc_mnmajor(b_base + ks * 2048, 64 * 128)
                                      : sdesc_kmajor(b_base + ks * 32);
-            mma_ss(acc, da, db, idesc, kb != kb0 || ks != 0);
+            if (FP8) mma_ss_f8(acc, da, db, idesc, kb != kb0 || ks != 0);
+            else mma_ss(acc, da, db, idesc, kb != kb0 || ks != 0);
           }
           tc_commit(&s.empty[st]);
         }
@@ -306,12 +316,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   }
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT>
+template <int BN, int STAGES, bool A_MN, bool B_MN, typename OutT, bool FP8 = false>
 static int launch_gemm(const void* A, const void* B, void* C, const float* bias, int M, int N,
                        int K, int64_t lda, int64_t ldb, int64_t ldc, int bias_rows, float alpha,
                        int accumulate_out, int* status, cudaStream_t stream, int batch = 1,
                        int64_t sa = 0, int64_t sb = 0, int64_t sc = 0, const void* Cin = nullptr,
-                       float beta = 0.f, int splits = 1) {
+                       float beta = 0.f, int splits = 1, const float* alpha_dev = nullptr) {
+  constexpr int OES = FP8 ? 1 : 2;                      // operand element size
+  constexpr CUtensorMapDataType ODT =
+      FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  constexpr uint32_t KBOX = FP8 ? 128u : 64u;           // K elements of one 128-byte row
   CUtensorMap ta, tb, tc;
   int rc;
   if (splits > 1 && batch != 1) return IMF_ERR_ARG;
@@ -320,17 +334,17 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
     // K-major: dims (K, M), box (64, 128).  MN-major: dims (M, K), box (64, 64).
     uint64_t dims[3] = {A_MN ? (uint64_t)M : (uint64_t)K, A_MN ? (uint64_t)K : (uint64_t)M,
                         (uint64_t)batch};
-    uint64_t str[3] = {2, (uint64_t)lda * 2, (uint64_t)(batch > 1 ? sa : (int64_t)lda) * 2};
-    uint32_t box[3] = {64, A_MN ? 64u : (uint32_t)GEMM_BM, 1};
-    rc = make_tmap(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(A), dims, str, box);
+    uint64_t str[3] = {OES, (uint64_t)lda * OES, (uint64_t)(batch > 1 ? sa : (int64_t)lda) * OES};
+    uint32_t box[3] = {A_MN ? 64u : KBOX, A_MN ? 64u : (uint32_t)GEMM_BM, 1};
+    rc = make_tmap(&ta, ODT, 3, const_cast<void*>(A), dims, str, box);
     if (rc) return rc;
   }
   {
     uint64_t dims[3] = {B_MN ? (uint64_t)N : (uint64_t)K, B_MN ? (uint64_t)K : (uint64_t)N,
                         (uint64_t)batch};
-    uint64_t str[3] = {2, (uint64_t)ldb * 2, (uint64_t)(batch > 1 ? sb : (int64_t)ldb) * 2};
-    uint32_t box[3] = {64, B_MN ? 64u : (uint32_t)BN, 1};
-    rc = make_tmap(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(B), dims, str, box);
+    uint64_t str[3] = {OES, (uint64_t)ldb * OES, (uint64_t)(batch > 1 ? sb : (int64_t)ldb) * OES};
+    uint32_t box[3] = {B_MN ? 64u : KBOX, B_MN ? 64u : (uint32_t)BN, 1};
+    rc = make_tmap(&tb, ODT, 3, const_cast<void*>(B), dims, str, box);
     if (rc) return rc;
   }
   // C through TMA when its pitch, batch stride and base are 16-byte multiples
@@ -347,7 +361,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
                         3, C, dims, str, box))
       tma_store = 0;
   }
-  auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, OutT>;
+  auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, OutT, FP8>;
   const size_t smem = sizeof(GemmSmem<BN, STAGES, OutT>) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
@@ -359,7 +373,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
   GemmTiles tiles;
   tiles.n_n = (N + BN - 1) / BN;
   tiles.n_m = (M + GEMM_BM - 1) / GEMM_BM;
-  const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  const int num_kb = (K + (int)KBOX - 1) / (int)KBOX;
   tiles.kb_per = splits > 1 ? (num_kb + splits - 1) / splits : num_kb;
   tiles.splits = splits > 1 ? (num_kb + tiles.kb_per - 1) / tiles.kb_per : 1;   // no empty slice
   if (splits > 1 && tiles.splits != splits) return IMF_ERR_ARG;
@@ -377,7 +391,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
   kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, tc, static_cast<OutT*>(C), bias, M, N, K, ldc,
                                              bias_rows, alpha, accumulate_out, status,
                                              static_cast<const OutT*>(Cin), beta, sc, tiles,
-                                             tma_store);
+                                             tma_store, alpha_dev);
   return cudaGetLastError() == cudaSuccess ? IMF_OK : IMF_ERR_LAUNCH;
 }
 
@@ -413,6 +427,26 @@ extern "C" int imf_gemm_bf16(const void* A, const void* B, void* C, const float*
     IMF_GEMM_CASE(true, true, __nv_bfloat16);
   }
 #undef IMF_GEMM_CASE
+}
+
+// fp8 (e4m3) operands, both K-major ([M, K] and [N, K] bytes, row pitches multiples of 16):
+// C = alpha * scales[0] * scales[1] * A B^T (+ bias), bf16 or fp32 output.  `scales`: two device
+// floats (the operands' de-quantisation scales, see imf_quantize_fp8) or null.  The B200 form
+// of the reference's `_fp8_mm` (reference models/triton_block_jvp.py:80-86).
+extern "C" int imf_gemm_fp8(const void* A, const void* B, void* C, const float* bias, int M, int N,
+                            int K, int64_t lda, int64_t ldb, int64_t ldc, int out_fp32,
+                            int bias_rows, float alpha, const float* scales, int* status,
+                            void* stream) {
+  using namespace imf;
+  if (M <= 0 || N <= 0 || K <= 0 || (lda & 15) || (ldb & 15)) return IMF_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_fp32)
+    return launch_gemm<128, 4, false, false, float, true>(A, B, C, bias, M, N, K, lda, ldb, ldc,
+                                                          bias_rows, alpha, 0, status, st, 1, 0, 0,
+                                                          0, nullptr, 0.f, 1, scales);
+  return launch_gemm<128, 2, false, false, __nv_bfloat16, true>(
+      A, B, C, bias, M, N, K, lda, ldb, ldc, bias_rows, alpha, 0, status, st, 1, 0, 0, 0, nullptr,
+      0.f, 1, scales);
 }
 
 // Split-K product for long-K / small-output shapes (weight gradients dY^T X with K = tokens):
@@ -500,3 +534,57 @@ extern "C" int imf_gemm_bf16_batched(const void* A, const void* B, void* C, cons
   }
 #undef IMF_GEMM_CASE
 }
+
+// ---------------------------------------------------------------------------
+// Per-tensor fp8 (e4m3) quantisation of a bf16 matrix for imf_gemm_fp8: x8 = round(x / s),
+// s = amax(|x|) / 448 (the largest e4m3 value), two launches; `scale_out` receives s.
+// ---------------------------------------------------------------------------
+#include <cuda_fp8.h>
+namespace imf {
+__global__ void fp8_amax_kernel(const __nv_bfloat16* __restrict__ x, long rows, int cols,
+                                int64_t ld, unsigned int* __restrict__ amax_bits) {
+  float m = 0.f;
+  const long n = rows * cols;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long)gridDim.x * blockDim.x)
+    m = fmaxf(m, fabsf(__bfloat162float(x[(i / cols) * ld + i % cols])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) atomicMax(amax_bits, __float_as_uint(m));   // m >= 0: bits order
+}
+__global__ void fp8_cast_kernel(const __nv_bfloat16* __restrict__ x, long rows, int cols, int64_t ld,
+                                uint8_t* __restrict__ out, int64_t ldo,
+                                const unsigned int* __restrict__ amax_bits,
+                                float* __restrict__ scale_out) {
+  const float amax = __uint_as_float(*amax_bits);
+  const float s = amax > 0.f ? amax / 448.f : 1.f;
+  const float inv = 1.f / s;
+  if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = s;
+  const long n = rows * ldo;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long)gridDim.x * blockDim.x) {
+    const long r = i / ldo;
+    const int c = (int)(i % ldo);
+    const float v = c < cols ? __bfloat162float(x[r * ld + c]) * inv : 0.f;   // pad columns: 0
+    out[i] = (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+  }
+}
+}  // namespace imf
+
+// x: (rows, cols) bf16 with row pitch ld; out: (rows, ldo) bytes, ldo >= cols and a multiple
+// of 16 (columns cols..ldo-1 are written as zero); amax_scratch: one zeroed device word.
+extern "C" int imf_quantize_fp8(const void* x, long rows, int cols, int64_t ld, void* out,
+                                int64_t ldo, unsigned int* amax_scratch, float* scale_out,
+                                void* stream) {
+  if (rows <= 0 || cols <= 0 || ldo < cols || (ldo & 15)) return imf::IMF_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  long blocks = (rows * cols + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  imf::fp8_amax_kernel<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows,
+                                                         cols, ld, amax_scratch);
+  imf::fp8_cast_kernel<<<(unsigned)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), rows,
+                                                         cols, ld, static_cast<uint8_t*>(out), ldo,
+                                                         amax_scratch, scale_out);
+  return cudaGetLastError() == cudaSuccess ? imf::IMF_OK : imf::IMF_ERR_LAUNCH;
+}
+

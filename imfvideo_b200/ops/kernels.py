@@ -118,6 +118,63 @@ if _has("imf_gemm_bf16_splitk"):
     _lib.imf_splitk_reduce.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, c_float,
                                        c_int, c_void_p]
 
+if _has("imf_gemm_fp8"):
+    _lib.imf_gemm_fp8.restype = c_int
+    _lib.imf_gemm_fp8.argtypes = [c_void_p] * 4 + [c_int] * 3 + [c_int64] * 3 + [c_int, c_int,
+                                                                                c_float, c_void_p,
+                                                                                c_void_p, c_void_p]
+    _lib.imf_quantize_fp8.restype = c_int
+    _lib.imf_quantize_fp8.argtypes = [c_void_p, ctypes.c_long, c_int, c_int64, c_void_p, c_int64,
+                                      c_void_p, c_void_p, c_void_p]
+
+
+def quantize_fp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-tensor e4m3 quantisation of a bf16 matrix [rows, K]: returns the bytes
+    ([rows, K rounded up to 16], pad columns zero) and the de-quantisation scale (1 float
+    on the device, amax / 448)."""
+    assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.stride(1) == 1
+    rows, cols = x.shape
+    ldo = (cols + 15) // 16 * 16
+    out = torch.empty(rows, ldo, dtype=torch.uint8, device=x.device)
+    amax = torch.zeros(1, dtype=torch.int32, device=x.device)
+    scale = torch.empty(1, dtype=torch.float32, device=x.device)
+    _check(_lib.imf_quantize_fp8(_ptr(x), rows, cols, x.stride(0), _ptr(out), ldo, _ptr(amax),
+                                 _ptr(scale), _stream()), "imf_quantize_fp8")
+    LAUNCHES.count += 2
+    return out, scale
+
+
+def gemm_fp8(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Tensor, *,
+             out_dtype: torch.dtype = torch.bfloat16, bias: Optional[torch.Tensor] = None,
+             bias_rows: Optional[int] = None) -> torch.Tensor:
+    """C[M, N] = sa * sb * A8 B8^T (+ bias) for e4m3 operands from ``quantize_fp8`` ([rows, K]
+    bytes each, same padded K), on the tcgen05 ``kind::f8f6f4`` path (twice the bf16 rate).
+    Counterpart of the reference's ``_fp8_mm`` (``models/triton_block_jvp.py:80-86``), which
+    like this one serves its reduced-precision block variants, not the training default."""
+    assert a8.dtype == torch.uint8 and b8.dtype == torch.uint8 and a8.shape[1] == b8.shape[1]
+    M, Kp = a8.shape
+    N = b8.shape[0]
+    out = torch.empty(M, N, dtype=out_dtype, device=a8.device)
+    scales = torch.cat([sa.reshape(1), sb.reshape(1)]).float()
+    fb = None if bias is None else bias.float().contiguous()
+    _check(_lib.imf_gemm_fp8(_ptr(a8), _ptr(b8), _ptr(out), _ptr(fb), M, N, Kp, a8.stride(0),
+                             b8.stride(0), out.stride(0), int(out_dtype == torch.float32),
+                             M if bias_rows is None else bias_rows, 1.0, _ptr(scales),
+                             _ptr(status_word(a8.device)), _stream()), "imf_gemm_fp8")
+    LAUNCHES.count += 1
+    return out
+
+
+def linear_fp8(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+               w_cache: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+    """y = x w^T (+ bias) with both operands quantised to e4m3 per tensor (the weight
+    quantisation can be passed in as ``w_cache`` to reuse it across calls)."""
+    x2 = x.reshape(-1, x.shape[-1]).to(torch.bfloat16)
+    a8, sa = quantize_fp8(x2 if x2.is_contiguous() else x2.contiguous())
+    b8, sb = w_cache if w_cache is not None else quantize_fp8(w.to(torch.bfloat16).contiguous())
+    return gemm_fp8(a8, sa, b8, sb, bias=bias).view(*x.shape[:-1], w.shape[0])
+
+
 SPLITK_TARGET_TILES = 296      # two CTAs per SM on 148 SMs
 
 

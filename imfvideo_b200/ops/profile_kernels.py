@@ -6,6 +6,7 @@ under ``ncu`` (or for a quick CUDA-event timing without it).
     python -m imfvideo_b200.ops.profile_kernels attn_bwd  --L 4736
     python -m imfvideo_b200.ops.profile_kernels attn_jvp  --L 32780 --H 12 --hd 128
     python -m imfvideo_b200.ops.profile_kernels gemm      --M 58280 --N 528 --K 256
+    python -m imfvideo_b200.ops.profile_kernels gemm_fp8  --M 65560 --N 4096 --K 1024   # e4m3 operands
     python -m imfvideo_b200.ops.profile_kernels sparse    --L 9472
     python -m imfvideo_b200.ops.profile_kernels resnorm   --rows 29140
     python -m imfvideo_b200.ops.profile_kernels resnorm_bwd --rows 29140 --D 256
@@ -44,7 +45,7 @@ def _time(fn, iters: int, flush) -> float:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["attn_fwd", "attn_jvp", "attn_bwd", "gemm", "sparse",
+    ap.add_argument("kernel", choices=["attn_fwd", "attn_jvp", "attn_bwd", "gemm", "gemm_fp8", "sparse",
                                        "sparse_jvp", "resnorm", "resnorm_bwd", "lin", "route"])
     ap.add_argument("--L", type=int, default=9472)
     ap.add_argument("--B", type=int, default=1)
@@ -85,6 +86,13 @@ def main() -> None:
         b = torch.randn(args.N, args.K, device=dev).bfloat16()
         fn, flops = (lambda: K.gemm(a, b)), 2.0 * args.M * args.N * args.K
         bytes_ = 2.0 * (args.M * args.K + args.N * args.K + args.M * args.N)
+    elif args.kernel == "gemm_fp8":
+        a = torch.randn(args.M, args.K, device=dev).bfloat16()
+        b = torch.randn(args.N, args.K, device=dev).bfloat16()
+        a8, sa = K.quantize_fp8(a)
+        b8, sb = K.quantize_fp8(b)
+        fn, flops = (lambda: K.gemm_fp8(a8, sa, b8, sb)), 2.0 * args.M * args.N * args.K
+        bytes_ = 1.0 * (args.M * args.K + args.N * args.K) + 2.0 * args.M * args.N
     elif args.kernel in ("sparse", "sparse_jvp"):
         from . import sparse as SP
 

@@ -65,6 +65,29 @@ def test_gemm_weight_gradient_splitk(K, rows, M, N):
     K.check_status()
 
 
+@pytest.mark.parametrize("M,N,Kd", [(256, 128, 128), (1000, 528, 256), (300, 200, 136), (4096, 768, 1024)])
+def test_gemm_fp8(K, M, N, Kd):
+    """e4m3 operands on the kind::f8f6f4 tensor path: exact against the same quantised values
+    multiplied in fp32, and within the reference's fp8 envelope (4e-2) of the unquantised product."""
+    torch.manual_seed(M)
+    A = torch.randn(M, Kd, device="cuda").bfloat16()
+    B = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    a8, sa = K.quantize_fp8(A)
+    b8, sb = K.quantize_fp8(B)
+    assert a8.shape == (M, (Kd + 15) // 16 * 16) and (a8[:, Kd:] == 0).all()
+    deq = lambda t8, s_: t8.view(torch.float8_e4m3fn).float() * s_
+    assert _rel(deq(a8, sa)[:, :Kd], A) < 4e-2 and float(sa) > 0
+    out = K.gemm_fp8(a8, sa, b8, sb, out_dtype=torch.float32, bias=bias)
+    exact = deq(a8, sa) @ deq(b8, sb).t() + bias
+    assert _rel(out, exact) < 1e-5
+    full = A.float() @ B.float().t() + bias
+    assert _rel(out, full) < 4e-2
+    y = K.linear_fp8(A, B, bias)
+    assert y.dtype == torch.bfloat16 and _rel(y, full) < 4e-2
+    K.check_status()
+
+
 def test_gemm_rejects_bad_stride(K):
     A = torch.randn(64, 12, device="cuda").bfloat16()      # K = 12: stride not 16-byte multiple
     with pytest.raises(ValueError):
