@@ -24,6 +24,12 @@
 
 namespace imf {
 
+#ifndef IMF_GEMM_WIDE_N
+#define IMF_GEMM_WIDE_N 1024
+#endif
+#ifndef IMF_GEMM_WIDE_K
+#define IMF_GEMM_WIDE_K 1280
+#endif
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_THREADS = 192;
@@ -421,6 +427,17 @@ extern "C" int imf_gemm_bf16(const void* A, const void* B, void* C, const float*
     if (a_mn && !b_mn) IMF_GEMM_CASE(true, false, float);
     IMF_GEMM_CASE(true, true, float);
   } else {
+    // wide, deep products: 128 x 256 tiles (one CTA per SM, three operand stages) halve the
+    // shared-memory traffic per flop of the A panel; short-K or narrow products keep two
+    // 128 x 128 CTAs per SM, which have more loads in flight
+    if (N >= IMF_GEMM_WIDE_N && K >= IMF_GEMM_WIDE_K) {
+#define IMF_GEMM_WIDE(AM, BM_)                                                              \
+  return launch_gemm<256, 3, AM, BM_, __nv_bfloat16>(                                       \
+      A, B, C, bias, M, N, K, lda, ldb, ldc, bias_rows, alpha, accumulate_out, status, st)
+      if (!a_mn && !b_mn) IMF_GEMM_WIDE(false, false);
+      if (!a_mn && b_mn) IMF_GEMM_WIDE(false, true);
+#undef IMF_GEMM_WIDE
+    }
     if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, __nv_bfloat16);
     if (!a_mn && b_mn) IMF_GEMM_CASE(false, true, __nv_bfloat16);
     if (a_mn && !b_mn) IMF_GEMM_CASE(true, false, __nv_bfloat16);

@@ -88,6 +88,21 @@ def test_gemm_fp8(K, M, N, Kd):
     K.check_status()
 
 
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("M,N,Kd", [(1000, 1024, 1536), (300, 1400, 2736)])
+def test_gemm_wide_tiles(K, M, N, Kd, b_mn):
+    """Wide and deep products take the 128 x 256 tile instance (ragged M and N included)."""
+    torch.manual_seed(N)
+    A = torch.randn(M, Kd, device="cuda").bfloat16()
+    B = (torch.randn(N, Kd, device="cuda") * 0.1).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    out = K.gemm(A, B.t().contiguous() if b_mn else B, b_mn=b_mn, bias=bias, bias_rows=M // 2)
+    ref = A.float() @ B.float().t()
+    ref[: M // 2] += bias
+    assert _rel(out, ref) < 4e-3
+    K.check_status()
+
+
 def test_gemm_rejects_bad_stride(K):
     A = torch.randn(64, 12, device="cuda").bfloat16()      # K = 12: stride not 16-byte multiple
     with pytest.raises(ValueError):
