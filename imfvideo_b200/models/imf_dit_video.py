@@ -387,7 +387,11 @@ class TransformerBlock(nn.Module):
                 "W_out": one(a.out_proj.weight),
                 "W13": [(mlp.w1.weight, 0, f, mlp.w1.weight.shape[1]),
                         (mlp.w3.weight, fp, f, mlp.w3.weight.shape[1])],
-                "W2": [(mlp.w2.weight, 0, mlp.w2.weight.shape[0], f)]})
+                "W2": [(mlp.w2.weight, 0, mlp.w2.weight.shape[0], f)]},
+                small={"g_n1": self.norm1.weight, "g_n2": self.norm2.weight,
+                       "g_qa": a.q_a_layernorm.weight, "g_kva": a.kv_a_layernorm.weight,
+                       "g_qn": a.q_norm.weight, "g_kn": a.k_norm.weight,
+                       "a_scale": self.attn_scale, "m_scale": self.mlp_scale})
         return sk
 
     def fused_forward(self, prefix: Dual, snaps, fresh: bool, use_res: bool, rope_cos, rope_sin,

@@ -61,12 +61,23 @@ class GradSinks:
     gradient for the matrices: no bf16 gradient tensors, no casts, no splits, no adds."""
 
     ORDER = ("W_a", "W_qb", "W_kvb", "W_out", "W13", "W2")
+    SMALL = ("g_n1", "g_n2", "g_qa", "g_kva", "g_qn", "g_kn", "a_scale", "m_scale")
 
-    def __init__(self, pieces):
+    def __init__(self, pieces, small=None):
         self.pieces = pieces
+        self.small = small or {}      # the 1-D parameters (gains, gates) by their role
         self.on_backward = None       # optional callable: this block's backward has begun
 
+    def small_dst(self, name: str):
+        """fp32 gradient buffer of the 1-D parameter in role ``name`` (flattened), or None."""
+        p = self.small.get(name)
+        if p is None or p.grad is None or p.grad.dtype != F32 or not p.grad.is_contiguous():
+            return None
+        return p.grad.view(-1)
+
     def direct(self) -> bool:
+        if any(self.small_dst(nm) is None for nm in self.SMALL):
+            return False
         for name in self.ORDER:
             for p, r0, _n, _c in self.pieces[name]:
                 g = p.grad
@@ -224,16 +235,23 @@ class _BlockFn(torch.autograd.Function):
         if getattr(ctx, "sinks", None) is not None and ctx.sinks.on_backward is not None:
             ctx.sinks.on_backward()
 
-        # 11'. out = p2 + m * mlp_scale
-        g_m, g_mscale = R.scale_add_bwd(m, m_scale, g_out, rows, d)
-        # 10'. MLP
         # data gradients dY W: W is [n_out, n_in] = [K, N], consumed MN-major as it is.
         # weight gradients dY^T X: split-K products (K = token rows), written straight into the
         # parameters' gradient buffers when they exist (`direct`), else returned to autograd.
+        # The gains' / gates' gradients come out of the row kernels as per-CTA partial sums; one
+        # launch at the end adds them all up, into the same kind of destination.
         sinks = getattr(ctx, "sinks", None)
         direct = sinks is not None and sinks.direct()
         wgrad = (lambda name, dy, x: sinks.accumulate(name, dy, x)) if direct else \
             (lambda name, dy, x: K.gemm_wgrad(dy, x).to(BF16))
+        cs = R.ColSums()
+        small = (lambda name, part, col, D: (cs.add(part, col, D, sinks.small_dst(name)), None)[1]) \
+            if direct else (lambda name, part, col, D: cs.add(part, col, D, None))
+
+        # 11'. out = p2 + m * mlp_scale
+        g_m, part_ms = R.scale_add_bwd(m, m_scale, g_out, rows, d, raw=True)
+        g_mscale = small("m_scale", part_ms, 0, d)
+        # 10'. MLP
         g_act = K.gemm(g_m, W2, b_mn=True)                          # [rows, fp]
         gW2 = wgrad("W2", g_m, act)
         g_gu = new(rows, 2 * g.fp)
@@ -242,9 +260,12 @@ class _BlockFn(torch.autograd.Function):
         gW13 = wgrad("W13", g_gu, n2)
         # 9'. residual + remix + norm2
         sn2 = sn + [pfx] if fresh else sn
-        g_res2, g_aout, g_sn2, gg_n2, g_w2, g_ascale = R.resnorm_bwd(
+        g_res2, g_aout, g_sn2, part2 = R.resnorm_bwd(
             None if fresh else pfx, a_out, a_scale, sn2, w2 if use_res else None, g_n2, eps,
-            g_n2v, g_out, want_g_res=not fresh)
+            g_n2v, g_out, want_g_res=not fresh, raw=True)
+        gg_n2 = small("g_n2", part2, 0, d)
+        g_w2 = cs.add(part2, 1, d, None) if use_res else None       # product of two parameters
+        g_ascale = small("a_scale", part2, 2, d)
         # 8'. output projection
         g_og = K.gemm(g_aout, W_out, b_mn=True)                     # [rows, hv]
         gW_out = wgrad("W_out", g_aout, og)
@@ -265,25 +286,33 @@ class _BlockFn(torch.autograd.Function):
                                gv_out=gkv4[..., g.dn:])
         # 5'. q / k preparation
         g_qb = new(rows, g.H * g.hd)
-        gg_qn, gg_kn = R.qkprep_bwd(qb, kvb, cos, sin, g_qn, g_kn, gq.contiguous(),
-                                    gk.contiguous(), g_qb, g_kvb, g_a[:, g.dq + g.dc:], rows, L,
-                                    g.H, g.dn, g.dr, g.dv, na, eps)
+        part_qk = R.qkprep_bwd(qb, kvb, cos, sin, g_qn, g_kn, gq.contiguous(),
+                                gk.contiguous(), g_qb, g_kvb, g_a[:, g.dq + g.dc:], rows, L,
+                                g.H, g.dn, g.dr, g.dv, na, eps, raw=True)
+        gg_qn = small("g_qn", part_qk, 0, g.dn)
+        gg_kn = small("g_kn", part_qk, 1, g.dn)
         # 4'. up-projections
         g_qlat = K.gemm(g_qb, W_qb, b_mn=True)
         gW_qb = wgrad("W_qb", g_qb, qlat)
         g_kvlat = K.gemm(g_kvb, W_kvb, b_mn=True)
         gW_kvb = wgrad("W_kvb", g_kvb, kvlat)
         # 3'. latent norms (write into the q / kv bands of g_a_)
-        gg_qa, gg_kva = R.rmsnorm_seg_bwd(
+        part_qa, part_kva = R.rmsnorm_seg_bwd(
             [(a_, g_qa, g_qlat, g_a, g.dq, na, g.dq),
-             (a_[:, g.dq:], g_kva, g_kvlat, g_a[:, g.dq:], g.dc, na, g.dc)], rows, eps)
+             (a_[:, g.dq:], g_kva, g_kvlat, g_a[:, g.dq:], g.dc, na, g.dc)], rows, eps, raw=True)
+        gg_qa = small("g_qa", part_qa, 0, g.dq)
+        gg_kva = small("g_kva", part_kva, 0, g.dc)
         # 2'. fused projection
         g_n1v = K.gemm(g_a, W_a, b_mn=True)
         gW_a = wgrad("W_a", g_a, n1)
         # 1'. remix + norm1; the prefix gradient of step 9' rides in as g_pfx_ext
         ext = g_sn2[-1] if fresh else g_res2
-        g_pfx, _, g_sn1, gg_n1, g_w1, _ = R.resnorm_bwd(
-            pfx, None, None, sn, w1 if (use_res and nsnap) else None, g_n1, eps, g_n1v, ext)
+        g_pfx, _, g_sn1, part1 = R.resnorm_bwd(
+            pfx, None, None, sn, w1 if (use_res and nsnap) else None, g_n1, eps, g_n1v, ext,
+            raw=True)
+        gg_n1 = small("g_n1", part1, 0, d)
+        g_w1 = cs.add(part1, 1, d, None) if (use_res and nsnap) else None
+        cs.flush()
         g_snaps = []
         for j in range(nsnap):
             g_snaps.append(g_sn1[j].add_(g_sn2[j]).view(B, L, d))

@@ -751,3 +751,47 @@ extern "C" int imf_elementwise(int op, void** p, const int* dims, float beta, fl
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+// ---------------------------------------------------------------------------
+// Column sums of the per-CTA partial gradients that the row kernels leave behind (gains,
+// gates, score weights): up to COLSUM_MAX vectors in ONE launch, each summed over its
+// partial rows in a fixed order and written -- or accumulated -- straight into its
+// destination (a parameter's gradient buffer).  Replaces one framework reduction plus one
+// gradient-accumulation add per vector.
+// ---------------------------------------------------------------------------
+namespace imf {
+constexpr int COLSUM_MAX = 12;
+struct ColSumEntry {
+  const float* part;     // first element of the column block: part[g * stride + d]
+  float* dst;            // [D]
+  int g, D, stride, accumulate;
+};
+struct ColSumArgs {
+  ColSumEntry e[COLSUM_MAX];
+};
+__global__ void __launch_bounds__(256) colsum_kernel(const __grid_constant__ ColSumArgs a) {
+  const ColSumEntry e = a.e[blockIdx.y];
+  const int d = blockIdx.x * 256 + threadIdx.x;
+  if (d >= e.D) return;
+  float acc = 0.f;
+  for (int i = 0; i < e.g; ++i) acc += e.part[(size_t)i * e.stride + d];
+  e.dst[d] = e.accumulate ? e.dst[d] + acc : acc;
+}
+}  // namespace imf
+
+// entries: host array of n records {const float* part, float* dst, int g, D, stride, accumulate}
+extern "C" int imf_colsum(const void* entries, int n, void* stream) {
+  if (n <= 0) return 0;
+  if (n > imf::COLSUM_MAX) return -1;
+  imf::ColSumArgs a;
+  int maxd = 0;
+  const imf::ColSumEntry* src = static_cast<const imf::ColSumEntry*>(entries);
+  for (int i = 0; i < imf::COLSUM_MAX; ++i) {
+    a.e[i] = src[i < n ? i : 0];
+    if (i < n && a.e[i].D > maxd) maxd = a.e[i].D;
+    if (i < n && (a.e[i].g <= 0 || a.e[i].D <= 0)) return -1;
+  }
+  imf::colsum_kernel<<<dim3((maxd + 255) / 256, n), 256, 0, (cudaStream_t)stream>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+

@@ -27,6 +27,9 @@ if K._has("imf_resnorm"):
                                      c_void_p]
     _lib.imf_qkprep.restype = c_int
     _lib.imf_qkprep.argtypes = [c_void_p] + [c_int] * 8 + [c_float, c_int, c_int, c_void_p]
+    if K._has("imf_colsum"):
+        _lib.imf_colsum.restype = c_int
+        _lib.imf_colsum.argtypes = [c_void_p, c_int, c_void_p]
     _lib.imf_elementwise.restype = c_int
     _lib.imf_elementwise.argtypes = [c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int,
                                      c_int, c_void_p]
@@ -72,9 +75,47 @@ def resnorm_fwd(res, dres, y, dy, gate, snaps: Sequence[torch.Tensor],
          "imf_resnorm fwd")
 
 
+class ColSums:
+    """Collects the partial-sum buffers of several row-kernel backward calls and reduces all
+    of them in one launch (``imf_colsum``), each straight into its destination: a parameter's
+    existing fp32 gradient buffer (accumulated) or a fresh tensor."""
+
+    MAX = 12
+
+    def __init__(self):
+        self.items = []        # (partial tensor, column index, D, dst tensor, accumulate)
+
+    def add(self, part: torch.Tensor, col: int, D: int, dst: Optional[torch.Tensor]):
+        """``part``: [g, C, D] or [g, D] fp32.  Returns the destination (a new tensor when
+        ``dst`` is None)."""
+        acc = dst is not None
+        if dst is None:
+            dst = torch.empty(D, dtype=F32, device=part.device)
+        self.items.append((part, col, D, dst, acc))
+        return dst
+
+    def flush(self) -> None:
+        import numpy as np
+
+        rec = np.dtype([("part", "<u8"), ("dst", "<u8"), ("g", "<i4"), ("D", "<i4"),
+                        ("stride", "<i4"), ("acc", "<i4")])
+        for i0 in range(0, len(self.items), self.MAX):
+            chunk = self.items[i0:i0 + self.MAX]
+            host = np.zeros(len(chunk), dtype=rec)
+            for i, (part, col, D, dst, acc) in enumerate(chunk):
+                stride = part.stride(0)
+                host[i] = (part.data_ptr() + 4 * col * D, dst.data_ptr(), part.shape[0], D, stride,
+                           int(acc))
+            _chk(_lib.imf_colsum(host.ctypes.data_as(ctypes.c_void_p), len(chunk), K._stream()),
+                 "imf_colsum")
+        self.items = []
+
+
 def resnorm_bwd(res, y, gate, snaps: Sequence[torch.Tensor], w, gain, eps: float, gn,
-                g_pfx_ext, want_g_res: bool = True):
-    """Returns (g_res fp32 | None, g_y bf16 | None, [g_snaps fp32], g_gain, g_w, g_gate)."""
+                g_pfx_ext, want_g_res: bool = True, raw: bool = False):
+    """Returns (g_res fp32 | None, g_y bf16 | None, [g_snaps fp32], g_gain, g_w, g_gate);
+    with ``raw`` the last three are replaced by the [g, 3, D] partial buffer (columns gain,
+    w, gate) for a later ``ColSums`` reduction."""
     rows, D = gn.shape
     dev = gn.device
     ns = len(snaps)
@@ -87,6 +128,8 @@ def resnorm_bwd(res, y, gate, snaps: Sequence[torch.Tensor], w, gain, eps: float
     ptrs += [_p(s) for s in snaps] + [0] * ns + [_p(s) for s in g_snaps]
     _chk(_lib.imf_resnorm(_ptr_array(ptrs), ns, rows, D, float(eps), 0, 1, K._stream()),
          "imf_resnorm bwd")
+    if raw:
+        return g_res, g_y, g_snaps, partial
     col = partial.sum(0)
     return g_res, g_y, g_snaps, col[0], (col[1] if w is not None else None), \
         (col[2] if y is not None else None)
@@ -104,8 +147,9 @@ def rmsnorm_seg_fwd(segs, rows: int, eps: float, has_t: bool) -> None:
                               int(has_t), 0, K._stream()), "imf_rmsnorm_seg fwd")
 
 
-def rmsnorm_seg_bwd(segs, rows: int, eps: float):
-    """segs: list of (x, gain, gy, gx, D, ld_x, ld_o); returns [g_gain per seg]."""
+def rmsnorm_seg_bwd(segs, rows: int, eps: float, raw: bool = False):
+    """segs: list of (x, gain, gy, gx, D, ld_x, ld_o); returns [g_gain per seg] (with ``raw``
+    the [g, D] partial buffers instead)."""
     ptrs, dims, parts = [], [], []
     g = row_grid(rows)
     for (x, gain, gy, gx, D, ld_x, ld_o) in segs:
@@ -115,7 +159,7 @@ def rmsnorm_seg_bwd(segs, rows: int, eps: float):
         dims += [D, ld_x, ld_o]
     _chk(_lib.imf_rmsnorm_seg(_ptr_array(ptrs), _ints(dims), len(segs), rows, float(eps), 0, 1,
                               K._stream()), "imf_rmsnorm_seg bwd")
-    return [p.sum(0) for p in parts]
+    return parts if raw else [p.sum(0) for p in parts]
 
 
 # ---------------------------------------------------------------- qk prep ---
@@ -128,12 +172,14 @@ def qkprep_fwd(qb, dqb, kvb, dkvb, kr, dkr, cos, sin, qg, kg, q, dq, k, dk, rows
 
 
 def qkprep_bwd(qb, kvb, cos, sin, qg, kg, gq, gk, g_qb, g_kvb, g_kr, rows, L, H, dn, dr, dv,
-               ld_gkr, eps):
+               ld_gkr, eps, raw: bool = False):
     part = torch.empty(row_grid(rows), 2, dn, dtype=F32, device=qb.device)
     ptrs = [_p(qb), 0, _p(kvb), 0, 0, 0, _p(cos), _p(sin), _p(qg), _p(kg), 0, 0, 0, 0, _p(gq),
             _p(gk), _p(g_qb), _p(g_kvb), _p(g_kr), _p(part)]
     _chk(_lib.imf_qkprep(_ptr_array(ptrs), rows, L, H, dn, dr, dv, 0, ld_gkr, float(eps), 0, 1,
                          K._stream()), "imf_qkprep bwd")
+    if raw:
+        return part            # [g, 2, dn]: columns q gain, k gain
     col = part.sum(0)
     return col[0], col[1]
 
@@ -175,10 +221,11 @@ def scale_add_fwd(res, dres, y, dy, gate, out, dout, rows, D) -> None:
     _ew(2, ptrs, [rows, D, D, D, D, 0, 0], has_t=int(dy is not None), name="scale_add fwd")
 
 
-def scale_add_bwd(y, gate, g_out, rows, D):
-    """Returns (g_y bf16, g_gate fp32); the gradient of `res` is g_out itself."""
+def scale_add_bwd(y, gate, g_out, rows, D, raw: bool = False):
+    """Returns (g_y bf16, g_gate fp32 -- the [g, D] partial buffer with ``raw``); the gradient
+    of `res` is g_out itself."""
     g_y = torch.empty(rows, D, dtype=BF16, device=y.device)
     part = torch.empty(row_grid(rows), D, dtype=F32, device=y.device)
     ptrs = [_p(y), 0, 0, 0, 0, 0, _p(gate), 0, 0, 0, 0, 0, _p(g_out), _p(g_y), 0, _p(part)]
     _ew(2, ptrs, [rows, D, D, D, D, D, D], bwd=1, name="scale_add bwd")
-    return g_y, part.sum(0)
+    return g_y, (part if raw else part.sum(0))
