@@ -414,11 +414,19 @@ class _LinearFn(torch.autograd.Function):
     def backward(ctx, gyp, _gyt):
         xp, w = ctx.saved_tensors
         g2 = gyp.reshape(-1, gyp.shape[-1])
+        x2 = xp.reshape(-1, xp.shape[-1])
         gx = gw = gb = None
+        # own GEMM when the operands meet its 16-byte rules (bf16, contiguous rows, widths
+        # that are multiples of 8); otherwise the framework's matmul
+        ok = (g2.dtype == torch.bfloat16 and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+              and g2.shape[1] % 8 == 0 and x2.shape[1] % 8 == 0)
+        if ok:
+            g2 = g2 if (g2.is_contiguous() and g2.data_ptr() % 16 == 0) else g2.contiguous()
+            x2 = x2 if (x2.is_contiguous() and x2.data_ptr() % 16 == 0) else x2.contiguous()
         if ctx.needs_input_grad[0]:
-            gx = (g2 @ w).view_as(xp)
+            gx = (gemm(g2, w, b_mn=True) if ok else g2 @ w).view_as(xp)
         if ctx.needs_input_grad[2]:
-            gw = g2.t() @ xp.reshape(-1, xp.shape[-1])
+            gw = gemm_wgrad(g2, x2).to(w.dtype) if ok else g2.t() @ x2
         if ctx.has_bias and ctx.needs_input_grad[3]:
             gb = g2.float().sum(0).to(g2.dtype)
         return gx, None, gw, gb
