@@ -40,6 +40,8 @@ constexpr int DQPANEL = QT * 128;    // bytes of one 32-float panel of the dQ st
 
 // TMEM columns
 constexpr int BC_S = 0, BC_DP = 64, BC_P = 128, BC_DQ = 192, BC_DK = 256, BC_DV = 384;
+// P^T is double-buffered (columns 128-159 and 160-191): the math warps write tile i+1 while the
+// dV MMA of tile i still reads its buffer, so they never wait for the tensor core's last tile
 
 struct Smem {
   alignas(1024) uint8_t k[2 * KPANEL];
@@ -52,7 +54,7 @@ struct Smem {
   alignas(16) float delta[QSTAGES][QT];
   uint64_t kv_full;
   uint64_t q_full[QSTAGES], q_empty[QSTAGES];
-  uint64_t s_full, s_taken, p_ready, p_free;
+  uint64_t s_full, s_taken, p_ready, p_free[2];
   uint64_t ds_free[2];
   uint64_t dq_full, dq_free;
   uint64_t final_bar;
@@ -107,7 +109,8 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     mbar_init(&s.s_full, 1);
     mbar_init(&s.s_taken, 8);      // one arrival per exp warp
     mbar_init(&s.p_ready, 8);
-    mbar_init(&s.p_free, 1);
+    mbar_init(&s.p_free[0], 1);
+    mbar_init(&s.p_free[1], 1);
     mbar_init(&s.ds_free[0], 1);
     mbar_init(&s.ds_free[1], 1);
     mbar_init(&s.dq_full, 1);
@@ -205,9 +208,9 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           // dV += P^T dO   (A = P^T in TMEM: 64 q as K -> 4 k-steps of 8 columns)
 #pragma unroll
           for (int ks = 0; ks < QT / 16; ++ks)
-            mma_ts(tmem + BC_DV, tmem + BC_P + ks * 8, sdesc_mnmajor(doa + ks * 2048, QPANEL),
-                   id_kn, (i | ks) != 0);
-          tc_commit(&s.p_free);
+            mma_ts(tmem + BC_DV, tmem + BC_P + (i & 1) * 32 + ks * 8,
+                   sdesc_mnmajor(doa + ks * 2048, QPANEL), id_kn, (i | ks) != 0);
+          tc_commit(&s.p_free[i & 1]);
           // dK += dS^T Q   (A = dS^T from smem, K-major: K = q)
 #pragma unroll
           for (int ks = 0; ks < QT / 16; ++ks)
@@ -319,14 +322,14 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         dk_[c / 2 + 1] = pack_bf16(p2 * (__uint_as_float(dp[c + 2]) - d4.z),
                                    p3 * (__uint_as_float(dp[c + 3]) - d4.w));
       }
-      // P^T goes to TMEM (A operand of the dV GEMM): dV of tile i-1 must have read it;
-      // dS^T goes to smem buffer i&1: the GEMMs of tile i-2 must have read it
-      if (i > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&s.p_free, (uint32_t)((i - 1) & 1), abort_flag,
-                                               p.status, STATUS_TIMEOUT_MMA));
+      // P^T goes to TMEM buffer i&1 (A operand of the dV GEMM) and dS^T to smem buffer i&1: the
+      // GEMMs of tile i-2 must have read them
+      if (i >= 2) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&s.p_free[i & 1], (uint32_t)(((i / 2) - 1) & 1),
+                                               abort_flag, p.status, STATUS_TIMEOUT_MMA));
         if (!ok) break;
       }
-      tmem_st16(tb + BC_P + wg * 16, pk);
+      tmem_st16(tb + BC_P + (i & 1) * 32 + wg * 16, pk);
       if (i >= 2) {
         ok = __all_sync(0xffffffffu,
                         mbar_wait(&s.ds_free[i & 1], (uint32_t)(((i / 2) - 1) & 1), abort_flag,
