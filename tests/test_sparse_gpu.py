@@ -326,3 +326,40 @@ def test_complement_mask_kernel_matches_scatter(SP):
         want[:, :, :cols] = cm.reshape(B * H, rows, cols)
         want[:, :, cp:cp + cols] = cm.reshape(B * H, rows, cols)
         assert got.dtype == torch.bfloat16 and torch.equal(got.float(), want)
+
+
+def test_sla2_sampler_kernels_vs_torch_formulas(SP):
+    """The few-step sampler of an SLA2 cube model (no-grad, primal-only kernels, INT8 score
+    grid) against the op-by-op torch path with the same routing: within the QAT tolerance."""
+    from imfvideo_b200.config import preset
+    from imfvideo_b200.loss import IMFVideoLoss
+    from imfvideo_b200.ops import cuda as cu
+    from imfvideo_b200.ops import kernels
+    from imfvideo_b200.train import build_model
+
+    cfg = preset("d256_sla2")
+    cfg.model.depth, cfg.model.aux_head_depth = 3, 1
+    cfg.model.sla2_topk = 0.25
+    cfg.data.latent_frames, cfg.data.latent_size = 8, (16, 32)
+    torch.manual_seed(0)
+    net, _, _ = build_model(cfg)
+    net = net.cuda().eval()
+    net.compute_dtype = torch.bfloat16
+    with torch.no_grad():
+        for p in net.parameters():
+            p.add_(torch.randn_like(p) * 0.03)
+    loss = IMFVideoLoss(net, cfg.model.num_classes, autocast_bf16=True)
+    g = torch.Generator(device="cuda").manual_seed(2)
+    z = torch.randn(1, 16, 8, 16, 32, device="cuda", generator=g)
+    y = torch.randint(0, 1000, (1,), device="cuda")
+    n0 = kernels.LAUNCHES.count
+    out_k = loss.sample(z, y, num_steps=4)
+    kernels.check_status()
+    assert kernels.LAUNCHES.count - n0 > 50
+    cu.disable("block")
+    try:
+        out_t = loss.sample(z, y, num_steps=4)
+    finally:
+        cu.enable("block")
+    assert torch.isfinite(out_k).all()
+    assert _rel(out_k, out_t) < 5e-2
