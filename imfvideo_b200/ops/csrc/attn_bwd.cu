@@ -521,13 +521,10 @@ __global__ void attn_bwd_combine_kernel(const float* __restrict__ part_dk,
 // Number of CTAs the query tiles of one K/V tile are split over (dense mode): the smallest
 // of 1..3 whose last wave wastes less than 6 % on this GPU.
 static int bwd_qsplit(int B, int L, int H) {
-  static int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-      sms = 148;
-  }
+  int dev = 0, sms = 0;        // of the current device (a host may hold GPUs of different sizes)
+  cudaGetDevice(&dev);
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    sms = 148;
   const long n_t = (L + BW_T - 1) / BW_T;
   const long items = n_t * H * B;
   int best = 1;

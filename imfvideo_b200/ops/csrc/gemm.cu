@@ -369,12 +369,18 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
   }
   auto kern = gemm_kernel<BN, STAGES, A_MN, B_MN, OutT, FP8>;
   const size_t smem = sizeof(GemmSmem<BN, STAGES, OutT>) + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // per device (the attribute belongs to the device's copy of the kernel)
+  constexpr int MAX_DEVICES = 64;
+  static bool attr_set[MAX_DEVICES] = {false};
+  static int sms_of[MAX_DEVICES] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int di = (dev >= 0 && dev < MAX_DEVICES) ? dev : 0;
+  if (!attr_set[di]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return IMF_ERR_LAUNCH;
-    attr_set = true;
+    attr_set[di] = true;
   }
   GemmTiles tiles;
   tiles.n_n = (N + BN - 1) / BN;
@@ -384,12 +390,11 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
   tiles.splits = splits > 1 ? (num_kb + tiles.kb_per - 1) / tiles.kb_per : 1;   // no empty slice
   if (splits > 1 && tiles.splits != splits) return IMF_ERR_ARG;
   tiles.total = tiles.n_n * tiles.n_m * (splits > 1 ? tiles.splits : batch);
-  static int sms = 0;
+  int sms = sms_of[di];
   if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       sms = 148;
+    sms_of[di] = sms;
   }
   // two persistent CTAs per SM when their shared memory allows it (256 TMEM columns each)
   const int per_sm = (2 * (smem + 1024) <= 233472) ? 2 : 1;

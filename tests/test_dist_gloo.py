@@ -137,3 +137,48 @@ def _heartbeat_rank(rank, world):
 def test_heartbeat_detects_lost_rank():
     res = _spawn(_heartbeat_rank, 2)
     assert res[0] == [1]
+
+
+def test_gradient_buckets_partition_the_arena():
+    """The per-block gradient buckets of the optimizer engine (what each rank reduces for
+    itself while backward runs) cover every parameter element exactly once, give every Muon
+    matrix to its owner rank and cut AdamW ranges at the shard boundaries -- for any world
+    size, built without communication (world = 3 here, single process)."""
+    import torch
+
+    from imfvideo_b200.config import preset
+    from imfvideo_b200.optim.moonlight import build_moonlight
+    from imfvideo_b200.parallel.flat_engine import FlatEngine
+    from imfvideo_b200.train import apply_lr_width_groups, build_model
+
+    cfg = preset("tiny")
+    cfg.model.attn_res_block_size = 1
+    net, _, _ = build_model(cfg)
+    opt = build_moonlight(net, lr=1e-3, weight_decay=0.1, coeff_mode="jordan")
+    apply_lr_width_groups(opt, net, cfg.model.hidden_size)
+    world = 3
+    eng = FlatEngine(opt, net, None, rank=1, world=world, mode="nccl_flat_like")
+    nblocks = len(net.shared_blocks) + len(net.u_heads) + len(net.v_heads)
+    assert len(eng.buckets) == nblocks + 1
+    cover = torch.zeros(eng.total, dtype=torch.int32)
+    shard = eng.adam_numel // world
+    for b in eng.buckets:
+        for start, numel, owner in b:
+            cover[start:start + numel] += 1
+            if start < eng.muon_total:
+                assert owner == start // eng.seg_pad            # the whole matrix sits in its owner's segment
+                assert (start + numel - 1) // eng.seg_pad == owner
+            else:
+                assert owner == (start - eng.muon_total) // shard
+                assert (start + numel - 1 - eng.muon_total) // shard == owner
+    used = torch.zeros(eng.total, dtype=torch.int32)
+    for i, (_, p) in enumerate(eng.muon):
+        used[eng.muon_off[i]:eng.muon_off[i] + p.numel()] = 1
+    for i, (_, p) in enumerate(eng.adam):
+        used[eng.adam_off[i]:eng.adam_off[i] + p.numel()] = 1
+    assert torch.equal(cover, used)                              # once each, padding untouched
+    # the parameters of block k are all in bucket k
+    blocks = list(net.shared_blocks) + list(net.u_heads) + list(net.v_heads)
+    for k, blk in enumerate(blocks):
+        n = sum(p.numel() for p in blk.parameters())
+        assert sum(numel for _, numel, _ in eng.buckets[k]) == n
