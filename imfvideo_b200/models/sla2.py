@@ -500,7 +500,7 @@ class SparseCore:
         lut, flags, cnt, fm = SP.route_tables(sel, self.qblk, q.shape[1])
         o_s, do_s, lse = SP.sparse_fwd(q, k, v, dq, dk, dv, lut, flags, self.qblk, self.int8,
                                        quant_p=self.int8, need_lse=True, cnt=cnt)
-        flags = fm          # reverse mode needs the nibble matrix, not the per-tile flags
+        flags = fm          # reverse mode needs the (K/V tile, query tile) maps, not the per-tile flags
         from ..ops import linattn as LA
 
         if LA.AVAILABLE:
@@ -561,8 +561,9 @@ class SparseCore:
                 _, _, qq = SP.quantize_blocks(K._tma_ok(q), self.qblk, want_q=False, want_fq=True)
                 _, _, kk = SP.quantize_blocks(K._tma_ok(k), 64, want_q=False, want_fq=True)
                 _, _, vv = SP.quantize_blocks(K._tma_ok(v), 64, want_q=False, want_fq=True)
-            qlist, qflags = SP.kv_lists(flags)      # `flags` holds the nibble matrix (see fwd)
-            gq_s, gk_s, gv_s = K.attn_bwd(qq, kk, vv, o_s, lse, g_os, qlist=qlist, qflags=qflags)
+            qlist, qflags, qrank = SP.kv_lists(flags, want_rank=True)   # `flags`: the maps (see fwd)
+            gq_s, gk_s, gv_s = K.attn_bwd(qq, kk, vv, o_s, lse, g_os, qlist=qlist, qflags=qflags,
+                                          qrank=qrank)
             back = lambda t: t.permute(0, 2, 1, 3)
             gq = (gq_s.float() + back(gq_l)).to(q.dtype)
             gk = (gk_s.float() + back(gk_l)).to(q.dtype)
@@ -599,8 +600,9 @@ def _sparse_core_bwd_kernels(self, q, k, v, saved, go, gv_out, alpha_param, cube
             _, _, qq = SP.quantize_blocks(K._tma_ok(q), self.qblk, want_q=False, want_fq=True)
             _, _, kk = SP.quantize_blocks(K._tma_ok(k), 64, want_q=False, want_fq=True)
             _, _, vv = SP.quantize_blocks(K._tma_ok(v), 64, want_q=False, want_fq=True)
-        qlist, qflags = SP.kv_lists(flags)          # `flags` holds the nibble matrix (see fwd)
-        gq_s, gk_s, gv_s = K.attn_bwd(qq, kk, vv, o_s, lse, g_os, qlist=qlist, qflags=qflags)
+        qlist, qflags, qrank = SP.kv_lists(flags, want_rank=True)       # `flags`: the maps (see fwd)
+        gq_s, gk_s, gv_s = K.attn_bwd(qq, kk, vv, o_s, lse, g_os, qlist=qlist, qflags=qflags,
+                                      qrank=qrank)
         gq = (gq_s.float() + gq_l).to(q.dtype)
         gk, gv = LA.backward_kv(q, k, v, gnum, gden, sel, gk_s, gv_s, self.qblk, self.bk,
                                 self.n_comp, gv_out=gv_out)

@@ -16,8 +16,16 @@
 // P^T can stay in TMEM as the A operand of the dV GEMM, and dK/dV accumulate
 // in TMEM for the whole walk.  dS^T goes through shared memory once and feeds
 // both the dK GEMM (K-major view) and the dQ GEMM (MN-major view).  dQ tiles
-// are added to an fp32 accumulator in global memory (red.global.add.v4.f32),
-// converted to bf16 by a small epilogue kernel.
+// are added to an fp32 accumulator in global memory by TMA (reduce-add),
+// converted to bf16 by a small epilogue kernel.  On request the adds to one
+// query tile happen in a FIXED order (a turn counter per query tile), so the
+// result is bit-identical from run to run: the grid is ordered so that a CTA
+// only ever waits for CTAs with a smaller linear block index (dispatched
+// before it), consecutive K/V tiles of one head are `chains` blocks apart, and
+// every CTA of a chain walks the query tiles in the same direction, so a CTA
+// runs about one tile behind its predecessor.  The resident CTAs of a chain
+// then move in lockstep at the pace of the slowest of them, which costs 13 %
+// of the kernel's time (dense, 29,140 tokens), hence an option.
 //
 // The per-query constants ride on the tensor core: the query tile carries Q * scale*log2e
 // and 16 extra K columns [-lse2_hi, -lse2_lo, 0 ...] (bf16 pair = fp32 to 2^-17), the K tile
@@ -84,6 +92,11 @@ struct BwParams {
   int qsplit;
   float* part_dk;
   float* part_dv;
+  // fixed-order dQ (null = adds land in arrival order): one counter per (batch, head, query
+  // tile), zeroed before the launch.  The CTA whose ordinal equals the counter adds its tile
+  // and then raises the counter.  Dense: ordinal = K/V tile index; block-sparse: qrank[entry]
+  int* turn;
+  const uint16_t* qrank;
 };
 
 IMF_DEVICE void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -109,13 +122,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // block-sparse lists can be very uneven (the always-attended tail tiles are attended by every
   // query tile and sit at the end): walk the K/V tiles from the back so the long ones start first
-  const int kvb = p.qlist ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z / p.qsplit;
-  const int qpart = blockIdx.z % p.qsplit;
-  const size_t lrow = (((size_t)b * p.H + h) * gridDim.x + kvb) * (size_t)p.qmax;
+  // grid = (chains, K/V tiles): blockIdx.x = head + H * (batch * qsplit + part) varies fastest,
+  // so the resident CTAs are a few K/V tiles of EVERY chain rather than many of one
+  const int kvb = p.qlist ? (int)(gridDim.y - 1 - blockIdx.y) : (int)blockIdx.y;
+  const int h = blockIdx.x % p.H, bz = blockIdx.x / p.H;
+  const int b = bz / p.qsplit, qpart = bz % p.qsplit;
+  const size_t lrow = (((size_t)b * p.H + h) * gridDim.y + kvb) * (size_t)p.qmax;
   const int* qlist = p.qlist ? p.qlist + lrow : nullptr;
   const uint8_t* qflags = p.qflags ? p.qflags + lrow : nullptr;
+  const uint16_t* qrank = (p.qlist && p.qrank) ? p.qrank + lrow : nullptr;
   int n_q = (p.L + BW_T - 1) / BW_T;       // query tiles this CTA walks over
+  int* turn = p.turn ? p.turn + ((size_t)b * p.H + h) * n_q : nullptr;
   int q_first = 0;                          // dense: they are q_first .. q_first + n_q - 1
   if (qlist) {
     n_q = 0;
@@ -267,6 +284,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int wl = warp & 3;
     const uint32_t tb = tmem_addr(tmem, wl * 32, BC_DQ);
     bool ok = true;
+    bool turn_live = true;          // false once a turn wait gave up (the status word says so)
+    int prev_qt = -1, prev_ord = 0;
     for (int i = 0; i < n_q && ok; ++i) {
       ok = __all_sync(0xffffffffu, mbar_wait(&s.dq_full, (uint32_t)(i & 1), abort_flag, p.status,
                                              STATUS_TIMEOUT_MMA));
@@ -281,8 +300,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (lane == 0) mbar_arrive(&s.dq_free);
       // stage the tile in shared memory (plain [128][64] fp32) and let TMA add it to
       // the fp32 accumulator in global memory: coalesced, asynchronous, rows >= L clipped
+      const int qt = qlist ? qlist[i] : q_first + i;
       if (i > 0) {
-        if (threadIdx.x == 8 * 32) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (threadIdx.x == 8 * 32) {
+          if (turn && turn_live) {
+            // the previous add has been performed (it had the time of this tile's TMEM read):
+            // pass its query tile on.  Measured faster than passing it one tile later.
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            turn_pass(turn + prev_qt, prev_ord + 1);
+          } else {
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          }
+        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
       // two 128-byte-swizzled panels [128 rows][32 floats] (columns 0-31 / 32-63)
@@ -296,19 +325,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       fence_proxy_async_smem();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 8 * 32) {
+        const int ord = qrank ? (int)qrank[i] : kvb;
+        if (turn && turn_live) turn_live = turn_wait(turn + qt, ord, abort_flag, p.status);
+        if (!turn || turn_live) {
 #pragma unroll
-        for (int pnl = 0; pnl < 2; ++pnl)
-          asm volatile(
-              "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group"
-              " [%0, {%2, %3, %4, %5}], [%1];"
-              ::"l"(reinterpret_cast<uint64_t>(&tm_dq)),
-              "r"(smem_u32(stage + pnl * (BW_T * 128))), "r"(pnl * 32), "r"(h),
-              "r"((qlist ? qlist[i] : q_first + i) * BW_T), "r"(b)
-              : "memory");
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          for (int pnl = 0; pnl < 2; ++pnl)
+            asm volatile(
+                "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group"
+                " [%0, {%2, %3, %4, %5}], [%1];"
+                ::"l"(reinterpret_cast<uint64_t>(&tm_dq)),
+                "r"(smem_u32(stage + pnl * (BW_T * 128))), "r"(pnl * 32), "r"(h), "r"(qt * BW_T),
+                "r"(b)
+                : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        prev_qt = qt;
+        prev_ord = ord;
       }
     }
-    if (threadIdx.x == 8 * 32) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (threadIdx.x == 8 * 32) {
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      if (turn && turn_live && n_q > 0 && prev_qt >= 0) turn_pass(turn + prev_qt, prev_ord + 1);
+    }
   } else {
     // ---------------------------------------------------- exp / dS math ----
     asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
@@ -558,8 +596,9 @@ extern "C" long imf_attn_bwd_scratch_bytes(int B, int L, int H) {
   const long Lp = ((L + 127) / 128) * 128;
   const int qs = imf::bwd_qsplit(B, L, H);
   const long part = qs > 1 ? 2L * qs * B * L * H * 64 * 4 : 0;
-  return (long)B * L * H * 64 * 4 + 2 * (long)B * H * Lp * 32 + (long)B * L * H * 64 * 2 + 1024 +
-         part;
+  const long turns = (long)B * H * (Lp / 128) * 4 + 256;     // fixed-order dQ: one counter per query tile
+  return (long)B * L * H * 64 * 4 + turns + 2 * (long)B * H * Lp * 32 + (long)B * L * H * 64 * 2 +
+         1024 + part;
 }
 
 // Same for either head_dim (64 or 128).
@@ -576,8 +615,9 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
                             int L, int H, int head_dim, const int64_t* strides,
                             const int64_t* o_strides, const int64_t* dk_strides,
                             const int64_t* dv_strides, float scale, void* scratch,
-                            long scratch_bytes, const int* qlist, const uint8_t* qflags, int qmax,
-                            int* status, void* stream) {
+                            long scratch_bytes, const int* qlist, const uint8_t* qflags,
+                            const uint16_t* qrank, int qmax, int fixed_order, int* status,
+                            void* stream) {
   using namespace imf;
   if ((head_dim != BW_HD && head_dim != 128) || B <= 0 || L <= 0 || H <= 0) return IMF_ERR_ARG;
   if (head_dim == 128) {
@@ -589,7 +629,8 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
       if ((dk_strides[i] & 7) || (dv_strides[i] & 7) || (o_strides[i] & 3) || (strides[9 + i] & 3))
         return IMF_ERR_ARG;
     Bwd128Args a{q, k, v, o, d_o, lse, dq, dk, dv, B, L, H, strides, o_strides, dk_strides,
-                 dv_strides, scale, scratch, scratch_bytes, status, stream};
+                 dv_strides, scale, scratch, scratch_bytes, status, stream,
+                 fixed_order && status != nullptr};
     return attn_bwd128_launch(a);
   }
   if (scratch == nullptr || scratch_bytes < imf_attn_bwd_scratch_bytes(B, L, H)) return IMF_ERR_ARG;
@@ -601,8 +642,13 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int Lp = ((L + 127) / 128) * 128;
   float* dq_acc = static_cast<float*>(scratch);
-  const size_t acc_bytes = (size_t)B * L * H * 64 * 4;
-  uint8_t* cur = static_cast<uint8_t*>(scratch) + ((acc_bytes + 255) & ~size_t(255));
+  const size_t acc_bytes = ((size_t)B * L * H * 64 * 4 + 255) & ~size_t(255);
+  // the turn counters follow the accumulator, so one memset clears both.  Fixed order needs a
+  // status word (how a CTA that gave up tells the others) and, block-sparse, the rank table
+  const bool ordered = fixed_order && status != nullptr && (qlist == nullptr || qrank != nullptr);
+  int* turn = reinterpret_cast<int*>(static_cast<uint8_t*>(scratch) + acc_bytes);
+  const size_t turn_bytes = ((size_t)B * H * (Lp / 128) * 4 + 255) & ~size_t(255);
+  uint8_t* cur = static_cast<uint8_t*>(scratch) + acc_bytes + turn_bytes;
   uint32_t* augq = reinterpret_cast<uint32_t*>(cur);
   cur += (size_t)B * H * Lp * 32;
   uint32_t* augd = reinterpret_cast<uint32_t*>(cur);
@@ -616,7 +662,7 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
     part_dk = reinterpret_cast<float*>(cur);
     part_dv = part_dk + (size_t)qsplit * B * L * H * 64;
   }
-  if (cudaMemsetAsync(dq_acc, 0, acc_bytes, st) != cudaSuccess) return IMF_ERR_LAUNCH;
+  if (cudaMemsetAsync(dq_acc, 0, acc_bytes + turn_bytes, st) != cudaSuccess) return IMF_ERR_LAUNCH;
   {
     const long warps = (long)B * H * Lp;
     const int threads = 256;
@@ -666,11 +712,13 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
   prm.qsplit = qsplit;
   prm.part_dk = part_dk;
   prm.part_dv = part_dv;
+  prm.turn = ordered ? turn : nullptr;
+  prm.qrank = ordered ? qrank : nullptr;
   const size_t smem = sizeof(BwSmem) + 1024;
   if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem) != cudaSuccess)
     return IMF_ERR_LAUNCH;
-  dim3 grid((L + BW_T - 1) / BW_T, H, B * qsplit);
+  dim3 grid(H * B * qsplit, (L + BW_T - 1) / BW_T, 1);
   attn_bwd_kernel<<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, mdq, maq, mad, prm);
   if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   if (qsplit > 1) {

@@ -76,6 +76,9 @@ struct Params {
   int qsplit;
   float* part_dk;
   float* part_dv;
+  // fixed-order dQ (null = arrival order): one counter per (batch, head, 64-row query step),
+  // zeroed before the launch; the CTA of K/V tile j adds when the counter shows j
+  int* turn;
 };
 
 IMF_DEVICE void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -93,10 +96,14 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   auto& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                      ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kvb = (int)blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z / p.qsplit;
-  const int qpart = blockIdx.z % p.qsplit;
+  // grid = (chains, K/V tiles) with blockIdx.x = head + H * (batch * qsplit + part) fastest: a
+  // CTA waits (fixed-order dQ) only for the K/V tile before it in its chain, whose block index
+  // is smaller, and the resident CTAs are a few tiles of every chain
+  const int kvb = (int)blockIdx.y;
+  const int h = blockIdx.x % p.H, bz = blockIdx.x / p.H;
+  const int b = bz / p.qsplit, qpart = bz % p.qsplit;
   int n_q = (p.L + QT - 1) / QT;
+  int* turn = p.turn ? p.turn + ((size_t)b * p.H + h) * n_q : nullptr;
   const int q_first = (int)((long)qpart * n_q / p.qsplit);
   n_q = (int)((long)(qpart + 1) * n_q / p.qsplit) - q_first;
 
@@ -241,6 +248,7 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const uint32_t tb = tmem_addr(tmem, wl * 32, BC_DQ);
     uint8_t* panel = s.dq_stage + wl * DQPANEL;
     bool ok = true;
+    bool turn_live = true;          // false once a turn wait gave up (the status word says so)
     for (int i = 0; i < n_q && ok; ++i) {
       ok = __all_sync(0xffffffffu, mbar_wait(&s.dq_full, (uint32_t)(i & 1), abort_flag, p.status,
                                              STATUS_TIMEOUT_MMA));
@@ -267,19 +275,31 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       fence_proxy_async_smem();
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (threadIdx.x == 8 * 32) {
+        if (turn && turn_live) turn_live = turn_wait(turn + q_first + i, kvb, abort_flag, p.status);
+        if (!turn || turn_live) {
 #pragma unroll
-        for (int pnl = 0; pnl < 4; ++pnl)
-          asm volatile(
-              "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group"
-              " [%0, {%2, %3, %4, %5}], [%1];"
-              ::"l"(reinterpret_cast<uint64_t>(&tm_dq)),
-              "r"(smem_u32(s.dq_stage + pnl * DQPANEL)), "r"(pnl * 32), "r"(h),
-              "r"((q_first + i) * QT), "r"(b)
-              : "memory");
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          for (int pnl = 0; pnl < 4; ++pnl)
+            asm volatile(
+                "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group"
+                " [%0, {%2, %3, %4, %5}], [%1];"
+                ::"l"(reinterpret_cast<uint64_t>(&tm_dq)),
+                "r"(smem_u32(s.dq_stage + pnl * DQPANEL)), "r"(pnl * 32), "r"(h),
+                "r"((q_first + i) * QT), "r"(b)
+                : "memory");
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        // the add before this one has had a whole step's time to be performed: once it has,
+        // pass its query rows on (this add stays in flight)
+        if (turn && turn_live && i > 0) {
+          asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");
+          turn_pass(turn + q_first + i - 1, kvb + 1);
+        }
       }
     }
-    if (threadIdx.x == 8 * 32) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (threadIdx.x == 8 * 32) {
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      if (turn && turn_live && ok && n_q > 0) turn_pass(turn + q_first + n_q - 1, kvb + 1);
+    }
   } else {
     // ------------------------------------------------------ exp / dS math ----
     asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
@@ -511,7 +531,8 @@ long attn_bwd128_scratch_bytes(int B, int L, int H) {
   const long Lp = ((L + 127) / 128) * 128;
   const int qs = b128::qsplit_for(B, L, H);
   const long part = qs > 1 ? 2L * qs * B * L * H * b128::HD * 4 : 0;
-  return (long)B * L * H * b128::HD * 4 + 2 * (long)B * H * Lp * 4 + 512 + part;
+  const long turns = (long)B * H * (Lp / b128::QT) * 4 + 256;   // fixed-order dQ counters
+  return (long)B * L * H * b128::HD * 4 + turns + 2 * (long)B * H * Lp * 4 + 512 + part;
 }
 
 int attn_bwd128_launch(const Bwd128Args& a) {
@@ -521,8 +542,11 @@ int attn_bwd128_launch(const Bwd128Args& a) {
   cudaStream_t st = static_cast<cudaStream_t>(a.stream);
   const int Lp = ((L + 127) / 128) * 128;
   float* dq_acc = static_cast<float*>(a.scratch);
-  const size_t acc_bytes = (size_t)B * L * H * HD * 4;
-  float* lse2 = reinterpret_cast<float*>(static_cast<uint8_t*>(a.scratch) + ((acc_bytes + 255) & ~size_t(255)));
+  const size_t acc_bytes = ((size_t)B * L * H * HD * 4 + 255) & ~size_t(255);
+  // the turn counters follow the accumulator, so one memset clears both
+  int* turn = reinterpret_cast<int*>(static_cast<uint8_t*>(a.scratch) + acc_bytes);
+  const size_t turn_bytes = ((size_t)B * H * (Lp / QT) * 4 + 255) & ~size_t(255);
+  float* lse2 = reinterpret_cast<float*>(static_cast<uint8_t*>(a.scratch) + acc_bytes + turn_bytes);
   float* delta = lse2 + (size_t)B * H * Lp;
   const int qsplit = qsplit_for(B, L, H);
   float* part_dk = nullptr;
@@ -532,7 +556,7 @@ int attn_bwd128_launch(const Bwd128Args& a) {
     part_dk = reinterpret_cast<float*>(end);
     part_dv = part_dk + (size_t)qsplit * B * L * H * HD;
   }
-  if (cudaMemsetAsync(dq_acc, 0, acc_bytes, st) != cudaSuccess) return IMF_ERR_LAUNCH;
+  if (cudaMemsetAsync(dq_acc, 0, acc_bytes + turn_bytes, st) != cudaSuccess) return IMF_ERR_LAUNCH;
   {
     const long warps = (long)B * H * Lp;
     const int threads = 256;
@@ -568,13 +592,14 @@ int attn_bwd128_launch(const Bwd128Args& a) {
   prm.scale = a.scale;
   prm.status = a.status;
   prm.qsplit = qsplit;
+  prm.turn = (a.fixed_order && a.status != nullptr) ? turn : nullptr;
   prm.part_dk = part_dk;
   prm.part_dv = part_dv;
   const size_t smem = sizeof(Smem) + 1024;
   if (cudaFuncSetAttribute(attn_bwd128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem) != cudaSuccess)
     return IMF_ERR_LAUNCH;
-  dim3 grid((L + KT - 1) / KT, H, B * qsplit);
+  dim3 grid(H * B * qsplit, (L + KT - 1) / KT, 1);
   attn_bwd128_kernel<<<grid, THREADS, smem, st>>>(mq, mk, mv, mdo, mdq, prm);
   if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   if (qsplit > 1) {

@@ -19,6 +19,7 @@ struct Bwd128Args {
   long scratch_bytes;
   int* status;
   void* stream;
+  bool fixed_order;                       // dQ adds in a fixed order (needs `status`)
 };
 
 long attn_bwd128_scratch_bytes(int B, int L, int H);

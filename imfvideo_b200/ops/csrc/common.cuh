@@ -45,6 +45,7 @@ enum : int {
   STATUS_TIMEOUT_EMPTY = 4,   // producer waited too long for a free stage
   STATUS_BAD_ARG = 5,
   STATUS_TIMEOUT_PEER = 6,    // waited too long for another rank's flag
+  STATUS_TIMEOUT_TURN = 7,    // waited too long for its turn in a fixed-order accumulation
 };
 
 // -------------------------------------------------------------- mbarrier ---
@@ -112,6 +113,37 @@ IMF_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_fl
       }
     }
   }
+}
+
+// Fixed-order accumulation: wait (bounded) until the counter of a query tile shows this CTA's
+// ordinal / hand the tile on after this CTA's add has been performed.  A CTA that gives up
+// records it in the status word; everyone else who is waiting sees the word and gives up too.
+IMF_DEVICE bool turn_wait(const int* addr, int want, volatile int* abort_flag, int* status) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    if (v == want) {
+      asm volatile("fence.proxy.async.global;" ::: "memory");   // the add that follows is a TMA op
+      return true;
+    }
+    if ((++spins & 31u) == 0) {
+      if (*abort_flag) return false;
+      if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > IMF_WAIT_LIMIT_NS) {
+        if (status) atomicCAS(status, 0, STATUS_TIMEOUT_TURN);
+        return false;
+      }
+    }
+  }
+}
+IMF_DEVICE void turn_pass(int* addr, int value) {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(addr), "r"(value) : "memory");
 }
 
 // ------------------------------------------------------------------ TMA ----

@@ -51,11 +51,13 @@ __device__ __forceinline__ int block_excl_scan(int v, int* total) {
 
 // sel: (B, H, Mb, T) int32 key-block ids (-1 = none).  rpt = routing blocks per query tile
 // (1 or 2).  Outputs: lut / flags (B, H, n_mt, tmax), cnt (B, H, n_mt), fm (B, H, n_kvt, n_mt)
-// nibble matrix (may be null).
+// nibble matrix (may be null) and rk (same shape, may be null): for a live (K/V tile, query
+// tile) pair, how many HIGHER K/V tiles also attend the query tile -- the backward's place in
+// the fixed order of additions to that query tile (it walks the K/V tiles from the back).
 __global__ void __launch_bounds__(RT_THREADS)
 tile_lut_kernel(const int* __restrict__ sel, int* __restrict__ lut, uint8_t* __restrict__ flags,
-                int* __restrict__ cnt, uint8_t* __restrict__ fm, int H, int Mb, int T, int rpt,
-                int n_mt, int tmax, int n_kblk, int n_kvt) {
+                int* __restrict__ cnt, uint8_t* __restrict__ fm, uint16_t* __restrict__ rk, int H,
+                int Mb, int T, int rpt, int n_mt, int tmax, int n_kblk, int n_kvt) {
   __shared__ unsigned int bm[2][RT_MAX_WORDS];
   const int mt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x;
@@ -110,12 +112,29 @@ tile_lut_kernel(const int* __restrict__ sel, int* __restrict__ lut, uint8_t* __r
       }
     }
   }
+  if (rk) {                      // block-uniform
+    const unsigned int both = b0 | b1;
+    const unsigned int pairs = (both | (both >> 1)) & 0x55555555u;   // bit 2 pp: K/V tile live
+    int live_total;
+    int below = block_excl_scan(__popc(pairs), &live_total);          // live K/V tiles before mine
+    if (tid < words) {
+#pragma unroll
+      for (int pp = 0; pp < 16; ++pp) {
+        const int kvt = tid * 16 + pp;
+        if (kvt < n_kvt && ((pairs >> (2 * pp)) & 1u)) {
+          rk[(((size_t)b * H + h) * n_kvt + kvt) * n_mt + mt] = (uint16_t)(live_total - 1 - below);
+          ++below;
+        }
+      }
+    }
+  }
 }
 
 // fm: (B, H, n_kvt, n_mt) nibbles -> qlist / qflags (B, H, n_kvt, qmax), -1 terminated.
 __global__ void __launch_bounds__(RT_THREADS)
-kv_lists_kernel(const uint8_t* __restrict__ fm, int* __restrict__ qlist,
-                uint8_t* __restrict__ qflags, int n_mt, int qmax) {
+kv_lists_kernel(const uint8_t* __restrict__ fm, const uint16_t* __restrict__ rk,
+                int* __restrict__ qlist, uint8_t* __restrict__ qflags,
+                uint16_t* __restrict__ qrank, int n_mt, int qmax) {
   const size_t rowi = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
   const uint8_t* row = fm + rowi * n_mt;
   const int tid = threadIdx.x;
@@ -131,6 +150,7 @@ kv_lists_kernel(const uint8_t* __restrict__ fm, int* __restrict__ qlist,
       if (pos < qmax) {
         qlist[rowi * qmax + pos] = i;
         qflags[rowi * qmax + pos] = f;
+        if (qrank) qrank[rowi * qmax + pos] = rk[rowi * n_mt + i];
       }
       ++pos;
     }
@@ -372,21 +392,23 @@ extern "C" int imf_route_topk(const float* qb, const float* kb, const float* Pq,
 }
 
 extern "C" int imf_build_tile_lut(const int* sel, int* lut, uint8_t* flags, int* cnt, uint8_t* fm,
-                                  int B, int H, int Mb, int T, int qblk, int L, int tmax,
-                                  void* stream) {
+                                  uint16_t* rk, int B, int H, int Mb, int T, int qblk, int L,
+                                  int tmax, void* stream) {
   if (B <= 0 || H <= 0 || Mb <= 0 || T <= 0 || (qblk != 64 && qblk != 128)) return -1;
   const int rpt = 128 / qblk;
   const int n_mt = (L + 127) / 128, n_kblk = (L + 63) / 64, n_kvt = (L + 127) / 128;
   if (n_kblk > RT_MAX_WORDS * 32 || tmax < 1) return -4;
   tile_lut_kernel<<<dim3(n_mt, H, B), RT_THREADS, 0, (cudaStream_t)stream>>>(
-      sel, lut, flags, cnt, fm, H, Mb, T, rpt, n_mt, tmax, n_kblk, n_kvt);
+      sel, lut, flags, cnt, fm, rk, H, Mb, T, rpt, n_mt, tmax, n_kblk, n_kvt);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-extern "C" int imf_build_kv_lists(const uint8_t* fm, int* qlist, uint8_t* qflags, int B, int H,
-                                  int n_kvt, int n_mt, int qmax, void* stream) {
+extern "C" int imf_build_kv_lists(const uint8_t* fm, const uint16_t* rk, int* qlist,
+                                  uint8_t* qflags, uint16_t* qrank, int B, int H, int n_kvt,
+                                  int n_mt, int qmax, void* stream) {
   if (B <= 0 || H <= 0 || n_kvt <= 0 || n_mt <= 0 || qmax <= 0) return -1;
-  kv_lists_kernel<<<dim3(n_kvt, H, B), RT_THREADS, 0, (cudaStream_t)stream>>>(fm, qlist, qflags,
-                                                                             n_mt, qmax);
+  if ((rk == nullptr) != (qrank == nullptr)) return -1;
+  kv_lists_kernel<<<dim3(n_kvt, H, B), RT_THREADS, 0, (cudaStream_t)stream>>>(
+      fm, rk, qlist, qflags, qrank, n_mt, qmax);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

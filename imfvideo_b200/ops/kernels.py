@@ -9,6 +9,7 @@ bounded wait through a per-device status word (``check_status``).
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from typing import Dict, Optional, Sequence, Tuple
 
@@ -23,7 +24,8 @@ c_void_p, c_int, c_int64, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_int6
 
 STATUS_NAMES = {0: "ok", 1: "timeout waiting for a TMA load", 2: "timeout waiting for tcgen05 MMA",
                 3: "timeout waiting for softmax warps", 4: "timeout waiting for a free stage",
-                5: "bad argument", 6: "timeout waiting for a peer rank"}
+                5: "bad argument", 6: "timeout waiting for a peer rank",
+                7: "timeout waiting for a turn in the fixed-order dQ accumulation"}
 _ERR = {-1: "bad shape/stride/alignment", -2: "tensor-map encode failed",
         -3: "kernel launch failed", -4: "size beyond the supported maximum"}
 
@@ -287,21 +289,36 @@ def attn_fwd(q, k, v, dq=None, dk=None, dv=None, scale: Optional[float] = None,
 if _has("imf_attn_bwd"):
     _lib.imf_attn_bwd.restype = c_int
     _lib.imf_attn_bwd.argtypes = [c_void_p] * 9 + [c_int] * 4 + [c_void_p] * 4 + \
-        [c_float, c_void_p, ctypes.c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+        [c_float, c_void_p, ctypes.c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+         c_void_p]
     _lib.imf_attn_bwd_scratch_bytes.restype = ctypes.c_long
     _lib.imf_attn_bwd_scratch_bytes.argtypes = [c_int, c_int, c_int]
     _lib.imf_attn_bwd_scratch_bytes_hd.restype = ctypes.c_long
     _lib.imf_attn_bwd_scratch_bytes_hd.argtypes = [c_int, c_int, c_int, c_int]
 
 
+# True: the dQ tiles of the attention backward are added in a fixed order, which makes a whole
+# training step bit-identical from run to run (every other reduction of the library already has
+# a fixed order) at 13 % (head_dim 64) to 34 % (head_dim 128) of that kernel's time.  False
+# (default; IMF_DETERMINISTIC=1 in the environment or ``run.deterministic`` in the config turn
+# it on): the tiles land in arrival order.
+DETERMINISTIC = os.environ.get("IMF_DETERMINISTIC", "0") == "1"
+
+
+def set_deterministic(on: bool) -> None:
+    global DETERMINISTIC
+    DETERMINISTIC = bool(on)
+
+
 def attn_bwd(q, k, v, o, lse, go, scale: Optional[float] = None,
              gv_out: Optional[torch.Tensor] = None, qlist: Optional[torch.Tensor] = None,
-             qflags: Optional[torch.Tensor] = None):
+             qflags: Optional[torch.Tensor] = None, qrank: Optional[torch.Tensor] = None):
     """(dq, dk, dv) of dense attention; ``gv_out`` lets dv land in a strided
     view (e.g. the value band of the kv up-projection gradient).  With
-    ``qlist`` / ``qflags`` (see ``ops.sparse.build_kv_lists``) the same kernel
+    ``qlist`` / ``qflags`` (see ``ops.sparse.kv_lists``) the same kernel
     runs the block-sparse backward: each 128-row K/V tile walks only the query
-    tiles that attend it."""
+    tiles that attend it; ``qrank`` (same source) gives the entries' places in the fixed
+    order of dQ additions (without it the block-sparse dQ adds land in arrival order)."""
     B, L, H, hd = q.shape
     scale = 1.0 / math.sqrt(hd) if scale is None else scale
     ts = [_tma_ok(t) for t in (q, k, v, go)]
@@ -323,8 +340,8 @@ def attn_bwd(q, k, v, o, lse, go, scale: Optional[float] = None,
                            _ptr(lse), _ptr(dq), _ptr(dk), _ptr(dv), B, L, H, hd,
                            ctypes.cast(arr, c_void_p), ctypes.cast(i3(o), c_void_p),
                            ctypes.cast(i3(dk), c_void_p), ctypes.cast(i3(dv), c_void_p),
-                           float(scale), _ptr(scr), nscr, _ptr(qlist), _ptr(qflags),
-                           0 if qlist is None else qlist.shape[-1],
+                           float(scale), _ptr(scr), nscr, _ptr(qlist), _ptr(qflags), _ptr(qrank),
+                           0 if qlist is None else qlist.shape[-1], int(DETERMINISTIC),
                            _ptr(status_word(q.device)), _stream())
     _check(rc, "imf_attn_bwd")
     LAUNCHES.count += 3

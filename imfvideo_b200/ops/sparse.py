@@ -25,9 +25,9 @@ if K._has("imf_attn_sparse_fwd"):
 
 if K._has("imf_build_tile_lut"):
     _lib.imf_build_tile_lut.restype = ci
-    _lib.imf_build_tile_lut.argtypes = [vp] * 5 + [ci] * 7 + [vp]
+    _lib.imf_build_tile_lut.argtypes = [vp] * 6 + [ci] * 7 + [vp]
     _lib.imf_build_kv_lists.restype = ci
-    _lib.imf_build_kv_lists.argtypes = [vp] * 3 + [ci] * 5 + [vp]
+    _lib.imf_build_kv_lists.argtypes = [vp] * 5 + [ci] * 5 + [vp]
 
 
 ROUTER_KERNELS = K._has("imf_route_topk")
@@ -79,8 +79,11 @@ def route_topk(qb: torch.Tensor, kb: torch.Tensor, T: int, proj_q: Optional[torc
 def route_tables(sel: torch.Tensor, qblk: int, L: int):
     """Device-built routing tables from the selection ``sel`` (B, H, Mb, T): the per-tile
     key-block lists of ``build_tile_lut`` (ascending, -1 padded), their flags, the entry
-    counts, and the (B, H, n_kvt, n_mt) nibble matrix the inverted lists are made from.
-    One launch, no host synchronisation."""
+    counts, and the maps the inverted lists are made from: one uint8 tensor
+    (3, B, H, n_kvt, n_mt) whose planes 0-1 are a uint16 rank matrix (for a live
+    (K/V tile, query tile) pair, how many higher K/V tiles attend the same query tile: the
+    backward's place in the fixed order of dQ additions) and whose plane 2 is the nibble
+    matrix of live 64 x 64 quadrants.  One launch, no host synchronisation."""
     B, H, Mb, T = sel.shape
     sel = sel.to(torch.int32).contiguous()
     n_mt = -(-L // 128)
@@ -89,25 +92,33 @@ def route_tables(sel: torch.Tensor, qblk: int, L: int):
     lut = torch.empty(B, H, n_mt, tmax, dtype=torch.int32, device=dev)
     flags = torch.empty(B, H, n_mt, tmax, dtype=torch.uint8, device=dev)
     cnt = torch.empty(B, H, n_mt, dtype=torch.int32, device=dev)
-    fm = torch.empty(B, H, n_mt, n_mt, dtype=torch.uint8, device=dev)
+    maps = torch.empty(3, B, H, n_mt, n_mt, dtype=torch.uint8, device=dev)
     K._check(_lib.imf_build_tile_lut(K._ptr(sel), K._ptr(lut), K._ptr(flags), K._ptr(cnt),
-                                     K._ptr(fm), B, H, Mb, T, qblk, L, tmax, K._stream()),
+                                     K._ptr(maps[2]), K._ptr(maps), B, H, Mb, T, qblk, L, tmax,
+                                     K._stream()),
              "imf_build_tile_lut")
     K.LAUNCHES.count += 1
-    return lut, flags, cnt, fm
+    return lut, flags, cnt, maps
 
 
-def kv_lists(fm: torch.Tensor):
-    """Inverted lists for the backward kernel from the nibble matrix of ``route_tables``:
-    (qlist int32 (B,H,n_kvt,n_mt) padded with -1, qflags uint8).  The list stride is the
-    static bound n_mt, so no host read of the longest list is needed."""
+def kv_lists(maps: torch.Tensor, want_rank: bool = False):
+    """Inverted lists for the backward kernel from the maps of ``route_tables`` (or a bare
+    (B, H, n_kvt, n_mt) nibble matrix): (qlist int32 (B,H,n_kvt,n_mt) padded with -1, qflags
+    uint8) and, with ``want_rank``, qrank int16 (the entry's place in the fixed order of dQ
+    additions; None for a bare nibble matrix).  The list stride is the static bound n_mt, so
+    no host read of the longest list is needed."""
+    packed = maps.dim() == 5
+    fm = maps[2] if packed else maps
     B, H, n_kvt, n_mt = fm.shape
     qlist = torch.empty(B, H, n_kvt, n_mt, dtype=torch.int32, device=fm.device)
     qflags = torch.empty(B, H, n_kvt, n_mt, dtype=torch.uint8, device=fm.device)
-    K._check(_lib.imf_build_kv_lists(K._ptr(fm), K._ptr(qlist), K._ptr(qflags), B, H, n_kvt, n_mt,
-                                     n_mt, K._stream()), "imf_build_kv_lists")
+    qrank = (torch.empty(B, H, n_kvt, n_mt, dtype=torch.int16, device=fm.device)
+             if packed and want_rank else None)
+    K._check(_lib.imf_build_kv_lists(K._ptr(fm), K._ptr(maps) if qrank is not None else None,
+                                     K._ptr(qlist), K._ptr(qflags), K._ptr(qrank), B, H, n_kvt,
+                                     n_mt, n_mt, K._stream()), "imf_build_kv_lists")
     K.LAUNCHES.count += 1
-    return qlist, qflags
+    return (qlist, qflags, qrank) if want_rank else (qlist, qflags)
 
 
 def quantize_blocks(x: torch.Tensor, block: int, want_q: bool = True, want_fq: bool = False):

@@ -301,6 +301,9 @@ class Trainer:
         self.grad_sync: GradSync = self._build_grad_sync()
         self.step = 0
         self.timer = PhaseTimer(enabled=cfg.run.profile_phases)
+        if cfg.run.deterministic and self.device.type == "cuda":
+            from .ops import kernels as _K
+            _K.set_deterministic(True)
         self._nan_dumped = False
         self.last: Dict[str, Any] = {}
         if self.verbose:

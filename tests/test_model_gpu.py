@@ -79,6 +79,40 @@ def test_trainer_steps_on_gpu(kernels):
     assert st[-1]["grad_norm"] > 0
 
 
+@pytest.mark.parametrize("name", ["d256", "d256_sla2"])
+def test_train_step_is_bitwise_repeatable(kernels, name):
+    """With ``run.deterministic`` two trainers built from the same seed and fed the same batches
+    end with bit-identical losses and parameters: every reduction of the step has a fixed
+    order (split-K, column sums, dQ accumulation, gradient norm)."""
+    from imfvideo_b200.config import preset
+    from imfvideo_b200.train import Trainer
+
+    def run():
+        cfg = preset(name)
+        cfg.model.depth, cfg.model.aux_head_depth = 3, 1
+        cfg.data.latent_frames, cfg.data.latent_size = 4, (32, 32)
+        cfg.optim.warmup_steps = 0
+        cfg.run.deterministic = True
+        tr = Trainer(cfg, device=torch.device("cuda", 0), verbose=False)
+        g = torch.Generator().manual_seed(7)
+        out = []
+        for _ in range(2):
+            x = torch.randn(1, 16, 4, 32, 32, generator=g).pin_memory()
+            y = torch.randint(0, 1000, (1,), generator=g)
+            out.append(tr.train_step(x, y))
+        flat = torch.cat([p.detach().float().flatten() for p in tr.net.parameters()])
+        return out, flat
+
+    try:
+        (s1, p1), (s2, p2) = run(), run()
+    finally:
+        kernels.set_deterministic(False)
+    kernels.check_status()
+    assert [s["loss"] for s in s1] == [s["loss"] for s in s2]
+    assert [s["grad_norm"] for s in s1] == [s["grad_norm"] for s in s2]
+    assert torch.equal(p1, p2)
+
+
 @pytest.mark.parametrize("bs,wide", [(0, False), (2, False), (2, True)])
 def test_fused_block_matches_generic_composition(kernels, bs, wide):
     """Same bf16 kernels for GEMM/attention; fused block node vs op-by-op path:

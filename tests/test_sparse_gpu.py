@@ -167,6 +167,36 @@ def test_sparse_backward_kernel(SP, qblk, L):
     kernels.check_status()
 
 
+def test_sparse_backward_bitwise_repeatable(SP):
+    from imfvideo_b200.ops import kernels
+    """Block-sparse backward with the device-built lists and ranks: dQ bit-identical from run
+    to run (fixed order of additions), and equal to the arrival-order result up to rounding."""
+    torch.manual_seed(11)
+    B, H, L, qblk = 1, 3, 5000, 64
+    mk = lambda: torch.randn(B, L, H, 64, device="cuda").bfloat16()
+    q, k, v, go = mk(), mk(), mk(), mk()
+    Mb, Nb = -(-L // qblk), -(-L // 64)
+    T = max(2, Nb // 5)
+    sel = torch.stack([torch.stack([torch.randperm(Nb, device="cuda")[:T] for _ in range(Mb)])
+                       for _ in range(H)]).unsqueeze(0).int()
+    lut, flags, cnt, maps = SP.route_tables(sel, qblk, L)
+    o, _, lse = SP.sparse_fwd(q, k, v, None, None, None, lut, flags, qblk, False, quant_p=False,
+                              cnt=cnt)
+    qlist, qflags, qrank = SP.kv_lists(maps, want_rank=True)
+    kernels.set_deterministic(True)
+    try:
+        first = kernels.attn_bwd(q, k, v, o, lse, go, qlist=qlist, qflags=qflags, qrank=qrank)
+        for _ in range(3):
+            again = kernels.attn_bwd(q, k, v, o, lse, go, qlist=qlist, qflags=qflags, qrank=qrank)
+            assert all(torch.equal(a, b) for a, b in zip(first, again))
+    finally:
+        kernels.set_deterministic(False)
+    loose = kernels.attn_bwd(q, k, v, o, lse, go, qlist=qlist, qflags=qflags)   # arrival order
+    assert _rel(loose[0], first[0]) < 1e-3
+    assert torch.equal(loose[1], first[1]) and torch.equal(loose[2], first[2])
+    kernels.check_status()
+
+
 def test_linear_branch_kernels_match_formulas():
     """Complement linear branch (states, mask product on the tcgen05 GEMM, apply, reverse
     mode) against the fp32 formulas of models/sla2.py and their torch.func.jvp / autograd."""
@@ -235,10 +265,16 @@ def test_device_routing_tables_match_torch_builders(SP, qblk):
         assert torch.equal(lut[..., :n][valid], lut_r[lut_r >= 0])
         assert torch.equal(fl[..., :n][valid], fl_r[lut_r >= 0])
     ql_r, qf_r = SP.build_kv_lists(lut_r, fl_r, L)
-    ql, qf = SP.kv_lists(fm)
+    ql, qf, qr = SP.kv_lists(fm, want_rank=True)
     m = ql_r.shape[-1]
     assert bool((ql[..., m:] < 0).all())
     assert torch.equal(ql[..., :m], ql_r) and torch.equal(qf[..., :m], qf_r)
+    # rank of an entry = how many higher K/V tiles attend the same query tile
+    live = fm[2] != 0                                           # (B, H, n_kvt, n_mt)
+    above = live.flip(2).cumsum(2).flip(2) - live.long()
+    valid = ql >= 0
+    want = torch.gather(above, 3, ql.clamp(min=0).long())
+    assert torch.equal(qr.long()[valid], want[valid])
 
 
 @pytest.mark.parametrize("L,bq,bk,n_keys,n_tail,proj", [
