@@ -29,6 +29,8 @@
 // rounding is a magic-number add, P is stored as the integer grid value (the
 // 1/127 cancels in O / l), and a 64-row half that does not attend a block
 // writes zeros without touching the scores.
+#include <type_traits>
+
 #include "common.cuh"
 #include "host_util.h"
 
@@ -517,46 +519,57 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
             tc_wait_st();
           }
         }
-        const float neg_m = grid_log2 - m2;
         const float magic = 12582912.f;            // 1.5 * 2^23: (x + magic) - magic rounds to nearest
+        // INT8 scores become floats without a conversion instruction (which would share the
+        // exponential's pipe): the bit pattern of magic plus the integer IS the float
+        // magic + x (|x| <= 64 * 127^2 < 2^22), and the FMA takes magic * cf back out
+        const float neg_m = INT8 ? (grid_log2 - m2) - magic * cf : grid_log2 - m2;
         // pass 2: P (and T) for 32 columns at a time; the packed bf16 results go over the
-        // first columns of S (dS), which have been read by then
+        // first columns of S (dS), which have been read by then.  Only the last key block of
+        // the sequence can be ragged: every other block runs the loop without the per-column
+        // bound test (two instructions per score).
+        auto pass2 = [&](auto ragged_tag) {
+          constexpr bool RAGGED = decltype(ragged_tag)::value;
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          uint32_t sv[32];
-          uint32_t dsv[TANGENT ? 32 : 1];
-          tmem_ld32(tb + C::SC_S + hh * 32, sv);
-          if (TANGENT) tmem_ld32(tb + C::SC_DS + hh * 32, dsv);
-          tc_wait_ld();
-          uint32_t pk[16];
-          uint32_t tk[TANGENT ? 16 : 1];
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t sv[32];
+            uint32_t dsv[TANGENT ? 32 : 1];
+            tmem_ld32(tb + C::SC_S + hh * 32, sv);
+            if (TANGENT) tmem_ld32(tb + C::SC_DS + hh * 32, dsv);
+            tc_wait_ld();
+            uint32_t pk[16];
+            uint32_t tk[TANGENT ? 16 : 1];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float x0 = INT8 ? static_cast<float>(static_cast<int>(sv[i])) : __uint_as_float(sv[i]);
-            const float x1 =
-                INT8 ? static_cast<float>(static_cast<int>(sv[i + 1])) : __uint_as_float(sv[i + 1]);
-            float p0 = ex2(fmaf(x0, cf, neg_m));
-            float p1 = ex2(fmaf(x1, cf, neg_m));
-            if (hh * 32 + i >= kv_rem) p0 = 0.f;         // ragged last key block
-            if (hh * 32 + i + 1 >= kv_rem) p1 = 0.f;
-            if (p.quant_p) {
-              p0 = (p0 + magic) - magic;
-              p1 = (p1 + magic) - magic;
+            for (int i = 0; i < 32; i += 2) {
+              const float x0 = __uint_as_float(INT8 ? sv[i] + 0x4B400000u : sv[i]);
+              const float x1 = __uint_as_float(INT8 ? sv[i + 1] + 0x4B400000u : sv[i + 1]);
+              float p0 = ex2(fmaf(x0, cf, neg_m));
+              float p1 = ex2(fmaf(x1, cf, neg_m));
+              if (RAGGED) {
+                if (hh * 32 + i >= kv_rem) p0 = 0.f;
+                if (hh * 32 + i + 1 >= kv_rem) p1 = 0.f;
+              }
+              if (p.quant_p) {
+                p0 = (p0 + magic) - magic;
+                p1 = (p1 + magic) - magic;
+              }
+              l_sum += p0;
+              l_sum2 += p1;
+              pk[i / 2] = pack_bf16(p0, p1);
+              if (TANGENT) {
+                const float t0 = p0 * __uint_as_float(dsv[i]) * p.scale;
+                const float t1 = p1 * __uint_as_float(dsv[i + 1]) * p.scale;
+                mu_sum += t0;
+                mu_sum2 += t1;
+                tk[i / 2] = pack_bf16(t0, t1);
+              }
             }
-            l_sum += p0;
-            l_sum2 += p1;
-            pk[i / 2] = pack_bf16(p0, p1);
-            if (TANGENT) {
-              const float t0 = p0 * __uint_as_float(dsv[i]) * p.scale;
-              const float t1 = p1 * __uint_as_float(dsv[i + 1]) * p.scale;
-              mu_sum += t0;
-              mu_sum2 += t1;
-              tk[i / 2] = pack_bf16(t0, t1);
-            }
+            tmem_st16(tb + C::SC_S + hh * 16, pk);
+            if (TANGENT) tmem_st16(tb + C::SC_DS + hh * 16, tk);
           }
-          tmem_st16(tb + C::SC_S + hh * 16, pk);
-          if (TANGENT) tmem_st16(tb + C::SC_DS + hh * 16, tk);
-        }
+        };
+        if (kv_rem >= SP_BK) pass2(std::false_type{});
+        else pass2(std::true_type{});
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
