@@ -260,6 +260,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int ks = 0; ks < BW_T / 16; ++ks)
             mma_ss(tmem + BC_DK, sdesc_kmajor(dsa + (ks / 4) * (BW_T * 128) + (ks % 4) * 32),
                    sdesc_mnmajor(qa + ks * 2048, BW_T * 128), id_kn, (i | ks) != 0);
+          // the query-side stage (Q, dO, bands) has had its last reader: hand it back to the
+          // TMA producer now, not after the dQ GEMM -- with two stages, the load of tile i+2
+          // starts here and its latency sets the pace of the whole pipeline
+          tc_commit(&s.q_empty[st]);
           // dQ_i = dS K    (A = dS^T from smem, MN-major view: M = q, K = kv)
           if (i > 0) {
             ok = mbar_wait(&s.dq_free, (uint32_t)((i - 1) & 1), abort_flag, p.status,
@@ -272,7 +276,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mma_ss(tmem + BC_DQ, sdesc_mnmajor(dsa + ks * 2048, BW_T * 128),
                    sdesc_mnmajor(ka + ks * 2048, BW_T * 128), id_mn, ks != 0);
           tc_commit(&s.dq_full);
-          tc_commit(&s.q_empty[st]);
           tc_commit(&s.ds_free[i & 1]);
         }
         if (ok) tc_commit(&s.final_bar);
