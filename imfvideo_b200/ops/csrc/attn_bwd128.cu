@@ -223,6 +223,9 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           for (int ks = 0; ks < QT / 16; ++ks)
             mma_ss(tmem + BC_DK, sdesc_kmajor(dsa + ks * 32), sdesc_mnmajor(qa + ks * 2048, QPANEL),
                    id_kn, (i | ks) != 0);
+          // Q and dO of this step have had their last reader: the stage goes back to the TMA
+          // producer before the dQ GEMM (the load latency of step i + QSTAGES sets the pace)
+          tc_commit(&s.q_empty[st]);
           // dQ_i^T = K^T dS^T   (A = K as MN-major: M = hd, K = kv; B = dS^T MN-major: N = q)
           if (i > 0) {
             ok = mbar_wait(&s.dq_free, (uint32_t)((i - 1) & 1), abort_flag, p.status,
@@ -235,7 +238,6 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             mma_ss(tmem + BC_DQ, sdesc_mnmajor(ka + ks * 2048, KPANEL),
                    sdesc_mnmajor(dsa + ks * 2048, KT * 128), id_dq, ks != 0);
           tc_commit(&s.dq_full);
-          tc_commit(&s.q_empty[st]);
           tc_commit(&s.ds_free[i & 1]);
         }
         if (ok) tc_commit(&s.final_bar);
