@@ -131,6 +131,9 @@ class RunConfig:
     master_dtype: str = "float32"
     # extras (not in the reference): phase timers / NVTX ranges, heartbeat
     profile_phases: bool = False
+    # the host waits for loss / norm / skip flag only (copied out before the update kernels) and
+    # reports QK-clip statistics and the kernel status word one step late
+    overlap_stats_read: bool = True
     # fixed-order dQ accumulation in the attention backward: training steps become bit-identical
     # from run to run (costs 13-34 % of that kernel's time)
     deterministic: bool = False

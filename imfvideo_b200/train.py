@@ -301,6 +301,8 @@ class Trainer:
         self.grad_sync: GradSync = self._build_grad_sync()
         self.step = 0
         self.timer = PhaseTimer(enabled=cfg.run.profile_phases)
+        self._early_host = self._late_host = self._early_ev = self._late_ev = None
+        self._late_pending = False
         if cfg.run.deterministic and self.device.type == "cuda":
             from .ops import kernels as _K
             _K.set_deterministic(True)
@@ -350,10 +352,12 @@ class Trainer:
             return self.grad_sync.clip_grad_norm_(max_norm)
         return torch.nn.utils.clip_grad_norm_(self.net.parameters(), max_norm)
 
-    def optimizer_step(self) -> Dict[str, Any]:
+    def optimizer_step(self, early=None) -> Dict[str, Any]:
         """Sync, lr, clip, (skip if non-finite) step, QK-clip, EMA.  With the
         flat engine the non-finite check happens on the device (skip flag), so
-        nothing here waits for the GPU; statistics are returned as tensors."""
+        nothing here waits for the GPU; statistics are returned as tensors.
+        ``early(grad_norm, skipped)`` is called (flat engine only) once the norm and the skip
+        flag are enqueued and before the update kernels are."""
         o = self.cfg.optim
         eng = self.grad_sync if getattr(self.grad_sync, "handles_ema", False) else None
         with self.timer.phase("grad_sync"):
@@ -364,6 +368,8 @@ class Trainer:
         with self.timer.phase("optimizer"):
             grad_norm = self._grad_norm_and_clip(o.grad_clip)
             if eng is not None:
+                if early is not None:
+                    early(grad_norm, eng.clip[1])
                 self.optimizer.step()
                 skipped = eng.clip[1]
                 # the fused update kernels have already folded the new weights into the
@@ -424,16 +430,48 @@ class Trainer:
                 self.grad_sync.armed = i == len(micro) - 1
             loss, parts = self.micro_step(lat, lab)
             losses.append(loss)
-        stats = self.optimizer_step()
         dt, dev = losses[0].dtype, losses[0].device
         as_t = lambda v: (v if torch.is_tensor(v) else torch.tensor(float(v))).to(dt).to(dev) \
             .reshape(())
-        # ONE device -> host read per step: losses, norm, skip flag, QK-clip statistics and
-        # the kernel status word (a bounded wait that ran out inside any kernel of this step)
-        vec = torch.stack([torch.stack(losses).mean(), parts["loss_u"], parts["loss_v"],
-                           as_t(stats["grad_norm"]), as_t(stats["skipped"]),
-                           as_t(stats["qk_hot"]), as_t(stats["qk_smax"]),
-                           as_t(self._status_scalar())]).tolist()
+        split = (self.cfg.run.overlap_stats_read and dev.type == "cuda"
+                 and getattr(self.grad_sync, "handles_ema", False))
+        if split:
+            # The host waits for the losses, the gradient norm and the skip flag only: they
+            # are copied to pinned memory BEFORE the update kernels are enqueued, so the
+            # optimizer phase of this step still runs while the host returns and enqueues the
+            # first (small, launch-bound) kernels of the next step.  The QK-clip statistics
+            # and the kernel status word, which exist only after the update, are those of the
+            # PREVIOUS step (``flush_stats`` returns the last ones).
+            if self._early_host is None:
+                self._early_host = torch.zeros(5, dtype=torch.float32).pin_memory()
+                self._late_host = torch.zeros(3, dtype=torch.float32).pin_memory()
+                self._early_ev, self._late_ev = torch.cuda.Event(), torch.cuda.Event()
+
+            def early(grad_norm, skipped):
+                v = torch.stack([torch.stack(losses).mean(), parts["loss_u"], parts["loss_v"],
+                                 as_t(grad_norm), as_t(skipped)]).float()
+                self._early_host.copy_(v, non_blocking=True)
+                self._early_ev.record()
+
+            stats = self.optimizer_step(early=early)
+            if self._late_pending:
+                self._late_ev.synchronize()          # long done: it is a step old
+            prev_late = self._late_host.tolist() if self._late_pending else [0.0, 0.0, 0.0]
+            late = torch.stack([as_t(stats["qk_hot"]), as_t(stats["qk_smax"]),
+                                as_t(self._status_scalar())]).float()
+            self._late_host.copy_(late, non_blocking=True)
+            self._late_ev.record()
+            self._late_pending = True
+            self._early_ev.synchronize()
+            vec = self._early_host.tolist() + prev_late
+        else:
+            stats = self.optimizer_step()
+            # ONE device -> host read per step: losses, norm, skip flag, QK-clip statistics and
+            # the kernel status word (a bounded wait that ran out inside any kernel of this step)
+            vec = torch.stack([torch.stack(losses).mean(), parts["loss_u"], parts["loss_v"],
+                               as_t(stats["grad_norm"]), as_t(stats["skipped"]),
+                               as_t(stats["qk_hot"]), as_t(stats["qk_smax"]),
+                               as_t(self._status_scalar())]).tolist()
         self._raise_on_status(int(vec[7]))
         if not math.isfinite(vec[0]):
             self._dump_nan_batch(parts["_latents"], parts["_labels"])
@@ -446,6 +484,19 @@ class Trainer:
                      qk_hot=int(vec[5]), qk_smax=vec[6])
         self.last = stats
         return stats
+
+    def flush_stats(self) -> Dict[str, float]:
+        """Waits for the last step's update kernels and returns its QK-clip statistics;
+        raises if one of its kernels gave up on a bounded wait.  Only needed with
+        ``run.overlap_stats_read`` (where ``train_step`` reports these one step late); call it
+        after the last step and before trusting the weights (``save`` does)."""
+        if not getattr(self, "_late_pending", False):
+            return {}
+        self._late_ev.synchronize()
+        hot, smax, status = self._late_host.tolist()
+        self._late_pending = False
+        self._raise_on_status(int(status))
+        return {"qk_hot": int(hot), "qk_smax": smax}
 
     def _status_scalar(self):
         """The device status word of this rank's GPU (0 on CPU or before any kernel ran)."""
@@ -481,6 +532,7 @@ class Trainer:
         rank runs ahead into the next step's peer barrier while rank 0 is still in fsync.
         ``extra`` carries the RNG state, the world size, the Muon owner map and the
         sampler position (epoch, batches consumed) for an exact resume."""
+        self.flush_stats()       # a pending kernel status of the last step raises here
         extra: Dict[str, Any] = {"rng": ckpt_mod.rng_state(), "world": self.world}
         if hasattr(self.grad_sync, "owner_table"):
             extra["muon_owner"] = list(self.grad_sync.owner_table())

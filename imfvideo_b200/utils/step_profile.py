@@ -5,6 +5,7 @@ the device time per kernel / operator, largest first.
     python -m imfvideo_b200.utils.step_profile --preset d256
     python -m imfvideo_b200.utils.step_profile --preset d256_sla2 --top 30
     python -m imfvideo_b200.utils.step_profile --preset d1024 optim.ns_cuda_graph=true
+    python -m imfvideo_b200.utils.step_profile --preset d256 --gaps 15     # longest idle gaps
 
 Times taken under the profiler are for comparing shares, not for quoting a step
 time (use ``bench.py`` for that).  The reference has no profiling entry point
@@ -20,9 +21,30 @@ from typing import List, Tuple
 import torch
 
 
-def profile_step(cfg, warmup: int = 2, device: int = 0):
+def idle_gaps(prof, top: int):
+    """The ``top`` longest intervals in which the device ran no kernel, from a profiler
+    record: [(gap_us, kernel before, kernel after)], plus the total idle time between the
+    first and the last kernel.  Kernels of all streams count as 'busy'."""
+    spans = []
+    for e in prof.events():
+        if e.device_type == torch.autograd.DeviceType.CUDA and e.time_range is not None:
+            spans.append((e.time_range.start, e.time_range.end, e.name))
+    spans.sort()
+    gaps, busy_until, last, idle = [], None, "", 0.0
+    for st, en, name in spans:
+        if busy_until is not None and st > busy_until:
+            gaps.append((st - busy_until, last, name))
+            idle += st - busy_until
+        if busy_until is None or en > busy_until:
+            busy_until, last = en, name
+    gaps.sort(reverse=True)
+    return gaps[:top], idle
+
+
+def profile_step(cfg, warmup: int = 2, device: int = 0, gaps: int = 0):
     """Returns (rows, step_wall_ms): rows = [(device_us, count, name)], largest first, for one
-    training step after ``warmup`` un-profiled steps."""
+    training step after ``warmup`` un-profiled steps.  With ``gaps`` > 0 a third value: the
+    result of ``idle_gaps``."""
     from torch.profiler import ProfilerActivity, profile
 
     from ..train import Trainer
@@ -47,6 +69,8 @@ def profile_step(cfg, warmup: int = 2, device: int = 0):
                 and not e.key.startswith("Optimizer.step")):      # a span, not a kernel
             rows.append((e.self_device_time_total, e.count, e.key))
     rows.sort(reverse=True)
+    if gaps > 0:
+        return rows, a.elapsed_time(b), idle_gaps(prof, gaps)
     return rows, a.elapsed_time(b)
 
 
@@ -55,6 +79,8 @@ def main(argv=None) -> None:
     ap.add_argument("--preset", default="d256")
     ap.add_argument("--top", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--gaps", type=int, default=0,
+                    help="also list this many of the longest idle gaps between kernels")
     ap.add_argument("overrides", nargs="*", help="group.key=value config overrides")
     args = ap.parse_args(argv)
     from ..config import parse_cli, preset
@@ -62,12 +88,18 @@ def main(argv=None) -> None:
     cfg = preset(args.preset)
     if args.overrides:
         parse_cli(args.overrides, cfg)
-    rows, wall = profile_step(cfg, args.warmup)
+    out = profile_step(cfg, args.warmup, gaps=args.gaps)
+    rows, wall = out[0], out[1]
     total = sum(r[0] for r in rows)
     print(f"preset {args.preset}: step {wall:.1f} ms under the profiler, "
           f"kernels {total / 1000:.1f} ms in {sum(r[1] for r in rows)} launches")
     for us, n, name in rows[:args.top]:
         print(f"{us / 1000:9.2f} ms {100 * us / total:5.1f} %  x{n:<5d} {name[:100]}")
+    if args.gaps:
+        top, idle = out[2]
+        print(f"idle between the first and the last kernel: {idle / 1000:.2f} ms; longest gaps:")
+        for g, before, after in top:
+            print(f"{g:9.1f} us  after {before[:60]}  before {after[:60]}")
 
 
 if __name__ == "__main__":
