@@ -111,6 +111,7 @@ IMF_DEVICE void red_add_v4(float* gptr, float a, float b, float c, float d) {
                : "memory");
 }
 
+template <bool SPARSE>      // block-sparse lists given (keeps the dense instance free of their tests)
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -210,18 +211,40 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         constexpr uint32_t id_mn = idesc_bf16(BW_T, BW_HD, 1, 1);    // dQ (A MN-major)
         const uint32_t ka = smem_u32(s.k), va = smem_u32(s.v);
         const uint64_t ones_d = sdesc_kmajor_sw32(smem_u32(s.ones));
-        auto issue_s = [&](int st) {
+        constexpr uint32_t id_st64 = idesc_bf16(BW_T, 64, 0, 0);     // one 64-row query half
+        // Block-sparse tiles: `f` has one bit per 64 x 64 quadrant (kv half * 2 + q half).  A
+        // query half that attends neither K/V half is left out of the score products (N = 64)
+        // and of the K dimension of dV / dK; a K/V half that no query half attends is left out
+        // of the K dimension of dQ.  The math warps write zeros for dead quadrants, so the
+        // skipped products would only have added zeros.  Dense: f = 15.
+        auto issue_s = [&](int st, uint32_t f) {
           const uint32_t qa = smem_u32(s.q[st]), doa = smem_u32(s.d_o[st]);
+          const uint32_t qh = ((f & 5u) ? 1u : 0u) | ((f & 10u) ? 2u : 0u);   // live query halves
+          if (qh == 3u) {
 #pragma unroll
-          for (int ks = 0; ks < BW_HD / 16; ++ks)
-            mma_ss(tmem + BC_S, sdesc_kmajor(ka + ks * 32), sdesc_kmajor(qa + ks * 32), id_st, ks != 0);
-          // + ones[kv] x (-lse2[q])  ->  the accumulator holds the exponent itself
-          mma_ss(tmem + BC_S, ones_d, sdesc_kmajor_sw32(smem_u32(s.augq[st])), id_st, 1);
+            for (int ks = 0; ks < BW_HD / 16; ++ks)
+              mma_ss(tmem + BC_S, sdesc_kmajor(ka + ks * 32), sdesc_kmajor(qa + ks * 32), id_st, ks != 0);
+            // + ones[kv] x (-lse2[q])  ->  the accumulator holds the exponent itself
+            mma_ss(tmem + BC_S, ones_d, sdesc_kmajor_sw32(smem_u32(s.augq[st])), id_st, 1);
 #pragma unroll
-          for (int ks = 0; ks < BW_HD / 16; ++ks)
-            mma_ss(tmem + BC_DP, sdesc_kmajor(va + ks * 32), sdesc_kmajor(doa + ks * 32), id_st, ks != 0);
-          // + ones[kv] x (-delta[q])  ->  dP - delta
-          mma_ss(tmem + BC_DP, ones_d, sdesc_kmajor_sw32(smem_u32(s.augd[st])), id_st, 1);
+            for (int ks = 0; ks < BW_HD / 16; ++ks)
+              mma_ss(tmem + BC_DP, sdesc_kmajor(va + ks * 32), sdesc_kmajor(doa + ks * 32), id_st, ks != 0);
+            // + ones[kv] x (-delta[q])  ->  dP - delta
+            mma_ss(tmem + BC_DP, ones_d, sdesc_kmajor_sw32(smem_u32(s.augd[st])), id_st, 1);
+          } else {
+            const uint32_t h = qh >> 1;                     // the live half: rows 64 h .. 64 h + 63
+            const uint32_t qo = h * (64 * 128), ao = h * (64 * 32), co = h * 64;
+#pragma unroll
+            for (int ks = 0; ks < BW_HD / 16; ++ks)
+              mma_ss(tmem + BC_S + co, sdesc_kmajor(ka + ks * 32), sdesc_kmajor(qa + qo + ks * 32),
+                     id_st64, ks != 0);
+            mma_ss(tmem + BC_S + co, ones_d, sdesc_kmajor_sw32(smem_u32(s.augq[st]) + ao), id_st64, 1);
+#pragma unroll
+            for (int ks = 0; ks < BW_HD / 16; ++ks)
+              mma_ss(tmem + BC_DP + co, sdesc_kmajor(va + ks * 32), sdesc_kmajor(doa + qo + ks * 32),
+                     id_st64, ks != 0);
+            mma_ss(tmem + BC_DP + co, ones_d, sdesc_kmajor_sw32(smem_u32(s.augd[st]) + ao), id_st64, 1);
+          }
           tc_commit(&s.s_full);
         };
         bool ok = n_q > 0 &&      // a K/V tile that no query tile attends has zero gradients
@@ -229,8 +252,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                   mbar_wait(&s.q_full[0], 0, abort_flag, p.status, STATUS_TIMEOUT_TMA);
         if (ok) {
           tc_fence_after();
-          issue_s(0);
+          issue_s(0, SPARSE ? qflags[0] : 15u);
         }
+        bool kv_started = false;     // dK / dV accumulators hold something
         for (int i = 0; i < n_q && ok; ++i) {
           const int st = i % BW_QSTAGES;
           const uint32_t par = (uint32_t)(i & 1);
@@ -242,24 +266,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                            p.status, STATUS_TIMEOUT_TMA);
             if (!ok) break;
             tc_fence_after();
-            issue_s(st1);
+            issue_s(st1, SPARSE ? qflags[i + 1] : 15u);
           }
           ok = mbar_wait(&s.p_ready, par, abort_flag, p.status, STATUS_TIMEOUT_SOFTMAX);
           if (!ok) break;
           tc_fence_after();
           const uint32_t qa = smem_u32(s.q[st]), doa = smem_u32(s.d_o[st]);
           const uint32_t dsa = smem_u32(s.ds[i & 1]);
+          const uint32_t f = SPARSE ? qflags[i] : 15u;
+          // k-steps of 16 query rows that belong to a live query half / of 16 K/V rows that
+          // belong to a live K/V half
+          const int q0 = (f & 5u) ? 0 : 4, q1 = (f & 10u) ? 8 : 4;
+          const int k0 = (f & 3u) ? 0 : 4, k1 = (f & 12u) ? 8 : 4;
           // dV += P^T dO   (A = P^T in TMEM: 128 q as K -> 8 k-steps of 8 columns)
 #pragma unroll
           for (int ks = 0; ks < BW_T / 16; ++ks)
-            mma_ts(tmem + BC_DV, tmem + BC_P + ks * 8, sdesc_mnmajor(doa + ks * 2048, BW_T * 128),
-                   id_kn, (i | ks) != 0);
+            if (ks >= q0 && ks < q1)
+              mma_ts(tmem + BC_DV, tmem + BC_P + ks * 8,
+                     sdesc_mnmajor(doa + ks * 2048, BW_T * 128), id_kn, kv_started || ks != q0);
           tc_commit(&s.p_free);
           // dK += dS^T Q   (A = dS^T from smem, K-major view: K = q)
 #pragma unroll
           for (int ks = 0; ks < BW_T / 16; ++ks)
-            mma_ss(tmem + BC_DK, sdesc_kmajor(dsa + (ks / 4) * (BW_T * 128) + (ks % 4) * 32),
-                   sdesc_mnmajor(qa + ks * 2048, BW_T * 128), id_kn, (i | ks) != 0);
+            if (ks >= q0 && ks < q1)
+              mma_ss(tmem + BC_DK, sdesc_kmajor(dsa + (ks / 4) * (BW_T * 128) + (ks % 4) * 32),
+                     sdesc_mnmajor(qa + ks * 2048, BW_T * 128), id_kn, kv_started || ks != q0);
+          kv_started = true;
           // the query-side stage (Q, dO, bands) has had its last reader: hand it back to the
           // TMA producer now, not after the dQ GEMM -- with two stages, the load of tile i+2
           // starts here and its latency sets the pace of the whole pipeline
@@ -273,8 +305,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
 #pragma unroll
           for (int ks = 0; ks < BW_T / 16; ++ks)
-            mma_ss(tmem + BC_DQ, sdesc_mnmajor(dsa + ks * 2048, BW_T * 128),
-                   sdesc_mnmajor(ka + ks * 2048, BW_T * 128), id_mn, ks != 0);
+            if (ks >= k0 && ks < k1)
+              mma_ss(tmem + BC_DQ, sdesc_mnmajor(dsa + ks * 2048, BW_T * 128),
+                     sdesc_mnmajor(ka + ks * 2048, BW_T * 128), id_mn, ks != k0);
           tc_commit(&s.dq_full);
           tc_commit(&s.ds_free[i & 1]);
         }
@@ -718,11 +751,12 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
   prm.turn = ordered ? turn : nullptr;
   prm.qrank = ordered ? qrank : nullptr;
   const size_t smem = sizeof(BwSmem) + 1024;
-  if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)smem) != cudaSuccess)
+  auto kern = (qlist != nullptr && qflags != nullptr) ? attn_bwd_kernel<true> : attn_bwd_kernel<false>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+      cudaSuccess)
     return IMF_ERR_LAUNCH;
   dim3 grid(H * B * qsplit, (L + BW_T - 1) / BW_T, 1);
-  attn_bwd_kernel<<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, mdq, maq, mad, prm);
+  kern<<<grid, BW_THREADS, smem, st>>>(mq, mk, mv, mdo, mdq, maq, mad, prm);
   if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   if (qsplit > 1) {
     const long n = (long)B * L * H * 16;
