@@ -498,8 +498,11 @@ class SparseCore:
         qh, kh, vh = (x.permute(0, 2, 1, 3) for x in (q, k, v))
         sel, a_rows = self._sel_and_alpha(qh.detach(), kh.detach())
         lut, flags, cnt, fm = SP.route_tables(sel, self.qblk, q.shape[1])
+        # inference form (no reverse mode to follow, e.g. the sampler and the guidance passes):
+        # no log-sum-exp, no saved state; the same INT8 block-sparse kernel and the same
+        # per-key-block states with the alpha mix fused into the apply kernel
         o_s, do_s, lse = SP.sparse_fwd(q, k, v, dq, dk, dv, lut, flags, self.qblk, self.int8,
-                                       quant_p=self.int8, need_lse=True, cnt=cnt)
+                                       quant_p=self.int8, need_lse=need_bwd, cnt=cnt)
         flags = fm          # reverse mode needs the (K/V tile, query tile) maps, not the per-tile flags
         from ..ops import linattn as LA
 
