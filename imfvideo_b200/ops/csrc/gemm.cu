@@ -232,6 +232,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 cv[4 * i] = t.x; cv[4 * i + 1] = t.y; cv[4 * i + 2] = t.z; cv[4 * i + 3] = t.w;
               }
             }
+            if (!Cin && !add_bias) {        // plain product: nothing to read, nothing to test
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                o[i] = pack_bf16(__uint_as_float(r[2 * i]) * alpha,
+                                 __uint_as_float(r[2 * i + 1]) * alpha);
+            } else
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               float x = __uint_as_float(r[2 * i]) * alpha;
@@ -257,6 +263,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                   make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
           } else {
             uint8_t* panel = s.c + (c / PANEL_COLS) * (GEMM_BM * 128) + r_in * 128;
+            if (!Cin && !add_bias) {        // plain product
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                *reinterpret_cast<float4*>(panel + ((i ^ (r_in & 7)) << 4)) =
+                    make_float4(__uint_as_float(r[4 * i]) * alpha, __uint_as_float(r[4 * i + 1]) * alpha,
+                                __uint_as_float(r[4 * i + 2]) * alpha, __uint_as_float(r[4 * i + 3]) * alpha);
+            } else
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               float4 v;
