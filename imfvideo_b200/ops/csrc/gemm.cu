@@ -434,7 +434,8 @@ extern "C" int imf_gemm_bf16(const void* A, const void* B, void* C, const float*
   if ((lda & 7) || (ldb & 7)) return IMF_ERR_ARG;  // TMA strides are multiples of 16 B
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 // fp32 output: the 64 KB staging tile leaves room for one CTA per SM only, so the operand
-// pipeline is four stages deep there; bf16 output: two CTAs per SM with two stages each.
+// pipeline is four stages deep there; bf16 output: see IMF_GEMM_DEEP below (two CTAs per SM
+// with two stages each only for the MN-major-A instances).
 #define IMF_GEMM_STAGES(OT) (sizeof(OT) == 4 ? 4 : 2)
 #define IMF_GEMM_CASE(AM, BM_, OT)                                                          \
   return launch_gemm<128, IMF_GEMM_STAGES(OT), AM, BM_, OT>(                                \
@@ -456,8 +457,23 @@ extern "C" int imf_gemm_bf16(const void* A, const void* B, void* C, const float*
       if (!a_mn && b_mn) IMF_GEMM_WIDE(false, true);
 #undef IMF_GEMM_WIDE
     }
-    if (!a_mn && !b_mn) IMF_GEMM_CASE(false, false, __nv_bfloat16);
-    if (!a_mn && b_mn) IMF_GEMM_CASE(false, true, __nv_bfloat16);
+    // One CTA per SM with a deep operand ring beats two CTAs with two stages each (a k-block
+    // takes about 1,450 cycles to land, so two stages cap a CTA at two k-blocks per 2,000
+    // cycles): four stages for short K (58,280 x 1,024 x 256: 51.8 -> 47.5 us), six from
+    // K = 512 on (65,560 x 5,472 x 1,024: 693 -> 624 us, 1,178 TFLOP/s).
+#define IMF_GEMM_DEEP(AM, BM_)                                                              \
+  {                                                                                         \
+    if (K >= 512)                                                                           \
+      return launch_gemm<128, 6, AM, BM_, __nv_bfloat16>(A, B, C, bias, M, N, K, lda, ldb,   \
+                                                        ldc, bias_rows, alpha,              \
+                                                        accumulate_out, status, st);        \
+    return launch_gemm<128, 4, AM, BM_, __nv_bfloat16>(A, B, C, bias, M, N, K, lda, ldb, ldc, \
+                                                      bias_rows, alpha, accumulate_out,     \
+                                                      status, st);                          \
+  }
+    if (!a_mn && !b_mn) IMF_GEMM_DEEP(false, false);
+    if (!a_mn && b_mn) IMF_GEMM_DEEP(false, true);
+#undef IMF_GEMM_DEEP
     if (a_mn && !b_mn) IMF_GEMM_CASE(true, false, __nv_bfloat16);
     IMF_GEMM_CASE(true, true, __nv_bfloat16);
   }
