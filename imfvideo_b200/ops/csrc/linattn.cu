@@ -12,7 +12,8 @@
 // so that the bf16 GEMM reproduces them to 2^-17.  Reverse mode has the same
 // two shapes of work: "rows x state" products (lin_apply / lin_bwd_rows /
 // lin_bwd_kv) and "rows^T rows" state builds (lin_states, reused with
-// (phi(q), dL/dnum | dL/dden) to get dL/dC).  Every reduction has a fixed
+// (phi(q), dL/dnum | dL/dden) to get dL/dC); both run on the tensor cores
+// (mma.sync, TF32 inputs, fp32 accumulation).  Every reduction has a fixed
 // order (no atomics).  Replaces the reference's `_hblocks`,
 // `_phi_states_kernel`, `_lin_fwd*`, `_linear_jvp`, `_lin_bwd_dq`,
 // `_lin_bwd_dkdv` (reference models/sla2_vendor/kernel.py,
@@ -67,6 +68,94 @@ __device__ __forceinline__ void softmax_row_jvp(float2 phi, float2 dx, float2& d
 }
 
 // --------------------------------------------------------------------------
+// 64 x 64 x 64 products in shared memory, on the tensor cores.  All matrices have pitch
+// LP = 68 floats.  `mma.sync.m16n8k8` with TF32 inputs (fp32 values rounded to nearest, 10
+// mantissa bits) and fp32 accumulation: the eight warps form a 4 x 2 grid, each with a
+// 16 x 32 piece of the result (four 16 x 8 accumulator fragments).  The results go through a
+// shared-memory tile S so that every thread ends up with the 4 x 4 block
+//     acc[i][j] += sum_k A[r0 + i][k] * Bm[k][c0 + j]        (A_T: A[k][r0 + i])
+// of the 16 x 16 thread grid that the row-wise epilogues of the callers are written for.
+// Fragment layout (g = lane / 4, t = lane % 4): A (row g | g + 8, col t | t + 4),
+// B (k t | t + 4, n g), C (row g | g + 8, col 2 t | 2 t + 1).  Must be called by all 256
+// threads.  The result tile S may be one of the operands' tiles: `frags_to_blocks` starts with
+// a block-wide barrier, after which no thread reads an operand any more.
+// --------------------------------------------------------------------------
+constexpr int LP = LW;
+
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4],
+                                         const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// d[n][.] += (A or A^T)[rows mr .. mr + 15][:] * Bm[:][cols nc + 8 n .. + 7], n = 0 .. 3
+template <bool A_T>
+__device__ __forceinline__ void warp_mm_tf32(const float* __restrict__ A,
+                                             const float* __restrict__ Bm, int mr, int nc,
+                                             int g, int t, float (&d)[4][4]) {
+#pragma unroll 2
+  for (int k = 0; k < 64; k += 8) {
+    uint32_t a[4];
+    if (A_T) {
+      a[0] = to_tf32(A[(k + t) * LP + mr + g]);
+      a[1] = to_tf32(A[(k + t) * LP + mr + g + 8]);
+      a[2] = to_tf32(A[(k + t + 4) * LP + mr + g]);
+      a[3] = to_tf32(A[(k + t + 4) * LP + mr + g + 8]);
+    } else {
+      a[0] = to_tf32(A[(mr + g) * LP + k + t]);
+      a[1] = to_tf32(A[(mr + g + 8) * LP + k + t]);
+      a[2] = to_tf32(A[(mr + g) * LP + k + t + 4]);
+      a[3] = to_tf32(A[(mr + g + 8) * LP + k + t + 4]);
+    }
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      uint32_t b[2];
+      b[0] = to_tf32(Bm[(k + t) * LP + nc + n * 8 + g]);
+      b[1] = to_tf32(Bm[(k + t + 4) * LP + nc + n * 8 + g]);
+      mma_tf32(d[n], a, b);
+    }
+  }
+}
+
+// fragments -> S -> 4 x 4 blocks (added to acc)
+__device__ __forceinline__ void frags_to_blocks(const float (&d)[4][4], float* __restrict__ S,
+                                                int mr, int nc, int g, int t, int r0, int c0,
+                                                float (&acc)[4][4]) {
+  __syncthreads();                  // earlier readers of S are done
+#pragma unroll
+  for (int n = 0; n < 4; ++n) {
+    *reinterpret_cast<float2*>(S + (mr + g) * LP + nc + n * 8 + 2 * t) = make_float2(d[n][0], d[n][1]);
+    *reinterpret_cast<float2*>(S + (mr + g + 8) * LP + nc + n * 8 + 2 * t) = make_float2(d[n][2], d[n][3]);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 v = *reinterpret_cast<const float4*>(S + (r0 + i) * LP + c0);
+    acc[i][0] += v.x; acc[i][1] += v.y; acc[i][2] += v.z; acc[i][3] += v.w;
+  }
+}
+
+// position of a thread in the warp grid / fragment layout of the products above
+struct MmaPos {
+  int mr, nc, g, t;
+  __device__ __forceinline__ explicit MmaPos(int tid) {
+    const int warp = tid >> 5, lane = tid & 31;
+    mr = (warp & 3) * 16;
+    nc = (warp >> 2) * 32;
+    g = lane >> 2;
+    t = lane & 3;
+  }
+};
+
+// --------------------------------------------------------------------------
 // State build: per block of `bs` rows, S = [ phi(X)^T Y | phi(X)^T w ] and the
 // tangent [ dphi^T Y + phi^T dY | dphi^T w ], written as bf16 hi / lo pairs.
 // --------------------------------------------------------------------------
@@ -80,67 +169,76 @@ struct StatesArgs {
 
 template <bool TANGENT>
 __global__ void __launch_bounds__(256) lin_states_kernel(const StatesArgs a) {
-  extern __shared__ float sm[];
-  float* X = sm;                     // [64][64]
-  float* Y = X + 64 * 64;            // [64][68]
-  float* dX = Y + 64 * LW;           // tangent only
-  float* dY = dX + 64 * 64;
+  extern __shared__ __align__(16) float sm[];
+  float* X = sm;                     // [64][LP]  phi rows
+  float* Y = X + 64 * LP;            // [64][LP]  y rows | w
+  float* S = X;                      // result tile of the products: X is dead by then
+  float* dX = Y + 64 * LP;           // tangent only
+  float* dY = dX + 64 * LP;
   const int n = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int d0 = (tid >> 4) * 4, e0 = (tid & 15) * 4;
+  const int g = lane >> 2, t = lane & 3, mr = (warp & 3) * 16, nc = (warp >> 2) * 32;
   float acc[4][4] = {}, dacc[4][4] = {};
+  float fr[4][4] = {}, dfr[4][4] = {};       // accumulator fragments of X^T Y and its tangent
   float zacc = 0.f, dzacc = 0.f;
   for (int c0 = 0; c0 < a.bs; c0 += 64) {
-    for (int rr = warp; rr < 64; rr += 8) {
-      const int row = n * a.bs + c0 + rr;
-      const bool valid = row < a.lim;
-      float2 phi = make_float2(0.f, 0.f), dphi = phi, yv = phi, dyv = phi;
-      float wv = 0.f;
-      if (valid) {
-        softmax_row(ld_bf16x2(a.x, b, row, h, 2 * lane), phi);
-        yv = a.y_fp32 ? ld_f32x2(a.y, b, row, h, 2 * lane) : ld_bf16x2(a.y, b, row, h, 2 * lane);
-        wv = a.w ? a.w[((int64_t)b * a.H + h) * a.L + row] : 1.f;
+    // Every warp has eight rows.  All their loads are issued before the first softmax (a
+    // row at a time would put eight global-memory latencies end to end), and the unrolled
+    // softmaxes give the scheduler eight independent shuffle chains.
+    float2 xr[8], yr[8], dxr[8], dyr[8];
+    float wr[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = n * a.bs + c0 + warp + 8 * i;
+      xr[i] = yr[i] = dxr[i] = dyr[i] = make_float2(0.f, 0.f);
+      wr[i] = 0.f;
+      if (row < a.lim) {
+        xr[i] = ld_bf16x2(a.x, b, row, h, 2 * lane);
+        yr[i] = a.y_fp32 ? ld_f32x2(a.y, b, row, h, 2 * lane) : ld_bf16x2(a.y, b, row, h, 2 * lane);
+        wr[i] = a.w ? a.w[((int64_t)b * a.H + h) * a.L + row] : 1.f;
         if (TANGENT) {
-          softmax_row_jvp(phi, ld_bf16x2(a.dx, b, row, h, 2 * lane), dphi);
-          dyv = ld_bf16x2(a.dy, b, row, h, 2 * lane);
+          dxr[i] = ld_bf16x2(a.dx, b, row, h, 2 * lane);
+          dyr[i] = ld_bf16x2(a.dy, b, row, h, 2 * lane);
         }
       }
-      *reinterpret_cast<float2*>(X + rr * 64 + 2 * lane) = phi;
-      *reinterpret_cast<float2*>(Y + rr * LW + 2 * lane) = yv;
-      if (lane == 0) Y[rr * LW + 64] = wv;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = warp + 8 * i;
+      const bool valid = n * a.bs + c0 + rr < a.lim;
+      float2 phi = make_float2(0.f, 0.f), dphi = phi;
+      if (valid) {
+        softmax_row(xr[i], phi);
+        if (TANGENT) softmax_row_jvp(phi, dxr[i], dphi);
+      }
+      *reinterpret_cast<float2*>(X + rr * LP + 2 * lane) = phi;
+      *reinterpret_cast<float2*>(Y + rr * LP + 2 * lane) = yr[i];
+      if (lane == 0) Y[rr * LP + 64] = wr[i];
       if (TANGENT) {
-        *reinterpret_cast<float2*>(dX + rr * 64 + 2 * lane) = dphi;
-        *reinterpret_cast<float2*>(dY + rr * LW + 2 * lane) = dyv;
+        *reinterpret_cast<float2*>(dX + rr * LP + 2 * lane) = dphi;
+        *reinterpret_cast<float2*>(dY + rr * LP + 2 * lane) = dyr[i];
       }
     }
     __syncthreads();
-#pragma unroll 4
-    for (int rr = 0; rr < 64; ++rr) {
-      const float4 xa = *reinterpret_cast<const float4*>(X + rr * 64 + d0);
-      const float4 yb = *reinterpret_cast<const float4*>(Y + rr * LW + e0);
-      const float xs[4] = {xa.x, xa.y, xa.z, xa.w}, ys[4] = {yb.x, yb.y, yb.z, yb.w};
-      float dxs[4], dys[4];
-      if (TANGENT) {
-        const float4 da = *reinterpret_cast<const float4*>(dX + rr * 64 + d0);
-        const float4 db = *reinterpret_cast<const float4*>(dY + rr * LW + e0);
-        dxs[0] = da.x; dxs[1] = da.y; dxs[2] = da.z; dxs[3] = da.w;
-        dys[0] = db.x; dys[1] = db.y; dys[2] = db.z; dys[3] = db.w;
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          acc[i][j] = fmaf(xs[i], ys[j], acc[i][j]);
-          if (TANGENT) dacc[i][j] = fmaf(dxs[i], ys[j], fmaf(xs[i], dys[j], dacc[i][j]));
-        }
-      if (tid < 64) {
-        const float wv = Y[rr * LW + 64];
-        zacc = fmaf(X[rr * 64 + tid], wv, zacc);
-        if (TANGENT) dzacc = fmaf(dX[rr * 64 + tid], wv, dzacc);
+    // [d][e] += sum over the 64 rows of phi[row][d] * y[row][e]: X^T Y on the tensor cores
+    warp_mm_tf32<true>(X, Y, mr, nc, g, t, fr);
+    if (TANGENT) {
+      warp_mm_tf32<true>(dX, Y, mr, nc, g, t, dfr);
+      warp_mm_tf32<true>(X, dY, mr, nc, g, t, dfr);
+    }
+    if (tid < 64) {                  // the extra column: sum of phi weighted by w
+#pragma unroll 8
+      for (int rr = 0; rr < 64; ++rr) {
+        const float wv = Y[rr * LP + 64];
+        zacc = fmaf(X[rr * LP + tid], wv, zacc);
+        if (TANGENT) dzacc = fmaf(dX[rr * LP + tid], wv, dzacc);
       }
     }
     __syncthreads();
   }
+  frags_to_blocks(fr, S, mr, nc, g, t, d0, e0, acc);
+  if (TANGENT) frags_to_blocks(dfr, S, mr, nc, g, t, d0, e0, dacc);
   const int64_t base = ((int64_t)b * a.H + h) * 2 * a.nblk_pad * LSTATE + (int64_t)n * LSTATE;
   const int64_t lo_off = (int64_t)a.nblk_pad * LSTATE;
   auto put = [&](__nv_bfloat16* dst, int d, int e, float v) {
@@ -171,39 +269,6 @@ __global__ void __launch_bounds__(256) lin_states_kernel(const StatesArgs a) {
     for (int e = 65; e < LW; ++e) {
       put(a.out, tid, e, 0.f);
       if (TANGENT) put(a.dout, tid, e, 0.f);
-    }
-  }
-}
-
-// --------------------------------------------------------------------------
-// 64 x 64 x 64 products in shared memory.  All matrices have pitch LP = 68
-// floats (rows 16-byte aligned; rows four apart sit 16 banks apart).  The 256
-// threads form a 16 x 16 grid, each with a 4 x 4 tile of the result:
-//     acc[i][j] += sum_k A[r0 + i][k] * Bm[k][c0 + j]
-// Per four k: four 16-byte loads of A (two addresses per warp, broadcast) and
-// four of Bm (256 contiguous bytes per half warp) feed 64 FMAs.
-// --------------------------------------------------------------------------
-constexpr int LP = LW;
-
-__device__ __forceinline__ void tile_mm(const float* __restrict__ A, const float* __restrict__ Bm,
-                                        int r0, int c0, float (&acc)[4][4]) {
-#pragma unroll 2
-  for (int k = 0; k < 64; k += 4) {
-    float4 av[4], bv[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) av[i] = *reinterpret_cast<const float4*>(A + (r0 + i) * LP + k);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) bv[j] = *reinterpret_cast<const float4*>(Bm + (k + j) * LP + c0);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float as[4] = {av[i].x, av[i].y, av[i].z, av[i].w};
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        acc[i][0] = fmaf(as[kk], bv[kk].x, acc[i][0]);
-        acc[i][1] = fmaf(as[kk], bv[kk].y, acc[i][1]);
-        acc[i][2] = fmaf(as[kk], bv[kk].z, acc[i][2]);
-        acc[i][3] = fmaf(as[kk], bv[kk].w, acc[i][3]);
-      }
     }
   }
 }
@@ -264,6 +329,7 @@ __global__ void __launch_bounds__(256) lin_apply_kernel(const ApplyArgs a) {
   float* P = C + LSTATE;              // phi rows [64][LP]
   float* dC = P + 64 * LP;            // tangent only
   float* dP = dC + LSTATE;
+  float* S = P;                       // result tile of the products (P is dead by then)
   __shared__ float Den[64], dDen[64];
   const int m = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -277,13 +343,24 @@ __global__ void __launch_bounds__(256) lin_apply_kernel(const ApplyArgs a) {
   const int r0 = (tid >> 4) * 4, c0 = (tid & 15) * 4;
   for (int ch = 0; ch < a.qblk; ch += 64) {
     if (ch) __syncthreads();
-#pragma unroll 4
-    for (int rr = warp; rr < 64; rr += 8) {
+    float2 qr[8], dqr[8];           // this warp's eight rows: loads first, then the softmaxes
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = m * a.qblk + ch + warp + 8 * i;
+      qr[i] = dqr[i] = make_float2(0.f, 0.f);
+      if (row < a.L) {
+        qr[i] = ld_bf16x2(a.q, b, row, h, 2 * lane);
+        if (TANGENT) dqr[i] = ld_bf16x2(a.dq, b, row, h, 2 * lane);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = warp + 8 * i;
       const int row = m * a.qblk + ch + rr;
       float2 phi = make_float2(0.f, 0.f), dphi = phi;
       if (row < a.L) {
-        softmax_row(ld_bf16x2(a.q, b, row, h, 2 * lane), phi);
-        if (TANGENT) softmax_row_jvp(phi, ld_bf16x2(a.dq, b, row, h, 2 * lane), dphi);
+        softmax_row(qr[i], phi);
+        if (TANGENT) softmax_row_jvp(phi, dqr[i], dphi);
       }
       *reinterpret_cast<float2*>(P + rr * LP + 2 * lane) = phi;
       const float den = warp_sum(fmaf(phi.x, z0, phi.y * z1));
@@ -296,10 +373,16 @@ __global__ void __launch_bounds__(256) lin_apply_kernel(const ApplyArgs a) {
     }
     __syncthreads();
     float num[4][4] = {}, dnum[4][4] = {};
-    tile_mm(P, C, r0, c0, num);
-    if (TANGENT) {
-      tile_mm(dP, C, r0, c0, dnum);
-      tile_mm(P, dC, r0, c0, dnum);
+    {
+      const MmaPos mp(tid);
+      float fr[4][4] = {}, dfr[4][4] = {};
+      warp_mm_tf32<false>(P, C, mp.mr, mp.nc, mp.g, mp.t, fr);
+      if (TANGENT) {
+        warp_mm_tf32<false>(dP, C, mp.mr, mp.nc, mp.g, mp.t, dfr);
+        warp_mm_tf32<false>(P, dC, mp.mr, mp.nc, mp.g, mp.t, dfr);
+      }
+      frags_to_blocks(fr, S, mp.mr, mp.nc, mp.g, mp.t, r0, c0, num);
+      if (TANGENT) frags_to_blocks(dfr, S, mp.mr, mp.nc, mp.g, mp.t, r0, c0, dnum);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -353,6 +436,7 @@ __global__ void __launch_bounds__(256) lin_bwd_rows_kernel(const BwdRowsArgs a) 
   float* Ct = C + LSTATE;             // [64 e][LP]: H^T
   float* P = Ct + 64 * LP;            // phi rows
   float* G = P + 64 * LP;             // g_num rows
+  float* S = G;                       // result tile of the products (G is dead at both times)
   __shared__ float Den[64], GD[64];
   const int m = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -366,18 +450,30 @@ __global__ void __launch_bounds__(256) lin_bwd_rows_kernel(const BwdRowsArgs a) 
   for (int j = 0; j < 4; ++j) zc[j] = C[(c0 + j) * LP + 64];
   for (int ch = 0; ch < a.qblk; ch += 64) {
     if (ch) __syncthreads();
-#pragma unroll 4
-    for (int rr = warp; rr < 64; rr += 8) {
-      const int row = m * a.qblk + ch + rr;
+    float2 qr[8];                   // this warp's eight rows: loads first, then the softmaxes
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = m * a.qblk + ch + warp + 8 * i;
+      qr[i] = row < a.L ? ld_bf16x2(a.q, b, row, h, 2 * lane) : make_float2(0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = warp + 8 * i;
       float2 phi = make_float2(0.f, 0.f);
-      if (row < a.L) softmax_row(ld_bf16x2(a.q, b, row, h, 2 * lane), phi);
+      if (m * a.qblk + ch + rr < a.L) softmax_row(qr[i], phi);
       *reinterpret_cast<float2*>(P + rr * LP + 2 * lane) = phi;
       const float den = warp_sum(fmaf(phi.x, z0, phi.y * z1));
       if (lane == 0) Den[rr] = den + LIN_EPS;
     }
     __syncthreads();                  // also orders the writes of Ct before its first use
     float num[4][4] = {};
-    tile_mm(P, C, r0, c0, num);
+    const MmaPos mp(tid);
+    {
+      float fr[4][4] = {};
+      warp_mm_tf32<false>(P, C, mp.mr, mp.nc, mp.g, mp.t, fr);
+      frags_to_blocks(fr, S, mp.mr, mp.nc, mp.g, mp.t, r0, c0, num);
+      __syncthreads();              // S (= G) has been read: the g_num rows may go in
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int row = m * a.qblk + ch + r0 + i;
@@ -417,7 +513,11 @@ __global__ void __launch_bounds__(256) lin_bwd_rows_kernel(const BwdRowsArgs a) 
     }
     __syncthreads();
     float gp[4][4] = {};
-    tile_mm(G, Ct, r0, c0, gp);       // columns are d here
+    {
+      float fr[4][4] = {};
+      warp_mm_tf32<false>(G, Ct, mp.mr, mp.nc, mp.g, mp.t, fr);       // columns are d here
+      frags_to_blocks(fr, S, mp.mr, mp.nc, mp.g, mp.t, r0, c0, gp);
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int row = m * a.qblk + ch + r0 + i;
@@ -456,28 +556,43 @@ __global__ void __launch_bounds__(256) lin_bwd_kv_kernel(const BwdKvArgs a) {
   float* Ct = C + LSTATE;             // [64 e][LP]: gH^T
   float* P = Ct + 64 * LP;            // phi(k) rows
   float* V = P + 64 * LP;             // v rows
+  float* S = V;                       // result tile of the products (V is dead by then)
   const int n = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   load_state(C, a.gS + (((int64_t)b * a.H + h) * a.Nb + n) * LSTATE, tid);
-#pragma unroll 4
-  for (int rr = warp; rr < 64; rr += 8) {
-    const int row = n * 64 + rr;
-    float2 phi = make_float2(0.f, 0.f), vv = phi;
-    if (row < a.lim) {
-      softmax_row(ld_bf16x2(a.k, b, row, h, 2 * lane), phi);
-      vv = ld_bf16x2(a.v, b, row, h, 2 * lane);
+  {
+    float2 kr[8], vr[8];              // this warp's eight rows: loads first, then the softmaxes
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int row = n * 64 + warp + 8 * i;
+      kr[i] = vr[i] = make_float2(0.f, 0.f);
+      if (row < a.lim) {
+        kr[i] = ld_bf16x2(a.k, b, row, h, 2 * lane);
+        vr[i] = ld_bf16x2(a.v, b, row, h, 2 * lane);
+      }
     }
-    *reinterpret_cast<float2*>(P + rr * LP + 2 * lane) = phi;
-    *reinterpret_cast<float2*>(V + rr * LP + 2 * lane) = vv;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = warp + 8 * i;
+      float2 phi = make_float2(0.f, 0.f);
+      if (n * 64 + rr < a.lim) softmax_row(kr[i], phi);
+      *reinterpret_cast<float2*>(P + rr * LP + 2 * lane) = phi;
+      *reinterpret_cast<float2*>(V + rr * LP + 2 * lane) = vr[i];
+    }
   }
   __syncthreads();
   transpose_state(Ct, C, tid);
   const int r0 = (tid >> 4) * 4, c0 = (tid & 15) * 4;
-  float gv[4][4] = {};
-  tile_mm(P, C, r0, c0, gv);          // g_v, columns e
-  __syncthreads();
-  float gp[4][4] = {};
-  tile_mm(V, Ct, r0, c0, gp);         // g_phi, columns d
+  float gv[4][4] = {}, gp[4][4] = {};
+  {
+    const MmaPos mp(tid);
+    float f1[4][4] = {}, f2[4][4] = {};
+    __syncthreads();                  // Ct is complete
+    warp_mm_tf32<false>(P, C, mp.mr, mp.nc, mp.g, mp.t, f1);     // g_v, columns e
+    warp_mm_tf32<false>(V, Ct, mp.mr, mp.nc, mp.g, mp.t, f2);    // g_phi, columns d
+    frags_to_blocks(f1, S, mp.mr, mp.nc, mp.g, mp.t, r0, c0, gv);
+    frags_to_blocks(f2, S, mp.mr, mp.nc, mp.g, mp.t, r0, c0, gp);
+  }
   float gz[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) gz[j] = C[(c0 + j) * LP + 64];
@@ -628,12 +743,12 @@ extern "C" int imf_lin_states(const void* x, const void* dx, const void* y, cons
   a.L = L; a.H = H; a.bs = bs; a.nblk_pad = nblk_pad; a.lim = lim < L ? lim : L; a.y_fp32 = y_fp32;
   a.tangent = dx != nullptr;
   const dim3 grid(nblk, H, B);
-  const size_t base = (size_t)(64 * 64 + 64 * LW) * sizeof(float);
+  const size_t tile = (size_t)64 * LP * sizeof(float);      // X, Y (+ dX, dY with a tangent)
   if (dx) {
-    if (set_smem(lin_states_kernel<true>, 2 * base)) return -3;
-    lin_states_kernel<true><<<grid, 256, 2 * base, (cudaStream_t)stream>>>(a);
+    if (set_smem(lin_states_kernel<true>, 4 * tile)) return -3;
+    lin_states_kernel<true><<<grid, 256, 4 * tile, (cudaStream_t)stream>>>(a);
   } else {
-    lin_states_kernel<false><<<grid, 256, base, (cudaStream_t)stream>>>(a);
+    lin_states_kernel<false><<<grid, 256, 2 * tile, (cudaStream_t)stream>>>(a);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
