@@ -545,35 +545,41 @@ attn_fwd_combine_kernel(const AttParams p, int G) {
   const int item = (int)(bound / p.n_kv);
   if (item >= p.n_items) return;
   const int qb = item % p.n_qblk, h = (item / p.n_qblk) % p.H, b = item / (p.n_qblk * p.H);
-  const int r = threadIdx.x;
-  const int q_row = qb * C::ITEM_M + r;
-  if (q_row >= p.L) return;
   const float* pa = p.scratch + ((size_t)c * 2 + 0) * att_part_floats<TANGENT, NTP>();
   const float* pb = p.scratch + ((size_t)c * 2 + 1) * att_part_floats<TANGENT, NTP>();
   const float* sa = pa + (size_t)C::ITEM_M * C::ACC;
   const float* sb = pb + (size_t)C::ITEM_M * C::ACC;
-  const float ma = sa[r], mb = sb[r];
-  const float m = fmaxf(ma, mb);
   const float scale_log2 = p.scale * 1.4426950408889634f;
-  const float wa = ex2((ma - m) * scale_log2), wb = ex2((mb - m) * scale_log2);
-  const float l = sa[C::ITEM_M + r] * wa + sb[C::ITEM_M + r] * wb;
-  const float mu = sa[2 * C::ITEM_M + r] * wa + sb[2 * C::ITEM_M + r] * wb;
-  const float inv_l = 1.f / l;
-  const float* aa = pa + (size_t)r * C::ACC;
-  const float* ab = pb + (size_t)r * C::ACC;
-  const int64_t off = (int64_t)b * p.o_sb + (int64_t)q_row * p.o_sl + (int64_t)h * p.o_sh;
-  for (int col = 0; col < ATT_HD; col += 2) {
-    const float o0 = (aa[col] * wa + ab[col] * wb) * inv_l;
-    const float o1 = (aa[col + 1] * wa + ab[col + 1] * wb) * inv_l;
+  // one warp per row, a lane per pair of columns: 256-byte reads of the two partial rows and
+  // a 128-byte write of the merged row (a thread per row would touch a cache line per value)
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int r = warp; r < C::ITEM_M; r += nwarps) {
+    const int q_row = qb * C::ITEM_M + r;
+    if (q_row >= p.L) break;
+    const float ma = sa[r], mb = sb[r];
+    const float m = fmaxf(ma, mb);
+    const float wa = ex2((ma - m) * scale_log2), wb = ex2((mb - m) * scale_log2);
+    const float l = sa[C::ITEM_M + r] * wa + sb[C::ITEM_M + r] * wb;
+    const float mu = sa[2 * C::ITEM_M + r] * wa + sb[2 * C::ITEM_M + r] * wb;
+    const float inv_l = 1.f / l;
+    const float* aa = pa + (size_t)r * C::ACC;
+    const float* ab = pb + (size_t)r * C::ACC;
+    const int64_t off = (int64_t)b * p.o_sb + (int64_t)q_row * p.o_sl + (int64_t)h * p.o_sh;
+    const int col = 2 * lane;
+    const float2 xa = *reinterpret_cast<const float2*>(aa + col);
+    const float2 xb = *reinterpret_cast<const float2*>(ab + col);
+    const float o0 = (xa.x * wa + xb.x * wb) * inv_l;
+    const float o1 = (xa.y * wa + xb.y * wb) * inv_l;
     *reinterpret_cast<uint32_t*>(p.o + off + col) = pack_bf16(o0, o1);
     if (TANGENT) {
-      const float d0 = (aa[ATT_HD + col] * wa + ab[ATT_HD + col] * wb) * inv_l - mu * inv_l * o0;
-      const float d1 =
-          (aa[ATT_HD + col + 1] * wa + ab[ATT_HD + col + 1] * wb) * inv_l - mu * inv_l * o1;
+      const float2 ya = *reinterpret_cast<const float2*>(aa + ATT_HD + col);
+      const float2 yb = *reinterpret_cast<const float2*>(ab + ATT_HD + col);
+      const float d0 = (ya.x * wa + yb.x * wb) * inv_l - mu * inv_l * o0;
+      const float d1 = (ya.y * wa + yb.y * wb) * inv_l - mu * inv_l * o1;
       *reinterpret_cast<uint32_t*>(p.dout + off + col) = pack_bf16(d0, d1);
     }
+    if (p.lse && lane == 0) p.lse[((int64_t)b * p.H + h) * p.L + q_row] = m * p.scale + __logf(l);
   }
-  if (p.lse) p.lse[((int64_t)b * p.H + h) * p.L + q_row] = m * p.scale + __logf(l);
 }
 
 static int make_qkv_map(CUtensorMap* m, const void* ptr, int B, int L, int H, int64_t sb,
