@@ -307,15 +307,17 @@ class _BlockFn(torch.autograd.Function):
         gW_a = wgrad("W_a", g_a, n1)
         # 1'. remix + norm1; the prefix gradient of step 9' rides in as g_pfx_ext
         ext = g_sn2[-1] if fresh else g_res2
+        # the snapshot gradients of step 9' are added in by the kernel (no separate adds)
         g_pfx, _, g_sn1, part1 = R.resnorm_bwd(
             pfx, None, None, sn, w1 if (use_res and nsnap) else None, g_n1, eps, g_n1v, ext,
-            raw=True)
+            raw=True, g_snaps_ext=g_sn2[:nsnap] if (use_res and nsnap) else None)
         gg_n1 = small("g_n1", part1, 0, d)
         g_w1 = cs.add(part1, 1, d, None) if (use_res and nsnap) else None
         cs.flush()
         g_snaps = []
         for j in range(nsnap):
-            g_snaps.append(g_sn1[j].add_(g_sn2[j]).view(B, L, d))
+            g_snaps.append((g_sn1[j] if (use_res and nsnap) else g_sn1[j].add_(g_sn2[j]))
+                           .view(B, L, d))
         if g_w1 is None:
             g_w1 = torch.zeros_like(w1) if w1 is not None else None
         if g_w2 is None:

@@ -22,7 +22,7 @@ struct ResNormArgs {
   const __nv_bfloat16* dy;
   const float* gate;
   const float* snaps[MAX_CANDS];
-  const float* dsnaps[MAX_CANDS];
+  const float* dsnaps[MAX_CANDS];   // forward: tangents; backward: gradients added to g_snaps
   int nsnap;
   const float* w;
   const float* gain;
@@ -313,8 +313,8 @@ __global__ void __launch_bounds__(ROW_THREADS, NV <= 2 ? 4 : 1) resnorm_bwd_kern
           const float4 gv = fma4(v, -c3, fma4(w4, c1, h[i] * p[j]));
           float* aw = acc + 1 * D + lane * 4 + i * 128;
           st4(aw, fma4(v, c1, ld4(aw)));  // g_w += gs r_j v_j
-          if (j < a.nsnap)
-            st4(a.g_snaps[j] + o, gv);
+          if (j < a.nsnap)   // backward: dsnaps[j], when given, is a gradient to add in
+            st4(a.g_snaps[j] + o, a.dsnaps[j] ? gv + ld4(a.dsnaps[j] + o) : gv);
           else
             gp_last[i] = gv;
         }

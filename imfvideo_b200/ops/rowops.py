@@ -112,10 +112,12 @@ class ColSums:
 
 
 def resnorm_bwd(res, y, gate, snaps: Sequence[torch.Tensor], w, gain, eps: float, gn,
-                g_pfx_ext, want_g_res: bool = True, raw: bool = False):
+                g_pfx_ext, want_g_res: bool = True, raw: bool = False,
+                g_snaps_ext: Optional[Sequence[torch.Tensor]] = None):
     """Returns (g_res fp32 | None, g_y bf16 | None, [g_snaps fp32], g_gain, g_w, g_gate);
     with ``raw`` the last three are replaced by the [g, 3, D] partial buffer (columns gain,
-    w, gate) for a later ``ColSums`` reduction."""
+    w, gate) for a later ``ColSums`` reduction.  ``g_snaps_ext``: fp32 gradients (one per
+    snapshot) that the kernel adds to the snapshot gradients it writes."""
     rows, D = gn.shape
     dev = gn.device
     ns = len(snaps)
@@ -125,7 +127,8 @@ def resnorm_bwd(res, y, gate, snaps: Sequence[torch.Tensor], w, gain, eps: float
     partial = torch.empty(row_grid(rows), 3, D, dtype=F32, device=dev)
     ptrs = [_p(res), 0, _p(y), 0, _p(gate), _p(w), _p(gain), 0, 0, 0, 0, _p(gn), _p(g_pfx_ext),
             _p(g_res), _p(g_y), _p(partial)]
-    ptrs += [_p(s) for s in snaps] + [0] * ns + [_p(s) for s in g_snaps]
+    ext = [0] * ns if g_snaps_ext is None else [_p(e) for e in g_snaps_ext[:ns]]
+    ptrs += [_p(s) for s in snaps] + ext + [_p(s) for s in g_snaps]
     _chk(_lib.imf_resnorm(_ptr_array(ptrs), ns, rows, D, float(eps), 0, 1, K._stream()),
          "imf_resnorm bwd")
     if raw:
