@@ -312,3 +312,22 @@ def test_attention_backward_bitwise_repeatable_over_several_waves(K, hd, B, L, H
         K.set_deterministic(False)
     assert _rel(first[0], loose[0]) < 1e-3
     K.check_status()
+
+
+@pytest.mark.parametrize("M,N,Kd", [(20480, 528, 256), (29140, 1000, 200), (58280, 264, 64),
+                                    (19000, 768, 256)])
+def test_gemm_short_k_many_tiles(K, M, N, Kd):
+    """Short-K products with many tiles (the projections of a narrow model on a long sequence):
+    ragged M, N and K, a strided A, bit-equal repeats."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + Kd)
+    a_wide = torch.randn(M, Kd + 24, device="cuda", generator=g).bfloat16()
+    a = a_wide[:, 8:8 + Kd]                                   # row pitch != K, 16-byte aligned
+    b = torch.randn(N, Kd, device="cuda", generator=g).bfloat16()
+    out = K.gemm(a, b, alpha=0.5)
+    ref = 0.5 * (a.float() @ b.float().t())
+    assert _rel(out, ref) < 4e-3
+    idx = torch.tensor([0, 127, 128, M // 2, M - 1], device="cuda")
+    assert torch.allclose(out[idx].float(), ref[idx], rtol=2e-2, atol=2e-2 * ref.abs().max().item())
+    out2 = K.gemm(a, b, alpha=0.5)
+    assert torch.equal(out, out2)
+    K.check_status()
