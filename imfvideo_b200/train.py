@@ -171,23 +171,41 @@ def qk_clip(net, tau: float, world: int = 1, skip: Optional[torch.Tensor] = None
 
     Returns (#clipped heads, global max logit) as Python numbers, or as two
     device scalars with ``as_tensors`` (no host read)."""
-    mods = [(n, m) for n, m in net.named_modules() if isinstance(m, M.MLAAttention)
-            and getattr(m.attn_impl, "logit_max_log2", None) is not None]
-    if not mods:
+    # the module walk, the EMA pairing and (below) the kernel's pointer table are the same
+    # every step: they are built once per (net, ema) and kept on the net
+    cache = net.__dict__.setdefault("_qk_clip_cache", {})
+    key = (id(ema) if (ema is not None and ema_w > 0) else None)
+    if cache.get("key", "unset") != key:
+        cache.clear()
+        cache["key"] = key
+        named = [(n, m) for n, m in net.named_modules() if isinstance(m, M.MLAAttention)]
+        ema_mods = dict(ema.named_modules()) if key is not None else {}
+        cache["named"] = [(m, ema_mods.get(n)) for n, m in named]
+    pairs = [(m, e) for m, e in cache["named"]
+             if getattr(m.attn_impl, "logit_max_log2", None) is not None]
+    if not pairs:
         if as_tensors:
-            z = torch.zeros((), device=next(net.parameters()).device)
+            z = cache.get("zero")
+            if z is None:
+                z = cache["zero"] = torch.zeros((), device=next(net.parameters()).device)
             return z, z
         return 0, 0.0
-    ema_mods = dict(ema.named_modules()) if (ema is not None and ema_w > 0) else {}
-    emas = [ema_mods.get(n) for n, _ in mods]
-    mods = [m for _, m in mods]
-    stats = torch.stack([m.attn_impl.logit_max_log2.float() for m in mods])   # (n, H)
+    mods = [m for m, _ in pairs]
+    emas = [e for _, e in pairs]
+    rows = [m.attn_impl.logit_max_log2.float() for m in mods]
+    buf = cache.get("stats")
+    if buf is None or buf.shape != (len(rows),) + tuple(rows[0].shape) or buf.device != rows[0].device:
+        buf = cache["stats"] = torch.empty(len(rows), *rows[0].shape, dtype=torch.float32,
+                                           device=rows[0].device)
+        cache.pop("table", None)
+    stats = torch.stack(rows, out=buf)                                          # (n, H)
     if world > 1:
         if max_reduce is not None:
             stats = max_reduce(stats)
         else:
             dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    fused = _qk_clip_kernel(mods, emas, stats, tau, skip, ema_w)
+    fused = _qk_clip_kernel(mods, emas, stats, tau, skip, ema_w,
+                            cache if (world == 1 or max_reduce is None) else None)
     if fused is not None:
         n_hot, s_max = fused
     else:
@@ -213,9 +231,12 @@ def qk_clip(net, tau: float, world: int = 1, skip: Optional[torch.Tensor] = None
     return int(n), float(mx)
 
 
-def _qk_clip_kernel(mods, emas, stats: torch.Tensor, tau: float, skip, ema_w: float):
+def _qk_clip_kernel(mods, emas, stats: torch.Tensor, tau: float, skip, ema_w: float,
+                    cache: Optional[dict] = None):
     """All modules in one launch of the library's kernel (fp32 contiguous weights on a GPU);
-    None when that does not apply.  Returns two device scalars."""
+    None when that does not apply.  Returns two device scalars.  ``cache``: a dict in which the
+    device copy of the pointer table is kept while ``stats`` and the weights stay where they
+    are (the caller passes its persistent statistics buffer then)."""
     w0 = mods[0].q_b_proj.weight
     if not w0.is_cuda or any(m.q_b_proj.weight.dtype != torch.float32
                              or not m.q_b_proj.weight.is_contiguous() for m in mods):
@@ -236,16 +257,24 @@ def _qk_clip_kernel(mods, emas, stats: torch.Tensor, tau: float, skip, ema_w: fl
     rec = np.dtype([("w", "<u8"), ("stat", "<u8"), ("H", "<i4"), ("hd", "<i4"), ("dn", "<i4"),
                     ("cols", "<i4"), ("ema", "<u8")])
     stats = stats.contiguous()
-    host = np.zeros(len(mods), dtype=rec)
-    for i, (m, e) in enumerate(zip(mods, emas)):
-        w = m.q_b_proj.weight
-        ew = 0
-        if e is not None and e.q_b_proj.weight.dtype == torch.float32 \
-                and e.q_b_proj.weight.is_contiguous():
-            ew = e.q_b_proj.weight.data_ptr()
-        host[i] = (w.data_ptr(), stats[i].data_ptr(), m.num_heads, m.qk_head_dim,
-                   m.qk_nope_head_dim, w.shape[1], ew)
-    table = torch.from_numpy(host.view(np.uint8).reshape(-1).copy()).to(w0.device)
+    sig = (stats.data_ptr(), tuple(m.q_b_proj.weight.data_ptr() for m in mods),
+           tuple(0 if e is None else e.q_b_proj.weight.data_ptr() for e in emas))
+    table = None
+    if cache is not None and cache.get("table_sig") == sig:
+        table = cache.get("table")
+    if table is None:
+        host = np.zeros(len(mods), dtype=rec)
+        for i, (m, e) in enumerate(zip(mods, emas)):
+            w = m.q_b_proj.weight
+            ew = 0
+            if e is not None and e.q_b_proj.weight.dtype == torch.float32 \
+                    and e.q_b_proj.weight.is_contiguous():
+                ew = e.q_b_proj.weight.data_ptr()
+            host[i] = (w.data_ptr(), stats[i].data_ptr(), m.num_heads, m.qk_head_dim,
+                       m.qk_nope_head_dim, w.shape[1], ew)
+        table = torch.from_numpy(host.view(np.uint8).reshape(-1).copy()).to(w0.device)
+        if cache is not None:
+            cache["table"], cache["table_sig"] = table, sig
     summary = torch.zeros(2, dtype=torch.float32, device=w0.device)
     lib = K._lib
     lib.imf_qk_clip.restype = ctypes.c_int
