@@ -604,9 +604,9 @@ def _sparse_core_bwd_kernels(self, q, k, v, saved, go, gv_out, alpha_param, cube
             _, _, kk = SP.quantize_blocks(K._tma_ok(k), 64, want_q=False, want_fq=True)
             _, _, vv = SP.quantize_blocks(K._tma_ok(v), 64, want_q=False, want_fq=True)
         qlist, qflags, qrank = SP.kv_lists(flags, want_rank=True)       # `flags`: the maps (see fwd)
-        gq_s, gk_s, gv_s = K.attn_bwd(qq, kk, vv, o_s, lse, g_os, qlist=qlist, qflags=qflags,
-                                      qrank=qrank)
-        gq = (gq_s.float() + gq_l).to(q.dtype)
+        # the linear branch's query gradient rides into the block-sparse backward's dQ epilogue
+        gq, gk_s, gv_s = K.attn_bwd(qq, kk, vv, o_s, lse, g_os, qlist=qlist, qflags=qflags,
+                                    qrank=qrank, dq_add=gq_l)
         gk, gv = LA.backward_kv(q, k, v, gnum, gden, sel, gk_s, gv_s, self.qblk, self.bk,
                                 self.n_comp, gv_out=gv_out)
     return gq, gk, gv

@@ -551,14 +551,20 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ q,
   }
 }
 
+// dq = bf16(acc * scale (+ add)); `add`: an fp32 (B, L, H, 64) gradient from another branch
 __global__ void attn_bwd_post_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
-                                     long n4, float scale) {
+                                     long n4, float scale, const float* __restrict__ add) {
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n4) return;
-  const float4 v = reinterpret_cast<const float4*>(acc)[i];
+  float4 v = reinterpret_cast<const float4*>(acc)[i];
+  v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+  if (add) {
+    const float4 a = reinterpret_cast<const float4*>(add)[i];
+    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+  }
   uint2 o;
-  o.x = pack_bf16(v.x * scale, v.y * scale);
-  o.y = pack_bf16(v.z * scale, v.w * scale);
+  o.x = pack_bf16(v.x, v.y);
+  o.y = pack_bf16(v.z, v.w);
   reinterpret_cast<uint2*>(dq)[i] = o;
 }
 
@@ -644,7 +650,8 @@ extern "C" long imf_attn_bwd_scratch_bytes_hd(int B, int L, int H, int head_dim)
 }
 
 // All tensors (B, L, H, head_dim) bf16, head_dim 64 or 128 (128: dense only); strides[0..11]: (batch,row,head) for q,k,v,do;
-// o contiguous-like with its own strides; dq contiguous (B, L, H, 64);
+// o contiguous-like with its own strides; dq contiguous (B, L, H, 64); dq_add: optional fp32
+// (B, L, H, 64) contiguous, added to dq before the rounding to bf16 (another branch's gradient);
 // dk/dv with given strides (dv may point into a wider buffer).
 extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const void* o,
                             const void* d_o, const float* lse, void* dq, void* dk, void* dv, int B,
@@ -652,12 +659,12 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
                             const int64_t* o_strides, const int64_t* dk_strides,
                             const int64_t* dv_strides, float scale, void* scratch,
                             long scratch_bytes, const int* qlist, const uint8_t* qflags,
-                            const uint16_t* qrank, int qmax, int fixed_order, int* status,
-                            void* stream) {
+                            const uint16_t* qrank, int qmax, int fixed_order, const float* dq_add,
+                            int* status, void* stream) {
   using namespace imf;
   if ((head_dim != BW_HD && head_dim != 128) || B <= 0 || L <= 0 || H <= 0) return IMF_ERR_ARG;
   if (head_dim == 128) {
-    if (qlist != nullptr) return IMF_ERR_ARG;       // block-sparse lists: head_dim 64 only
+    if (qlist != nullptr || dq_add != nullptr) return IMF_ERR_ARG;   // head_dim 64 only
     if ((reinterpret_cast<uintptr_t>(scratch) & 255) || (reinterpret_cast<uintptr_t>(dq) & 15) ||
         (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15))
       return IMF_ERR_ARG;
@@ -671,7 +678,8 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
   }
   if (scratch == nullptr || scratch_bytes < imf_attn_bwd_scratch_bytes(B, L, H)) return IMF_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(scratch) & 255) || (reinterpret_cast<uintptr_t>(dq) & 15) ||
-      (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15))
+      (reinterpret_cast<uintptr_t>(dk) & 15) || (reinterpret_cast<uintptr_t>(dv) & 15) ||
+      (reinterpret_cast<uintptr_t>(dq_add) & 15))
     return IMF_ERR_ARG;
   for (int i = 0; i < 3; ++i)
     if ((dk_strides[i] & 7) || (dv_strides[i] & 7) || (o_strides[i] & 1)) return IMF_ERR_ARG;
@@ -768,6 +776,6 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
   }
   const long n4 = (long)B * L * H * 64 / 4;
   attn_bwd_post_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(
-      dq_acc, static_cast<__nv_bfloat16*>(dq), n4, scale);
+      dq_acc, static_cast<__nv_bfloat16*>(dq), n4, scale, dq_add);
   return cudaGetLastError() == cudaSuccess ? IMF_OK : IMF_ERR_LAUNCH;
 }

@@ -290,7 +290,7 @@ if _has("imf_attn_bwd"):
     _lib.imf_attn_bwd.restype = c_int
     _lib.imf_attn_bwd.argtypes = [c_void_p] * 9 + [c_int] * 4 + [c_void_p] * 4 + \
         [c_float, c_void_p, ctypes.c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
-         c_void_p]
+         c_void_p, c_void_p]
     _lib.imf_attn_bwd_scratch_bytes.restype = ctypes.c_long
     _lib.imf_attn_bwd_scratch_bytes.argtypes = [c_int, c_int, c_int]
     _lib.imf_attn_bwd_scratch_bytes_hd.restype = ctypes.c_long
@@ -312,13 +312,16 @@ def set_deterministic(on: bool) -> None:
 
 def attn_bwd(q, k, v, o, lse, go, scale: Optional[float] = None,
              gv_out: Optional[torch.Tensor] = None, qlist: Optional[torch.Tensor] = None,
-             qflags: Optional[torch.Tensor] = None, qrank: Optional[torch.Tensor] = None):
+             qflags: Optional[torch.Tensor] = None, qrank: Optional[torch.Tensor] = None,
+             dq_add: Optional[torch.Tensor] = None):
     """(dq, dk, dv) of dense attention; ``gv_out`` lets dv land in a strided
     view (e.g. the value band of the kv up-projection gradient).  With
     ``qlist`` / ``qflags`` (see ``ops.sparse.kv_lists``) the same kernel
     runs the block-sparse backward: each 128-row K/V tile walks only the query
     tiles that attend it; ``qrank`` (same source) gives the entries' places in the fixed
-    order of dQ additions (without it the block-sparse dQ adds land in arrival order)."""
+    order of dQ additions (without it the block-sparse dQ adds land in arrival order).
+    ``dq_add`` (fp32, (B, L, H, 64) contiguous, head_dim 64): added to dq before it is rounded
+    to bf16 (the query gradient of another branch of the same attention module)."""
     B, L, H, hd = q.shape
     scale = 1.0 / math.sqrt(hd) if scale is None else scale
     ts = [_tma_ok(t) for t in (q, k, v, go)]
@@ -327,6 +330,9 @@ def attn_bwd(q, k, v, o, lse, go, scale: Optional[float] = None,
         strides += list(_bls(t))
     arr = (c_int64 * 12)(*strides)
     o = o if o.stride(3) == 1 else o.contiguous()
+    if dq_add is not None:
+        assert dq_add.dtype == torch.float32 and dq_add.shape == (B, L, H, hd) \
+            and dq_add.is_contiguous() and hd == 64
     dq = torch.empty(B, L, H, hd, dtype=torch.bfloat16, device=q.device)
     dk = torch.empty(B, L, H, hd, dtype=torch.bfloat16, device=q.device)
     dv = gv_out if gv_out is not None else torch.empty(B, L, H, hd, dtype=torch.bfloat16,
@@ -342,7 +348,7 @@ def attn_bwd(q, k, v, o, lse, go, scale: Optional[float] = None,
                            ctypes.cast(i3(dk), c_void_p), ctypes.cast(i3(dv), c_void_p),
                            float(scale), _ptr(scr), nscr, _ptr(qlist), _ptr(qflags), _ptr(qrank),
                            0 if qlist is None else qlist.shape[-1], int(DETERMINISTIC),
-                           _ptr(status_word(q.device)), _stream())
+                           _ptr(dq_add), _ptr(status_word(q.device)), _stream())
     _check(rc, "imf_attn_bwd")
     LAUNCHES.count += 3
     return dq, dk, dv
