@@ -654,6 +654,7 @@ def main(argv=None) -> None:
             t_log = time.time()
         if step % cfg.run.ckpt_every == 0:
             trainer.save(sampler_state=inf.state(prefetched=1))
+    trainer.flush_stats()        # the last step's kernel status word (raises if one gave up)
     if hb is not None:
         hb.stop()
     pdist.shutdown()
