@@ -212,7 +212,10 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
       };
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        ti[t] = blockIdx.x * NT + t; kv_it[t] = 0; qn[t] = 0;
+        // slot t of every CTA takes tile t * grid + cta of each round: a last, partial round
+        // then leaves every CTA with fewer busy slots (whose steps run faster) instead of
+        // some CTAs with all four busy and the others idle
+        ti[t] = t * (int)gridDim.x + blockIdx.x; kv_it[t] = 0; qn[t] = 0;
         open_tile(t);
         n_active += n_j[t] > 0;
       }
@@ -289,54 +292,65 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
       };
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        ti[t] = blockIdx.x * NT + t; kv_it[t] = 0; step[t] = 0; qn[t] = 0;
+        ti[t] = t * (int)gridDim.x + blockIdx.x; kv_it[t] = 0; step[t] = 0; qn[t] = 0;
         open_tile(t);
         n_active += n_j[t] > 0;
       }
       uint32_t spins = 0;
       uint64_t t_start = globaltimer_ns();
+      // score product of slot t's next step, if its operands have landed.  It is tried in
+      // the same visit that issued the previous step's PV product as well (the tensor pipe
+      // runs the two in order, so P is read before the new scores land on it): a slot then
+      // does not wait a whole round over the other slots between the two.
+      auto issue_s = [&](int t) -> bool {
+        auto& sl = s.slot[t];
+        const uint32_t tb = tmem + t * C::TILE_COLS;
+        const int st = kv_it[t] % C::STAGES;
+        if (jj[t] == 0 && !mbar_test(&sl.q_full, qn[t] & 1)) return false;
+        if (!mbar_test(&sl.kv_full[st], (kv_it[t] / C::STAGES) & 1)) return false;
+        tc_fence_after();
+        // S (s32) = Q8 K8^T : K = 64 int8 = two k-steps of 32 bytes
+        if (INT8) {
+          const uint32_t q8a = smem_u32(sl.q8), k8a = smem_u32(sl.k8[st]);
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks)
+            mma_ss_i8(tb + C::SC_S, sdesc_kmajor_sw64(q8a + ks * 32),
+                      sdesc_kmajor_sw64(k8a + ks * 32), id_i8, ks != 0);
+        } else {
+          const uint32_t qa = smem_u32(sl.q[0]), ka = smem_u32(sl.kv[st][KI]);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            mma_ss(tb + C::SC_S, sdesc_kmajor(qa + ks * 32), sdesc_kmajor(ka + ks * 32), id_qk,
+                   ks != 0);
+        }
+        if (TANGENT) {
+          const uint32_t qa = smem_u32(sl.q[0]), dqa = smem_u32(sl.q[C::NQ - 1]);
+          const uint32_t ka = smem_u32(sl.kv[st][KI]), dka = smem_u32(sl.kv[st][DKI]);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            mma_ss(tb + C::SC_DS, sdesc_kmajor(dqa + ks * 32), sdesc_kmajor(ka + ks * 32),
+                   id_qk, ks != 0);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            mma_ss(tb + C::SC_DS, sdesc_kmajor(qa + ks * 32), sdesc_kmajor(dka + ks * 32),
+                   id_qk, 1);
+        }
+        tc_commit(&sl.s_full);
+        if (jj[t] == n_j[t] - 1) tc_commit(&sl.q_empty);      // last read of this tile's Q
+        want_pv[t] = true;
+        spins = 0;
+        return true;
+      };
       while (n_active > 0) {
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
           if (n_j[t] == 0) continue;
           auto& sl = s.slot[t];
           const uint32_t tb = tmem + t * C::TILE_COLS;
-          const int st = kv_it[t] % C::STAGES;
           if (!want_pv[t]) {
-            if (jj[t] == 0 && !mbar_test(&sl.q_full, qn[t] & 1)) continue;
-            if (!mbar_test(&sl.kv_full[st], (kv_it[t] / C::STAGES) & 1)) continue;
-            tc_fence_after();
-            // S (s32) = Q8 K8^T : K = 64 int8 = two k-steps of 32 bytes
-            if (INT8) {
-              const uint32_t q8a = smem_u32(sl.q8), k8a = smem_u32(sl.k8[st]);
-#pragma unroll
-              for (int ks = 0; ks < 2; ++ks)
-                mma_ss_i8(tb + C::SC_S, sdesc_kmajor_sw64(q8a + ks * 32),
-                          sdesc_kmajor_sw64(k8a + ks * 32), id_i8, ks != 0);
-            } else {
-              const uint32_t qa = smem_u32(sl.q[0]), ka = smem_u32(sl.kv[st][KI]);
-#pragma unroll
-              for (int ks = 0; ks < 4; ++ks)
-                mma_ss(tb + C::SC_S, sdesc_kmajor(qa + ks * 32), sdesc_kmajor(ka + ks * 32), id_qk,
-                       ks != 0);
-            }
-            if (TANGENT) {
-              const uint32_t qa = smem_u32(sl.q[0]), dqa = smem_u32(sl.q[C::NQ - 1]);
-              const uint32_t ka = smem_u32(sl.kv[st][KI]), dka = smem_u32(sl.kv[st][DKI]);
-#pragma unroll
-              for (int ks = 0; ks < 4; ++ks)
-                mma_ss(tb + C::SC_DS, sdesc_kmajor(dqa + ks * 32), sdesc_kmajor(ka + ks * 32),
-                       id_qk, ks != 0);
-#pragma unroll
-              for (int ks = 0; ks < 4; ++ks)
-                mma_ss(tb + C::SC_DS, sdesc_kmajor(qa + ks * 32), sdesc_kmajor(dka + ks * 32),
-                       id_qk, 1);
-            }
-            tc_commit(&sl.s_full);
-            if (jj[t] == n_j[t] - 1) tc_commit(&sl.q_empty);      // last read of this tile's Q
-            want_pv[t] = true;
-            spins = 0;
+            issue_s(t);
           } else {
+            const int st = kv_it[t] % C::STAGES;
             if (!mbar_test(&sl.p_full, step[t] & 1)) continue;
             // first PV of a tile overwrites O: the previous tile's epilogue must have read it
             if (jj[t] == 0 && qn[t] > 0 && !mbar_test(&sl.o_free, (qn[t] - 1) & 1)) continue;
@@ -370,6 +384,7 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
               open_tile(t);
               n_active -= n_j[t] == 0;
             }
+            if (n_j[t] != 0) issue_s(t);
           }
         }
         if ((++spins & 1023u) == 0) {
@@ -396,7 +411,7 @@ attn_sparse_fwd_kernel(const __grid_constant__ CUtensorMap tm_q8,
     const float grid_log2 = p.quant_p ? 6.9886846867721655f : 0.f;
     uint32_t step = 0;
     bool ok = true;
-    for (int ti = blockIdx.x * NT + t; ti < p.n_tiles && ok; ti += tile_stride) {
+    for (int ti = t * (int)gridDim.x + blockIdx.x; ti < p.n_tiles && ok; ti += tile_stride) {
       const SpTile tl = sp_tile(p, ti);
       const int q_row = tl.mt * SP_M + row;
       const bool live = q_row < p.L;
