@@ -330,17 +330,27 @@ class TransformerBlock(nn.Module):
         return supported(self.fused_geom())
 
     def fused_params(self, use_res: bool):
-        """(w1, w2, gains..., bf16 weights) for ops.block.run_block.  Under
-        no_grad the bf16 weight copies are cached until a parameter changes."""
+        """(w1, w2, gains..., bf16 weights) for ops.block.run_block.
+
+        The bf16 weight copies (casts / concatenations of the fp32 parameters) are cached
+        until a parameter's version counter moves, for gradient-free passes and also for
+        passes under autograd whose weight gradients go straight into the parameters'
+        gradient buffers (``GradSinks.direct``): those return no gradient for the
+        matrices, so the copies need no autograd history and one set serves every pass
+        of a step.  ``sinks.mats_cached`` tells the backward that this happened."""
         a, mlp = self.attn, self.mlp
         ws = [a.q_a_proj.weight, a.kv_a_proj.weight] + ([a.g_proj.weight] if a.use_output_gate else [])
         srcs = ws + [a.q_b_proj.weight, a.kv_b_proj.weight, a.out_proj.weight, mlp.w1.weight,
                      mlp.w3.weight, mlp.w2.weight]
         key = tuple(w._version for w in srcs)
         cache = getattr(self, "_wcache", None)
-        if not torch.is_grad_enabled() and cache is not None and cache[0] == key:
-            mats = cache[1]
-        else:
+        grad_on = torch.is_grad_enabled()
+        sinks = self.fused_sinks() if grad_on else None
+        cacheable = not grad_on or sinks.direct()
+        if sinks is not None:
+            sinks.mats_cached = cacheable
+
+        def build():
             bf = torch.bfloat16
             f = mlp.w1.out_features
             pad = (-f) % 8
@@ -351,14 +361,30 @@ class TransformerBlock(nn.Module):
                 w2_ = torch.nn.functional.pad(w2_, (0, pad))
             else:
                 w13 = torch.cat([w1_, w3_], dim=0)
-            mats = (torch.cat(ws, dim=0).to(bf), a.q_b_proj.weight.to(bf),
+            return (torch.cat(ws, dim=0).to(bf), a.q_b_proj.weight.to(bf),
                     a.kv_b_proj.weight.to(bf), a.out_proj.weight.to(bf), w13.to(bf),
                     w2_.to(bf).contiguous())
-            if not torch.is_grad_enabled():
-                self._wcache = (key, mats)
+
+        if not cacheable:
+            mats = build()                      # autograd carries the weight gradients back
+        elif cache is not None and cache[0] == key:
+            mats = cache[1]
+        else:
+            with torch.no_grad():
+                mats = build()
+            self._wcache = (key, mats)
         if use_res:
-            w1 = self.attn_res_norm.weight * self.attn_res_proj.weight.reshape(-1)
-            w2 = self.mlp_res_norm.weight * self.mlp_res_proj.weight.reshape(-1)
+            rs = (self.attn_res_norm.weight, self.attn_res_proj.weight,
+                  self.mlp_res_norm.weight, self.mlp_res_proj.weight)
+            rkey = tuple(w._version for w in rs)
+            rc = getattr(self, "_rcache", None)
+            if not grad_on and rc is not None and rc[0] == rkey:
+                w1, w2 = rc[1]
+            else:
+                w1 = rs[0] * rs[1].reshape(-1)
+                w2 = rs[2] * rs[3].reshape(-1)
+                if not grad_on:
+                    self._rcache = (rkey, (w1, w2))
         else:
             w1 = w2 = None
         return (w1, w2, self.norm1.weight, self.norm2.weight, a.q_a_layernorm.weight,

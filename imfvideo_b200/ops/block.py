@@ -67,6 +67,7 @@ class GradSinks:
         self.pieces = pieces
         self.small = small or {}      # the 1-D parameters (gains, gates) by their role
         self.on_backward = None       # optional callable: this block's backward has begun
+        self.mats_cached = False      # the last forward used weight copies without autograd history
 
     def small_dst(self, name: str):
         """fp32 gradient buffer of the 1-D parameter in role ``name`` (flattened), or None."""
@@ -210,6 +211,7 @@ class _BlockFn(torch.autograd.Function):
                                   act[:rows], m[:rows], *core_saved)
             ctx.meta = (g, core, fresh, use_res, eps, beta, lbeta, nsnap, B, L, len(core_saved))
             ctx.sinks = sinks
+            ctx.mats_cached = bool(getattr(sinks, "mats_cached", False))
         new_p = out[0].view(B, L, d)
         new_t = out[1].view(B, L, d) if has_t else out.new_empty(0)
         ctx.mark_non_differentiable(new_t)
@@ -242,6 +244,11 @@ class _BlockFn(torch.autograd.Function):
         # launch at the end adds them all up, into the same kind of destination.
         sinks = getattr(ctx, "sinks", None)
         direct = sinks is not None and sinks.direct()
+        if not direct and getattr(ctx, "mats_cached", False):
+            # the forward used cached weight copies without autograd history because the
+            # gradient buffers existed then; returned gradients would reach no parameter
+            raise RuntimeError("the parameters' fp32 gradient buffers were removed between the "
+                               "forward and the backward pass of a fused block")
         wgrad = (lambda name, dy, x: sinks.accumulate(name, dy, x)) if direct else \
             (lambda name, dy, x: K.gemm_wgrad(dy, x).to(BF16))
         cs = R.ColSums()

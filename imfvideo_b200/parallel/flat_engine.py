@@ -46,6 +46,7 @@ import torch
 import torch.distributed as dist
 
 from ..optim.moonlight import Moonlight, get_ns_coefficients, zeropower_via_newtonschulz5
+from ..utils.versions import mark_written
 from .grad_sync import GradSync
 from .owner import assign_owners
 
@@ -224,17 +225,20 @@ class FlatEngine(GradSync):
     # ------------------------------------------------------------- set-up ---
     def _repoint(self, name_of, ema_of) -> None:
         opt = self.opt
+        self._written = []        # every tensor a step writes through the arenas (see step())
         with torch.no_grad():
             def place(p, off):
                 n = p.numel()
                 self.P[off:off + n].copy_(p.detach().reshape(-1))
                 p.data = self.P[off:off + n].view(p.shape)
                 p.grad = self.G[off:off + n].view(p.shape)
+                self._written.append(p)
                 if self.E is not None:
                     q = ema_of.get(name_of[id(p)])
                     if q is not None:
                         self.E[off:off + n].copy_(q.detach().reshape(-1))
                         q.data = self.E[off:off + n].view(q.shape)
+                        self._written.append(q)
             for i, (_, p) in enumerate(self.muon):
                 place(p, self.muon_off[i])
                 st = opt.state[p]
@@ -465,6 +469,9 @@ class FlatEngine(GradSync):
         if not use_k and self.E is not None:
             lerp = self.E + self.ema_w * (self.P - self.E)
             self.E.copy_(torch.where(skip.bool(), self.E, lerp))
+        # the arenas were written through raw pointers / other views: move the parameters'
+        # version counters, which the blocks' cached bf16 weight copies are keyed on
+        mark_written(self._written)
 
     def _newton_schulz_eager(self, opt: Moonlight, g0) -> None:
         """Batched Newton-Schulz per contiguous same-shape run of the owned segment:

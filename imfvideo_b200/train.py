@@ -36,6 +36,7 @@ from .utils import checkpoint as ckpt_mod
 from .utils.ema import ema_update
 from .utils.schedule import lr_at as _lr_at
 from .utils.timers import PhaseTimer
+from .utils.versions import mark_written
 
 D0 = 256.0   # width the learning rates were tuned at (muP reference width)
 
@@ -285,6 +286,9 @@ def _qk_clip_kernel(mods, emas, stats: torch.Tensor, tau: float, skip, ema_w: fl
                              K._ptr(summary), K._ptr(skip), float(ema_w), K._stream()),
              "imf_qk_clip")
     K.LAUNCHES.count += 1
+    # the kernel wrote the weights through raw pointers: move their version counters
+    mark_written([m.q_b_proj.weight for m in mods] +
+                 [e.q_b_proj.weight for e in emas if e is not None])
     return summary[0], summary[1]
 
 

@@ -41,10 +41,29 @@ def idle_gaps(prof, top: int):
     return gaps[:top], idle
 
 
-def profile_step(cfg, warmup: int = 2, device: int = 0, gaps: int = 0):
+def launch_counts(prof, top: int):
+    """Which framework ops launch the most kernels: [(launches, device_us, op name, input
+    shapes)], most launches first.  Only kernels launched from inside a torch op are
+    attributed (this library's own launches go through ctypes and belong to no op); the
+    profile must have been recorded with ``record_shapes=True`` for the shapes to show."""
+    acc = {}
+    for e in prof.events():
+        ks = getattr(e, "kernels", None)
+        if e.device_type != torch.autograd.DeviceType.CPU or not ks:
+            continue
+        key = (e.name, str(getattr(e, "input_shapes", "")))
+        c = acc.setdefault(key, [0, 0.0])
+        c[0] += len(ks)
+        c[1] += sum(k.duration for k in ks)
+    rows = [(n, us, name, shapes) for (name, shapes), (n, us) in acc.items()]
+    rows.sort(key=lambda r: (-r[0], -r[1], r[2]))
+    return rows[:top]
+
+
+def profile_step(cfg, warmup: int = 2, device: int = 0, gaps: int = 0, ops: int = 0):
     """Returns (rows, step_wall_ms): rows = [(device_us, count, name)], largest first, for one
     training step after ``warmup`` un-profiled steps.  With ``gaps`` > 0 a third value: the
-    result of ``idle_gaps``."""
+    result of ``idle_gaps``; with ``ops`` > 0 one more: the result of ``launch_counts``."""
     from torch.profiler import ProfilerActivity, profile
 
     from ..train import Trainer
@@ -58,7 +77,8 @@ def profile_step(cfg, warmup: int = 2, device: int = 0, gaps: int = 0):
         tr.train_step(x, y)
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA],
+                 record_shapes=ops > 0) as prof:
         a.record()
         tr.train_step(x, y)
         b.record()
@@ -69,9 +89,12 @@ def profile_step(cfg, warmup: int = 2, device: int = 0, gaps: int = 0):
                 and not e.key.startswith("Optimizer.step")):      # a span, not a kernel
             rows.append((e.self_device_time_total, e.count, e.key))
     rows.sort(reverse=True)
+    out = [rows, a.elapsed_time(b)]
     if gaps > 0:
-        return rows, a.elapsed_time(b), idle_gaps(prof, gaps)
-    return rows, a.elapsed_time(b)
+        out.append(idle_gaps(prof, gaps))
+    if ops > 0:
+        out.append(launch_counts(prof, ops))
+    return tuple(out)
 
 
 def main(argv=None) -> None:
@@ -81,6 +104,8 @@ def main(argv=None) -> None:
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--gaps", type=int, default=0,
                     help="also list this many of the longest idle gaps between kernels")
+    ap.add_argument("--ops", type=int, default=0,
+                    help="also list this many torch ops by the number of kernels they launch")
     ap.add_argument("overrides", nargs="*", help="group.key=value config overrides")
     args = ap.parse_args(argv)
     from ..config import parse_cli, preset
@@ -88,7 +113,7 @@ def main(argv=None) -> None:
     cfg = preset(args.preset)
     if args.overrides:
         parse_cli(args.overrides, cfg)
-    out = profile_step(cfg, args.warmup, gaps=args.gaps)
+    out = profile_step(cfg, args.warmup, gaps=args.gaps, ops=args.ops)
     rows, wall = out[0], out[1]
     total = sum(r[0] for r in rows)
     print(f"preset {args.preset}: step {wall:.1f} ms under the profiler, "
@@ -100,6 +125,10 @@ def main(argv=None) -> None:
         print(f"idle between the first and the last kernel: {idle / 1000:.2f} ms; longest gaps:")
         for g, before, after in top:
             print(f"{g:9.1f} us  after {before[:60]}  before {after[:60]}")
+    if args.ops:
+        print("torch ops by kernels launched:")
+        for n, us, name, shapes in out[-1]:
+            print(f"  x{n:<5d} {us / 1000:8.2f} ms  {name}  {shapes[:90]}")
 
 
 if __name__ == "__main__":

@@ -275,3 +275,41 @@ def test_cli_preset_and_overrides():
     assert cfg.data.latent_size == (56, 104) and cfg.data.latent_frames == 20
     assert cfg.optim.total_steps == 7 and cfg.model.depth == 3
     assert cfg.model.grad_checkpoint is False
+
+
+def test_optimizer_step_moves_version_counters_and_refreshes_weight_caches(tmp_path):
+    """The flat engine writes parameters through its arenas (a parameter's ``.data`` is a
+    view with a version counter of its own), so the step itself must move the counters:
+    the blocks key their cached bf16 weight copies for gradient-free passes on them, and a
+    stale copy would feed the tangent / guidance passes the weights of an earlier step."""
+    cfg = _cfg(tmp_path)
+    cfg.optim.warmup_steps = 0
+    tr = Trainer(cfg, verbose=False)
+    x, y = torch.randn(2, 16, 4, 16, 16), torch.randint(0, 1000, (2,))
+    blk = next(m for m in tr.net.modules() if hasattr(m, "fused_params"))
+    with torch.no_grad():
+        first = blk.fused_params(False)
+        again = blk.fused_params(False)
+    assert all(a is b for a, b in zip(first[-6:], again[-6:]))          # cached while unchanged
+    v0 = [p._version for p in tr.net.parameters()]
+    e0 = [p._version for p in tr.ema.parameters()]
+    st = tr.train_step(x, y)
+    assert not st["skipped"]
+    assert all(p._version > v for p, v in zip(tr.net.parameters(), v0))
+    assert all(p._version > v for p, v in zip(tr.ema.parameters(), e0))
+    with torch.no_grad():
+        after = blk.fused_params(False)
+    w_qb = blk.attn.q_b_proj.weight
+    assert torch.equal(after[-5], w_qb.to(torch.bfloat16))
+    assert not torch.equal(first[-5].float(), after[-5].float())
+
+
+def test_mark_written_moves_counters_without_touching_data():
+    from imfvideo_b200.utils import mark_written
+
+    a, b = torch.arange(4.0), torch.nn.Parameter(torch.ones(3))
+    va, vb = a._version, b._version
+    mark_written([a, None, b])
+    assert a._version > va and b._version > vb
+    assert torch.equal(a, torch.arange(4.0)) and torch.equal(b.detach(), torch.ones(3))
+    mark_written([])

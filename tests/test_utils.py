@@ -25,3 +25,33 @@ def test_step_profile_idle_gaps_from_a_fake_record():
     gaps, idle = idle_gaps(Prof(), 5)
     assert idle == 2 + 10
     assert gaps[0] == (10, "side", "k4") and gaps[1] == (2, "k1", "k2")
+
+
+def test_step_profile_launch_counts_from_a_fake_record():
+    """Kernels are attributed to the torch op that launched them, grouped by op name and
+    input shapes, most launches first; device events and ops without kernels are skipped."""
+    from collections import namedtuple
+
+    import torch
+
+    from imfvideo_b200.utils.step_profile import launch_counts
+
+    Kern = namedtuple("Kern", "name device duration")
+    CPU, CUDA = torch.autograd.DeviceType.CPU, torch.autograd.DeviceType.CUDA
+
+    class Ev:
+        def __init__(self, name, shapes, kernels, dev=CPU):
+            self.name, self.input_shapes, self.kernels, self.device_type = name, shapes, kernels, dev
+
+    class Prof:
+        def events(self):
+            return [Ev("aten::add_", [[256], [256]], [Kern("add", 0, 2.0)]),
+                    Ev("aten::add_", [[256], [256]], [Kern("add", 0, 3.0)]),
+                    Ev("aten::mul", [[4, 4]], [Kern("mul", 0, 1.0), Kern("mul2", 0, 1.0),
+                                               Kern("mul3", 0, 1.0)]),
+                    Ev("aten::view", [[4, 4]], []),
+                    Ev("add", [], [Kern("x", 0, 9.0)], dev=CUDA)]
+
+    rows = launch_counts(Prof(), 5)
+    assert rows == [(3, 3.0, "aten::mul", "[[4, 4]]"), (2, 5.0, "aten::add_", "[[256], [256]]")]
+    assert launch_counts(Prof(), 1) == rows[:1]
