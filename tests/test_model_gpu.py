@@ -113,6 +113,41 @@ def test_train_step_is_bitwise_repeatable(kernels, name):
     assert torch.equal(p1, p2)
 
 
+def test_weight_copies_follow_the_optimizer_kernels(kernels):
+    """The optimizer's apply kernels and QK-clip write the parameters through raw pointers;
+    the blocks' cached bf16 weight copies (gradient-free passes, and the pass under autograd
+    when the weight gradients go straight to their buffers) must be rebuilt after each
+    step: after two steps the copies a gradient-free pass gets equal the current weights,
+    and the step's own passes used the weights of that step (the copies of step 2 differ
+    from those of step 1)."""
+    from imfvideo_b200.config import preset
+    from imfvideo_b200.train import Trainer
+
+    cfg = preset("d256")
+    cfg.model.depth, cfg.model.aux_head_depth = 2, 1
+    cfg.data.latent_frames, cfg.data.latent_size = 4, (32, 32)
+    cfg.optim.warmup_steps = 0
+    tr = Trainer(cfg, device=torch.device("cuda", 0), verbose=False)
+    blocks = [m for m in tr.net.modules() if hasattr(m, "fused_params")]
+    g = torch.Generator().manual_seed(3)
+    seen = []
+    for _ in range(2):
+        x = torch.randn(1, 16, 4, 32, 32, generator=g).pin_memory()
+        y = torch.randint(0, 1000, (1,), generator=g)
+        st = tr.train_step(x, y)
+        assert not st["skipped"]
+        assert all(getattr(b, "_wcache", None) is not None for b in blocks)     # the fused path ran
+        seen.append([b._wcache[1][1].clone() for b in blocks])
+    kernels.check_status()
+    assert all(not torch.equal(a, b) for a, b in zip(*seen))
+    with torch.no_grad():
+        for b in blocks + [m for m in tr.ema.modules() if hasattr(m, "fused_params")]:
+            mats = b.fused_params(True)
+            assert torch.equal(mats[-5], b.attn.q_b_proj.weight.to(torch.bfloat16))
+            f = b.mlp.w2.weight.shape[1]                       # the copy is padded to 8 columns
+            assert torch.equal(mats[-1][:, :f], b.mlp.w2.weight.to(torch.bfloat16))
+
+
 @pytest.mark.parametrize("bs,wide", [(0, False), (2, False), (2, True)])
 def test_fused_block_matches_generic_composition(kernels, bs, wide):
     """Same bf16 kernels for GEMM/attention; fused block node vs op-by-op path:
