@@ -6,6 +6,7 @@ the device time per kernel / operator, largest first.
     python -m imfvideo_b200.utils.step_profile --preset d256_sla2 --top 30
     python -m imfvideo_b200.utils.step_profile --preset d1024 optim.ns_cuda_graph=true
     python -m imfvideo_b200.utils.step_profile --preset d256 --gaps 15     # longest idle gaps
+    python -m imfvideo_b200.utils.step_profile --preset d256 --ops 40      # launches per torch op
 
 Times taken under the profiler are for comparing shares, not for quoting a step
 time (use ``bench.py`` for that).  The reference has no profiling entry point
