@@ -51,6 +51,9 @@ struct GemmTiles {
   int n_m, n_n, total;     // tiles along M, N; total = n_m * n_n * batch * splits
   int splits, kb_per;      // split-K: slice z of the K loop covers k-blocks [z kb_per, (z+1) kb_per)
                            // and writes plane z of C (batch must be 1 then)
+  int sym;                 // the product is symmetric (X X^T, A A with A symmetric): only the tiles
+                           // on and above the diagonal are computed (n_m (n_m + 1) / 2 per
+                           // batch entry) and the epilogue writes each one's mirror image too
 };
 
 // FP8: operands are e4m3 bytes (K-major only); a 128-byte shared-memory row then holds 128
@@ -98,9 +101,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   volatile int* abort_flag = &s.abort_flag;
   // bz: batch index of the operands; cz: plane of C (batch index, or K slice under split-K)
   auto tile_coords = [&](int tile, int& n0, int& m0, int& bz, int& cz, int& kb0, int& kb1) {
-    n0 = (tile % tiles.n_n) * BN;
-    m0 = ((tile / tiles.n_n) % tiles.n_m) * GEMM_BM;
-    cz = tile / (tiles.n_n * tiles.n_m);
+    if (tiles.sym) {
+      const int per = tiles.n_m * (tiles.n_m + 1) / 2;
+      cz = tile / per;
+      int u = tile % per, tm = 0, len = tiles.n_m;       // row tm holds the tiles tn = tm .. n_m - 1
+      while (u >= len) { u -= len; --len; ++tm; }
+      m0 = tm * GEMM_BM;
+      n0 = (tm + u) * BN;
+    } else {
+      n0 = (tile % tiles.n_n) * BN;
+      m0 = ((tile / tiles.n_n) % tiles.n_m) * GEMM_BM;
+      cz = tile / (tiles.n_n * tiles.n_m);
+    }
     if (tiles.splits > 1) {
       bz = 0;
       kb0 = cz * tiles.kb_per;
@@ -255,6 +267,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
               }
               o[i] = pack_bf16(x, y);
             }
+            if (tiles.sym && m0 != n0 && row < M) {
+              // mirror image of an off-diagonal tile: element (row, col) also goes to (col, row);
+              // for a fixed column the 32 lanes write 32 consecutive bf16 of one row of C
+              uint16_t* Ct = reinterpret_cast<uint16_t*>(C);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const int col = n0 + c + 2 * i;
+                if (col < N) Ct[(int64_t)col * ldc + row] = (uint16_t)(o[i] & 0xffffu);
+                if (col + 1 < N) Ct[(int64_t)(col + 1) * ldc + row] = (uint16_t)(o[i] >> 16);
+              }
+            }
             uint8_t* panel = s.c + (c / PANEL_COLS) * (GEMM_BM * 128) + r_in * 128;
             const int k0 = (c % PANEL_COLS) / 8;          // first 16-byte chunk of this group
 #pragma unroll
@@ -340,7 +363,8 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
                        int K, int64_t lda, int64_t ldb, int64_t ldc, int bias_rows, float alpha,
                        int accumulate_out, int* status, cudaStream_t stream, int batch = 1,
                        int64_t sa = 0, int64_t sb = 0, int64_t sc = 0, const void* Cin = nullptr,
-                       float beta = 0.f, int splits = 1, const float* alpha_dev = nullptr) {
+                       float beta = 0.f, int splits = 1, const float* alpha_dev = nullptr,
+                       int sym = 0) {
   constexpr int OES = FP8 ? 1 : 2;                      // operand element size
   constexpr CUtensorMapDataType ODT =
       FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -403,6 +427,12 @@ static int launch_gemm(const void* A, const void* B, void* C, const float* bias,
   tiles.splits = splits > 1 ? (num_kb + tiles.kb_per - 1) / tiles.kb_per : 1;   // no empty slice
   if (splits > 1 && tiles.splits != splits) return IMF_ERR_ARG;
   tiles.total = tiles.n_n * tiles.n_m * (splits > 1 ? tiles.splits : batch);
+  tiles.sym = sym;
+  if (sym) {
+    // square bf16 result through the staged (TMA store) epilogue, square tiles, no split-K
+    if (M != N || BN != GEMM_BM || ES != 2 || !tma_store || splits > 1 || bias) return IMF_ERR_ARG;
+    tiles.total = tiles.n_m * (tiles.n_m + 1) / 2 * batch;
+  }
   int sms = sms_of[di];
   if (!sms) {
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
@@ -585,6 +615,27 @@ extern "C" int imf_gemm_bf16_batched(const void* A, const void* B, void* C, cons
     IMF_GEMM_CASE(true, true, __nv_bfloat16);
   }
 #undef IMF_GEMM_CASE
+}
+
+// The same for a product that is known to be symmetric (M = N; X X^T, X^T X, or A A with A
+// symmetric; Cin symmetric too): computes the tiles on and above the diagonal only and writes
+// their mirror images from the epilogue.  bf16 output, ldc a multiple of 8.
+extern "C" int imf_gemm_bf16_batched_sym(const void* A, const void* B, void* C, const void* Cin,
+                                         int M, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                                         int batch, int64_t sa, int64_t sb, int64_t sc, int mn,
+                                         float alpha, float beta, int* status, void* stream) {
+  using namespace imf;
+  if (M <= 0 || K <= 0 || batch <= 0) return IMF_ERR_ARG;
+  if ((lda & 7) || (ldb & 7) || (batch > 1 && ((sa & 7) || (sb & 7)))) return IMF_ERR_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  using OT = __nv_bfloat16;
+  if (mn)      // both operands MN-major ([K, M]): X^T X
+    return launch_gemm<128, IMF_GEMM_STAGES(OT), true, true, OT>(
+        A, B, C, nullptr, M, M, K, lda, ldb, ldc, 0, alpha, 0, status, st, batch, sa, sb, sc, Cin,
+        beta, 1, nullptr, 1);
+  return launch_gemm<128, IMF_GEMM_STAGES(OT), false, false, OT>(
+      A, B, C, nullptr, M, M, K, lda, ldb, ldc, 0, alpha, 0, status, st, batch, sa, sb, sc, Cin,
+      beta, 1, nullptr, 1);
 }
 
 // ---------------------------------------------------------------------------

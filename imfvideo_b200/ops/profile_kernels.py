@@ -46,7 +46,7 @@ def _time(fn, iters: int, flush) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["attn_fwd", "attn_jvp", "attn_bwd", "gemm", "gemm_fp8", "sparse",
-                                       "sparse_jvp", "resnorm", "resnorm_bwd", "lin", "route"])
+                                       "sparse_jvp", "resnorm", "resnorm_bwd", "lin", "route", "ns"])
     ap.add_argument("--L", type=int, default=9472)
     ap.add_argument("--B", type=int, default=1)
     ap.add_argument("--H", type=int, default=4)
@@ -93,6 +93,13 @@ def main() -> None:
         b8, sb = K.quantize_fp8(b)
         fn, flops = (lambda: K.gemm_fp8(a8, sa, b8, sb)), 2.0 * args.M * args.N * args.K
         bytes_ = 1.0 * (args.M * args.K + args.N * args.K) + 2.0 * args.M * args.N
+    elif args.kernel == "ns":
+        # Newton-Schulz on a batch of B matrices of M x K (5 iterations, 3 launches each)
+        G = torch.randn(B, args.M, args.K, device=dev)
+        co = (3.4445, -4.7750, 2.0315)
+        fn = lambda: K.newton_schulz(G, co, steps=5)
+        g_, o_ = min(args.M, args.K), max(args.M, args.K)
+        flops = 5 * B * (2.0 * g_ * g_ * o_ + 2.0 * g_ ** 3 + 2.0 * g_ * g_ * o_)
     elif args.kernel in ("sparse", "sparse_jvp"):
         from . import sparse as SP
 

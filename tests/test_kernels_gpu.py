@@ -265,7 +265,7 @@ def test_attention_backward_hd128(K, B, L, H):
 
 
 @pytest.mark.parametrize("k,n,m", [(3, 128, 256), (2, 256, 128), (2, 256, 682), (2, 682, 256),
-                                   (4, 1, 256), (1, 448, 128)])
+                                   (4, 1, 256), (1, 448, 128), (1, 520, 1024)])
 def test_newton_schulz_kernel(K, k, n, m):
     from imfvideo_b200.ops import reference as ref
 
@@ -291,6 +291,32 @@ def test_batched_gemm_with_additive_source(K):
     out = K.gemm_batched(a, b, cin=cin, alpha=0.5, beta=2.0)
     ref = 0.5 * torch.einsum("zmk,znk->zmn", a.float(), b.float()) + 2.0 * cin.float()
     assert _rel(out, ref) < 5e-3
+    K.check_status()
+
+
+@pytest.mark.parametrize("n,kdim,mn", [(200, 136, False), (264, 520, True), (1024, 256, False),
+                                       (128, 64, False), (392, 1032, True)])
+def test_batched_gemm_symmetric_products(K, n, kdim, mn):
+    """X X^T / X^T X and b A + c A A with the symmetric mode (upper tiles + mirror image in
+    the epilogue) against the full product: the upper triangle is bit-identical, the result
+    exactly symmetric, and both agree with fp32."""
+    torch.manual_seed(n)
+    Z = 3
+    x = (torch.randn(Z, kdim, n, device="cuda") if mn else
+         torch.randn(Z, n, kdim, device="cuda")).bfloat16() * 0.1
+    full = K.gemm_batched(x, x, a_mn=mn, b_mn=mn)
+    sym = K.gemm_batched(x, x, a_mn=mn, b_mn=mn, sym=True)
+    xf = x.float().transpose(1, 2) if mn else x.float()
+    ref = torch.einsum("zik,zjk->zij", xf, xf)
+    assert _rel(sym, ref) < 5e-3
+    assert torch.equal(sym, sym.transpose(1, 2))
+    iu = torch.triu_indices(n, n, device="cuda")
+    # tiles on the diagonal are computed whole, tiles above it are the same launches' tiles
+    assert torch.equal(sym[:, iu[0], iu[1]], full[:, iu[0], iu[1]])
+    b2 = K.gemm_batched(sym, sym, cin=sym, alpha=2.0, beta=-4.75, sym=True)
+    ref2 = 2.0 * torch.einsum("zik,zjk->zij", sym.float(), sym.float()) - 4.75 * sym.float()
+    assert _rel(b2, ref2) < 5e-3
+    assert torch.equal(b2, b2.transpose(1, 2))
     K.check_status()
 
 
