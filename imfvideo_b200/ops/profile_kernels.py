@@ -12,6 +12,7 @@ under ``ncu`` (or for a quick CUDA-event timing without it).
     python -m imfvideo_b200.ops.profile_kernels resnorm_bwd --rows 29140 --D 256
     python -m imfvideo_b200.ops.profile_kernels lin       --L 29140      # linear-branch kernels, one line each
     python -m imfvideo_b200.ops.profile_kernels route     --L 29140      # block means, top-k, INT8 quantiser
+    python -m imfvideo_b200.ops.profile_kernels ns --B 24 --M 1024 --K 1024  # Newton-Schulz, 5 iterations
 
 Prints the CUDA-event time per launch (after warm-up, inputs larger than L2
 or L2 flushed between launches) and the achieved fraction of the measured
