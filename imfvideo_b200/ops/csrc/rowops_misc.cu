@@ -387,6 +387,142 @@ __global__ void __launch_bounds__(ROW_THREADS) qkprep_bwd_kernel(const PrepArgs 
   }
 }
 
+// Wide variant of the backward, laid out like the wide forward: a lane owns 8 consecutive
+// channels, a head is HD / 8 lanes, a warp handles 32 / (HD / 8) heads at once.  A unit of work
+// is a row with all its heads, query and key side (a loop over groups of heads when H is larger
+// than a warp holds), so that the shared rope key's gradient -- the sum over heads of the rotated
+// key gradient -- is formed in registers, in a fixed order, and written once.  The gains'
+// gradients accumulate in registers over a warp's rows and are summed over lane groups,
+// warps (shared memory) and CTAs (partial buffer) in fixed orders as well.
+template <int HD>
+__global__ void __launch_bounds__(ROW_THREADS) qkprep_bwd_wide_kernel(const PrepArgs a) {
+  constexpr int LPH = HD / 8;            // lanes per head: 8 or 16
+  constexpr int UPW = 32 / LPH;          // heads per warp pass: 4 or 2
+  extern __shared__ float smem_acc[];    // [ROW_WARPS][2][dn]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane / LPH, c0 = (lane % LPH) * 8;
+  const bool nope = c0 < a.dn;
+  const float inv_dn = 1.f / a.dn;
+  const int kvw = a.H * (a.dn + a.dv);
+  const int half_dr = a.dr / 2;
+  float accq[8], acck[8], gain_q[8], gain_k[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) accq[e] = acck[e] = gain_q[e] = gain_k[e] = 0.f;
+  if (nope) {
+    const float4 q0 = ld4(a.qg + c0), q1 = ld4(a.qg + c0 + 4);
+    const float4 k0 = ld4(a.kg + c0), k1 = ld4(a.kg + c0 + 4);
+    gain_q[0] = q0.x; gain_q[1] = q0.y; gain_q[2] = q0.z; gain_q[3] = q0.w;
+    gain_q[4] = q1.x; gain_q[5] = q1.y; gain_q[6] = q1.z; gain_q[7] = q1.w;
+    gain_k[0] = k0.x; gain_k[1] = k0.y; gain_k[2] = k0.z; gain_k[3] = k0.w;
+    gain_k[4] = k1.x; gain_k[5] = k1.y; gain_k[6] = k1.z; gain_k[7] = k1.w;
+  }
+  for (int row = blockIdx.x * ROW_WARPS + warp; row < a.rows; row += gridDim.x * ROW_WARPS) {
+    float cs[4] = {0.f, 0.f, 0.f, 0.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+    if (!nope) {
+      const size_t ro = (size_t)(row % a.L) * half_dr + (c0 - a.dn) / 2;
+      const float4 c4 = ld4(a.cos_ + ro), s4 = ld4(a.sin_ + ro);
+      cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w;
+      sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+    }
+    float kr_sum[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) kr_sum[e] = 0.f;
+    for (int hb = 0; hb < a.H; hb += UPW) {
+      const int h = hb + sub;
+      const bool live = h < a.H;
+      // all four loads of the pass (q and k side) are issued before any of them is used
+      uint4 raw_g[2], raw_x[2];
+      raw_g[0] = raw_g[1] = raw_x[0] = raw_x[1] = make_uint4(0u, 0u, 0u, 0u);
+      if (live) {
+        const size_t go = ((size_t)row * a.H + h) * HD + c0;
+        raw_g[0] = *reinterpret_cast<const uint4*>(a.gq + go);
+        raw_g[1] = *reinterpret_cast<const uint4*>(a.gk + go);
+        if (nope) {
+          raw_x[0] = *reinterpret_cast<const uint4*>(a.qb + (size_t)row * a.H * HD + h * HD + c0);
+          raw_x[1] = *reinterpret_cast<const uint4*>(a.kvb + (size_t)row * kvw +
+                                                     h * (a.dn + a.dv) + c0);
+        }
+      }
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        float g[8], x[8];
+        unpack8(raw_g[which], g);
+        unpack8(raw_x[which], x);
+        float ss = 0.f, ux = 0.f;
+        if (nope) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            ss += x[e] * x[e];
+            ux += g[e] * (which == 0 ? gain_q[e] : gain_k[e]) * x[e];
+          }
+        }
+#pragma unroll
+        for (int o = LPH / 2; o > 0; o >>= 1) {   // reduction inside the head's lane group
+          ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          ux += __shfl_xor_sync(0xffffffffu, ux, o);
+        }
+        float gx[8];
+        if (nope) {
+          const float r = rsqrtf(ss * inv_dn + a.eps);
+          const float c3 = ux * inv_dn * r * r * r;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float gn = which == 0 ? gain_q[e] : gain_k[e];
+            gx[e] = g[e] * gn * r - x[e] * c3;
+            const float ga = g[e] * x[e] * r;     // zero for a head that is not live
+            if (which == 0) accq[e] += ga;
+            else acck[e] += ga;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; e += 2) {
+            gx[e] = g[e] * cs[e / 2] + g[e + 1] * sn[e / 2];
+            gx[e + 1] = -g[e] * sn[e / 2] + g[e + 1] * cs[e / 2];
+          }
+          if (which == 1) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) kr_sum[e] += gx[e];
+          }
+        }
+        if (live && (which == 0 || nope)) {
+          bf16* dst = which == 0 ? a.g_qb + (size_t)row * a.H * HD + h * HD + c0
+                                 : a.g_kvb + (size_t)row * kvw + h * (a.dn + a.dv) + c0;
+          *reinterpret_cast<uint4*>(dst) = pack8(gx);
+        }
+      }
+    }
+    // sum of the rotated key gradient over the heads of a warp pass (lane groups)
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+#pragma unroll
+      for (int o = LPH; o < 32; o <<= 1) kr_sum[e] += __shfl_xor_sync(0xffffffffu, kr_sum[e], o);
+    if (!nope && sub == 0)
+      *reinterpret_cast<uint4*>(a.g_kr + (size_t)row * a.ld_gkr + (c0 - a.dn)) = pack8(kr_sum);
+  }
+  // gains' gradients: lane groups -> warp -> CTA, fixed orders
+#pragma unroll
+  for (int e = 0; e < 8; ++e)
+#pragma unroll
+    for (int o = LPH; o < 32; o <<= 1) {
+      accq[e] += __shfl_xor_sync(0xffffffffu, accq[e], o);
+      acck[e] += __shfl_xor_sync(0xffffffffu, acck[e], o);
+    }
+  float* acc = smem_acc + (size_t)warp * 2 * a.dn;
+  if (nope && sub == 0) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      acc[c0 + e] = accq[e];
+      acc[a.dn + c0 + e] = acck[e];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * a.dn; c += blockDim.x) {
+    float t = 0.f;
+    for (int w = 0; w < ROW_WARPS; ++w) t += smem_acc[(size_t)w * 2 * a.dn + c];
+    a.partial[(size_t)blockIdx.x * 2 * a.dn + c] = t;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Elementwise: output gate, SituAndMul, gated residual add
 // ---------------------------------------------------------------------------
@@ -685,7 +821,14 @@ extern "C" int imf_qkprep(void** p, int rows, int L, int H, int dn, int dr, int 
   } else {
     const int grid = row_grid(rows);     // partial buffers are sized by imf_row_grid(rows)
     const size_t smem = (size_t)ROW_WARPS * 2 * dn * sizeof(float);
-    if (epl == 2) qkprep_bwd_kernel<2><<<grid, ROW_THREADS, smem, st>>>(a);
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    const bool wide = dn % 8 == 0 && dr % 8 == 0 && (dn + dv) % 8 == 0 && ld_gkr % 8 == 0 &&
+                      al16(a.qb) && al16(a.kvb) && al16(a.gq) && al16(a.gk) && al16(a.g_qb) &&
+                      al16(a.g_kvb) && al16(a.g_kr) && al16(a.cos_) && al16(a.sin_) &&
+                      al16(a.qg) && al16(a.kg);
+    if (wide && HD == 64) qkprep_bwd_wide_kernel<64><<<grid, ROW_THREADS, smem, st>>>(a);
+    else if (wide && HD == 128) qkprep_bwd_wide_kernel<128><<<grid, ROW_THREADS, smem, st>>>(a);
+    else if (epl == 2) qkprep_bwd_kernel<2><<<grid, ROW_THREADS, smem, st>>>(a);
     else qkprep_bwd_kernel<4><<<grid, ROW_THREADS, smem, st>>>(a);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -3;

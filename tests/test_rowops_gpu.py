@@ -135,18 +135,23 @@ def _prep_ref(qb, kvb, kr, cos, sin, qg, kg, B, L, H, dn, dr, dv, eps):
     return torch.cat([qn, qr], -1), torch.cat([kn, krr], -1)
 
 
-def test_qk_prep(R):
+@pytest.mark.parametrize("H,dn,dr,dv", [(4, 48, 16, 64), (5, 48, 16, 64), (3, 96, 32, 128),
+                                        (12, 64, 64, 128), (2, 44, 20, 64)])
+def test_qk_prep(R, H, dn, dr, dv):
+    """(4, 48, 16, 64): the model's geometry; 5 heads: a last pass with one live head of four;
+    head_dim 128: two heads per warp pass; (2, 44, 20, 64): not 8-aligned, the narrow kernels."""
     torch.manual_seed(0)
-    B, L, H, dn, dr, dv, eps = 2, 77, 4, 48, 16, 64, 1e-5
-    rows, na = B * L, 40
-    qb, dqb = _rn(rows, H * 64, dt=BF16), _rn(rows, H * 64, dt=BF16)
-    kvb, dkvb = _rn(rows, H * 112, dt=BF16), _rn(rows, H * 112, dt=BF16)
+    B, L, eps = 2, 77, 1e-5
+    hd = dn + dr
+    rows, na = B * L, 8 + dr + 16
+    qb, dqb = _rn(rows, H * hd, dt=BF16), _rn(rows, H * hd, dt=BF16)
+    kvb, dkvb = _rn(rows, H * (dn + dv), dt=BF16), _rn(rows, H * (dn + dv), dt=BF16)
     a, da = _rn(rows, na, dt=BF16), _rn(rows, na, dt=BF16)
     kr, dkr = a[:, 8:8 + dr], da[:, 8:8 + dr]
     ang = torch.rand(L, dr // 2, device="cuda") * 6
     cos, sin = torch.cos(ang), torch.sin(ang)
     qg, kg = torch.rand(dn, device="cuda") + 0.5, torch.rand(dn, device="cuda") + 0.5
-    mk = lambda: torch.empty(B, L, H, 64, dtype=BF16, device="cuda")
+    mk = lambda: torch.empty(B, L, H, hd, dtype=BF16, device="cuda")
     q, dq, k, dk = mk(), mk(), mk(), mk()
     R.qkprep_fwd(qb, dqb, kvb, dkvb, kr, dkr, cos, sin, qg, kg, q, dq, k, dk, rows, L, H, dn, dr,
                  dv, na, eps)
@@ -156,7 +161,7 @@ def test_qk_prep(R):
     for x, x0 in ((q, q0), (dq, dq0), (k, k0), (dk, dk0)):
         assert _rel(x, x0) < 5e-3
     # backward
-    gq, gk = _rn(B, L, H, 64, dt=BF16), _rn(B, L, H, 64, dt=BF16)
+    gq, gk = _rn(B, L, H, hd, dt=BF16), _rn(B, L, H, hd, dt=BF16)
     g_qb = torch.empty_like(qb)
     g_kvb = torch.zeros_like(kvb)
     g_a = torch.zeros_like(a)
