@@ -509,6 +509,66 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // Per (b, l, h) row, one warp:  delta = rowsum(dO .* O) and lse2 = lse * log2(e) as the bf16
 // (hi, lo) pairs the main kernel feeds to the tensor core (16 columns per row, the rest zero;
 // rows l >= L of the padded length Lp get lse2 = 30000, i.e. P = 0), and Q * scale*log2e as bf16.
+// Wide form of the kernel below: a lane owns 8 consecutive channels (one 16-byte access per
+// tensor), a row is 8 lanes, a warp takes 4 rows -- the H index fastest, so that a warp reads
+// neighbouring heads of one token.  Needs 16-byte aligned rows in q, o and dO.
+__global__ void attn_bwd_prep_wide_kernel(const __nv_bfloat16* __restrict__ q,
+                                          const __nv_bfloat16* __restrict__ o,
+                                          const __nv_bfloat16* __restrict__ d_o,
+                                          const float* __restrict__ lse,
+                                          __nv_bfloat16* __restrict__ qs, uint32_t* __restrict__ augq,
+                                          uint32_t* __restrict__ augd, int B, int L, int H, int Lp,
+                                          int64_t q_sb, int64_t q_sl, int64_t q_sh, int64_t o_sb,
+                                          int64_t o_sl, int64_t o_sh, int64_t g_sb, int64_t g_sl,
+                                          int64_t g_sh, float scale_log2) {
+  const int lane = threadIdx.x & 31, sub = lane >> 3, part = lane & 7, c0 = part * 8;
+  const long grp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long total = (long)B * H * Lp;
+  const long u = grp * 4 + sub;
+  const bool in = u < total;             // no early exit: the shuffles below need every lane
+  int h = 0, l = 0, b = 0;
+  if (in) {
+    h = (int)(u % H);
+    l = (int)((u / H) % Lp);
+    b = (int)(u / ((long)H * Lp));
+  }
+  const bool live = in && l < L;
+  float v = 0.f;
+  if (live) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + b * o_sb + (int64_t)l * o_sl + h * o_sh + c0);
+    const uint4 g = *reinterpret_cast<const uint4*>(d_o + b * g_sb + (int64_t)l * g_sl + h * g_sh + c0);
+    const uint4 qq = *reinterpret_cast<const uint4*>(q + b * q_sb + (int64_t)l * q_sl + h * q_sh + c0);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+    const uint32_t qw[4] = {qq.x, qq.y, qq.z, qq.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v += bf16_lo(aw[i]) * bf16_lo(gw[i]) + bf16_hi(aw[i]) * bf16_hi(gw[i]);
+      ow[i] = pack_bf16(bf16_lo(qw[i]) * scale_log2, bf16_hi(qw[i]) * scale_log2);
+    }
+    *reinterpret_cast<uint4*>(qs + (((int64_t)b * L + l) * H + h) * 64 + c0) =
+        make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+#pragma unroll
+  for (int off = 4; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  if (!in) return;
+  float x = 30000.f, dl = 0.f;           // padding rows: exp2(S - 30000) = 0
+  if (live) {
+    dl = v;
+    x = lse[((long)b * H + h) * L + l] * 1.4426950408889634f;
+    x = fminf(fmaxf(x, -30000.f), 30000.f);
+  }
+  uint32_t wq = 0u, wd = 0u;             // 16 bf16 = 8 words per row, one per lane of the row
+  if (part == 0) {
+    const float xh = bf16_lo(pack_bf16(-x, 0.f)), dh = bf16_lo(pack_bf16(-dl, 0.f));
+    wq = pack_bf16(xh, -x - xh);
+    wd = pack_bf16(dh, -dl - dh);
+  }
+  const long row = ((long)b * H + h) * Lp + l;
+  augq[row * 8 + part] = wq;
+  augd[row * 8 + part] = wd;
+}
+
 __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ q,
                                      const __nv_bfloat16* __restrict__ o,
                                      const __nv_bfloat16* __restrict__ d_o,
@@ -708,10 +768,17 @@ extern "C" int imf_attn_bwd(const void* q, const void* k, const void* v, const v
   }
   if (cudaMemsetAsync(dq_acc, 0, acc_bytes + turn_bytes, st) != cudaSuccess) return IMF_ERR_LAUNCH;
   {
-    const long warps = (long)B * H * Lp;
+    const long rows = (long)B * H * Lp;
     const int threads = 256;
+    auto ok16 = [](const void* p, int64_t s0, int64_t s1, int64_t s2) {
+      return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && s0 % 8 == 0 && s1 % 8 == 0 && s2 % 8 == 0;
+    };
+    const bool wide = ok16(q, strides[0], strides[1], strides[2]) &&
+                      ok16(o, o_strides[0], o_strides[1], o_strides[2]) &&
+                      ok16(d_o, strides[9], strides[10], strides[11]);
+    const long warps = wide ? (rows + 3) / 4 : rows;
     const long blocks = (warps * 32 + threads - 1) / threads;
-    attn_bwd_prep_kernel<<<(unsigned)blocks, threads, 0, st>>>(
+    (wide ? attn_bwd_prep_wide_kernel : attn_bwd_prep_kernel)<<<(unsigned)blocks, threads, 0, st>>>(
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(o),
         static_cast<const __nv_bfloat16*>(d_o), lse, qs, augq, augd, B, L, H, Lp, strides[0],
         strides[1], strides[2], o_strides[0], o_strides[1], o_strides[2], strides[9], strides[10],
