@@ -535,8 +535,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // Merge the two halves of every split item (one CTA per share boundary).
+constexpr int ATT_COMBINE_THREADS = 1024;
 template <bool TANGENT, int NTP>
-__global__ void __launch_bounds__(AttCfg<TANGENT, NTP>::ITEM_M)
+__global__ void __launch_bounds__(ATT_COMBINE_THREADS)
 attn_fwd_combine_kernel(const AttParams p, int G) {
   using C = AttCfg<TANGENT, NTP>;
   const int c = blockIdx.x;              // boundary between CTA c and c + 1
@@ -551,11 +552,14 @@ attn_fwd_combine_kernel(const AttParams p, int G) {
   const float* sb = pb + (size_t)C::ITEM_M * C::ACC;
   const float scale_log2 = p.scale * 1.4426950408889634f;
   // one warp per row, a lane per pair of columns: 256-byte reads of the two partial rows and
-  // a 128-byte write of the merged row (a thread per row would touch a cache line per value)
+  // a 128-byte write of the merged row (a thread per row would touch a cache line per value).
+  // The CTA is alone on its SM with one item to merge, so it is as wide as a CTA gets (32
+  // warps) and the row loop is unrolled: the time goes into load latency, not into bytes.
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+#pragma unroll 4
   for (int r = warp; r < C::ITEM_M; r += nwarps) {
     const int q_row = qb * C::ITEM_M + r;
-    if (q_row >= p.L) break;
+    if (q_row >= p.L) continue;
     const float ma = sa[r], mb = sb[r];
     const float m = fmaxf(ma, mb);
     const float wa = ex2((ma - m) * scale_log2), wb = ex2((mb - m) * scale_log2);
@@ -656,7 +660,7 @@ static int launch_attn_fwd(const void* q, const void* k, const void* v, const vo
   kern<<<G, C::THREADS, smem, stream>>>(mq, mk, mv, mdq, mdk, mdv, prm);
   if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   if (G > 1 && prm.n_items > G) {
-    attn_fwd_combine_kernel<TANGENT, NTP><<<G - 1, C::ITEM_M, 0, stream>>>(prm, G);
+    attn_fwd_combine_kernel<TANGENT, NTP><<<G - 1, ATT_COMBINE_THREADS, 0, stream>>>(prm, G);
     if (cudaGetLastError() != cudaSuccess) return IMF_ERR_LAUNCH;
   }
   return IMF_OK;
