@@ -912,22 +912,27 @@ struct ColSumEntry {
 struct ColSumArgs {
   ColSumEntry e[COLSUM_MAX];
 };
-// block = 32 columns x 8 row groups: thread (x, y) adds rows y, y + 8, ... of its column, the
-// eight group sums are added in a fixed order
-__global__ void __launch_bounds__(256) colsum_kernel(const __grid_constant__ ColSumArgs a) {
+// block = 32 columns x 32 row groups: thread (x, y) adds rows y, y + 32, ... of its column
+// (four loads in flight: the partial rows are few and the time is load latency), the group
+// sums are added in a fixed order
+constexpr int COLSUM_GROUPS = 32;
+__global__ void __launch_bounds__(32 * COLSUM_GROUPS)
+colsum_kernel(const __grid_constant__ ColSumArgs a) {
   const ColSumEntry e = a.e[blockIdx.y];
   const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
   const int d = blockIdx.x * 32 + x;
-  __shared__ float s_part[8][32];
+  __shared__ float s_part[COLSUM_GROUPS][32];
   float acc = 0.f;
-  if (d < e.D)
-    for (int i = y; i < e.g; i += 8) acc += e.part[(size_t)i * e.stride + d];
+  if (d < e.D) {
+#pragma unroll 4
+    for (int i = y; i < e.g; i += COLSUM_GROUPS) acc += e.part[(size_t)i * e.stride + d];
+  }
   s_part[y][x] = acc;
   __syncthreads();
   if (y == 0 && d < e.D) {
     float t = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) t += s_part[k][x];
+    for (int k = 0; k < COLSUM_GROUPS; ++k) t += s_part[k][x];
     e.dst[d] = e.accumulate ? e.dst[d] + t : t;
   }
 }
@@ -945,7 +950,8 @@ extern "C" int imf_colsum(const void* entries, int n, void* stream) {
     if (i < n && a.e[i].D > maxd) maxd = a.e[i].D;
     if (i < n && (a.e[i].g <= 0 || a.e[i].D <= 0)) return -1;
   }
-  imf::colsum_kernel<<<dim3((maxd + 31) / 32, n), 256, 0, (cudaStream_t)stream>>>(a);
+  imf::colsum_kernel<<<dim3((maxd + 31) / 32, n), 32 * imf::COLSUM_GROUPS, 0,
+                       (cudaStream_t)stream>>>(a);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
