@@ -39,6 +39,36 @@ __global__ void __launch_bounds__(ROW_THREADS) rmsnorm_seg_fwd_kernel(const Norm
   const NormSeg& s = a.seg[blockIdx.y];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float inv_d = 1.f / s.D;
+  if (s.D <= 128) {
+    // a row is one 8-byte load per lane: four rows per warp pass, all loads issued before the
+    // first reduction, or the kernel is a chain of load latencies
+    const int c = lane * 4, step = gridDim.x * ROW_WARPS;
+    const bool in = c < s.D;
+    const float4 g = in ? ld4(s.gain + c) : f4zero();
+    for (int row0 = blockIdx.x * ROW_WARPS + warp; row0 < a.rows; row0 += 4 * step) {
+      float4 v[4], dv[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int row = row0 + k * step;
+        const bool ok = in && row < a.rows;
+        v[k] = ok ? ld4(s.x + (size_t)row * s.ld_x + c) : f4zero();
+        dv[k] = (ok && a.has_t) ? ld4(s.dx + (size_t)row * s.ld_x + c) : f4zero();
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int row = row0 + k * step;
+        const float ss = warp_sum(dot4(v[k], v[k]));
+        const float r = rsqrtf(ss * inv_d + a.eps);
+        float c2 = 0.f;
+        if (a.has_t) c2 = warp_sum(dot4(v[k], dv[k])) * inv_d * r * r * r;
+        if (in && row < a.rows) {
+          st4(s.out + (size_t)row * s.ld_o + c, v[k] * g * r);
+          if (a.has_t) st4(s.dout + (size_t)row * s.ld_o + c, fma4(v[k], -c2, dv[k] * r) * g);
+        }
+      }
+    }
+    return;
+  }
   for (int row = blockIdx.x * ROW_WARPS + warp; row < a.rows; row += gridDim.x * ROW_WARPS) {
     const bf16* x = s.x + (size_t)row * s.ld_x;
     const bf16* dx = a.has_t ? s.dx + (size_t)row * s.ld_x : nullptr;
