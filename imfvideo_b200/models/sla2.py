@@ -599,7 +599,10 @@ def _sparse_core_bwd_kernels(self, q, k, v, saved, go, gv_out, alpha_param, cube
         ga = ga.to(alpha_param.dtype)
         alpha_param.grad = ga if alpha_param.grad is None else alpha_param.grad + ga
         qq, kk, vv = q, k, v
-        if self.int8:
+        if self.int8 and self.qblk == 64:
+            (_, _, qq), (_, _, kk), (_, _, vv) = SP.quantize_blocks_many(
+                [(q, False, True), (k, False, True), (v, False, True)])
+        elif self.int8:
             _, _, qq = SP.quantize_blocks(K._tma_ok(q), self.qblk, want_q=False, want_fq=True)
             _, _, kk = SP.quantize_blocks(K._tma_ok(k), 64, want_q=False, want_fq=True)
             _, _, vv = SP.quantize_blocks(K._tma_ok(v), 64, want_q=False, want_fq=True)

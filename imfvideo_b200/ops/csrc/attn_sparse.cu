@@ -696,12 +696,13 @@ __global__ void quantize_blocks_kernel(const __nv_bfloat16* __restrict__ x, int8
 // 8 columns (16 bytes) of NR rows, so every row is read once with NR independent loads in
 // flight and written with 8-byte (int8) / 16-byte (bf16) stores.  block = 16 * NR rows.
 template <int NR>
-__global__ void __launch_bounds__(128)
-quantize_blocks_vec_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ xq,
-                           float* __restrict__ xs, __nv_bfloat16* __restrict__ xfq, int L, int H,
-                           int n_blk, int64_t sb, int64_t sl, int64_t sh) {
+__device__ __forceinline__ void quantize_block_vec(const __nv_bfloat16* __restrict__ x,
+                                                   int8_t* __restrict__ xq, float* __restrict__ xs,
+                                                   __nv_bfloat16* __restrict__ xfq, int L, int H,
+                                                   int n_blk, int64_t sb, int64_t sl, int64_t sh,
+                                                   int b) {
   __shared__ float s_max[4];
-  const int blk = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int blk = blockIdx.x, h = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int rsub = lane >> 3, c8 = (lane & 7) * 8;
   const int r0 = blk * (16 * NR) + warp * (4 * NR);
@@ -761,6 +762,31 @@ quantize_blocks_vec_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restri
   }
 }
 
+template <int NR>
+__global__ void __launch_bounds__(128)
+quantize_blocks_vec_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ xq,
+                           float* __restrict__ xs, __nv_bfloat16* __restrict__ xfq, int L, int H,
+                           int n_blk, int64_t sb, int64_t sl, int64_t sh) {
+  quantize_block_vec<NR>(x, xq, xs, xfq, L, H, n_blk, sb, sl, sh, blockIdx.z);
+}
+
+// Up to three tensors of one shape (q, k, v of an attention call) in one launch:
+// blockIdx.z = tensor * B + batch.
+struct QuantMany {
+  const __nv_bfloat16* x[3];
+  int8_t* xq[3];
+  float* xs[3];
+  __nv_bfloat16* xfq[3];
+  int64_t sb[3], sl[3], sh[3];
+};
+template <int NR>
+__global__ void __launch_bounds__(128)
+quantize_blocks_many_kernel(const __grid_constant__ QuantMany a, int B, int L, int H, int n_blk) {
+  const int t = blockIdx.z / B, b = blockIdx.z % B;
+  quantize_block_vec<NR>(a.x[t], a.xq[t], a.xs[t], a.xfq[t], L, H, n_blk, a.sb[t], a.sl[t],
+                         a.sh[t], b);
+}
+
 static int map_rows(CUtensorMap* m, const void* ptr, int B, int L, int H, int64_t sb, int64_t sl,
                     int64_t sh, int rows, bool int8) {
   uint64_t dims[4] = {64, (uint64_t)H, (uint64_t)L, (uint64_t)B};
@@ -798,6 +824,30 @@ extern "C" int imf_quantize_blocks(const void* x, void* xq, float* xs, void* xfq
   const long blocks = (warps * 32 + 255) / 256;
   quantize_blocks_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (int8_t*)xq, xs, (__nv_bfloat16*)xfq, B, L, H, block, n_blk, sb, sl, sh);
+  return cudaGetLastError() == cudaSuccess ? IMF_OK : IMF_ERR_LAUNCH;
+}
+
+// The same for n <= 3 tensors of one shape with 64-row blocks in ONE launch.  ptrs: n records of
+// (x, xq | null, xs, xfq | null); strides: n records of (sb, sl, sh).  Needs 16-byte aligned
+// rows (returns IMF_ERR_ARG otherwise: the caller then quantises the tensors one by one).
+extern "C" int imf_quantize_blocks_many(void** ptrs, const int64_t* strides, int n, int B, int L,
+                                        int H, void* stream) {
+  if (n <= 0 || n > 3 || B <= 0 || L <= 0 || H <= 0) return IMF_ERR_ARG;
+  QuantMany a;
+  for (int t = 0; t < 3; ++t) {
+    const int u = t < n ? t : 0;
+    a.x[t] = static_cast<const __nv_bfloat16*>(ptrs[4 * u]);
+    a.xq[t] = static_cast<int8_t*>(ptrs[4 * u + 1]);
+    a.xs[t] = static_cast<float*>(ptrs[4 * u + 2]);
+    a.xfq[t] = static_cast<__nv_bfloat16*>(ptrs[4 * u + 3]);
+    a.sb[t] = strides[3 * u]; a.sl[t] = strides[3 * u + 1]; a.sh[t] = strides[3 * u + 2];
+    if (!a.x[t] || !a.xs[t] || (reinterpret_cast<uintptr_t>(a.x[t]) & 15) ||
+        ((a.sb[t] | a.sl[t] | a.sh[t]) & 7))
+      return IMF_ERR_ARG;
+  }
+  const int n_blk = (L + 63) / 64;
+  const dim3 grid(n_blk, H, n * B);
+  quantize_blocks_many_kernel<4><<<grid, 128, 0, (cudaStream_t)stream>>>(a, B, L, H, n_blk);
   return cudaGetLastError() == cudaSuccess ? IMF_OK : IMF_ERR_LAUNCH;
 }
 

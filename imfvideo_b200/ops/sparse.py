@@ -23,6 +23,11 @@ if K._has("imf_attn_sparse_fwd"):
     _lib.imf_attn_sparse_fwd.argtypes = [vp] * 16 + [ci] * 5 + [vp, c64, c64, c64, cf, ci, ci, vp, vp]
 
 
+_HAS_MANY = K._has("imf_quantize_blocks_many")
+if _HAS_MANY:
+    _lib.imf_quantize_blocks_many.restype = ci
+    _lib.imf_quantize_blocks_many.argtypes = [vp, vp, ci, ci, ci, ci, vp]
+
 if K._has("imf_build_tile_lut"):
     _lib.imf_build_tile_lut.restype = ci
     _lib.imf_build_tile_lut.argtypes = [vp] * 6 + [ci] * 7 + [vp]
@@ -137,6 +142,37 @@ def quantize_blocks(x: torch.Tensor, block: int, want_q: bool = True, want_fq: b
     return xq, xs, xf
 
 
+def quantize_blocks_many(items, block: int = 64):
+    """``quantize_blocks`` for up to three tensors of one shape -- the q, k, v of an attention
+    call -- in one launch.  items: [(x, want_q, want_fq)]; returns [(xq, xs, xf)].  Falls back
+    to one launch per tensor when the shapes differ, the blocks are not 64 rows, or a tensor's
+    rows are not 16-byte aligned."""
+    xs_ = [K._tma_ok(x) for x, _, _ in items]
+    same = all(x.shape == xs_[0].shape and x.dtype == torch.bfloat16 and x.stride(3) == 1
+               and x.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in x.stride()[:3])
+               for x in xs_)
+    if not (_HAS_MANY and block == 64 and 1 < len(items) <= 3 and same and xs_[0].shape[3] == 64):
+        return [quantize_blocks(x, block, want_q=wq, want_fq=wf) for x, (_, wq, wf) in zip(xs_, items)]
+    B, L, H, D = xs_[0].shape
+    nb = -(-L // 64)
+    dev = xs_[0].device
+    outs, ptrs, strides = [], [], []
+    for x, (_, wq, wf) in zip(xs_, items):
+        xq = torch.empty(B, L, H, D, dtype=torch.int8, device=dev) if wq else None
+        sc = torch.empty(B, H, nb, dtype=torch.float32, device=dev)
+        xf = torch.empty(B, L, H, D, dtype=torch.bfloat16, device=dev) if wf else None
+        outs.append((xq, sc, xf))
+        ptrs += [x.data_ptr(), 0 if xq is None else xq.data_ptr(), sc.data_ptr(),
+                 0 if xf is None else xf.data_ptr()]
+        strides += [x.stride(0), x.stride(1), x.stride(2)]
+    parr = (ctypes.c_void_p * len(ptrs))(*ptrs)
+    sarr = (c64 * len(strides))(*strides)
+    K._check(_lib.imf_quantize_blocks_many(parr, sarr, len(items), B, L, H, K._stream()),
+             "imf_quantize_blocks_many")
+    K.LAUNCHES.count += 1
+    return outs
+
+
 def build_tile_lut(sel: torch.Tensor, qblk: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """Per-128-row query tile list of 64-key blocks from the per-routing-block
     selection ``sel`` (B, H, Mb, T).  qblk 128: one routing block per tile.
@@ -180,7 +216,10 @@ def sparse_fwd(q, k, v, dq, dk, dv, lut, flags, qblk: int, int8: bool, quant_p: 
     tang = dq is not None
     q8 = k8 = qs = ks = None
     vv = K._tma_ok(v)
-    if int8:
+    if int8 and qblk == 64:
+        (q8, qs, _), (k8, ks, _), (_, _, vv) = quantize_blocks_many(
+            [(q, True, False), (k, True, False), (vv, False, True)])
+    elif int8:
         q8, qs, _ = quantize_blocks(K._tma_ok(q), qblk)
         k8, ks, _ = quantize_blocks(K._tma_ok(k), 64)
         _, _, vv = quantize_blocks(vv, 64, want_q=False, want_fq=True)

@@ -39,6 +39,27 @@ def test_quantiser_matches_reference(SP):
     assert _rel(xf, rf) < 4e-3
 
 
+def test_quantiser_of_three_tensors_in_one_launch(SP):
+    """q, k, v of an attention call through one launch: bit-identical to three launches, with
+    strided inputs (column views of a wider buffer) and with outputs left out per tensor."""
+    torch.manual_seed(1)
+    wide = torch.randn(2, 333, 3, 192, device="cuda").bfloat16()
+    q, k, v = wide[..., :64], wide[..., 64:128], wide[..., 128:]
+    many = SP.quantize_blocks_many([(q, True, False), (k, True, True), (v, False, True)])
+    one = [SP.quantize_blocks(q, 64), SP.quantize_blocks(k, 64, want_fq=True),
+           SP.quantize_blocks(v, 64, want_q=False, want_fq=True)]
+    for (aq, as_, af), (bq, bs, bf) in zip(many, one):
+        assert (aq is None) == (bq is None) and (af is None) == (bf is None)
+        assert torch.equal(as_, bs)
+        assert aq is None or torch.equal(aq, bq)
+        assert af is None or torch.equal(af, bf)
+    # differing shapes: one launch per tensor, same results
+    q2 = torch.randn(2, 100, 3, 64, device="cuda").bfloat16()
+    mixed = SP.quantize_blocks_many([(q2, True, False), (k, True, False)])
+    assert torch.equal(mixed[0][0], SP.quantize_blocks(q2, 64)[0])
+    assert torch.equal(mixed[1][0], one[1][0])
+
+
 def test_tile_lut_union(SP):
     sel = torch.tensor([[[[0, 3], [3, 5], [1, 2]]]], device="cuda")        # Mb = 3, T = 2
     lut, fl = SP.build_tile_lut(sel, 64)
