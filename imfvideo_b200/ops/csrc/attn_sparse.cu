@@ -892,12 +892,17 @@ extern "C" int imf_attn_sparse_fwd(const void* q8, const void* k8, const float* 
   p.status = status;
   p.n_tiles = p.n_mt * H * B;
   cudaStream_t st = (cudaStream_t)stream;
-  static int sms = 0;
+  // SM count of the CURRENT device, cached per device index (a host may hold GPUs of
+  // different sizes; every thread that fills a slot writes the same value)
+  constexpr int MAX_DEVICES = 64;
+  static int sms_of_device[MAX_DEVICES] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int sms = (dev >= 0 && dev < MAX_DEVICES) ? sms_of_device[dev] : 0;
   if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
       sms = 148;
+    if (dev >= 0 && dev < MAX_DEVICES) sms_of_device[dev] = sms;
   }
 #define IMF_SP_LAUNCH(T_, I_)                                                                   \
   do {                                                                                          \
