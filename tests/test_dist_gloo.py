@@ -76,21 +76,27 @@ def _train_rank(rank, world, mode, steps):
     tr = Trainer(_cfg(mode), rank, world, torch.device("cpu"), verbose=False)
     g = torch.Generator().manual_seed(100 + rank)
     stats = []
+    versions_moved = True
     for s in range(steps):
         x = torch.randn(1, 16, 4, 16, 16, generator=g)
         y = torch.randint(0, 1000, (1,), generator=g)
         torch.manual_seed(1000 * s + rank)          # loss-internal noise
+        v0 = [p._version for p in tr.net.parameters()]
         stats.append(tr.train_step(x, y))
+        # owned or not, a parameter that a step rewrote (through the arenas, after the gather
+        # of the other ranks' updates) must show it in its version counter on every rank
+        versions_moved &= all(p._version > v for p, v in zip(tr.net.parameters(), v0))
     flat = torch.cat([p.detach().reshape(-1) for p in tr.net.parameters()])
-    return flat.numpy().tobytes(), [s["grad_norm"] for s in stats]
+    return flat.numpy().tobytes(), [s["grad_norm"] for s in stats], versions_moved
 
 
 @pytest.mark.parametrize("mode", ["nccl_flat", "fused_p2p"])
 def test_replicas_stay_identical_and_modes_agree(mode):
     res = _spawn(_train_rank, 2, mode, 2)
-    (w0, gn0), (w1, gn1) = res[0], res[1]
+    (w0, gn0, moved0), (w1, gn1, moved1) = res[0], res[1]
     assert w0 == w1, "replicas diverged"
     assert gn0 == gn1
+    assert moved0 and moved1, "a step left version counters where they were"
     if mode != "nccl_flat":
         base = _spawn(_train_rank, 2, "nccl_flat", 2)[0][0]
         a = torch.frombuffer(bytearray(w0), dtype=torch.float32)
