@@ -313,3 +313,31 @@ def test_mark_written_moves_counters_without_touching_data():
     assert a._version > va and b._version > vb
     assert torch.equal(a, torch.arange(4.0)) and torch.equal(b.detach(), torch.ones(3))
     mark_written([])
+
+
+def test_weight_copies_under_autograd_follow_the_gradient_buffers():
+    """With fp32 gradient buffers on every parameter the fused block writes its weight
+    gradients straight into them, so the bf16 weight copies carry no autograd history and are
+    shared with the gradient-free passes; without the buffers autograd has to carry the
+    gradients back through the copies, which are then rebuilt with history on every call."""
+    cfg = _cfg()
+    cfg.model.attn_res_block_size = 2           # blocks with the attention-residual re-mix
+    net = build_model(cfg)[0]
+    blk = next(m for m in net.modules() if hasattr(m, "fused_params") and hasattr(m, "attn_res_norm"))
+    with torch.no_grad():
+        cached = blk.fused_params(False)[-6:]
+    # no gradient buffers yet: the copies must be differentiable
+    mats = blk.fused_params(False)[-6:]
+    assert all(m.requires_grad for m in mats) and not blk.fused_sinks().mats_cached
+    for p in blk.parameters():
+        p.grad = torch.zeros_like(p)
+    mats = blk.fused_params(False)[-6:]
+    assert blk.fused_sinks().direct() and blk.fused_sinks().mats_cached
+    assert all((not m.requires_grad) and m is c for m, c in zip(mats, cached))
+    # the small products of two parameters keep their history under autograd
+    w1, w2 = blk.fused_params(True)[:2]
+    assert w1.requires_grad and w2.requires_grad
+    with torch.no_grad():
+        a1, _ = blk.fused_params(True)[:2]
+        b1, _ = blk.fused_params(True)[:2]
+    assert a1 is b1 and not a1.requires_grad and torch.equal(a1, w1.detach())
