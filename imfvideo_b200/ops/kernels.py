@@ -576,7 +576,7 @@ def newton_schulz(G: torch.Tensor, coeffs, steps: int = 5, eps: float = 1e-7,
               and out.shape == (k, n, m))
     # upper tiles + mirror pays from four tiles along the Gram side on (measured: 24 x 1024 x
     # 1024 1.10 -> 0.93 ms, 30 x 1536 x 1536 3.93 -> 2.93 ms, but 64 x 256 x 256 0.25 -> 0.28 ms)
-    sym = g >= 512
+    sym = g >= 512 and os.environ.get("IMF_NS_SYM", "1") != "0"     # IMF_NS_SYM=0: full products
     for it in range(steps):
         dst = out if (direct and it == steps - 1) else Y
         if small_rows:

@@ -13,6 +13,8 @@ under ``ncu`` (or for a quick CUDA-event timing without it).
     python -m imfvideo_b200.ops.profile_kernels lin       --L 29140      # linear-branch kernels, one line each
     python -m imfvideo_b200.ops.profile_kernels route     --L 29140      # block means, top-k, INT8 quantiser
     python -m imfvideo_b200.ops.profile_kernels ns --B 24 --M 1024 --K 1024  # Newton-Schulz, 5 iterations
+    IMF_NS_SYM=0 python -m imfvideo_b200.ops.profile_kernels ns --B 24 --M 1024 --K 1024   # full products
+    python -m imfvideo_b200.ops.profile_kernels qkprep_bwd --rows 29140 --H 4   # q/k preparation backward
 
 Prints the CUDA-event time per launch (after warm-up, inputs larger than L2
 or L2 flushed between launches) and the achieved fraction of the measured
@@ -47,7 +49,8 @@ def _time(fn, iters: int, flush) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("kernel", choices=["attn_fwd", "attn_jvp", "attn_bwd", "gemm", "gemm_fp8", "sparse",
-                                       "sparse_jvp", "resnorm", "resnorm_bwd", "lin", "route", "ns"])
+                                       "sparse_jvp", "resnorm", "resnorm_bwd", "lin", "route", "ns",
+                                       "qkprep_bwd"])
     ap.add_argument("--L", type=int, default=9472)
     ap.add_argument("--B", type=int, default=1)
     ap.add_argument("--H", type=int, default=4)
@@ -94,6 +97,27 @@ def main() -> None:
         b8, sb = K.quantize_fp8(b)
         fn, flops = (lambda: K.gemm_fp8(a8, sa, b8, sb)), 2.0 * args.M * args.N * args.K
         bytes_ = 1.0 * (args.M * args.K + args.N * args.K) + 2.0 * args.M * args.N
+    elif args.kernel == "qkprep_bwd":
+        # backward of the q / k preparation (per-head RMSNorm + partial RoPE + shared rope key):
+        # --rows tokens, --H heads, --hd 64 | 128 (half of each head takes the rope)
+        from . import rowops as R
+
+        rows, hd = args.rows, args.hd
+        dn = dr = hd // 2
+        dv = hd
+        rn = lambda *sh: torch.randn(*sh, device=dev).bfloat16()
+        qb, kvb = rn(rows, H * hd), rn(rows, H * (dn + dv))
+        ang = torch.rand(rows, dr // 2, device=dev) * 6
+        cos, sin = torch.cos(ang), torch.sin(ang)
+        qg, kg = torch.rand(dn, device=dev) + 0.5, torch.rand(dn, device=dev) + 0.5
+        gq, gk = rn(rows, H * hd), rn(rows, H * hd)
+        g_qb, g_kvb = torch.empty_like(qb), torch.zeros_like(kvb)
+        na = 256 + dr
+        g_a = torch.zeros(rows, na, device=dev, dtype=torch.bfloat16)
+        fn = lambda: R.qkprep_bwd(qb, kvb, cos, sin, qg, kg, gq, gk, g_qb, g_kvb, g_a[:, 256:], rows,
+                                  rows, H, dn, dr, dv, na, 1e-5, raw=True)
+        # reads gq, gk, q_b, the k half of kv_b; writes g_qb, the k half of g_kvb, g_k_rope
+        bytes_ = 2.0 * rows * (2 * H * hd + H * hd + H * dn + H * hd + H * dn + dr)
     elif args.kernel == "ns":
         # Newton-Schulz on a batch of B matrices of M x K (5 iterations, 3 launches each)
         G = torch.randn(B, args.M, args.K, device=dev)
