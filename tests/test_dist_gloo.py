@@ -188,3 +188,61 @@ def test_gradient_buckets_partition_the_arena():
     for k, blk in enumerate(blocks):
         n = sum(p.numel() for p in blk.parameters())
         assert sum(numel for _, numel, _ in eng.buckets[k]) == n
+
+
+def _train_and_save(rank, world, out_dir):
+    from imfvideo_b200.train import Trainer
+
+    cfg = _cfg("fused_p2p")
+    cfg.run.out_dir = out_dir
+    cfg.run.ema_decay = 0.9
+    tr = Trainer(cfg, rank, world, torch.device("cpu"), verbose=False)
+    g = torch.Generator().manual_seed(5 + rank)
+    for s in range(4):       # the zero-initialised output layers pass no gradient back at first
+        x = torch.randn(1, 16, 4, 16, 16, generator=g)
+        y = torch.randint(0, 1000, (1,), generator=g)
+        torch.manual_seed(77 * s + rank)
+        tr.train_step(x, y)
+    path = tr.save()                                    # collective; rank 0 writes
+    flat = torch.cat([p.detach().reshape(-1) for p in tr.net.parameters()])
+    ema = torch.cat([p.detach().reshape(-1) for p in tr.ema.parameters()])
+    # after the save every rank holds the gathered optimizer state: momentum by parameter name
+    mom = {n: tr.optimizer.state[p]["momentum_buffer"].clone().reshape(-1).numpy().tobytes()
+           for n, p in tr.net.named_parameters() if "momentum_buffer" in tr.optimizer.state.get(p, {})}
+    return flat.numpy().tobytes(), ema.numpy().tobytes(), path, mom
+
+
+def test_checkpoint_of_two_ranks_resumes_on_one(tmp_path):
+    """Elastic resume: a checkpoint written by an owner-partitioned two-rank job (each rank holds
+    the Muon momentum and the AdamW moments of its own share) loads into a single-rank trainer
+    with the full state -- weights, EMA, every momentum buffer of either owner -- and training
+    goes on."""
+    from imfvideo_b200.train import Trainer
+
+    res = _spawn(_train_and_save, 2, str(tmp_path))
+    w0, e0, path, mom0 = res[0]
+    assert path and os.path.exists(path) and res[1][2] in (None, path)
+    assert mom0 == res[1][3]                            # both ranks hold the gathered state
+    cfg = _cfg("none")
+    cfg.run.out_dir = str(tmp_path)
+    cfg.run.ema_decay = 0.9
+    tr = Trainer(cfg, 0, 1, torch.device("cpu"), verbose=False)
+    tr.load(path)
+    assert tr.step == 4
+    flat = torch.cat([p.detach().reshape(-1) for p in tr.net.parameters()])
+    ema = torch.cat([p.detach().reshape(-1) for p in tr.ema.parameters()])
+    assert flat.numpy().tobytes() == w0 and ema.numpy().tobytes() == e0
+    n_muon = n_live = 0
+    for name, p in tr.net.named_parameters():
+        st = tr.optimizer.state.get(p, {})
+        if "momentum_buffer" in st:
+            buf = st["momentum_buffer"]
+            n_muon += 1
+            n_live += int(buf.abs().sum() > 0)
+            assert buf.reshape(-1).numpy().tobytes() == mom0[name], name
+        elif "exp_avg" in st:
+            assert float(st["step"]) == 4.0
+    assert n_muon == len(mom0) > 0 and n_live == n_muon
+    x, y = torch.randn(1, 16, 4, 16, 16), torch.randint(0, 1000, (1,))
+    st = tr.train_step(x, y)
+    assert st["loss"] == st["loss"] and not st["skipped"] and tr.step == 5
