@@ -246,3 +246,43 @@ def test_checkpoint_of_two_ranks_resumes_on_one(tmp_path):
     x, y = torch.randn(1, 16, 4, 16, 16), torch.randint(0, 1000, (1,))
     st = tr.train_step(x, y)
     assert st["loss"] == st["loss"] and not st["skipped"] and tr.step == 5
+
+
+def _load_and_step(rank, world, out_dir, path):
+    from imfvideo_b200.train import Trainer
+
+    cfg = _cfg("fused_p2p")
+    cfg.run.out_dir = out_dir
+    cfg.run.ema_decay = 0.9
+    tr = Trainer(cfg, rank, world, torch.device("cpu"), verbose=False)
+    tr.load(path)
+    before = torch.cat([p.detach().reshape(-1) for p in tr.net.parameters()]).clone()
+    g = torch.Generator().manual_seed(9 + rank)
+    x = torch.randn(1, 16, 4, 16, 16, generator=g)
+    y = torch.randint(0, 1000, (1,), generator=g)
+    st = tr.train_step(x, y)
+    after = torch.cat([p.detach().reshape(-1) for p in tr.net.parameters()])
+    return (before.numpy().tobytes(), after.numpy().tobytes(), tr.step, bool(st["skipped"]))
+
+
+def test_checkpoint_of_one_rank_resumes_on_two(tmp_path):
+    """The other direction: a single-rank checkpoint loads on two ranks, each taking the
+    momentum of the matrices it owns; both start from the saved weights and stay identical
+    through the next step."""
+    from imfvideo_b200.train import Trainer
+
+    cfg = _cfg("none")
+    cfg.run.out_dir = str(tmp_path)
+    cfg.run.ema_decay = 0.9
+    tr = Trainer(cfg, 0, 1, torch.device("cpu"), verbose=False)
+    g = torch.Generator().manual_seed(2)
+    for _ in range(4):
+        tr.train_step(torch.randn(1, 16, 4, 16, 16, generator=g),
+                      torch.randint(0, 1000, (1,), generator=g))
+    path = tr.save()
+    saved = torch.cat([p.detach().reshape(-1) for p in tr.net.parameters()]).numpy().tobytes()
+    res = _spawn(_load_and_step, 2, str(tmp_path), path)
+    (b0, a0, s0, k0), (b1, a1, s1, k1) = res[0], res[1]
+    assert b0 == saved and b1 == saved
+    assert a0 == a1 and a0 != saved
+    assert s0 == s1 == 5 and not k0 and not k1
